@@ -1,0 +1,458 @@
+#!/usr/bin/env python
+"""Benchmark of the KV-append + cached decode-attention path.
+
+A step = one decode step of the workload: every sequence of the batch advances one
+position through ALL layers (per layer: append the new K/V row at the device-side cache
+position, then grouped-query attention over the cache). Default workload: the
+Qwen2-7B-shaped 28-layer config at context 32768 with the largest batch of {64,32,8,1}
+that fits this GPU. Inputs are synthetic (seeded, approximately N(0,1) fp16), positions
+uniform in [ctx/2, ctx).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl hkv|reference]
+
+Prints ONE JSON line (rank 0). `value` is whole-job tokens/s with everything resident in
+HBM; `e2e` is the same metric through the host-buffer C-ABI call (H2D of q/k_new/v_new and
+D2H of the attention output inside the timed region); `roofline` is the split-K decode
+kernel's algorithmic HBM bytes / its CUDA-event duration; `cpu_baseline` is the scalar CPU
+oracle timed on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+SEED = 0x48454B56
+WORKLOADS = {
+    # name: layers, H, KVH, HD, window pattern (None = all global)
+    "qwen2-7b": dict(layers=28, H=28, KVH=4, HD=128),
+    "qwen2-0.5b": dict(layers=1, H=14, KVH=2, HD=64),
+    "phi3-mini": dict(layers=32, H=32, KVH=32, HD=96),
+}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="hkv", choices=["hkv", "reference"])
+    ap.add_argument("--workload", default="qwen2-7b", choices=sorted(WORKLOADS))
+    ap.add_argument("--ctx", type=int, default=32768)
+    ap.add_argument("--batch", type=int, default=0, help="sequences per GPU (0 = largest that fits)")
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (parity/debug runs)")
+    ap.add_argument("--kernel", type=int, default=0, help="0 auto, 1 generic, 2 tma")
+    ap.add_argument("--chunk-tiles", type=int, default=0)
+    ap.add_argument("--no-verify", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--ref-layers", type=int, default=2, help="layers the reference arm runs per step")
+    return ap.parse_args()
+
+
+# ---------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_id: str):
+        self.gpu_id = gpu_id
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", self.gpu_id, f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 7:
+                    continue
+                try:
+                    sm.append(float(parts[0])); smax.append(float(parts[1])); power.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, parts[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(smax)), samples=len(sm),
+                       power_w_max=float(max(power)))
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# ---------------------------------------------------------------------------
+# workload
+# ---------------------------------------------------------------------------
+def pick_batch(torch, cfg, ctx, requested):
+    per_seq = 2 * cfg["layers"] * ctx * cfg["KVH"] * cfg["HD"] * 2
+    free, _ = torch.cuda.mem_get_info()
+    if requested:
+        return requested
+    for b in (64, 32, 8, 1):
+        if b * per_seq + (6 << 30) < free:
+            return b
+    raise SystemExit("not enough free device memory for batch 1")
+
+
+class Workload:
+    def __init__(self, torch, hkv, cfg, ctx, B, rank, kernel=0, chunk_tiles=0):
+        self.torch, self.hkv, self.cfg, self.ctx_len, self.B, self.rank = torch, hkv, cfg, ctx, B, rank
+        L, H, KVH, HD = cfg["layers"], cfg["H"], cfg["KVH"], cfg["HD"]
+        self.scale = 1.0 / math.sqrt(HD)
+        dev = "cuda"
+        self.k = torch.empty((L, B, ctx, KVH, HD), dtype=torch.float16, device=dev)
+        self.v = torch.empty((L, B, ctx, KVH, HD), dtype=torch.float16, device=dev)
+        self.q = torch.empty((L, B, H, HD), dtype=torch.float16, device=dev)
+        self.kn = torch.empty((L, B, KVH, HD), dtype=torch.float16, device=dev)
+        self.vn = torch.empty((L, B, KVH, HD), dtype=torch.float16, device=dev)
+        self.out = torch.zeros((L, B, H, HD), dtype=torch.float16, device=dev)
+        self.seeds = {n: SEED ^ (rank * 0x10001) ^ (i << 20) for i, n in enumerate(("k", "v", "q", "kn", "vn"))}
+        for n, t in (("k", self.k), ("v", self.v), ("q", self.q), ("kn", self.kn), ("vn", self.vn)):
+            hkv.fill_synthetic(t, self.seeds[n])
+        rng = np.random.default_rng(SEED + rank)
+        self.pos0 = rng.integers(ctx // 2, ctx, size=B).astype(np.int32)  # per-sequence cache_pos
+        self.h_pos = torch.from_numpy(self.pos0.copy()).pin_memory()
+        self.d_pos = torch.from_numpy(self.pos0.copy()).to(dev)
+        self.hctx = hkv.Context(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=ctx,
+                                             kernel_select=kernel, chunk_tiles=chunk_tiles))
+        torch.cuda.synchronize()
+
+    def positions_at(self, step):
+        return np.minimum(self.pos0 + step, self.ctx_len - 1)
+
+    def reset_positions(self):
+        self.d_pos.copy_(self.h_pos, non_blocking=True)
+
+    def advance(self):
+        self.d_pos.add_(1).clamp_(max=self.ctx_len - 1)
+
+    def step_device(self):
+        c = self.hctx
+        for l in range(self.cfg["layers"]):
+            c.append_decode_attention(self.q[l], self.kn[l], self.vn[l], self.k[l], self.v[l], self.out[l],
+                                      self.d_pos, self.scale)
+        self.advance()
+
+    def algorithmic_bytes_per_layer(self, step):
+        """Sum over sequences of 4*L*KVH*HD (read K and V) + 8*KVH*HD (new row in, row out)
+        + 4*H*HD (q in, out)."""
+        H, KVH, HD = self.cfg["H"], self.cfg["KVH"], self.cfg["HD"]
+        Ls = self.positions_at(step).astype(np.int64) + 1
+        return int((4 * Ls * KVH * HD).sum() + self.B * (8 * KVH * HD + 4 * H * HD))
+
+
+def verify(w: Workload, oracle, layer, seqs):
+    """Full-size parity: regenerate the cache rows of (layer, b) on the CPU from the seed,
+    append the new row, attend with the oracle, compare with the GPU's output."""
+    torch, cfg = w.torch, w.cfg
+    L, H, KVH, HD, ctx, B = cfg["layers"], cfg["H"], cfg["KVH"], cfg["HD"], w.ctx_len, w.B
+    w.reset_positions()
+    w.hctx.append_decode_attention(w.q[layer], w.kn[layer], w.vn[layer], w.k[layer], w.v[layer],
+                                   w.out[layer], w.d_pos, w.scale)
+    status = w.hctx.device_status()
+    assert status == 0, f"device status word {status}"
+    worst = 0.0
+    for b in seqs:
+        pos = int(w.pos0[b])
+        row = KVH * HD
+        base = ((layer * B + b) * ctx) * row
+        kc = oracle.fill(w.seeds["k"], base, (pos + 1) * row).reshape(1, pos + 1, KVH, HD).copy()
+        vc = oracle.fill(w.seeds["v"], base, (pos + 1) * row).reshape(1, pos + 1, KVH, HD).copy()
+        nb = (layer * B + b) * row
+        kc[0, pos] = oracle.fill(w.seeds["kn"], nb, row).reshape(KVH, HD)
+        vc[0, pos] = oracle.fill(w.seeds["vn"], nb, row).reshape(KVH, HD)
+        q = oracle.fill(w.seeds["q"], (layer * B + b) * H * HD, H * HD).reshape(1, H, HD)
+        ref = oracle.decode(q, kc, vc, [pos + 1], w.scale, threads=oracle.hardware_threads())
+        got = w.out[layer, b].cpu().numpy()
+        ok, err = oracle.within_tolerance(got, ref[0])
+        assert ok, f"parity failed at layer {layer} seq {b}: max abs err {err:.3e}"
+        # the appended row must be in the cache, bit-exact
+        assert np.array_equal(w.k[layer, b, pos].cpu().numpy().view(np.uint16), kc[0, pos].view(np.uint16))
+        assert np.array_equal(w.v[layer, b, pos].cpu().numpy().view(np.uint16), vc[0, pos].view(np.uint16))
+        worst = max(worst, err)
+    return worst
+
+
+def cpu_baseline(w: Workload, oracle, budget_s=12.0):
+    """Scalar CPU oracle on a bounded sample: whole sequences of ONE layer, all heads, all
+    host threads; tokens/s = sequences / (seconds * layers)."""
+    cfg = w.cfg
+    H, KVH, HD, ctx, B = cfg["H"], cfg["KVH"], cfg["HD"], w.ctx_len, w.B
+    threads = oracle.hardware_threads()
+    row = KVH * HD
+    done, secs = 0, 0.0
+    for b in range(B):
+        pos = int(w.pos0[b])
+        base = (b * ctx) * row
+        kc = oracle.fill(w.seeds["k"], base, (pos + 1) * row).reshape(1, pos + 1, KVH, HD)
+        vc = oracle.fill(w.seeds["v"], base, (pos + 1) * row).reshape(1, pos + 1, KVH, HD)
+        q = oracle.fill(w.seeds["q"], b * H * HD, H * HD).reshape(1, H, HD)
+        t0 = time.perf_counter()
+        oracle.decode(q, kc, vc, [pos + 1], w.scale, threads=threads)
+        secs += time.perf_counter() - t0
+        done += 1
+        if secs > budget_s:
+            break
+    tok_s = done / (secs * cfg["layers"])
+    return {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"{done} sequence(s) x 1 layer x {H} heads of the same workload "
+                      f"({secs:.1f} s of CPU time), scaled to {cfg['layers']} layers"}
+
+
+# ---------------------------------------------------------------------------
+# reference arm: the reference's own kernels rebuilt for sm_100a (GPU only)
+# ---------------------------------------------------------------------------
+def run_reference(args, torch, hkv, oracle, cfg, ctx, B, rank):
+    ref = oracle.load_reference()
+    if ref is None:
+        return None
+    w = Workload(torch, hkv, cfg, ctx, B, rank)
+    L, H, KVH, HD = cfg["layers"], cfg["H"], cfg["KVH"], cfg["HD"]
+    nl = max(1, min(args.ref_layers, L))
+    d_total = (w.d_pos + 1).contiguous()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step():
+        # The reference op is batch 1 with one scalar device position
+        # (kernels/register_kernels.cpp:870): one launch pair per sequence, serially.
+        for l in range(nl):
+            for b in range(B):
+                ref.hector_ref_kv_cache_update_dp(w.kn[l, b].data_ptr(), w.vn[l, b].data_ptr(),
+                                                  w.k[l, b].data_ptr(), w.v[l, b].data_ptr(), 1, 1, KVH, HD,
+                                                  ctx, w.d_pos.data_ptr() + 4 * b, stream)
+                ref.hector_ref_attention_cached_dp(w.q[l, b].data_ptr(), w.k[l, b].data_ptr(),
+                                                   w.v[l, b].data_ptr(), w.out[l, b].data_ptr(), 1,
+                                                   d_total.data_ptr() + 4 * b, H, KVH, HD, ctx, w.scale, 0,
+                                                   stream)
+        w.advance()
+        torch.add(w.d_pos, 1, out=d_total)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps * (L / nl)  # scaled from nl layers to all layers
+    return w, ms, nl
+
+
+def main():
+    args = parse_args()
+    import torch
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference" and rank != 0:
+        return 0  # the reference has no multi-GPU path: rank 0 alone measures it
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU path exists)")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1 and args.impl != "reference":
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    hkv = importlib.import_module("hector-engine_b200")
+    hkv._capi.load()  # fail loudly if the native library is missing
+    sys.path.insert(0, os.path.join(REPO, "oracle"))
+    import hkv_oracle as oracle
+
+    cfg = dict(WORKLOADS[args.workload])
+    if args.layers:
+        cfg["layers"] = args.layers
+    ctx = args.ctx
+    B = pick_batch(torch, cfg, ctx, args.batch)
+    n_gpus = world if args.impl != "reference" else 1
+    try:
+        gpu_id = str(torch.cuda.get_device_properties(local).uuid)
+        gpu_id = gpu_id if gpu_id.startswith("GPU-") else "GPU-" + gpu_id
+    except Exception:
+        gpu_id = str(local)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    workload_name = (f"{args.workload}-shaped decode: {cfg['layers']} layers, {cfg['H']}q/{cfg['KVH']}kv heads, "
+                     f"head_dim {cfg['HD']}, ctx {ctx}, batch {B} per GPU, cache_pos ~ U[ctx/2, ctx)")
+    config = {"workload": workload_name, "batch_per_gpu": B, "global_batch": B * n_gpus, "ctx": ctx,
+              "layers": cfg["layers"], "parallelism": f"batch-sharded x{n_gpus} (no data-path collective)",
+              "l2": "inputs larger than L2 (K/V read per step >> 126 MB)", "fp16_kv": True}
+    base = {"metric": "decode attn+KV-append tokens/s", "unit": "tokens/s", "n_gpus": n_gpus,
+            "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp16 storage / fp32 accumulate", "data": "synthetic",
+            "config": config}
+
+    # ------------------------------------------------------------------ reference arm
+    if args.impl == "reference":
+        sampler = ClockSampler(gpu_id)
+        sampler.start()
+        res = run_reference(args, torch, hkv, oracle, cfg, ctx, B, rank)
+        clocks = sampler.stop()
+        if res is None:
+            print(json.dumps({"impl": "reference", "unavailable":
+                              "oracle/_ref/libhector_ref_attention.so not built (reference checkout absent at build time)"}))
+            return 0
+        w, ms, nl = res
+        tok_s = B / (ms / 1e3)
+        line = dict(base, impl="reference", value=tok_s, ms_per_step=ms, clocks=clocks,
+                    gpu_launches=args.steps * nl * B * 3,
+                    e2e={"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                    cpu_baseline={"value": tok_s, "unit": "tokens/s", "cores": 0, "kind": "reference",
+                                  "sample": f"the reference's own attention.cu + kv_cache_update kernels rebuilt for "
+                                            f"sm_100a, run on the GPU (the reference has no CPU implementation of "
+                                            f"this path): {nl} of {cfg['layers']} layers per step, one launch pair "
+                                            f"per sequence as its batch-1 op does, time scaled to all layers"})
+        print(json.dumps(line))
+        return 0
+
+    # ------------------------------------------------------------------ this library
+    w = Workload(torch, hkv, cfg, ctx, B, rank, args.kernel, args.chunk_tiles)
+    L = cfg["layers"]
+    verify_err = None
+    if not args.no_verify:
+        verify_err = verify(w, oracle, layer=L // 2, seqs=sorted({0, B // 2, B - 1}))
+
+    # device-resident timing
+    w.reset_positions()
+    for _ in range(args.warmup):
+        w.step_device()
+    w.reset_positions()
+    sampler = ClockSampler(gpu_id)
+    barrier()
+    sampler.start()
+    w.hctx.profile_begin(args.steps * L)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        w.step_device()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    dec_ms, comb_ms, calls = w.hctx.profile_end()
+    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    if dist is not None:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = float(ms.item()) / args.steps
+    status = w.hctx.device_status()
+    assert status == 0, f"device status word {status}"
+    tok_s = B * n_gpus / (ms_per_step / 1e3)
+
+    alg_bytes = float(np.mean([w.algorithmic_bytes_per_layer(s) for s in range(args.steps)]))
+    peaks_path = os.path.join(REPO, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    dec_avg_ms = dec_ms / max(calls, 1)
+    achieved = alg_bytes / (dec_avg_ms * 1e-3) / 1e9
+    traffic = None
+    tpath = os.path.join(REPO, "profiles", "decode_tma_traffic.json")
+    if os.path.exists(tpath) and w.hctx.kernel == 2:
+        tr = json.load(open(tpath))
+        traffic = tr["dram_bytes_per_algorithmic_byte"] * alg_bytes
+    roofline = {"bound": "hbm", "kernel": "hkv_decode_tma_kernel" if w.hctx.kernel == 2 else "hkv_decode_generic_kernel",
+                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "frac_of_8TBs": achieved / 8000.0, "peak_source": peak_src, "traffic": traffic,
+                "algorithmic_bytes_per_launch": alg_bytes, "avg_launch_ms": dec_avg_ms,
+                "combine_avg_ms": comb_ms / max(calls, 1), "launches_timed": calls}
+    step_gbs = alg_bytes * L / (ms_per_step * 1e-3) / 1e9
+
+    # end to end through the host-buffer entry point
+    e2e = None
+    if not args.no_e2e:
+        H, KVH, HD = cfg["H"], cfg["KVH"], cfg["HD"]
+        hq = w.q.cpu().pin_memory()
+        hk = w.kn.cpu().pin_memory()
+        hv = w.vn.cpu().pin_memory()
+        ho = torch.zeros((L, B, H, HD), dtype=torch.float16).pin_memory()
+        w.reset_positions()
+
+        def e2e_step():
+            w.d_pos.copy_(w.h_pos, non_blocking=True)  # this step's positions, host -> device
+            for l in range(L):
+                w.hctx.append_decode_attention_host(hq[l], hk[l], hv[l], w.k[l], w.v[l], ho[l], w.d_pos, w.scale)
+            torch.cuda.current_stream().synchronize()   # the step's result is now readable on the host
+            w.h_pos.add_(1).clamp_(max=ctx - 1)
+
+        for _ in range(min(args.warmup, 2)):
+            e2e_step()
+        barrier()
+        t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        t1.record()
+        barrier()
+        ems = torch.tensor([t0.elapsed_time(t1)], device="cuda")
+        if dist is not None:
+            dist.all_reduce(ems, op=dist.ReduceOp.MAX)
+        e_ms = float(ems.item()) / args.steps
+        e2e = {"value": B * n_gpus / (e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e_ms,
+               "h2d_bytes_per_step": int(L * (B * H * HD + 2 * B * KVH * HD) * 2 + B * 4),
+               "d2h_bytes_per_step": int(L * B * H * HD * 2)}
+
+    cpu = None
+    if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline(w, oracle)
+
+    if rank == 0:
+        line = dict(base, impl="hkv", value=tok_s, ms_per_step=ms_per_step, clocks=clocks, e2e=e2e,
+                    gpu_launches=args.steps * L * w.hctx.launches_per_decode, roofline=roofline,
+                    cpu_baseline=cpu, hbm_gbs_step=step_gbs, hbm_frac_of_8TBs_step=step_gbs / 8000.0,
+                    parity_max_abs_err=verify_err)
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

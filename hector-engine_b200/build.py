@@ -1,0 +1,87 @@
+"""Builds the native pieces in-tree.
+
+  libhkv.so          the product: CUDA kernels + C ABI (nvcc, sm_100a only)
+  hkv_host_tests     C++ host adapter tests (registry shim + KV cache objects)
+  oracle/_build, oracle/_ref   the test-only checkers (see oracle/Makefile)
+
+Run as a script (`python hector-engine_b200/build.py`) or through __graft_entry__.build().
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+REPO = os.path.dirname(PKG_DIR)
+CSRC = os.path.join(PKG_DIR, "csrc")
+HOST = os.path.join(PKG_DIR, "host")
+LIB = os.path.join(PKG_DIR, "libhkv.so")
+HOST_TESTS = os.path.join(PKG_DIR, "hkv_host_tests")
+
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
+
+
+def _nvcc() -> str:
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        raise RuntimeError("nvcc not found: libhkv can only be built with the CUDA toolkit")
+    return nvcc
+
+
+def _newer(target: str, sources: list[str]) -> bool:
+    if not os.path.exists(target):
+        return False
+    t = os.path.getmtime(target)
+    return all(os.path.getmtime(s) <= t for s in sources)
+
+
+def _sources(*dirs: str) -> list[str]:
+    out = [os.path.join(REPO, "include", "hkv.h")]
+    for d in dirs:
+        for name in sorted(os.listdir(d)):
+            if name.endswith((".cu", ".cuh", ".cpp", ".hpp", ".h")):
+                out.append(os.path.join(d, name))
+    return out
+
+
+def build_lib(force: bool = False, verbose: bool = False) -> str:
+    srcs = _sources(CSRC)
+    if not force and _newer(LIB, srcs):
+        return LIB
+    cmd = [_nvcc(), *ARCH, *NVCC_FLAGS, "-shared", "-o", LIB, os.path.join(CSRC, "hkv_api.cu")]
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+    subprocess.run(cmd, check=True)
+    return LIB
+
+
+def build_host_tests(force: bool = False) -> str | None:
+    main = os.path.join(HOST, "hkv_host_tests.cpp")
+    if not os.path.exists(main):
+        return None
+    srcs = _sources(HOST)
+    if not force and _newer(HOST_TESTS, srcs + [LIB]):
+        return HOST_TESTS
+    cmd = [_nvcc(), *ARCH, "-O2", "-std=c++17", "-o", HOST_TESTS, main,
+           os.path.join(HOST, "hkv_register.cpp"), "-I", os.path.join(REPO, "include"), "-I", HOST,
+           "-L", PKG_DIR, "-lhkv", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+    subprocess.run(cmd, check=True)
+    return HOST_TESTS
+
+
+def build_oracle() -> None:
+    subprocess.run(["make", "-s", "-C", os.path.join(REPO, "oracle"), "all"], check=True)
+
+
+def build_all(force: bool = False) -> None:
+    build_lib(force=force)
+    build_host_tests(force=force)
+    build_oracle()
+
+
+if __name__ == "__main__":
+    build_all(force="--force" in sys.argv)
+    print("built", LIB)

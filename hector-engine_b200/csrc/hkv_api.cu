@@ -1,0 +1,749 @@
+// hkv_api.cu — the C ABI of libhkv (declared in include/hkv.h): argument validation,
+// context and workspace ownership, tensor-map encoding and kernel dispatch.
+// Host side only enqueues work; there is no CPU compute path in this library.
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/hkv.h"
+#include "hkv_basic.cuh"
+#include "hkv_decode_tma.cuh"
+#include "hkv_prefill.cuh"
+
+using namespace hkv;
+
+// ---------------------------------------------------------------------------
+// Context
+// ---------------------------------------------------------------------------
+struct TmapPair {
+    CUtensorMap k, v;
+};
+
+struct hkv_ctx {
+    hkv_geometry g;
+    SeqMap map;
+    int device = -1;
+    int sm_count = 0;
+    size_t smem_optin = 0;
+    int G = 0;
+    long long batch_stride = 0;
+    int chunk_tiles = 1, max_chunks = 1;
+    int kernel = HKV_KERNEL_GENERIC;  // preferred kernel
+    int tma_groups = 2;
+    TmaSmemPlan plan{0, 0};
+    float* workspace = nullptr;
+    size_t workspace_bytes = 0;
+    int32_t* d_status = nullptr;
+    int32_t* d_len = nullptr;       // [B] for the host-length / host-position twins
+    int32_t* h_len = nullptr;       // pinned staging for d_len
+    // host-buffer entry point staging
+    __half *st_q = nullptr, *st_k = nullptr, *st_v = nullptr, *st_out = nullptr;
+    std::unordered_map<unsigned long long, TmapPair> tmaps;
+    std::string err;
+    // per-kernel timing (hkv_ctx_profile_begin/end)
+    std::vector<cudaEvent_t> prof_events;  // 3 per timed call
+    int prof_calls = 0, prof_max = 0;
+};
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+                cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+int fail(hkv_ctx* c, int code, const char* msg) {
+    if (c) c->err = msg;
+    return code;
+}
+int fail_cuda(hkv_ctx* c, cudaError_t e, const char* where) {
+    if (c) c->err = std::string(where) + ": " + cudaGetErrorString(e);
+    return HKV_ERR_CUDA;
+}
+
+bool aligned(const void* p, size_t n) { return (reinterpret_cast<uintptr_t>(p) % n) == 0; }
+
+int validate_geometry(const hkv_geometry* g, const char** why) {
+    if (!g) { *why = "geometry is null"; return HKV_ERR_INVALID_ARG; }
+    if (g->batch <= 0 || g->slots <= 0 || g->window_size < 0 || g->chunk_tiles < 0 ||
+        g->batch_stride_elems < 0 || g->max_seq_new < 0) {
+        *why = "batch/slots must be positive; window/chunk_tiles/stride non-negative";
+        return HKV_ERR_INVALID_ARG;
+    }
+    // same guard as the reference op (kernels/register_kernels.cpp:858-861)
+    if (g->head_dim <= 0 || g->head_dim > 512 || g->num_kv_heads <= 0 || g->num_heads <= 0 ||
+        g->num_heads % g->num_kv_heads != 0) {
+        *why = "unsupported head geometry";
+        return HKV_ERR_GEOMETRY;
+    }
+    if (g->layout != HKV_LAYOUT_LINEAR && g->layout != HKV_LAYOUT_RING) {
+        *why = "unknown layout";
+        return HKV_ERR_INVALID_ARG;
+    }
+    if (g->kernel_select < 0 || g->kernel_select > 2) {
+        *why = "unknown kernel_select";
+        return HKV_ERR_INVALID_ARG;
+    }
+    if (g->batch > 65535) { *why = "batch exceeds 65535"; return HKV_ERR_TOO_LARGE; }
+    const long long dense = (long long)g->slots * g->num_kv_heads * g->head_dim;
+    if (g->batch_stride_elems != 0 && g->batch_stride_elems < dense) {
+        *why = "batch_stride_elems smaller than one sequence's plane";
+        return HKV_ERR_INVALID_ARG;
+    }
+    if (g->shard_count > 1) {
+        if (g->shard_rank < 0 || g->shard_rank >= g->shard_count || g->shard_block <= 0 ||
+            g->shard_block % kTileRows != 0) {
+            *why = "shard_rank/shard_block invalid (block must be a positive multiple of 64)";
+            return HKV_ERR_INVALID_ARG;
+        }
+        if (g->layout == HKV_LAYOUT_RING) {
+            *why = "ring layout cannot be sequence-sharded";
+            return HKV_ERR_GEOMETRY;
+        }
+    }
+    return HKV_OK;
+}
+
+bool tma_geometry_ok(const hkv_geometry& g) {
+    const int G = g.num_heads / g.num_kv_heads;
+    const bool hd_ok = g.head_dim == 64 || g.head_dim == 96 || g.head_dim == 128 || g.head_dim == 256;
+    const long long bs = g.batch_stride_elems ? g.batch_stride_elems
+                                              : (long long)g.slots * g.num_kv_heads * g.head_dim;
+    return hd_ok && G <= 16 && g.batch <= kTmaMaxBatch && bs % 8 == 0;
+}
+
+int auto_chunk_tiles(const hkv_geometry& g, int sm_count) {
+    int rows = g.slots;
+    if (g.window_size > 0 && g.window_size < rows) rows = g.window_size + kTileRows;
+    const long long tiles = (long long)g.batch * g.num_kv_heads * ((rows + kTileRows - 1) / kTileRows);
+    long long ct = tiles / ((long long)sm_count * 8);
+    if (ct < 1) ct = 1;
+    if (ct > 16) ct = 16;
+    return (int)ct;
+}
+
+void fill_plan(const hkv_geometry& g, int sm_count, int& chunk_tiles, int& max_chunks) {
+    chunk_tiles = g.chunk_tiles > 0 ? g.chunk_tiles : auto_chunk_tiles(g, sm_count > 0 ? sm_count : 148);
+    const int tiles = (g.slots + kTileRows - 1) / kTileRows;
+    max_chunks = (tiles + chunk_tiles - 1) / chunk_tiles;
+    if (max_chunks < 1) max_chunks = 1;
+}
+
+size_t workspace_bytes_for(const hkv_geometry& g, int max_chunks) {
+    return (size_t)g.batch * max_chunks * g.num_heads * (g.head_dim + 2) * sizeof(float);
+}
+
+// ---- TMA kernel table ------------------------------------------------------
+typedef void (*TmaKernel)(const CUtensorMap, const CUtensorMap, const DecodeArgs, const int);
+
+template <int HD>
+TmaKernel pick_tma_hd(int nt, int groups) {
+    if (nt == 1) return groups == 1 ? hkv_decode_tma_kernel<HD, 1, 1> : hkv_decode_tma_kernel<HD, 1, 2>;
+    return groups == 1 ? hkv_decode_tma_kernel<HD, 2, 1> : hkv_decode_tma_kernel<HD, 2, 2>;
+}
+TmaKernel pick_tma(int HD, int nt, int groups) {
+    switch (HD) {
+        case 64: return pick_tma_hd<64>(nt, groups);
+        case 96: return pick_tma_hd<96>(nt, groups);
+        case 128: return pick_tma_hd<128>(nt, groups);
+        case 256: return pick_tma_hd<256>(nt, groups);
+    }
+    return nullptr;
+}
+
+int encode_map(hkv_ctx* c, const void* base, CUtensorMap* out) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(c, HKV_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    const hkv_geometry& g = c->g;
+    const int CW = tma_chunk_width(g.head_dim);
+    cuuint64_t dims[4] = {(cuuint64_t)g.head_dim, (cuuint64_t)g.num_kv_heads, (cuuint64_t)g.slots,
+                          (cuuint64_t)g.batch};
+    cuuint64_t strides[3] = {(cuuint64_t)g.head_dim * 2, (cuuint64_t)g.num_kv_heads * g.head_dim * 2,
+                             (cuuint64_t)c->batch_stride * 2};
+    cuuint32_t box[4] = {(cuuint32_t)CW, 1u, (cuuint32_t)kTileRows, 1u};
+    cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims,
+                           strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CW == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char buf[96];
+        snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed (CUresult %d)", (int)r);
+        return fail(c, HKV_ERR_CUDA, buf);
+    }
+    return HKV_OK;
+}
+
+int get_maps(hkv_ctx* c, const void* k, const void* v, const TmapPair** out) {
+    const unsigned long long key =
+        (unsigned long long)reinterpret_cast<uintptr_t>(k) * 0x9E3779B97F4A7C15ull ^
+        (unsigned long long)reinterpret_cast<uintptr_t>(v);
+    auto it = c->tmaps.find(key);
+    if (it == c->tmaps.end()) {
+        TmapPair p;
+        int st = encode_map(c, k, &p.k);
+        if (st) return st;
+        st = encode_map(c, v, &p.v);
+        if (st) return st;
+        if (c->tmaps.size() > 4096) c->tmaps.clear();
+        it = c->tmaps.emplace(key, p).first;
+    }
+    *out = &it->second;
+    return HKV_OK;
+}
+
+SeqMap make_map(const hkv_geometry& g) {
+    SeqMap m;
+    m.slots = g.slots;
+    m.layout = g.layout;
+    m.window = g.window_size;
+    m.shard_rank = g.shard_count > 1 ? g.shard_rank : 0;
+    m.shard_count = g.shard_count > 1 ? g.shard_count : 1;
+    m.shard_block = g.shard_count > 1 ? g.shard_block : kTileRows;
+    return m;
+}
+
+int launch_append(hkv_ctx* c, const void* k_new, const void* v_new, void* k_cache, void* v_cache,
+                  const int32_t* d_pos, int pos_bias, int host_pos, int seq_new, cudaStream_t st) {
+    if (!k_new || !v_new || !k_cache || !v_cache) return fail(c, HKV_ERR_INVALID_ARG, "append: null tensor");
+    if (seq_new < 0) return fail(c, HKV_ERR_INVALID_ARG, "append: negative seq_new");
+    if (!aligned(k_new, 2) || !aligned(v_new, 2) || !aligned(k_cache, 2) || !aligned(v_cache, 2))
+        return fail(c, HKV_ERR_ALIGNMENT, "append: fp16 pointer not 2-byte aligned");
+    if (seq_new == 0) return HKV_OK;
+    AppendArgs a;
+    a.k_new = (const __half*)k_new;
+    a.v_new = (const __half*)v_new;
+    a.k_cache = (__half*)k_cache;
+    a.v_cache = (__half*)v_cache;
+    a.d_pos = d_pos;
+    a.host_pos = host_pos;
+    a.pos_bias = pos_bias;
+    a.map = c->map;
+    a.B = c->g.batch;
+    a.S = seq_new;
+    a.row_elems = c->g.num_kv_heads * c->g.head_dim;
+    a.batch_stride = c->batch_stride;
+    const bool vec = aligned(k_new, 16) && aligned(v_new, 16) && aligned(k_cache, 16) &&
+                     aligned(v_cache, 16) && a.row_elems % 8 == 0 && c->batch_stride % 8 == 0;
+    const long long pieces = 2ll * a.B * a.S * (vec ? a.row_elems / 8 : a.row_elems);
+    long long blocks = (pieces + 255) / 256;
+    const long long cap = (long long)c->sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    if (vec) hkv_append_kernel<uint4><<<(unsigned)blocks, 256, 0, st>>>(a);
+    else hkv_append_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(a);
+    return HKV_OK;
+}
+
+// Decode into the workspace; `fused` appends k_new/v_new at position total-1.
+int launch_decode(hkv_ctx* c, const void* q, const void* k_new, const void* v_new, void* k_cache,
+                  void* v_cache, const int32_t* d_total, int pos_is_index, float scale,
+                  cudaStream_t st) {
+    const hkv_geometry& g = c->g;
+    if (!q || !k_cache || !v_cache || !d_total) return fail(c, HKV_ERR_INVALID_ARG, "decode: null tensor");
+    if (!aligned(q, 2) || !aligned(k_cache, 2) || !aligned(v_cache, 2))
+        return fail(c, HKV_ERR_ALIGNMENT, "decode: fp16 pointer not 2-byte aligned");
+    if (!std::isfinite(scale)) return fail(c, HKV_ERR_INVALID_ARG, "decode: scale is not finite");
+    const bool fused = k_new != nullptr;
+    if (fused && !v_new) return fail(c, HKV_ERR_INVALID_ARG, "decode: k_new without v_new");
+
+    DecodeArgs a;
+    a.q = (const __half*)q;
+    a.k_cache = (const __half*)k_cache;
+    a.v_cache = (const __half*)v_cache;
+    a.k_new = nullptr;
+    a.v_new = nullptr;
+    a.k_cache_w = (__half*)k_cache;
+    a.v_cache_w = (__half*)v_cache;
+    a.part = c->workspace;
+    a.total = d_total;
+    a.status = c->d_status;
+    a.map = c->map;
+    a.B = g.batch;
+    a.H = g.num_heads;
+    a.KVH = g.num_kv_heads;
+    a.HD = g.head_dim;
+    a.chunk_tiles = c->chunk_tiles;
+    a.max_chunks = c->max_chunks;
+    a.pos_is_index = pos_is_index;
+    a.batch_stride = c->batch_stride;
+    a.scale_log2 = scale * 1.4426950408889634f;
+
+    bool use_tma = c->kernel == HKV_KERNEL_TMA && aligned(q, 16) && aligned(k_cache, 16) &&
+                   aligned(v_cache, 16) &&
+                   (!fused || (aligned(k_new, 16) && aligned(v_new, 16)));
+    if (!use_tma && g.kernel_select == HKV_KERNEL_TMA)
+        return fail(c, HKV_ERR_ALIGNMENT, "decode: TMA kernel requires 16-byte aligned tensors");
+
+    if (use_tma) {
+        const TmapPair* maps = nullptr;
+        const int stt = get_maps(c, k_cache, v_cache, &maps);
+        if (stt) return stt;
+        if (fused) { a.k_new = (const __half*)k_new; a.v_new = (const __half*)v_new; }
+        const int nt = (c->G + 7) / 8;
+        TmaKernel kern = pick_tma(g.head_dim, nt, c->tma_groups);
+        long long items = (long long)g.batch * c->max_chunks * g.num_kv_heads;
+        int grid = c->sm_count;
+        if (items < grid) grid = (int)items;
+        const int threads = (c->tma_groups * 4 + 1) * 32;
+        kern<<<grid, threads, c->plan.bytes, st>>>(maps->k, maps->v, a, c->plan.stages);
+    } else {
+        if (fused) {
+            // generic path: append first (its own launch), then attend
+            const int32_t* d_pos = d_total;
+            if (!pos_is_index) return fail(c, HKV_ERR_INVALID_ARG, "fused decode needs cache positions");
+            const int stt = launch_append(c, k_new, v_new, k_cache, v_cache, d_pos, 0, 0, 1, st);
+            if (stt) return stt;
+        }
+        dim3 grid((unsigned)c->max_chunks, (unsigned)g.num_heads, (unsigned)g.batch);
+        hkv_decode_generic_kernel<<<grid, kGenWarps * 32, 0, st>>>(a);
+    }
+    return HKV_OK;
+}
+
+int launch_combine(hkv_ctx* c, const float* part, long long stride_b, long long stride_c,
+                   const int32_t* d_total, int pos_is_index, int fixed_count, void* out,
+                   float* out_partial, cudaStream_t st) {
+    CombineArgs a;
+    a.part = part;
+    a.stride_b = stride_b;
+    a.stride_c = stride_c;
+    a.total = d_total;
+    a.pos_is_index = pos_is_index;
+    a.fixed_count = fixed_count;
+    a.map = c->map;
+    a.chunk_tiles = c->chunk_tiles;
+    a.H = c->g.num_heads;
+    a.HD = c->g.head_dim;
+    a.out = (__half*)out;
+    a.out_partial = out_partial;
+    dim3 grid((unsigned)c->g.num_heads, (unsigned)c->g.batch);
+    hkv_combine_kernel<<<grid, 128, 0, st>>>(a);
+    return HKV_OK;
+}
+
+int decode_full(hkv_ctx* c, const void* q, const void* k_new, const void* v_new, void* k_cache,
+                void* v_cache, void* out, float* out_partial, const int32_t* d_total,
+                int pos_is_index, float scale, cudaStream_t st) {
+    if (!out && !out_partial) return fail(c, HKV_ERR_INVALID_ARG, "decode: null output");
+    if (out && !aligned(out, 2)) return fail(c, HKV_ERR_ALIGNMENT, "decode: out not 2-byte aligned");
+    const bool timed = c->prof_calls < c->prof_max;
+    cudaEvent_t* ev = timed ? &c->prof_events[(size_t)c->prof_calls * 3] : nullptr;
+    if (timed) cudaEventRecord(ev[0], st);
+    int stt = launch_decode(c, q, k_new, v_new, k_cache, v_cache, d_total, pos_is_index, scale, st);
+    if (stt) return stt;
+    if (timed) cudaEventRecord(ev[1], st);
+    const long long PW = c->g.head_dim + 2;
+    stt = launch_combine(c, c->workspace, (long long)c->max_chunks * c->g.num_heads * PW,
+                         (long long)c->g.num_heads * PW, d_total, pos_is_index, 0, out, out_partial,
+                         st);
+    if (stt) return stt;
+    if (timed) {
+        cudaEventRecord(ev[2], st);
+        ++c->prof_calls;
+    }
+    const cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) return fail_cuda(c, e, "decode launch");
+    return HKV_OK;
+}
+
+int set_host_len(hkv_ctx* c, int32_t v, cudaStream_t st) {
+    for (int b = 0; b < c->g.batch; ++b) c->h_len[b] = v;
+    const cudaError_t e = cudaMemcpyAsync(c->d_len, c->h_len, sizeof(int32_t) * c->g.batch,
+                                          cudaMemcpyHostToDevice, st);
+    return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "cudaMemcpyAsync(length)");
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------
+extern "C" {
+
+int hkv_abi_version(void) { return HKV_ABI_VERSION; }
+
+const char* hkv_status_string(int s) {
+    switch (s) {
+        case HKV_OK: return "ok";
+        case HKV_ERR_INVALID_ARG: return "invalid argument";
+        case HKV_ERR_GEOMETRY: return "unsupported geometry";
+        case HKV_ERR_ALIGNMENT: return "misaligned pointer or stride";
+        case HKV_ERR_CUDA: return "CUDA call failed";
+        case HKV_ERR_NO_DEVICE: return "no usable B200-class CUDA device";
+        case HKV_ERR_WORKSPACE: return "workspace too small";
+        case HKV_ERR_TOO_LARGE: return "size exceeds a documented maximum";
+        case HKV_ERR_DEVICE_FAULT: return "device status word reports a fault";
+    }
+    return "unknown status";
+}
+
+size_t hkv_workspace_bytes(const hkv_geometry* g) {
+    const char* why;
+    if (validate_geometry(g, &why) != HKV_OK) return 0;
+    int sm = 148;
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0) sm = v;
+    } else {
+        cudaGetLastError();
+    }
+    int ct, mc;
+    fill_plan(*g, sm, ct, mc);
+    return workspace_bytes_for(*g, mc);
+}
+
+size_t hkv_partial_floats(const hkv_geometry* g) { return g ? (size_t)g->head_dim + 2 : 0; }
+
+int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
+    if (!out) return HKV_ERR_INVALID_ARG;
+    *out = nullptr;
+    const char* why = "";
+    const int vst = validate_geometry(geometry, &why);
+    hkv_ctx* c = new (std::nothrow) hkv_ctx();
+    if (!c) return HKV_ERR_CUDA;
+    *out = c;  // returned even on failure so the caller can read the message; destroy it
+    if (vst) return fail(c, vst, why);
+    c->g = *geometry;
+
+    int dev = 0, ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+        cudaGetLastError();
+        return fail(c, HKV_ERR_NO_DEVICE, "no CUDA device");
+    }
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail_cuda(c, e, "cudaGetDevice");
+    int major = 0, sm = 0, optin = 0;
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    if (major != 10) return fail(c, HKV_ERR_NO_DEVICE, "device is not compute capability 10.x (built for sm_100a only)");
+    c->device = dev;
+    c->sm_count = sm;
+    c->smem_optin = (size_t)optin;
+    c->G = geometry->num_heads / geometry->num_kv_heads;
+    c->batch_stride = geometry->batch_stride_elems
+                          ? geometry->batch_stride_elems
+                          : (long long)geometry->slots * geometry->num_kv_heads * geometry->head_dim;
+    c->map = make_map(*geometry);
+    fill_plan(*geometry, sm, c->chunk_tiles, c->max_chunks);
+
+    // kernel choice
+    const bool tma_ok = tma_geometry_ok(*geometry);
+    if (geometry->kernel_select == HKV_KERNEL_TMA && !tma_ok)
+        return fail(c, HKV_ERR_GEOMETRY, "TMA kernel needs head_dim in {64,96,128,256}, group <= 16, stride % 8 == 0");
+    c->kernel = (geometry->kernel_select != HKV_KERNEL_GENERIC && tma_ok) ? HKV_KERNEL_TMA
+                                                                           : HKV_KERNEL_GENERIC;
+    if (c->kernel == HKV_KERNEL_TMA) {
+        const char* env = getenv("HKV_TMA_GROUPS");
+        c->tma_groups = (env && atoi(env) == 1) ? 1 : 2;
+        c->plan = tma_plan(geometry->head_dim, c->G, c->tma_groups * 4, geometry->batch, c->smem_optin);
+        if (c->plan.stages < 2 && c->tma_groups == 2) {
+            c->tma_groups = 1;
+            c->plan = tma_plan(geometry->head_dim, c->G, 4, geometry->batch, c->smem_optin);
+        }
+        if (c->plan.stages < 2) {
+            if (geometry->kernel_select == HKV_KERNEL_TMA)
+                return fail(c, HKV_ERR_GEOMETRY, "TMA kernel: shared memory too small for two stages");
+            c->kernel = HKV_KERNEL_GENERIC;
+        } else {
+            if (!encode_tiled_fn()) return fail(c, HKV_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+            TmaKernel kern = pick_tma(geometry->head_dim, (c->G + 7) / 8, c->tma_groups);
+            e = cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)c->plan.bytes);
+            if (e != cudaSuccess) return fail_cuda(c, e, "cudaFuncSetAttribute(shared memory)");
+        }
+    }
+
+    c->workspace_bytes = workspace_bytes_for(*geometry, c->max_chunks);
+    e = cudaMalloc(&c->workspace, c->workspace_bytes);
+    if (e != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(workspace)");
+    e = cudaMalloc(&c->d_status, sizeof(int32_t));
+    if (e != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(status)");
+    e = cudaMemset(c->d_status, 0, sizeof(int32_t));
+    if (e != cudaSuccess) return fail_cuda(c, e, "cudaMemset(status)");
+    e = cudaMalloc(&c->d_len, sizeof(int32_t) * geometry->batch);
+    if (e != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(length)");
+    e = cudaMallocHost(&c->h_len, sizeof(int32_t) * geometry->batch);
+    if (e != cudaSuccess) return fail_cuda(c, e, "cudaMallocHost(length)");
+    return HKV_OK;
+}
+
+int hkv_ctx_destroy(hkv_ctx* c) {
+    if (!c) return HKV_OK;
+    if (c->workspace) cudaFree(c->workspace);
+    if (c->d_status) cudaFree(c->d_status);
+    if (c->d_len) cudaFree(c->d_len);
+    if (c->h_len) cudaFreeHost(c->h_len);
+    if (c->st_q) cudaFree(c->st_q);
+    if (c->st_k) cudaFree(c->st_k);
+    if (c->st_v) cudaFree(c->st_v);
+    if (c->st_out) cudaFree(c->st_out);
+    for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
+    delete c;
+    return HKV_OK;
+}
+
+const char* hkv_ctx_last_error(const hkv_ctx* c) { return c ? c->err.c_str() : "null context"; }
+int hkv_ctx_kernel(const hkv_ctx* c) { return c ? c->kernel : 0; }
+int hkv_ctx_launches_per_decode(const hkv_ctx* c) { return c ? 2 : 0; }
+
+int hkv_ctx_device_status(hkv_ctx* c, void* stream, int32_t* status_out) {
+    if (!c || !status_out) return HKV_ERR_INVALID_ARG;
+    if (!c->d_status) return fail(c, HKV_ERR_INVALID_ARG, "context not initialised");
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail_cuda(c, e, "cudaStreamSynchronize");
+    e = cudaMemcpy(status_out, c->d_status, sizeof(int32_t), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail_cuda(c, e, "cudaMemcpy(status)");
+    if (*status_out != 0) {
+        cudaMemset(c->d_status, 0, sizeof(int32_t));
+        return fail(c, HKV_ERR_DEVICE_FAULT, "device status word is non-zero");
+    }
+    return HKV_OK;
+}
+
+#define HKV_CHECK_CTX(c)                                                        \
+    do {                                                                        \
+        if (!(c)) return HKV_ERR_INVALID_ARG;                                   \
+        if (!(c)->workspace) return fail((c), HKV_ERR_INVALID_ARG, "context not initialised"); \
+    } while (0)
+
+int hkv_append(hkv_ctx* c, const void* k_new, const void* v_new, void* k_cache, void* v_cache,
+               const int32_t* d_cache_pos, int32_t seq_new, void* stream) {
+    HKV_CHECK_CTX(c);
+    if (!d_cache_pos) return fail(c, HKV_ERR_INVALID_ARG, "append: null position array");
+    const int st = launch_append(c, k_new, v_new, k_cache, v_cache, d_cache_pos, 0, 0, seq_new,
+                                 (cudaStream_t)stream);
+    if (st) return st;
+    const cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "append launch");
+}
+
+int hkv_append_at(hkv_ctx* c, const void* k_new, const void* v_new, void* k_cache, void* v_cache,
+                  int32_t position, int32_t seq_new, void* stream) {
+    HKV_CHECK_CTX(c);
+    if (position < 0) return fail(c, HKV_ERR_INVALID_ARG, "append: negative position");
+    const int st = launch_append(c, k_new, v_new, k_cache, v_cache, nullptr, 0, position, seq_new,
+                                 (cudaStream_t)stream);
+    if (st) return st;
+    const cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "append launch");
+}
+
+int hkv_decode_attention(hkv_ctx* c, const void* q, const void* k_cache, const void* v_cache,
+                         void* out, const int32_t* d_total_seq, float scale, void* stream) {
+    HKV_CHECK_CTX(c);
+    return decode_full(c, q, nullptr, nullptr, const_cast<void*>(k_cache), const_cast<void*>(v_cache),
+                       out, nullptr, d_total_seq, 0, scale, (cudaStream_t)stream);
+}
+
+int hkv_decode_attention_len(hkv_ctx* c, const void* q, const void* k_cache, const void* v_cache,
+                             void* out, int32_t seq_len, float scale, void* stream) {
+    HKV_CHECK_CTX(c);
+    if (seq_len < 0) return fail(c, HKV_ERR_INVALID_ARG, "decode: negative seq_len");
+    const int st = set_host_len(c, seq_len, (cudaStream_t)stream);
+    if (st) return st;
+    return decode_full(c, q, nullptr, nullptr, const_cast<void*>(k_cache), const_cast<void*>(v_cache),
+                       out, nullptr, c->d_len, 0, scale, (cudaStream_t)stream);
+}
+
+int hkv_append_decode_attention(hkv_ctx* c, const void* q, const void* k_new, const void* v_new,
+                                void* k_cache, void* v_cache, void* out,
+                                const int32_t* d_cache_pos, float scale, void* stream) {
+    HKV_CHECK_CTX(c);
+    if (!k_new || !v_new) return fail(c, HKV_ERR_INVALID_ARG, "fused decode: null k_new/v_new");
+    if (!aligned(k_new, 2) || !aligned(v_new, 2))
+        return fail(c, HKV_ERR_ALIGNMENT, "fused decode: fp16 pointer not 2-byte aligned");
+    return decode_full(c, q, k_new, v_new, k_cache, v_cache, out, nullptr, d_cache_pos, 1, scale,
+                       (cudaStream_t)stream);
+}
+
+int hkv_decode_partials(hkv_ctx* c, const void* q, const void* k_new, const void* v_new,
+                        void* k_cache, void* v_cache, float* partial_out,
+                        const int32_t* d_total_seq, float scale, void* stream) {
+    HKV_CHECK_CTX(c);
+    if (!partial_out) return fail(c, HKV_ERR_INVALID_ARG, "decode_partials: null output");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (k_new) {
+        // d_total_seq holds attended lengths, so the new row sits at position total - 1.
+        // Only the rank that owns that position stores it (slot_of_pos is -1 elsewhere).
+        if (!v_new) return fail(c, HKV_ERR_INVALID_ARG, "decode_partials: k_new without v_new");
+        const int stt = launch_append(c, k_new, v_new, k_cache, v_cache, d_total_seq, -1, 0, 1, st);
+        if (stt) return stt;
+    }
+    return decode_full(c, q, nullptr, nullptr, k_cache, v_cache, nullptr, partial_out, d_total_seq, 0,
+                       scale, st);
+}
+
+int hkv_combine_partials(hkv_ctx* c, const float* partials, int32_t num_parts, void* out,
+                         void* stream) {
+    HKV_CHECK_CTX(c);
+    if (!partials || !out || num_parts <= 0) return fail(c, HKV_ERR_INVALID_ARG, "combine: bad arguments");
+    if (!aligned(out, 2)) return fail(c, HKV_ERR_ALIGNMENT, "combine: out not 2-byte aligned");
+    const long long PW = c->g.head_dim + 2;
+    const int st = launch_combine(c, partials, (long long)c->g.num_heads * PW,
+                                  (long long)c->g.batch * c->g.num_heads * PW, nullptr, 0, num_parts,
+                                  out, nullptr, (cudaStream_t)stream);
+    if (st) return st;
+    const cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "combine launch");
+}
+
+int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const void* v_cache,
+                          void* out, int32_t seq_new, int32_t past_len, float scale, void* stream) {
+    HKV_CHECK_CTX(c);
+    if (!q || !k_cache || !v_cache || !out) return fail(c, HKV_ERR_INVALID_ARG, "prefill: null tensor");
+    if (seq_new < 0 || past_len < 0) return fail(c, HKV_ERR_INVALID_ARG, "prefill: negative length");
+    if (!aligned(q, 2) || !aligned(k_cache, 2) || !aligned(v_cache, 2) || !aligned(out, 2))
+        return fail(c, HKV_ERR_ALIGNMENT, "prefill: fp16 pointer not 2-byte aligned");
+    if (c->g.layout != HKV_LAYOUT_LINEAR || c->g.shard_count > 1)
+        return fail(c, HKV_ERR_GEOMETRY, "prefill: linear unsharded cache only");
+    if (seq_new == 0) return HKV_OK;
+    PrefillArgs a;
+    a.q = (const __half*)q;
+    a.k_cache = (const __half*)k_cache;
+    a.v_cache = (const __half*)v_cache;
+    a.out = (__half*)out;
+    a.S_new = seq_new;
+    a.past_len = past_len;
+    a.H = c->g.num_heads;
+    a.KVH = c->g.num_kv_heads;
+    a.HD = c->g.head_dim;
+    a.slots = c->g.slots;
+    a.window = c->g.window_size;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    dim3 grid((unsigned)seq_new, (unsigned)c->g.num_heads);
+    hkv_prefill_generic_kernel<<<grid, kGenWarps * 32, 0, (cudaStream_t)stream>>>(a);
+    const cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "prefill launch");
+}
+
+int hkv_append_decode_attention_host(hkv_ctx* c, const void* h_q, const void* h_k_new,
+                                     const void* h_v_new, void* k_cache, void* v_cache,
+                                     void* h_out, const int32_t* d_cache_pos, float scale,
+                                     void* stream) {
+    HKV_CHECK_CTX(c);
+    if (!h_q || !h_k_new || !h_v_new || !h_out) return fail(c, HKV_ERR_INVALID_ARG, "host op: null buffer");
+    const size_t qb = (size_t)c->g.batch * c->g.num_heads * c->g.head_dim * 2;
+    const size_t kb = (size_t)c->g.batch * c->g.num_kv_heads * c->g.head_dim * 2;
+    cudaError_t e;
+    if (!c->st_q) {
+        if ((e = cudaMalloc(&c->st_q, qb)) != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(staging)");
+        if ((e = cudaMalloc(&c->st_k, kb)) != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(staging)");
+        if ((e = cudaMalloc(&c->st_v, kb)) != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(staging)");
+        if ((e = cudaMalloc(&c->st_out, qb)) != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(staging)");
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    if ((e = cudaMemcpyAsync(c->st_q, h_q, qb, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
+        (e = cudaMemcpyAsync(c->st_k, h_k_new, kb, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
+        (e = cudaMemcpyAsync(c->st_v, h_v_new, kb, cudaMemcpyHostToDevice, st)) != cudaSuccess)
+        return fail_cuda(c, e, "cudaMemcpyAsync(H2D)");
+    const int stt = decode_full(c, c->st_q, c->st_k, c->st_v, k_cache, v_cache, c->st_out, nullptr,
+                                d_cache_pos, 1, scale, st);
+    if (stt) return stt;
+    if ((e = cudaMemcpyAsync(h_out, c->st_out, qb, cudaMemcpyDeviceToHost, st)) != cudaSuccess)
+        return fail_cuda(c, e, "cudaMemcpyAsync(D2H)");
+    return HKV_OK;
+}
+
+int hkv_ctx_profile_begin(hkv_ctx* c, int32_t max_calls) {
+    HKV_CHECK_CTX(c);
+    if (max_calls < 0 || max_calls > (1 << 20)) return fail(c, HKV_ERR_INVALID_ARG, "profile: bad max_calls");
+    while ((int)c->prof_events.size() < max_calls * 3) {
+        cudaEvent_t e;
+        const cudaError_t err = cudaEventCreate(&e);
+        if (err != cudaSuccess) return fail_cuda(c, err, "cudaEventCreate");
+        c->prof_events.push_back(e);
+    }
+    c->prof_calls = 0;
+    c->prof_max = max_calls;
+    return HKV_OK;
+}
+
+int hkv_ctx_profile_end(hkv_ctx* c, void* stream, float* decode_ms, float* combine_ms, int32_t* calls) {
+    HKV_CHECK_CTX(c);
+    cudaError_t err = cudaStreamSynchronize((cudaStream_t)stream);
+    if (err != cudaSuccess) return fail_cuda(c, err, "cudaStreamSynchronize");
+    float d = 0.0f, m = 0.0f;
+    for (int i = 0; i < c->prof_calls; ++i) {
+        float a = 0.0f, b = 0.0f;
+        cudaEventElapsedTime(&a, c->prof_events[(size_t)i * 3], c->prof_events[(size_t)i * 3 + 1]);
+        cudaEventElapsedTime(&b, c->prof_events[(size_t)i * 3 + 1], c->prof_events[(size_t)i * 3 + 2]);
+        d += a;
+        m += b;
+    }
+    if (decode_ms) *decode_ms = d;
+    if (combine_ms) *combine_ms = m;
+    if (calls) *calls = c->prof_calls;
+    c->prof_max = 0;
+    c->prof_calls = 0;
+    return HKV_OK;
+}
+
+int32_t hkv_slot_of_position(const hkv_geometry* g, int32_t pos) {
+    const char* why;
+    if (validate_geometry(g, &why) != HKV_OK) return -1;
+    return slot_of_pos(make_map(*g), pos);
+}
+
+int32_t hkv_position_of_slot(const hkv_geometry* g, int32_t slot, int32_t total_seq) {
+    const char* why;
+    if (validate_geometry(g, &why) != HKV_OK || slot < 0 || slot >= g->slots) return -1;
+    return pos_of_slot(make_map(*g), slot, total_seq);
+}
+
+int hkv_plan_sequence(const hkv_geometry* g, int32_t total_seq, int32_t chunk_tiles,
+                      int32_t* first, int32_t* tile_lo, int32_t* n_tiles, int32_t* n_chunks) {
+    const char* why;
+    const int st = validate_geometry(g, &why);
+    if (st) return st;
+    if (chunk_tiles <= 0 || total_seq < 0) return HKV_ERR_INVALID_ARG;
+    const SeqMap m = make_map(*g);
+    int tl, nt;
+    tile_range(m, total_seq, tl, nt);
+    if (first) *first = first_pos(m, total_seq);
+    if (tile_lo) *tile_lo = tl;
+    if (n_tiles) *n_tiles = nt;
+    if (n_chunks) *n_chunks = (nt + chunk_tiles - 1) / chunk_tiles;
+    return HKV_OK;
+}
+
+int hkv_fill_synthetic(void* dst, uint64_t seed, uint64_t first_index, uint64_t count, void* stream) {
+    if (!dst && count) return HKV_ERR_INVALID_ARG;
+    if (!aligned(dst, 2)) return HKV_ERR_ALIGNMENT;
+    if (count == 0) return HKV_OK;
+    unsigned long long blocks = (count + 255) / 256;
+    if (blocks > 148ull * 32) blocks = 148ull * 32;
+    hkv_fill_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((__half*)dst, seed, first_index,
+                                                                        count);
+    return cudaPeekAtLastError() == cudaSuccess ? HKV_OK : HKV_ERR_CUDA;
+}
+
+}  // extern "C"

@@ -1,0 +1,227 @@
+// hkv_basic.cuh — append, any-geometry split-K decode, combine and synthetic fill.
+//
+// Reference semantics restated here (paths relative to the reference project root):
+//   append   kernels/attention.cu:1119-1151   decode  kernels/attention.cu:337-494
+#pragma once
+
+#include "hkv_common.cuh"
+
+namespace hkv {
+
+// ---------------------------------------------------------------------------
+// Append: K and V rows of `seq_new` tokens per sequence in ONE launch.
+// One thread per VEC-byte piece of a (sequence, token, plane) row of KVH*HD halfs.
+// VEC = 16 when every pointer/stride allows it, else 2.
+// ---------------------------------------------------------------------------
+struct AppendArgs {
+    const __half* k_new;
+    const __half* v_new;
+    __half* k_cache;
+    __half* v_cache;
+    const int32_t* d_pos;  // [B] or null -> host_pos
+    int host_pos;
+    int pos_bias;          // added to the position read from d_pos (e.g. -1: length -> index)
+    SeqMap map;
+    int B, S, row_elems;   // row_elems = KVH*HD
+    long long batch_stride;
+};
+
+template <typename VecT>
+__global__ void __launch_bounds__(256) hkv_append_kernel(const AppendArgs a) {
+    constexpr int kPer = (int)(sizeof(VecT) / sizeof(__half));
+    const int pieces = a.row_elems / kPer;  // per row
+    const long long total = 2ll * a.B * a.S * pieces;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int piece = (int)(i % pieces);
+        long long r = i / pieces;
+        const int plane = (int)(r & 1);
+        r >>= 1;
+        const int s = (int)(r % a.S);
+        const int b = (int)(r / a.S);
+        const int pos = (a.d_pos ? a.d_pos[b] + a.pos_bias : a.host_pos) + s;
+        const int slot = slot_of_pos(a.map, pos);
+        if (slot < 0) continue;
+        const __half* src = (plane ? a.v_new : a.k_new) + ((long long)b * a.S + s) * a.row_elems;
+        __half* dst = (plane ? a.v_cache : a.k_cache) + (long long)b * a.batch_stride +
+                      (long long)slot * a.row_elems;
+        reinterpret_cast<VecT*>(dst)[piece] = reinterpret_cast<const VecT*>(src)[piece];
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Generic split-K decode (SIMT). One CTA of 4 warps per (chunk, head, sequence);
+// warp w takes rows lo+w, lo+w+4, ... of the chunk; lane-strided dot product and
+// online softmax per warp in the log2 domain; warps merged in shared memory; one
+// partial (m, l, o[HD]) per (sequence, chunk, head). Any head_dim <= 512, any group.
+// ---------------------------------------------------------------------------
+constexpr int kGenWarps = 4;
+constexpr int kGenMaxPerLane = 16;  // head_dim <= 512
+
+__global__ void __launch_bounds__(kGenWarps * 32) hkv_decode_generic_kernel(const DecodeArgs a) {
+    const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total = attended_len(a, b);
+    int tile_lo, n_tiles;
+    tile_range(a.map, total, tile_lo, n_tiles);
+    const int n_chunks = (n_tiles + a.chunk_tiles - 1) / a.chunk_tiles;
+    if (chunk >= n_chunks) return;
+
+    const int G = a.H / a.KVH;
+    const int kvh = h / G;
+    const int first = first_pos(a.map, total);
+    const int row0 = (tile_lo + chunk * a.chunk_tiles) * kTileRows;
+    int row1 = row0 + a.chunk_tiles * kTileRows;
+    const int row_end = (tile_lo + n_tiles) * kTileRows;
+    if (row1 > row_end) row1 = row_end;
+    if (row1 > a.map.slots) row1 = a.map.slots;
+
+    float qr[kGenMaxPerLane], acc[kGenMaxPerLane];
+    const __half* qp = a.q + ((long long)b * a.H + h) * a.HD;
+#pragma unroll
+    for (int i = 0; i < kGenMaxPerLane; ++i) {
+        const int d = lane + 32 * i;
+        qr[i] = d < a.HD ? __half2float(qp[d]) : 0.0f;
+        acc[i] = 0.0f;
+    }
+    float m = kNegBig, l = 0.0f;
+    const long long plane_off = (long long)b * a.batch_stride + (long long)kvh * a.HD;
+    const int row_elems = a.KVH * a.HD;
+
+    for (int s = row0 + warp; s < row1; s += kGenWarps) {
+        const int p = pos_of_slot(a.map, s, total);
+        if (p < first || p >= total) continue;  // warp-uniform
+        const __half* kr = a.k_cache + plane_off + (long long)s * row_elems;
+        const __half* vr = a.v_cache + plane_off + (long long)s * row_elems;
+        float dot = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kGenMaxPerLane; ++i) {
+            const int d = lane + 32 * i;
+            if (d < a.HD) dot = fmaf(qr[i], __half2float(kr[d]), dot);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        const float sc = dot * a.scale_log2;
+        const float mn = fmaxf(m, sc);
+        const float corr = exp2f(m - mn), e = exp2f(sc - mn);
+        l = l * corr + e;
+#pragma unroll
+        for (int i = 0; i < kGenMaxPerLane; ++i) {
+            const int d = lane + 32 * i;
+            if (d < a.HD) acc[i] = fmaf(e, __half2float(vr[d]), acc[i] * corr);
+        }
+        m = mn;
+    }
+
+    __shared__ float s_m[kGenWarps], s_l[kGenWarps];
+    __shared__ float s_acc[kGenWarps][kGenMaxPerLane * 32];
+    if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < kGenMaxPerLane; ++i) s_acc[warp][lane + 32 * i] = acc[i];
+    __syncthreads();
+
+    float gm = s_m[0];
+#pragma unroll
+    for (int w = 1; w < kGenWarps; ++w) gm = fmaxf(gm, s_m[w]);
+    float gl = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kGenWarps; ++w) gl += s_l[w] * exp2f(s_m[w] - gm);
+    float* prow = a.part + (((long long)b * a.max_chunks + chunk) * a.H + h) * (a.HD + 2);
+    for (int d = threadIdx.x; d < a.HD; d += kGenWarps * 32) {
+        float o = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kGenWarps; ++w) o += s_acc[w][d] * exp2f(s_m[w] - gm);
+        prow[d] = o;
+    }
+    if (threadIdx.x == 0) {
+        prow[a.HD] = gm;
+        prow[a.HD + 1] = gl;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Combine: merge the partials of one (sequence, head).
+//   o = sum_c 2^(m_c - M) o_c,  l = sum_c 2^(m_c - M) l_c,  M = max_c m_c
+// A partial is a row of HD+2 floats (o[0..HD), m, l); partial c of (b, h) starts at
+// part[b*stride_b + c*stride_c + h*(HD+2)]. Count: from the sequence length (local
+// split-K) or fixed (partials gathered from other GPUs).
+// Output: fp16 rows (RN, zero when l == 0 — kernels/attention.cu:478) and/or one merged
+// partial [B, H, HD+2] for the cross-GPU exchange.
+// ---------------------------------------------------------------------------
+struct CombineArgs {
+    const float* part;
+    long long stride_b, stride_c;  // floats
+    const int32_t* total;          // null -> fixed_count
+    int pos_is_index;
+    int fixed_count;
+    SeqMap map;
+    int chunk_tiles;
+    int H, HD;
+    __half* out;         // [B, H, HD] or null
+    float* out_partial;  // [B, H, HD+2] or null
+};
+
+__global__ void __launch_bounds__(128) hkv_combine_kernel(const CombineArgs a) {
+    const int h = blockIdx.x, b = blockIdx.y;
+    int n = a.fixed_count;
+    if (a.total) {
+        const int t = a.total[b] + a.pos_is_index;
+        n = num_chunks(a.map, t > 0 ? t : 0, a.chunk_tiles);
+    }
+    const int PW = a.HD + 2;
+    const float* base = a.part + b * a.stride_b + (long long)h * PW;
+    float M = kNegBig;
+    for (int c = 0; c < n; ++c) M = fmaxf(M, base[c * a.stride_c + a.HD]);
+    float L = 0.0f;
+    for (int c = 0; c < n; ++c) {
+        const float* row = base + c * a.stride_c;
+        L += row[a.HD + 1] * exp2f(row[a.HD] - M);
+    }
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    for (int d = threadIdx.x; d < a.HD; d += blockDim.x) {
+        float o = 0.0f;
+        for (int c = 0; c < n; ++c) {
+            const float* row = base + c * a.stride_c;
+            o = fmaf(row[d], exp2f(row[a.HD] - M), o);
+        }
+        if (a.out) a.out[((long long)b * a.H + h) * a.HD + d] = __float2half_rn(o * inv);
+        if (a.out_partial) a.out_partial[((long long)b * a.H + h) * PW + d] = o;
+    }
+    if (a.out_partial && threadIdx.x == 0) {
+        float* row = a.out_partial + ((long long)b * a.H + h) * PW;
+        row[a.HD] = M;
+        row[a.HD + 1] = L;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Synthetic data (same bits as the CPU generator of the test oracle): the sum of
+// twelve 16-bit uniform fields of three splitmix64 outputs, centred and scaled by an
+// exact power of two (Irwin-Hall(12): mean 0, variance 1), rounded RN to fp16.
+// ---------------------------------------------------------------------------
+__host__ __device__ inline unsigned long long splitmix64(unsigned long long x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+__global__ void __launch_bounds__(256) hkv_fill_kernel(__half* dst, unsigned long long seed,
+                                                       unsigned long long first,
+                                                       unsigned long long count) {
+    for (unsigned long long i = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x;
+         i < count; i += (unsigned long long)gridDim.x * blockDim.x) {
+        const unsigned long long base = splitmix64(seed ^ ((first + i) * 0xD1342543DE82EF95ull));
+        unsigned int sum = 0;
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+            const unsigned long long v = splitmix64(base + (unsigned long long)r);
+            sum += (unsigned int)(v & 0xFFFF) + (unsigned int)((v >> 16) & 0xFFFF) +
+                   (unsigned int)((v >> 32) & 0xFFFF) + (unsigned int)((v >> 48) & 0xFFFF);
+        }
+        const float x = (float)((int)(2u * sum) - 786420) * (1.0f / 131072.0f);
+        dst[i] = __float2half_rn(x);
+    }
+}
+
+}  // namespace hkv

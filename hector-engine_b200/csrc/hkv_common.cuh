@@ -1,0 +1,216 @@
+// hkv_common.cuh — shared device-side definitions: how a sequence's logical positions
+// map to rows ("slots") of a cache plane, how a sequence is cut into split-K work
+// items, the partial (m, l, o) format, and thin wrappers over the sm_100a PTX used by
+// the kernels (mbarrier, bulk-tensor copies, ldmatrix, mma, movmatrix).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace hkv {
+
+constexpr int kTileRows = 64;          // rows per split-K tile (unit of chunk_tiles)
+constexpr float kNegBig = -1.0e30f;    // "minus infinity" that survives subtraction
+constexpr int kStatusWaitRanOut = 1;   // device status bits
+constexpr int kStatusBoundCheck = 2;
+
+// How logical positions of one sequence map to rows of its cache plane.
+struct SeqMap {
+    int slots;        // rows per sequence
+    int layout;       // 0 linear, 1 ring
+    int window;       // 0 = none
+    int shard_rank;   // block-cyclic sequence split (shard_count <= 1: off)
+    int shard_count;
+    int shard_block;
+};
+
+// Row that holds logical position p on this rank, or -1 (not stored here / dropped).
+__host__ __device__ inline int slot_of_pos(const SeqMap& m, int p) {
+    if (p < 0) return -1;
+    if (m.shard_count > 1) {
+        const int blk = p / m.shard_block;
+        if (blk % m.shard_count != m.shard_rank) return -1;
+        const int s = (blk / m.shard_count) * m.shard_block + p % m.shard_block;
+        return s < m.slots ? s : -1;
+    }
+    if (m.layout == 1) return p % m.slots;
+    return p < m.slots ? p : -1;  // reference drops rows past the plane (attention.cu:1143)
+}
+
+// Logical position held by row s when the sequence has `total` positions; may be < 0
+// or >= total (then the row is not attended).
+__host__ __device__ inline int pos_of_slot(const SeqMap& m, int s, int total) {
+    if (m.shard_count > 1) {
+        return ((s / m.shard_block) * m.shard_count + m.shard_rank) * m.shard_block +
+               s % m.shard_block;
+    }
+    if (m.layout == 1) {
+        const int last = total - 1;
+        int r = (last - s) % m.slots;
+        if (r < 0) r += m.slots;
+        return last - r;
+    }
+    return s;
+}
+
+// First attended logical position (reference: kernels/attention.cu:385-389).
+__host__ __device__ inline int first_pos(const SeqMap& m, int total) {
+    int f = m.window > 0 ? (total - m.window > 0 ? total - m.window : 0) : 0;
+    if (m.layout == 1 && total - m.slots > f) f = total - m.slots;
+    return f;
+}
+
+// Rows [lo, hi) of this rank's plane that can hold attended positions.
+__host__ __device__ inline void slot_range(const SeqMap& m, int total, int& lo, int& hi) {
+    if (total <= 0) { lo = hi = 0; return; }
+    if (m.shard_count > 1) {
+        const int full = total / m.shard_block, rem = total % m.shard_block;
+        int n = ((full + m.shard_count - 1 - m.shard_rank) / m.shard_count) * m.shard_block;
+        if (full % m.shard_count == m.shard_rank) n += rem;
+        lo = 0;
+        hi = n < m.slots ? n : m.slots;
+        return;
+    }
+    if (m.layout == 1 && total > m.slots) { lo = 0; hi = m.slots; return; }
+    lo = first_pos(m, total);
+    hi = total < m.slots ? total : m.slots;
+    if (lo > hi) lo = hi;
+}
+
+// Split-K work items of one sequence: tiles are kTileRows-aligned in row space.
+__host__ __device__ inline void tile_range(const SeqMap& m, int total, int& tile_lo, int& n_tiles) {
+    int lo, hi;
+    slot_range(m, total, lo, hi);
+    if (hi <= lo) { tile_lo = 0; n_tiles = 0; return; }
+    tile_lo = lo / kTileRows;
+    n_tiles = (hi + kTileRows - 1) / kTileRows - tile_lo;
+}
+__host__ __device__ inline int num_chunks(const SeqMap& m, int total, int chunk_tiles) {
+    int tile_lo, n_tiles;
+    tile_range(m, total, tile_lo, n_tiles);
+    return (n_tiles + chunk_tiles - 1) / chunk_tiles;
+}
+
+// Arguments shared by the decode kernels.
+struct DecodeArgs {
+    const __half* q;        // [B, H, HD]
+    const __half* k_cache;  // [B, slots, KVH, HD]
+    const __half* v_cache;
+    const __half* k_new;    // fused append: [B, KVH, HD] or null
+    const __half* v_new;
+    __half* k_cache_w;      // writable aliases of the planes (fused append)
+    __half* v_cache_w;
+    float* part;            // [B, max_chunks, H, HD+2]: o[HD], m (log2 domain), l
+    const int32_t* total;   // [B] attended length, or cache position when pos_is_index
+    int32_t* status;        // device status word
+    SeqMap map;
+    int B, H, KVH, HD;
+    int chunk_tiles, max_chunks;
+    int pos_is_index;       // 1: total[b] holds cache_pos, attended length = cache_pos + 1
+    long long batch_stride; // elements
+    float scale_log2;       // scale * log2(e)
+};
+
+__device__ __forceinline__ int attended_len(const DecodeArgs& a, int b) {
+    const int t = a.total[b] + a.pos_is_index;
+    return t > 0 ? t : 0;
+}
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after ~2 s of wall time, records it in the status word and
+// returns false so the caller can leave its loops; the context stays usable.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t* status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0 = 0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+        for (int i = 0; i < 1024; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        unsigned long long t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (t1 - t0 > 2000000000ull) break;
+    }
+    atomicOr(status, kStatusWaitRanOut);
+    return false;
+}
+
+// 4-D bulk-tensor load global -> shared (no multicast), completion on an mbarrier.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint32_t bar, int c0,
+                                            int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                        uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                          uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                          uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t movmatrix_t(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+}  // namespace hkv

@@ -1,0 +1,214 @@
+/* hkv.h — C ABI of libhkv: KV-cache append + cached grouped-query attention for
+ * NVIDIA B200 (sm_100a), a drop-in for that one hot path of the Héctor / HELIOS engine.
+ *
+ * Conventions
+ *   - Every entry point returns an hkv_status (0 = ok); nothing throws, nothing is
+ *     printed. hkv_ctx_last_error() gives the text of the last failure of a context.
+ *   - All tensors are IEEE binary16 ("fp16") in device memory, passed as void*;
+ *     positions are int32 in DEVICE memory (one per sequence); `stream` is a
+ *     cudaStream_t passed as void* (NULL = the legacy default stream).
+ *   - Launch entry points only enqueue work on `stream`: no allocation, no
+ *     synchronisation, no host read of device memory. They may be called while the
+ *     stream is being captured into a CUDA graph; per-step variation then comes only
+ *     from the device-side position arrays. hkv_ctx_create / destroy / *_host /
+ *     hkv_ctx_device_status are NOT capturable (they allocate or synchronise).
+ *   - There is no CPU path. Without a usable CUDA device every call fails with
+ *     HKV_ERR_NO_DEVICE or HKV_ERR_CUDA.
+ *
+ * Layouts (row-major, matching the reference engine; paths below are relative to the
+ * reference project root)
+ *   q, out        [batch, 1, num_heads, head_dim]           kernels/attention.cu:156-159
+ *   k/v plane     [batch, slots, num_kv_heads, head_dim]    src/kv_cache.hpp:175-189
+ *   k_new, v_new  [batch, seq_new, num_kv_heads, head_dim]  kernels/attention.cu:1092-1094
+ *   prefill q/out [seq_new, num_heads, head_dim], batch 1   kernels/attention.cu:665-668
+ */
+#ifndef HKV_H_
+#define HKV_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HKV_ABI_VERSION 1
+
+typedef enum hkv_status {
+    HKV_OK = 0,
+    HKV_ERR_INVALID_ARG = 1, /* null pointer, negative size, unknown enum value          */
+    HKV_ERR_GEOMETRY = 2,    /* head geometry the reference op would also reject, or a
+                                combination this library does not implement              */
+    HKV_ERR_ALIGNMENT = 3,   /* a pointer or stride is not a multiple of 2 bytes         */
+    HKV_ERR_CUDA = 4,        /* a CUDA runtime / driver call failed                      */
+    HKV_ERR_NO_DEVICE = 5,   /* no CUDA device, or not compute capability 10.x           */
+    HKV_ERR_WORKSPACE = 6,   /* caller-supplied workspace too small                      */
+    HKV_ERR_TOO_LARGE = 7,   /* a size exceeds a documented maximum                      */
+    HKV_ERR_DEVICE_FAULT = 8 /* the device status word reports a bounded wait that ran out */
+} hkv_status;
+
+typedef enum hkv_layout {
+    HKV_LAYOUT_LINEAR = 0, /* row = position; rows >= slots are dropped on append
+                              (kernels/attention.cu:1143-1144)                           */
+    HKV_LAYOUT_RING = 1    /* row = position mod slots (sliding-window layers). Not in the
+                              reference; results equal the reference's linear cache with
+                              window_size = slots                                        */
+} hkv_layout;
+
+typedef enum hkv_kernel_select {
+    HKV_KERNEL_AUTO = 0,    /* TMA-staged tensor-tile kernel when the geometry allows    */
+    HKV_KERNEL_GENERIC = 1, /* force the any-geometry SIMT kernel                        */
+    HKV_KERNEL_TMA = 2      /* require the TMA kernel; HKV_ERR_GEOMETRY if not eligible  */
+} hkv_kernel_select;
+
+/* Geometry of one attention layer's cache and op. Zero-initialise, then fill in. */
+typedef struct hkv_geometry {
+    int32_t batch;        /* sequences per call (the reference op is always 1,
+                             kernels/register_kernels.cpp:870)                           */
+    int32_t num_heads;    /* query heads H                                               */
+    int32_t num_kv_heads; /* KV heads; H % KVH == 0 (kernels/register_kernels.cpp:858)   */
+    int32_t head_dim;     /* 1..512 (kernels/register_kernels.cpp:858)                   */
+    int32_t slots;        /* rows per sequence in a plane = the reference's max_seq_len  */
+    int32_t window_size;  /* 0 = attend everything; W = last W positions
+                             (kernels/attention.cu:385)                                  */
+    int32_t layout;       /* hkv_layout                                                  */
+    int32_t chunk_tiles;  /* split-K work item size in 64-row tiles; 0 = auto            */
+    int64_t batch_stride_elems; /* elements between sequences in a plane; 0 = dense      */
+    /* Sequence-split sharding of ONE logical cache over several GPUs: logical blocks of
+     * `shard_block` positions are dealt round-robin, block j lives on rank j % shard_count
+     * as local block j / shard_count. shard_count <= 1 means not sharded.               */
+    int32_t shard_rank;
+    int32_t shard_count;
+    int32_t shard_block;  /* multiple of 64                                              */
+    int32_t kernel_select; /* hkv_kernel_select                                          */
+    int32_t max_seq_new;  /* largest seq_new for hkv_prefill_attention; 0 = decode only   */
+    int32_t reserved[3];
+} hkv_geometry;
+
+typedef struct hkv_ctx hkv_ctx;
+
+/* ---- lifetime ------------------------------------------------------------------- */
+
+int hkv_abi_version(void);
+const char* hkv_status_string(int status);
+
+/* Validates the geometry and allocates the split-K workspace and the device status
+ * word on the CURRENT device. Replaces nothing in the reference (its kernel needs no
+ * workspace); the reference-side owner is the object that registers the ops
+ * (kernels/register_kernels.cpp:649). */
+int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry);
+int hkv_ctx_destroy(hkv_ctx* ctx);
+const char* hkv_ctx_last_error(const hkv_ctx* ctx);
+/* Bytes of split-K workspace hkv_ctx_create allocates for this geometry. */
+size_t hkv_workspace_bytes(const hkv_geometry* geometry);
+/* Synchronises `stream`, reads the device status word and clears it. 0 = clean.
+ * Non-zero bits: 1 = a bounded barrier wait ran out, 2 = an internal bound check failed. */
+int hkv_ctx_device_status(hkv_ctx* ctx, void* stream, int32_t* status_out);
+/* Which kernel the context selected: 1 = generic, 2 = TMA. */
+int hkv_ctx_kernel(const hkv_ctx* ctx);
+/* Kernels one decode call launches (for launch accounting). */
+int hkv_ctx_launches_per_decode(const hkv_ctx* ctx);
+
+/* ---- the path ------------------------------------------------------------------- */
+
+/* KV append. Replaces launch_kv_cache_update_dp (kernels/attention.cu:1153-1170,
+ * declared kernels/kernels.hpp:428-440) — K and V in one launch, 16-byte accesses.
+ * d_cache_pos[b] is the write index of token 0 of sequence b. */
+int hkv_append(hkv_ctx* ctx, const void* k_new, const void* v_new, void* k_cache, void* v_cache,
+               const int32_t* d_cache_pos, int32_t seq_new, void* stream);
+
+/* Host-position twin. Replaces launch_kv_cache_update (kernels/attention.cu:1099-1116):
+ * every sequence writes at `position`. */
+int hkv_append_at(hkv_ctx* ctx, const void* k_new, const void* v_new, void* k_cache,
+                  void* v_cache, int32_t position, int32_t seq_new, void* stream);
+
+/* Cached decode attention. Replaces launch_attention_cached_fp16_dp
+ * (kernels/attention.cu:496-510, declared kernels/kernels.hpp:468-482).
+ * d_total_seq[b] = attended length (cache position + 1). */
+int hkv_decode_attention(hkv_ctx* ctx, const void* q, const void* k_cache, const void* v_cache,
+                         void* out, const int32_t* d_total_seq, float scale, void* stream);
+
+/* Host-length twin. Replaces launch_attention_cached_fp16 (kernels/attention.cu:318-334):
+ * every sequence attends `seq_len` positions. Uses a context-owned device int32[batch]
+ * that is refreshed with an async copy on `stream` (so: not for graph replay). */
+int hkv_decode_attention_len(hkv_ctx* ctx, const void* q, const void* k_cache,
+                             const void* v_cache, void* out, int32_t seq_len, float scale,
+                             void* stream);
+
+/* Fused append + decode attention: the op the reference registry declares with five
+ * inputs (Q, K_cache, V_cache, K_new, V_new; src/optype.cpp:118-120) but never
+ * implements. Equals hkv_append(seq_new = 1) followed by hkv_decode_attention with
+ * total = cache_pos + 1, in one pass over the cache. */
+int hkv_append_decode_attention(hkv_ctx* ctx, const void* q, const void* k_new, const void* v_new,
+                                void* k_cache, void* v_cache, void* out,
+                                const int32_t* d_cache_pos, float scale, void* stream);
+
+/* Prefill over the cache, batch 1. Replaces launch_attention_prefill_cached_fp16
+ * (kernels/attention.cu:775-788). The cache must already hold the chunk. */
+int hkv_prefill_attention(hkv_ctx* ctx, const void* q, const void* k_cache, const void* v_cache,
+                          void* out, int32_t seq_new, int32_t past_len, float scale, void* stream);
+
+/* ---- sequence-split (multi-GPU) -------------------------------------------------- */
+
+/* Floats per (sequence, head) in an exchanged partial: head_dim + 2  (o[], m, l). */
+size_t hkv_partial_floats(const hkv_geometry* geometry);
+/* Decode over this rank's shard of the cache; writes ONE merged fp32 partial per
+ * (sequence, head) to `partial_out` [batch, num_heads, head_dim + 2]: un-normalised
+ * output, running maximum (log2 domain) and sum. No counterpart in the reference
+ * (it is single-GPU). k_new/v_new may be NULL (no append); otherwise the rank that
+ * owns position d_cache_pos[b] appends it. */
+int hkv_decode_partials(hkv_ctx* ctx, const void* q, const void* k_new, const void* v_new,
+                        void* k_cache, void* v_cache, float* partial_out,
+                        const int32_t* d_total_seq, float scale, void* stream);
+/* Merge `num_parts` partials laid out [num_parts, batch, num_heads, head_dim + 2] (as an
+ * all-gather delivers them) into fp16 `out`. */
+int hkv_combine_partials(hkv_ctx* ctx, const float* partials, int32_t num_parts, void* out,
+                         void* stream);
+
+/* ---- host-buffer convenience (end-to-end timing, tests) --------------------------- */
+
+/* Fused op with HOST q / k_new / v_new / out (pinned memory recommended): copies the
+ * inputs to context-owned device staging, runs hkv_append_decode_attention, copies the
+ * result back; all on `stream`, no synchronisation. Not capturable. */
+int hkv_append_decode_attention_host(hkv_ctx* ctx, const void* h_q, const void* h_k_new,
+                                     const void* h_v_new, void* k_cache, void* v_cache,
+                                     void* h_out, const int32_t* d_cache_pos, float scale,
+                                     void* stream);
+
+/* ---- per-kernel timing (benchmarks; not capturable) -------------------------------- */
+
+/* After hkv_ctx_profile_begin every decode call records CUDA events on its stream before
+ * the split-K kernel, between it and the combine kernel, and after the combine kernel
+ * (up to `max_calls` calls; later calls are not timed). hkv_ctx_profile_end synchronises
+ * the stream, returns the summed durations in milliseconds and the number of timed
+ * calls, and switches timing off. No counterpart in the reference at this level (its
+ * Engine times whole ops, src/engine.cpp:299-316). */
+int hkv_ctx_profile_begin(hkv_ctx* ctx, int32_t max_calls);
+int hkv_ctx_profile_end(hkv_ctx* ctx, void* stream, float* decode_ms, float* combine_ms,
+                        int32_t* calls);
+
+/* ---- planning (host arithmetic only; works without a GPU) ------------------------- */
+
+/* Row of this rank's plane that stores logical position `pos`, or -1 when the position
+ * is not stored here (dropped past the end of a linear plane as in
+ * kernels/attention.cu:1143-1144, or owned by another rank). */
+int32_t hkv_slot_of_position(const hkv_geometry* geometry, int32_t pos);
+/* Logical position held by row `slot` for a sequence of `total_seq` positions (may lie
+ * outside the attended range). */
+int32_t hkv_position_of_slot(const hkv_geometry* geometry, int32_t slot, int32_t total_seq);
+/* Split-K plan of one sequence: first attended position, first 64-row tile, number of
+ * tiles and number of work items (chunks) for `chunk_tiles` tiles per item. */
+int hkv_plan_sequence(const hkv_geometry* geometry, int32_t total_seq, int32_t chunk_tiles,
+                      int32_t* first_pos, int32_t* tile_lo, int32_t* n_tiles, int32_t* n_chunks);
+
+/* ---- utilities ------------------------------------------------------------------- */
+
+/* Deterministic synthetic fp16 data, bit-identical to the CPU generator used by the
+ * test oracle: element i gets value(seed, first_index + i), approximately N(0,1). */
+int hkv_fill_synthetic(void* dst, uint64_t seed, uint64_t first_index, uint64_t count,
+                       void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HKV_H_ */

@@ -1,0 +1,173 @@
+"""CPU suite: the C-ABI library loads, exports every symbol include/hkv.h declares, rejects
+bad geometry before touching a device, and its host-side planning arithmetic is right.
+No compute call is made here (no GPU in this suite)."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(REPO, "include", "hkv.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(hkv_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(hkv):
+    lib = C.CDLL(hkv._capi.LIB_PATH)
+    names = declared_symbols()
+    assert len(names) >= 20
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in include/hkv.h but not exported"
+    assert set(names) == set(hkv._capi.SIGNATURES), "ctypes table and header disagree"
+    assert hkv._capi.load().hkv_abi_version() == 1
+
+
+def test_product_library_has_no_oracle_or_torch_dependency(hkv):
+    """The shipped library must not link the test oracle or PyTorch."""
+    import subprocess
+    out = subprocess.run(["ldd", hkv._capi.LIB_PATH], capture_output=True, text=True).stdout
+    assert "oracle" not in out and "torch" not in out and "libc10" not in out
+
+
+def test_geometry_validation_needs_no_device(hkv):
+    bad = [
+        (dict(num_heads=14, num_kv_heads=3, head_dim=64), 2),     # H % KVH != 0 (reference guard)
+        (dict(num_heads=8, num_kv_heads=8, head_dim=513), 2),     # head_dim > 512
+        (dict(num_heads=8, num_kv_heads=8, head_dim=0), 2),
+        (dict(num_heads=8, num_kv_heads=8, head_dim=64, batch=0), 1),
+        (dict(num_heads=8, num_kv_heads=8, head_dim=64, slots=0), 1),
+        (dict(num_heads=8, num_kv_heads=8, head_dim=64, layout=7), 1),
+        (dict(num_heads=8, num_kv_heads=8, head_dim=64, shard_count=2, shard_rank=2), 1),
+        (dict(num_heads=8, num_kv_heads=8, head_dim=64, shard_count=2, shard_block=100), 1),
+        (dict(num_heads=8, num_kv_heads=8, head_dim=64, shard_count=2, layout=1), 2),
+        (dict(num_heads=8, num_kv_heads=8, head_dim=64, slots=100, batch_stride_elems=8), 1),
+    ]
+    for kw, status in bad:
+        with pytest.raises(hkv.HkvError) as e:
+            hkv.Context(hkv.Geometry(**kw))
+        assert e.value.status == status, (kw, e.value)
+
+
+def test_no_cpu_fallback(hkv):
+    """Without a CUDA device a valid geometry must fail loudly, not compute on the host."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(hkv.HkvError) as e:
+        hkv.Context(hkv.Geometry(batch=1, num_heads=14, num_kv_heads=2, head_dim=64, slots=2048))
+    assert e.value.status in (4, 5)
+
+
+def _plan(hkv, g, total, ct):
+    lib = hkv._capi.load()
+    vals = [C.c_int32() for _ in range(4)]
+    st = lib.hkv_plan_sequence(C.byref(g.to_c()), total, ct, *[C.byref(v) for v in vals])
+    assert st == 0
+    return [v.value for v in vals]
+
+
+def test_slot_maps_linear_ring_sharded(hkv):
+    lib = hkv._capi.load()
+    lin = hkv.Geometry(num_heads=4, num_kv_heads=2, head_dim=64, slots=100)
+    g = lin.to_c()
+    assert lib.hkv_slot_of_position(C.byref(g), 99) == 99
+    assert lib.hkv_slot_of_position(C.byref(g), 100) == -1      # dropped, as the reference does
+    ring = hkv.Geometry(num_heads=4, num_kv_heads=2, head_dim=64, slots=16, layout=1, window_size=16).to_c()
+    for p in range(80):
+        s = lib.hkv_slot_of_position(C.byref(ring), p)
+        assert s == p % 16
+        assert lib.hkv_position_of_slot(C.byref(ring), s, p + 1) == p
+    # every row of a full ring holds one of the last 16 positions
+    held = sorted(lib.hkv_position_of_slot(C.byref(ring), s, 50) for s in range(16))
+    assert held == list(range(34, 50))
+    # block-cyclic sequence split: every position has exactly one owner, rows are dense per rank
+    N, BLK, slots = 4, 64, 256
+    seen = {}
+    for r in range(N):
+        gr = hkv.Geometry(num_heads=4, num_kv_heads=2, head_dim=64, slots=slots, shard_rank=r,
+                          shard_count=N, shard_block=BLK).to_c()
+        for p in range(N * slots):
+            s = lib.hkv_slot_of_position(C.byref(gr), p)
+            if s >= 0:
+                assert p not in seen
+                seen[p] = (r, s)
+                assert lib.hkv_position_of_slot(C.byref(gr), s, N * slots) == p
+    assert len(seen) == N * slots
+    for r in range(N):
+        rows = sorted(s for (rr, s) in seen.values() if rr == r)
+        assert rows == list(range(slots))
+
+
+def test_split_plan_covers_attended_rows_exactly_once(hkv):
+    lib = hkv._capi.load()
+    rng = np.random.default_rng(0)
+    for kw in (dict(slots=1000), dict(slots=1000, window_size=130), dict(slots=128, layout=1, window_size=128),
+               dict(slots=300, layout=1, window_size=100)):
+        geo = hkv.Geometry(num_heads=4, num_kv_heads=2, head_dim=64, **kw)
+        g = geo.to_c()
+        for total in [0, 1, 63, 64, 65, 127, 128, 129, 999, 1000] + list(rng.integers(1, 2000, 10)):
+            total = int(total)
+            if geo.layout == 0 and total > geo.slots:
+                continue
+            for ct in (1, 3, 16):
+                first, tile_lo, n_tiles, n_chunks = _plan(hkv, geo, total, ct)
+                assert n_chunks == -(-n_tiles // ct)
+                attended = set(range(max(first, 0), total))
+                covered = set()
+                for s in range(tile_lo * 64, min((tile_lo + n_tiles) * 64, geo.slots)):
+                    p = lib.hkv_position_of_slot(C.byref(g), s, total)
+                    if first <= p < total:
+                        assert p not in covered
+                        covered.add(p)
+                assert covered == attended, (kw, total, ct)
+
+
+def test_sharded_plans_partition_the_sequence(hkv):
+    lib = hkv._capi.load()
+    N, BLK = 8, 128
+    for total in (1, 127, 128, 129, 5000, 16384, 131072):
+        covered = set()
+        for r in range(N):
+            geo = hkv.Geometry(num_heads=4, num_kv_heads=2, head_dim=64, slots=16384, shard_rank=r,
+                               shard_count=N, shard_block=BLK)
+            g = geo.to_c()
+            first, tile_lo, n_tiles, _ = _plan(hkv, geo, total, 4)
+            for s in range(tile_lo * 64, (tile_lo + n_tiles) * 64, 64):  # tile starts suffice
+                p0 = lib.hkv_position_of_slot(C.byref(g), s, total)
+                for p in range(p0, p0 + 64):
+                    if p < total:
+                        assert p not in covered
+                        covered.add(p)
+        assert len(covered) == total
+
+
+def test_workspace_bytes_formula(hkv):
+    geo = hkv.Geometry(batch=8, num_heads=28, num_kv_heads=4, head_dim=128, slots=4096, chunk_tiles=4)
+    lib = hkv._capi.load()
+    n = lib.hkv_workspace_bytes(C.byref(geo.to_c()))
+    assert n == 8 * (4096 // 64 // 4) * 28 * (128 + 2) * 4
+    assert lib.hkv_partial_floats(C.byref(geo.to_c())) == 130
+
+
+def test_cache_owner_position_bookkeeping(hkv):
+    """advance clamps, rewind_to only moves back, reset zeroes (src/kv_cache.hpp:93-96, :243-248)."""
+    c = hkv.KVCache()
+    c._max_seq = 10
+    c.advance(4)
+    assert c.position() == 4
+    c.rewind_to(7)
+    assert c.position() == 4
+    c.rewind_to(2)
+    assert c.position() == 2
+    c.advance(100)
+    assert c.position() == 10
+    c.reset()
+    assert c.position() == 0
+    cfg = hkv.KVCacheConfig(num_layers=28, num_kv_heads=4, head_dim=128, max_batch_size=64, max_seq_len=32768)
+    assert cfg.total_bytes() == 28 * 2 * 64 * 32768 * 4 * 128 * 2
+    assert not hkv.KVCache().allocate(hkv.KVCacheConfig())  # zero dims refused like the reference

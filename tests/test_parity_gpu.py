@@ -1,0 +1,306 @@
+"""GPU parity suite: libhkv's CUDA kernels, called through the C ABI, against the CPU
+oracle on the same seeded inputs. Append: bit-exact over the whole plane. Attention:
+|x - ref| <= 2e-3 + 1e-2*|ref| on every fp16 output element."""
+import math
+import zlib
+
+import numpy as np
+import pytest
+
+from _kat import build, load_kats
+from _util import assert_close, make_case, normal_f16, to_dev
+
+pytestmark = pytest.mark.gpu
+KATS = load_kats()
+
+GENERIC, TMA = 1, 2
+
+
+def run_decode(hkv, torch, q, kc, vc, totals, scale, *, H, KVH, HD, window=0, layout=0, kernel=0,
+               chunk_tiles=0):
+    B, slots = kc.shape[0], kc.shape[1]
+    ctx = hkv.Context(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots,
+                                   window_size=window, layout=layout, kernel_select=kernel,
+                                   chunk_tiles=chunk_tiles))
+    dq, dk, dv = to_dev(torch, q), to_dev(torch, kc), to_dev(torch, vc)
+    out = torch.full((B, H, HD), float("nan"), dtype=torch.float16, device="cuda")
+    dt = to_dev(torch, np.asarray(totals, dtype=np.int32))
+    ctx.decode_attention(dq, dk, dv, out, dt, scale)
+    assert ctx.device_status() == 0
+    res = out.cpu().numpy()
+    kern = ctx.kernel
+    ctx.close()
+    return res, kern
+
+
+# ---------------------------------------------------------------------------
+# known answers of the reference's own test, through the GPU path
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("case", KATS["cases"], ids=lambda c: c["name"])
+def test_reference_known_answers_on_gpu(hkv, cuda, case):
+    torch = cuda
+    q, k, v, scale, expect = build(case)
+    H, KVH, HD, S = case["H"], case["KVH"], case["HD"], case["max_seq"]
+    if case["op"] == "decode":
+        out = torch.zeros(1, H, HD, dtype=torch.float16, device="cuda")
+        # host-length launcher, as the reference test calls it (engine.execute, no device pos)
+        hkv.launch_attention_cached_fp16(to_dev(torch, q), to_dev(torch, k), to_dev(torch, v), out, 1,
+                                         case["seq_len"], H, KVH, HD, S, scale, case["window"])
+        got = out.cpu().numpy().astype(np.float32).reshape(1, -1)
+    else:
+        out = torch.zeros(case["seq_new"], H, HD, dtype=torch.float16, device="cuda")
+        hkv.launch_attention_prefill_cached_fp16(to_dev(torch, q), to_dev(torch, k), to_dev(torch, v),
+                                                 out, case["seq_new"], case["past_len"], H, KVH, HD, S,
+                                                 scale, case["window"])
+        got = out.cpu().numpy().astype(np.float32).reshape(case["seq_new"], -1)
+    torch.cuda.synchronize()
+    assert np.all(np.abs(got - expect) < 0.01), (got, expect)
+
+
+# ---------------------------------------------------------------------------
+# append: bit-exact
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("B,S,KVH,HD,slots,layout", [
+    (1, 1, 2, 64, 2048, 0),     # config 1 shape
+    (8, 1, 4, 128, 4096, 0),    # config 2 shape
+    (16, 1, 32, 96, 512, 0),    # config 3 shape (non power of two head_dim)
+    (8, 1, 8, 256, 1024, 1),    # config 4 local layer: ring
+    (3, 5, 2, 64, 40, 0),       # multi-token, runs off the end for one sequence
+    (3, 5, 2, 64, 16, 1),       # multi-token ring wrap
+    (2, 3, 1, 2, 9, 0),         # tiny head_dim: 2-byte path
+    (2, 1, 3, 7, 9, 0),         # odd row size: 2-byte path
+])
+def test_append_bit_exact(hkv, cuda, oracle, B, S, KVH, HD, slots, layout):
+    torch = cuda
+    rng = np.random.default_rng(B * 1000 + HD)
+    nk, nv = normal_f16(rng, B, S, KVH, HD), normal_f16(rng, B, S, KVH, HD)
+    kc, vc = normal_f16(rng, B, slots, KVH, HD), normal_f16(rng, B, slots, KVH, HD)
+    if layout == 1:
+        pos = rng.integers(0, 5 * slots, size=B).astype(np.int32)
+    else:
+        pos = rng.integers(0, slots, size=B).astype(np.int32)
+        pos[-1] = slots - 2  # crosses the end when S > 2: rows past the plane are dropped
+    ref_k, ref_v = kc.copy(), vc.copy()
+    oracle.append(nk, nv, ref_k, ref_v, pos, layout=layout)
+    ctx = hkv.Context(hkv.Geometry(batch=B, num_heads=KVH, num_kv_heads=KVH, head_dim=HD, slots=slots,
+                                   layout=layout))
+    dk, dv = to_dev(torch, kc), to_dev(torch, vc)
+    ctx.append(to_dev(torch, nk), to_dev(torch, nv), dk, dv, to_dev(torch, pos), S)
+    torch.cuda.synchronize()
+    assert np.array_equal(dk.cpu().numpy().view(np.uint16), ref_k.view(np.uint16))
+    assert np.array_equal(dv.cpu().numpy().view(np.uint16), ref_v.view(np.uint16))
+    # host-position twin (launch_kv_cache_update): every sequence writes at the same position
+    if layout == 0:
+        ref_k, ref_v = kc.copy(), vc.copy()
+        oracle.append(nk, nv, ref_k, ref_v, np.full(B, 3, np.int32))
+        dk, dv = to_dev(torch, kc), to_dev(torch, vc)
+        hkv.launch_kv_cache_update(to_dev(torch, nk), to_dev(torch, nv), dk, dv, B, S, KVH, HD, slots, 3)
+        torch.cuda.synchronize()
+        assert np.array_equal(dk.cpu().numpy().view(np.uint16), ref_k.view(np.uint16))
+        assert np.array_equal(dv.cpu().numpy().view(np.uint16), ref_v.view(np.uint16))
+    ctx.close()
+
+
+def test_append_unaligned_views_use_narrow_stores(hkv, cuda, oracle):
+    """k_new/v_new may be views into a fused QKV buffer that are only 2-byte aligned."""
+    torch = cuda
+    rng = np.random.default_rng(9)
+    B, KVH, HD, slots = 2, 2, 64, 32
+    nk, nv = normal_f16(rng, B, 1, KVH, HD), normal_f16(rng, B, 1, KVH, HD)
+    kc, vc = normal_f16(rng, B, slots, KVH, HD), normal_f16(rng, B, slots, KVH, HD)
+    pos = np.array([4, 31], np.int32)
+    ref_k, ref_v = kc.copy(), vc.copy()
+    oracle.append(nk, nv, ref_k, ref_v, pos)
+    buf = torch.zeros(nk.size + nv.size + 8, dtype=torch.float16, device="cuda")
+    buf[1:1 + nk.size] = to_dev(torch, nk).flatten()            # offset by one half: 2-byte aligned
+    buf[3 + nk.size:3 + nk.size + nv.size] = to_dev(torch, nv).flatten()
+    dk, dv = to_dev(torch, kc), to_dev(torch, vc)
+    ctx = hkv.Context(hkv.Geometry(batch=B, num_heads=KVH, num_kv_heads=KVH, head_dim=HD, slots=slots))
+    ctx.append(buf[1:], buf[3 + nk.size:], dk, dv, to_dev(torch, pos), 1)
+    torch.cuda.synchronize()
+    assert np.array_equal(dk.cpu().numpy().view(np.uint16), ref_k.view(np.uint16))
+    assert np.array_equal(dv.cpu().numpy().view(np.uint16), ref_v.view(np.uint16))
+    ctx.close()
+
+
+# ---------------------------------------------------------------------------
+# decode attention vs the oracle
+# ---------------------------------------------------------------------------
+DECODE_CASES = [
+    # name, B, H, KVH, HD, slots, window, totals (None = seeded ragged)
+    ("cfg1_qwen05b", 1, 14, 2, 64, 2048, 0, [512]),
+    ("cfg2_qwen7b_ragged", 4, 28, 4, 128, 4096, 0, None),
+    ("cfg3_phi3_mha", 3, 32, 32, 96, 1024, 0, None),
+    ("cfg4_gemma_global", 2, 16, 8, 256, 2048, 0, None),
+    ("cfg4_gemma_local_window", 2, 16, 8, 256, 2048, 1024, [2048, 1500]),
+    ("group16", 2, 32, 2, 64, 700, 0, None),
+    ("tiny_lengths", 6, 14, 2, 64, 256, 0, [0, 1, 2, 63, 64, 65]),
+    ("window_edges", 5, 8, 4, 128, 512, 100, [1, 99, 100, 101, 512]),
+]
+
+
+@pytest.mark.parametrize("kernel", [GENERIC, TMA], ids=["generic", "tma"])
+@pytest.mark.parametrize("case", DECODE_CASES, ids=lambda c: c[0])
+def test_decode_matches_oracle(hkv, cuda, oracle, case, kernel):
+    name, B, H, KVH, HD, slots, window, totals = case
+    rng = np.random.default_rng(zlib.crc32(name.encode()))
+    if totals is None:
+        totals = rng.integers(slots // 2, slots + 1, size=B)
+    totals = np.asarray(totals, dtype=np.int32)
+    # rows past `total` hold garbage (incl. NaN bit patterns) to prove they are never used
+    q, _, _, kc, vc = make_case(int(rng.integers(1 << 30)), B, H, KVH, HD, slots, totals, fill="garbage")
+    for b, t in enumerate(totals):
+        kc[b, t:] = np.float16(np.nan)
+        vc[b, t:] = np.float16(np.inf)
+    for scale in (1.0 / math.sqrt(HD), 1.0):  # 1.0 = the reference's Gemma setting (near one-hot softmax)
+        ref = oracle.decode(q, kc, vc, totals, scale, window=window, threads=8)
+        for ct in (0, 1, 3):
+            got, kern = run_decode(hkv, cuda, q, kc, vc, totals, scale, H=H, KVH=KVH, HD=HD,
+                                   window=window, kernel=kernel, chunk_tiles=ct)
+            assert kern == kernel
+            assert not np.isnan(got.astype(np.float32)).any()
+            assert_close(oracle, got, ref, f"{name} scale={scale:.3f} chunk_tiles={ct}")
+
+
+@pytest.mark.parametrize("kernel", [GENERIC, TMA], ids=["generic", "tma"])
+def test_ring_cache_equals_linear_window(hkv, cuda, oracle, kernel):
+    """Ring plane of W rows (pos mod W) vs the reference semantics: linear cache + window W."""
+    torch = cuda
+    rng = np.random.default_rng(21)
+    B, H, KVH, HD, W, ctx_len = 3, 16, 8, 256, 128, 500
+    lin_k = normal_f16(rng, B, ctx_len, KVH, HD)
+    lin_v = normal_f16(rng, B, ctx_len, KVH, HD)
+    totals = np.array([ctx_len, 301, 77], np.int32)   # wrapped twice, wrapped, not yet full
+    ring_k = np.zeros((B, W, KVH, HD), np.float16)
+    ring_v = np.zeros_like(ring_k)
+    for b, t in enumerate(totals):
+        for p in range(t):
+            ring_k[b, p % W] = lin_k[b, p]
+            ring_v[b, p % W] = lin_v[b, p]
+    q = normal_f16(rng, B, H, HD)
+    scale = 1.0 / math.sqrt(HD)
+    ref = oracle.decode(q, lin_k, lin_v, totals, scale, window=W, threads=8)
+    got, _ = run_decode(hkv, torch, q, ring_k, ring_v, totals, scale, H=H, KVH=KVH, HD=HD, window=W,
+                        layout=1, kernel=kernel)
+    assert_close(oracle, got, ref, "ring vs linear+window")
+
+
+# ---------------------------------------------------------------------------
+# fused append + decode == append, then decode
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("kernel", [GENERIC, TMA], ids=["generic", "tma"])
+@pytest.mark.parametrize("shape", [
+    (1, 14, 2, 64, 2048, 0, 0, [511]),                # config 1: append at cache_pos = 511
+    (4, 28, 4, 128, 1024, 0, 0, [0, 63, 64, 1023]),   # tile edges, first and last row
+    (3, 16, 8, 256, 128, 128, 1, [5, 128, 1000]),     # ring
+    (2, 32, 32, 96, 300, 0, 0, [17, 299]),
+], ids=["cfg1", "edges", "ring", "hd96"])
+def test_fused_append_decode(hkv, cuda, oracle, shape, kernel):
+    torch = cuda
+    B, H, KVH, HD, slots, window, layout, pos = shape
+    pos = np.asarray(pos, np.int32)
+    rng = np.random.default_rng(B + HD)
+    q, nk, nv, kc, vc = make_case(int(rng.integers(1 << 30)), B, H, KVH, HD, slots, fill="garbage")
+    scale = 1.0 / math.sqrt(HD)
+    ref_k, ref_v = kc.copy(), vc.copy()
+    oracle.append(nk, nv, ref_k, ref_v, pos, layout=layout)
+    ref = oracle.decode(q, ref_k, ref_v, pos + 1, scale, window=window, layout=layout, threads=8)
+    ctx = hkv.Context(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots,
+                                   window_size=window, layout=layout, kernel_select=kernel))
+    dk, dv = to_dev(torch, kc), to_dev(torch, vc)
+    out = torch.zeros(B, H, HD, dtype=torch.float16, device="cuda")
+    ctx.append_decode_attention(to_dev(torch, q), to_dev(torch, nk), to_dev(torch, nv), dk, dv, out,
+                                to_dev(torch, pos), scale)
+    assert ctx.device_status() == 0
+    assert np.array_equal(dk.cpu().numpy().view(np.uint16), ref_k.view(np.uint16)), "cache K not bit-exact"
+    assert np.array_equal(dv.cpu().numpy().view(np.uint16), ref_v.view(np.uint16)), "cache V not bit-exact"
+    assert_close(oracle, out.cpu().numpy(), ref, "fused op")
+    # host-buffer entry point: same result through pinned host tensors
+    hq = torch.from_numpy(q).pin_memory()
+    hk = torch.from_numpy(nk).pin_memory()
+    hv = torch.from_numpy(nv).pin_memory()
+    ho = torch.zeros(B, H, HD, dtype=torch.float16).pin_memory()
+    dk2, dv2 = to_dev(torch, kc), to_dev(torch, vc)
+    ctx.append_decode_attention_host(hq, hk, hv, dk2, dv2, ho, to_dev(torch, pos), scale)
+    torch.cuda.synchronize()
+    assert np.array_equal(ho.numpy().view(np.uint16), out.cpu().numpy().view(np.uint16))
+    assert np.array_equal(dk2.cpu().numpy().view(np.uint16), ref_k.view(np.uint16))
+    ctx.close()
+
+
+def test_strided_batch_and_engine_scalar_position(hkv, cuda, oracle):
+    """batch = 1 with scalar device positions is the engine's own contract; a batch stride
+    larger than one sequence's plane addresses sequences inside a bigger allocation."""
+    torch = cuda
+    B, H, KVH, HD, slots = 2, 28, 4, 128, 256
+    pad = 64 * KVH * HD
+    rng = np.random.default_rng(4)
+    q, _, _, kc, vc = make_case(5, B, H, KVH, HD, slots, fill="garbage")
+    totals = np.array([200, 131], np.int32)
+    ref = oracle.decode(q, kc, vc, totals, 0.1, threads=4)
+    stride = slots * KVH * HD + pad
+    big_k = torch.zeros(B * stride, dtype=torch.float16, device="cuda")
+    big_v = torch.zeros(B * stride, dtype=torch.float16, device="cuda")
+    for b in range(B):
+        big_k[b * stride:b * stride + slots * KVH * HD] = to_dev(torch, kc[b]).flatten()
+        big_v[b * stride:b * stride + slots * KVH * HD] = to_dev(torch, vc[b]).flatten()
+    ctx = hkv.Context(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots,
+                                   batch_stride_elems=stride))
+    out = torch.zeros(B, H, HD, dtype=torch.float16, device="cuda")
+    ctx.decode_attention(to_dev(torch, q), big_k, big_v, out, to_dev(torch, totals), 0.1)
+    assert ctx.device_status() == 0
+    assert_close(oracle, out.cpu().numpy(), ref, "strided batch")
+    ctx.close()
+    # engine contract: one sequence, scalar device total
+    one = torch.zeros(1, H, HD, dtype=torch.float16, device="cuda")
+    hkv.launch_attention_cached_fp16_dp(to_dev(torch, q[1:2]), to_dev(torch, kc[1:2]), to_dev(torch, vc[1:2]),
+                                        one, 1, to_dev(torch, totals[1:2]), H, KVH, HD, slots, 0.1, 0)
+    torch.cuda.synchronize()
+    assert_close(oracle, one.cpu().numpy(), ref[1:2], "batch-1 scalar position")
+
+
+def test_prefill_matches_oracle(hkv, cuda, oracle):
+    torch = cuda
+    rng = np.random.default_rng(8)
+    for (H, KVH, HD, slots, past, S_new, window) in [(28, 4, 128, 512, 100, 64, 0), (16, 8, 256, 256, 0, 40, 32),
+                                                     (32, 32, 96, 300, 250, 50, 0)]:
+        k = normal_f16(rng, 1, slots, KVH, HD)
+        v = normal_f16(rng, 1, slots, KVH, HD)
+        q = normal_f16(rng, S_new, H, HD)
+        scale = 1.0 / math.sqrt(HD)
+        ref = oracle.prefill(q, k[0], v[0], past, scale, window=window, threads=8)
+        out = torch.zeros(S_new, H, HD, dtype=torch.float16, device="cuda")
+        hkv.launch_attention_prefill_cached_fp16(to_dev(torch, q), to_dev(torch, k), to_dev(torch, v), out,
+                                                 S_new, past, H, KVH, HD, slots, scale, window)
+        torch.cuda.synchronize()
+        assert_close(oracle, out.cpu().numpy(), ref, f"prefill HD={HD}")
+
+
+def test_synthetic_fill_matches_cpu_generator(hkv, cuda, oracle):
+    torch = cuda
+    n = 1 << 16
+    buf = torch.zeros(n, dtype=torch.float16, device="cuda")
+    hkv.fill_synthetic(buf, 0x48454B56, 12345)
+    torch.cuda.synchronize()
+    assert np.array_equal(buf.cpu().numpy().view(np.uint16), oracle.fill(0x48454B56, 12345, n).view(np.uint16))
+
+
+def test_runtime_argument_errors(hkv, cuda):
+    torch = cuda
+    ctx = hkv.Context(hkv.Geometry(batch=1, num_heads=4, num_kv_heads=2, head_dim=64, slots=64))
+    t = torch.zeros(4 * 64 * 64, dtype=torch.float16, device="cuda")
+    pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(hkv.HkvError) as e:
+        ctx.decode_attention(None, t, t, t, pos)
+    assert e.value.status == 1
+    with pytest.raises(hkv.HkvError) as e:
+        ctx.decode_attention(t.data_ptr() + 1, t, t, t, pos)
+    assert e.value.status == 3
+    with pytest.raises(hkv.HkvError) as e:
+        ctx.decode_attention(t, t, t, t, pos, scale=float("nan"))
+    assert e.value.status == 1
+    with pytest.raises(hkv.HkvError) as e:
+        ctx.append(t, t, t, t, None)
+    assert e.value.status == 1
+    assert ctx.device_status() == 0  # nothing ran, nothing faulted
+    ctx.close()
