@@ -747,3 +747,140 @@ int hkv_fill_synthetic(void* dst, uint64_t seed, uint64_t first_index, uint64_t 
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Decode attention for callers that must not allocate
+// ---------------------------------------------------------------------------
+// Some hosts of this library cannot call cudaMalloc at the point where they need
+// attention: code running under a memory plan fixed at start-up (every byte of HBM already
+// handed to the KV planes), plugin sandboxes that forbid allocation after initialisation,
+// and latency-critical serving threads for which an allocation's implicit device
+// synchronisation is not acceptable. hkv_decode_attention_static serves them: the split-K
+// partials live in the fixed array below instead of a context-owned workspace.
+//
+// The array is part of the library image, so EVERY GPU that loads libhkv holds these
+// HKV_STATIC_SCRATCH_BYTES (8 MiB) from load until the process exits, used or not.
+//
+// In host code the name `g_static_scratch` is only a host-side stand-in for the symbol, not
+// a device address; the address a kernel may use comes from cudaGetSymbolAddress, asked
+// once per device with that device current (static_scratch_for_current_device below).
+static __device__ __align__(256) unsigned char g_static_scratch[HKV_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+constexpr int kStaticMaxDevices = 64;
+struct StaticDeviceSlot {
+    void* scratch = nullptr;  // device address of g_static_scratch on this device
+    int sm_count = 0;
+};
+StaticDeviceSlot g_static_slots[kStaticMaxDevices];
+std::mutex g_static_mutex;
+
+// Set-up, once per device: resolves the device address of the array on the CURRENT device.
+// Runs on the first call made on that device; no allocation, but the runtime may load the
+// module here, so that first call belongs before any stream capture.
+int static_scratch_for_current_device(StaticDeviceSlot* out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        return HKV_ERR_NO_DEVICE;
+    }
+    if (dev < 0 || dev >= kStaticMaxDevices) return HKV_ERR_TOO_LARGE;
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    StaticDeviceSlot& slot = g_static_slots[dev];
+    if (!slot.scratch) {
+        int major = 0, sm = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+            cudaGetLastError();
+            return HKV_ERR_CUDA;
+        }
+        if (major != 10) return HKV_ERR_NO_DEVICE;
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p) {
+            cudaGetLastError();
+            return HKV_ERR_CUDA;
+        }
+        slot.sm_count = sm;
+        slot.scratch = p;
+    }
+    *out = slot;
+    return HKV_OK;
+}
+
+}  // namespace
+
+extern "C" int hkv_decode_attention_static(const hkv_geometry* geometry, const void* q,
+                                           const void* k_cache, const void* v_cache, void* out,
+                                           const int32_t* d_total_seq, float scale, void* stream) {
+    const char* why = "";
+    const int vst = validate_geometry(geometry, &why);
+    if (vst) return vst;
+    if (!q || !k_cache || !v_cache || !out || !d_total_seq) return HKV_ERR_INVALID_ARG;
+    if (!aligned(q, 2) || !aligned(k_cache, 2) || !aligned(v_cache, 2) || !aligned(out, 2))
+        return HKV_ERR_ALIGNMENT;
+    if (!std::isfinite(scale)) return HKV_ERR_INVALID_ARG;
+    StaticDeviceSlot slot;
+    const int sst = static_scratch_for_current_device(&slot);
+    if (sst) return sst;
+
+    // Split plan: the caller's chunk size (or the automatic one), coarsened until the
+    // partials fit the fixed array; refuse if even one partial per (sequence, head) does not.
+    const hkv_geometry& g = *geometry;
+    int chunk_tiles, max_chunks;
+    fill_plan(g, slot.sm_count, chunk_tiles, max_chunks);
+    const int tiles = (g.slots + kTileRows - 1) / kTileRows;
+    while (workspace_bytes_for(g, max_chunks) > (size_t)HKV_STATIC_SCRATCH_BYTES && max_chunks > 1) {
+        chunk_tiles *= 2;
+        max_chunks = (tiles + chunk_tiles - 1) / chunk_tiles;
+    }
+    if (workspace_bytes_for(g, max_chunks) > (size_t)HKV_STATIC_SCRATCH_BYTES)
+        return HKV_ERR_TOO_LARGE;  // batch * num_heads * (head_dim + 2) * 4 bytes exceeds the array
+
+    // Nothing in the array has to start at zero: the combine kernel reads exactly the partial
+    // rows the decode kernel of the same call has written (both derive the count from
+    // d_total_seq), so the previous call's contents are never observed.
+    DecodeArgs a;
+    a.q = (const __half*)q;
+    a.k_cache = (const __half*)k_cache;
+    a.v_cache = (const __half*)v_cache;
+    a.k_new = nullptr;
+    a.v_new = nullptr;
+    a.k_cache_w = nullptr;
+    a.v_cache_w = nullptr;
+    a.part = static_cast<float*>(slot.scratch);
+    a.total = d_total_seq;
+    a.status = nullptr;  // the SIMT kernel has no waits and never touches the status word
+    a.map = make_map(g);
+    a.B = g.batch;
+    a.H = g.num_heads;
+    a.KVH = g.num_kv_heads;
+    a.HD = g.head_dim;
+    a.chunk_tiles = chunk_tiles;
+    a.max_chunks = max_chunks;
+    a.pos_is_index = 0;
+    a.batch_stride = g.batch_stride_elems ? g.batch_stride_elems
+                                          : (long long)g.slots * g.num_kv_heads * g.head_dim;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    cudaStream_t st = (cudaStream_t)stream;
+    dim3 grid((unsigned)max_chunks, (unsigned)g.num_heads, (unsigned)g.batch);
+    hkv_decode_generic_kernel<<<grid, kGenWarps * 32, 0, st>>>(a);
+
+    CombineArgs c;
+    const long long PW = g.head_dim + 2;
+    c.part = static_cast<const float*>(slot.scratch);
+    c.stride_b = (long long)max_chunks * g.num_heads * PW;
+    c.stride_c = (long long)g.num_heads * PW;
+    c.total = d_total_seq;
+    c.pos_is_index = 0;
+    c.fixed_count = 0;
+    c.map = a.map;
+    c.chunk_tiles = chunk_tiles;
+    c.H = g.num_heads;
+    c.HD = g.head_dim;
+    c.out = (__half*)out;
+    c.out_partial = nullptr;
+    hkv_combine_kernel<<<dim3((unsigned)g.num_heads, (unsigned)g.batch), 128, 0, st>>>(c);
+    return cudaPeekAtLastError() == cudaSuccess ? HKV_OK : HKV_ERR_CUDA;
+}

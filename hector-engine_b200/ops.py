@@ -176,6 +176,23 @@ class Context:
                                                   _stream(stream)))
 
 
+STATIC_SCRATCH_BYTES = 8 << 20
+
+
+def decode_attention_static(geometry: Geometry, q, k_cache, v_cache, out, d_total_seq, scale=None,
+                            stream=None):
+    """Decode attention without a Context and without any allocation: the split-K partials
+    use the library's fixed 8 MiB array (hkv_decode_attention_static). For callers that may
+    not allocate device memory when they need attention; calls must not overlap on the GPU."""
+    lib = _capi.load()
+    scale = geometry.default_scale if scale is None else scale
+    g = geometry.to_c()
+    st = lib.hkv_decode_attention_static(C.byref(g), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out),
+                                         _ptr(d_total_seq), scale, _stream(stream))
+    if st != _capi.HKV_OK:
+        raise HkvError(st, lib.hkv_status_string(st).decode())
+
+
 def fill_synthetic(dst, seed: int, first_index: int = 0, count: int | None = None, stream=None):
     """Fills an fp16 CUDA tensor with the deterministic synthetic stream (see hkv_fill_synthetic)."""
     lib = _capi.load()

@@ -148,6 +148,30 @@ int hkv_append_decode_attention(hkv_ctx* ctx, const void* q, const void* k_new, 
 int hkv_prefill_attention(hkv_ctx* ctx, const void* q, const void* k_cache, const void* v_cache,
                           void* out, int32_t seq_new, int32_t past_len, float scale, void* stream);
 
+/* Cached decode attention for callers that cannot allocate. It has no counterpart in the
+ * reference. Same inputs, outputs and results as hkv_decode_attention, but it needs no
+ * context: the split-K partials are kept in a fixed array inside the library image
+ * instead of a cudaMalloc'ed workspace, and the call itself performs no cudaMalloc,
+ * cudaFree or other allocating routine. It is meant for hosts that run under a memory
+ * plan fixed at start-up (all HBM already given to the KV planes), for plugin sandboxes
+ * that forbid allocation after initialisation, and for serving threads that cannot
+ * accept the device-wide synchronisation an allocation implies.
+ *   - Limit: batch * num_heads * (head_dim + 2) * 4 bytes must fit in
+ *     HKV_STATIC_SCRATCH_BYTES (8 MiB); larger geometries get HKV_ERR_TOO_LARGE. Within
+ *     that limit the split is coarsened automatically until the partials fit.
+ *   - Every GPU that loads the library holds those 8 MiB until the process exits.
+ *   - The first call on each device resolves the array's device address (set-up, no
+ *     allocation); make that first call before any stream capture.
+ *   - All calls on a device share the one array, which keeps the previous call's
+ *     contents; nothing needs clearing between calls, but two calls that overlap on the
+ *     GPU (different streams, or graphs replayed concurrently) race on it. Keep them on
+ *     one stream or otherwise ordered.
+ *   - Always runs the any-geometry SIMT kernel, so it is slower than a context. */
+#define HKV_STATIC_SCRATCH_BYTES (8u << 20)
+int hkv_decode_attention_static(const hkv_geometry* geometry, const void* q, const void* k_cache,
+                                const void* v_cache, void* out, const int32_t* d_total_seq,
+                                float scale, void* stream);
+
 /* ---- sequence-split (multi-GPU) -------------------------------------------------- */
 
 /* Floats per (sequence, head) in an exchanged partial: head_dim + 2  (o[], m, l). */
