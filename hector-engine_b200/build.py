@@ -18,7 +18,7 @@ REPO = os.path.dirname(PKG_DIR)
 CSRC = os.path.join(PKG_DIR, "csrc")
 HOST = os.path.join(PKG_DIR, "host")
 LIB = os.path.join(PKG_DIR, "libhkv.so")
-HOST_TESTS = os.path.join(PKG_DIR, "hkv_host_tests")
+HOST_TESTS = os.path.join(REPO, "tests", "cpp", "hkv_host_tests")
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
@@ -59,15 +59,20 @@ def build_lib(force: bool = False, verbose: bool = False) -> str:
 
 
 def build_host_tests(force: bool = False) -> str | None:
-    main = os.path.join(HOST, "hkv_host_tests.cpp")
+    """C++ tests of the registry adapter (tests/cpp): link libhkv and, as the checker only,
+    the CPU oracle. Call after build_oracle()."""
+    main = os.path.join(REPO, "tests", "cpp", "hkv_host_tests.cpp")
+    oracle_dir = os.path.join(REPO, "oracle", "_build")
     if not os.path.exists(main):
         return None
-    srcs = _sources(HOST)
+    srcs = _sources(HOST) + [main]
     if not force and _newer(HOST_TESTS, srcs + [LIB]):
         return HOST_TESTS
     cmd = [_nvcc(), *ARCH, "-O2", "-std=c++17", "-o", HOST_TESTS, main,
            os.path.join(HOST, "hkv_register.cpp"), "-I", os.path.join(REPO, "include"), "-I", HOST,
-           "-L", PKG_DIR, "-lhkv", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+           "-L", PKG_DIR, "-lhkv", "-L", oracle_dir, "-lhkv_oracle",
+           "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../hector-engine_b200",
+           "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../oracle/_build"]
     subprocess.run(cmd, check=True)
     return HOST_TESTS
 
@@ -78,8 +83,8 @@ def build_oracle() -> None:
 
 def build_all(force: bool = False) -> None:
     build_lib(force=force)
-    build_host_tests(force=force)
     build_oracle()
+    build_host_tests(force=force)
 
 
 if __name__ == "__main__":

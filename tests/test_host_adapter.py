@@ -1,0 +1,32 @@
+"""Runs the C++ tests of the registry-boundary adapter (tests/cpp/hkv_host_tests.cpp): the
+reference's known answers as command buffers, the CUDA-graph capture-once contract, the fused
+five-input op, error behaviour and the C++ cache owner."""
+import os
+import subprocess
+
+import pytest
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BIN = os.path.join(REPO, "tests", "cpp", "hkv_host_tests")
+
+
+def _ensure_built():
+    if not os.path.exists(BIN):
+        import importlib
+        importlib.import_module("hector-engine_b200.build").build_all()
+    assert os.path.exists(BIN)
+
+
+def test_host_tests_binary_links_and_lists_cases():
+    _ensure_built()
+    out = subprocess.run([BIN, "--list"], capture_output=True, text=True, check=True).stdout.split()
+    assert out == ["known_answers", "graph_contract", "graph_contract_fused", "error_behaviour", "cache_owner"]
+
+
+@pytest.mark.gpu
+def test_host_adapter_cases_on_gpu():
+    _ensure_built()
+    res = subprocess.run([BIN], capture_output=True, text=True, timeout=300)
+    print(res.stdout, res.stderr)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert res.stdout.count("PASS:") == 5 and "ALL PASSED" in res.stdout
