@@ -47,10 +47,10 @@ def test_capture_once_replay_many(hkv, cuda, oracle, shape):
             dq.copy_(to_dev(torch, q)); dkn.copy_(to_dev(torch, kn)); dvn.copy_(to_dev(torch, vn))
             dpos.copy_(to_dev(torch, pos))
             if s == 0:
-                before = torch.cuda.memory_allocated()
-                with torch.cuda.graph(graph, stream=side):  # capture: nothing may allocate or sync
+                # global-mode capture: a cudaMalloc or a synchronisation inside the library
+                # would invalidate the capture and raise here
+                with torch.cuda.graph(graph, stream=side, capture_error_mode="global"):
                     enqueue()
-                assert torch.cuda.memory_allocated() == before
             graph.replay()
         side.synchronize()
         got = out.cpu().numpy()
