@@ -7,7 +7,7 @@ from ._capi import (HkvError, HkvGeometry, KERNEL_AUTO, KERNEL_GENERIC, KERNEL_T
                     LAYOUT_LINEAR, LAYOUT_RING)
 from .cache import (Gemma4KVCache, Gemma4Layer, Gemma4Layout, KVCache, KVCacheConfig,
                     gemma4_layout)
-from . import ops
+from . import dist, ops
 from .ops import (Context, Geometry, clear_context_cache, decode_attention_static, fill_synthetic,
                   launch_attention_cached_fp16, launch_attention_cached_fp16_dp,
                   launch_attention_prefill_cached_fp16, launch_kv_cache_update,

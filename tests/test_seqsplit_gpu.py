@@ -1,0 +1,125 @@
+"""GPU tests of the sequence-split path: hkv_decode_partials over block-cyclic shards of one
+logical cache, then hkv_combine_partials over the gathered partials, against the oracle on
+the full cache. On one GPU the ranks are run one after another (no kernel here waits on
+another rank, so this is the same computation); with >= 2 GPUs a real NCCL all-gather runs."""
+import importlib
+import math
+import os
+import sys
+
+import numpy as np
+import pytest
+
+from _util import assert_close, make_case, to_dev
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+REPO = os.path.dirname(HERE)
+
+
+def build_shards(hkv, world, BLK, kc, vc, totals, append_pos):
+    """Deal the logical planes to `world` local planes (rows of position p for p < total,
+    except the position being appended, which the kernel must write itself)."""
+    B, ctx, KVH, HD = kc.shape
+    shards = [hkv.dist.SeqShard(r, world, BLK) for r in range(world)]
+    slots = shards[0].slots_for(ctx)
+    lk = [np.zeros((B, slots, KVH, HD), np.float16) for _ in range(world)]
+    lv = [np.zeros((B, slots, KVH, HD), np.float16) for _ in range(world)]
+    for b in range(B):
+        for p in range(int(totals[b])):
+            if p == append_pos[b]:
+                continue
+            r = shards[0].owner(p)
+            row = shards[r].local_row(p)
+            lk[r][b, row], lv[r][b, row] = kc[b, p], vc[b, p]
+    return shards, slots, lk, lv
+
+
+@pytest.mark.parametrize("kernel", [1, 2], ids=["generic", "tma"])
+@pytest.mark.parametrize("world,BLK", [(2, 64), (4, 128), (8, 64)])
+def test_sequence_split_single_gpu_emulation(hkv, cuda, oracle, world, BLK, kernel):
+    torch = cuda
+    B, H, KVH, HD, ctx = 3, 28, 4, 128, 2048
+    totals = np.array([2048, 1000, 65], np.int32)
+    pos = totals - 1
+    q, nk, nv, kc, vc = make_case(world * 31 + BLK, B, H, KVH, HD, ctx, fill="garbage")
+    full_k, full_v = kc.copy(), vc.copy()
+    oracle.append(nk, nv, full_k, full_v, pos)
+    scale = 1.0 / math.sqrt(HD)
+    ref = oracle.decode(q, full_k, full_v, totals, scale, threads=8)
+
+    shards, slots, lk, lv = build_shards(hkv, world, BLK, kc, vc, totals, pos)
+    dq, dnk, dnv, dtot = to_dev(torch, q), to_dev(torch, nk), to_dev(torch, nv), to_dev(torch, totals)
+    parts = torch.zeros(world, B, H, HD + 2, dtype=torch.float32, device="cuda")
+    ctxs = []
+    for r in range(world):
+        ctx_r = hkv.Context(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots,
+                                         shard_rank=r, shard_count=world, shard_block=BLK,
+                                         kernel_select=kernel))
+        dk, dv = to_dev(torch, lk[r]), to_dev(torch, lv[r])
+        ctx_r.decode_partials(dq, dnk, dnv, dk, dv, parts[r], dtot, scale)
+        assert ctx_r.device_status() == 0
+        # the appended row landed on its owner only, bit-exact; other planes are untouched
+        gk, gv = dk.cpu().numpy(), dv.cpu().numpy()
+        want_k, want_v = lk[r].copy(), lv[r].copy()
+        for b in range(B):
+            row = shards[r].local_row(int(pos[b]))
+            if row >= 0:
+                want_k[b, row], want_v[b, row] = nk[b, 0], nv[b, 0]
+        assert np.array_equal(gk.view(np.uint16), want_k.view(np.uint16))
+        assert np.array_equal(gv.view(np.uint16), want_v.view(np.uint16))
+        ctxs.append(ctx_r)
+    out = torch.zeros(B, H, HD, dtype=torch.float16, device="cuda")
+    ctxs[0].combine_partials(parts, world, out)
+    torch.cuda.synchronize()
+    assert_close(oracle, out.cpu().numpy(), ref, f"sequence split over {world} ranks")
+    for c in ctxs:
+        c.close()
+
+
+def _nccl_rank(rank, world, port, result_dir):
+    sys.path[:0] = [REPO, os.path.join(REPO, "oracle"), HERE]
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import hkv_oracle as oracle
+        hkv = importlib.import_module("hector-engine_b200")
+        B, H, KVH, HD, ctx, BLK = 4, 28, 4, 128, 4096, 256
+        totals = np.array([4096, 3000, 257, 1], np.int32)
+        pos = totals - 1
+        q, nk, nv, kc, vc = make_case(5, B, H, KVH, HD, ctx, fill="garbage")
+        full_k, full_v = kc.copy(), vc.copy()
+        oracle.append(nk, nv, full_k, full_v, pos)
+        scale = 1.0 / math.sqrt(HD)
+        ref = oracle.decode(q, full_k, full_v, totals, scale, threads=4)
+        shards, slots, lk, lv = build_shards(hkv, world, BLK, kc, vc, totals, pos)
+        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+        dec = hkv.dist.SeqSplitDecoder(hkv, hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD,
+                                                         slots=slots), shards[rank])
+        out = torch.zeros(B, H, HD, dtype=torch.float16, device="cuda")
+        dk, dv = dev(lk[rank]), dev(lv[rank])
+        for _ in range(2):  # twice: the second call re-appends the same row and must agree
+            dec.step(dev(q), dev(nk), dev(nv), dk, dv, out, dev(totals), scale)
+        torch.cuda.synchronize()
+        assert dec.ctx.device_status() == 0
+        ok, err = oracle.within_tolerance(out.cpu().numpy(), ref)
+        assert ok, f"rank {rank}: {err}"
+        open(os.path.join(result_dir, f"ok{rank}"), "w").write("ok")
+        dec.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sequence_split_nccl_ranks(cuda, tmp_path):
+    torch = cuda
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs >= 2 GPUs (covered on one GPU by the emulation test and on CPU by gloo ranks)")
+    world = 2 if n < 4 else 4
+    import torch.multiprocessing as mp
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    mp.spawn(_nccl_rank, args=(world, 29700 + os.getpid() % 200, str(tmp_path)), nprocs=world, join=True)
+    assert len(os.listdir(tmp_path)) == world
