@@ -60,6 +60,11 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--ref-layers", type=int, default=2, help="layers the reference arm runs per step")
+    ap.add_argument("--mode", default="batch", choices=["batch", "seqsplit"],
+                    help="batch: sequences sharded over GPUs, no collective (default). seqsplit: every "
+                         "sequence's cache split block-cyclically over the GPUs, partials all-gathered "
+                         "over NCCL; --ctx is then the rows per sequence PER GPU")
+    ap.add_argument("--shard-block", type=int, default=1024)
     return ap.parse_args()
 
 
@@ -282,6 +287,80 @@ def run_reference(args, torch, hkv, oracle, cfg, ctx, B, rank):
     return w, ms, nl
 
 
+def run_seqsplit(args, torch, hkv, dist, cfg, ctx_local, B, rank, world, base, gpu_id):
+    """Long-context mode: one logical cache of ctx_local*world rows per sequence, dealt
+    block-cyclically over the ranks; per layer: local split-K decode to one partial per
+    (sequence, head), NCCL all-gather of the partials, merge. Output replicated on all ranks."""
+    L, H, KVH, HD = cfg["layers"], cfg["H"], cfg["KVH"], cfg["HD"]
+    logical = ctx_local * world
+    shard = hkv.dist.SeqShard(rank, world, args.shard_block)
+    assert shard.slots_for(logical) == ctx_local, "ctx per GPU must be a multiple of the shard block"
+    dev = "cuda"
+    k = torch.empty((L, B, ctx_local, KVH, HD), dtype=torch.float16, device=dev)
+    v = torch.empty((L, B, ctx_local, KVH, HD), dtype=torch.float16, device=dev)
+    q = torch.empty((L, B, H, HD), dtype=torch.float16, device=dev)
+    kn = torch.empty((L, B, KVH, HD), dtype=torch.float16, device=dev)
+    vn = torch.empty((L, B, KVH, HD), dtype=torch.float16, device=dev)
+    out = torch.zeros((L, B, H, HD), dtype=torch.float16, device=dev)
+    for i, t in enumerate((k, v)):
+        hkv.fill_synthetic(t, SEED ^ (rank * 0x10001) ^ (i << 20))
+    for i, t in enumerate((q, kn, vn)):      # replicated inputs: same seed on every rank
+        hkv.fill_synthetic(t, SEED ^ ((i + 2) << 20))
+    pos0 = np.random.default_rng(SEED).integers(logical // 2, logical, size=B).astype(np.int32)
+    d_tot = torch.from_numpy(pos0 + 1).to(dev)
+    h_tot = torch.from_numpy(pos0 + 1).pin_memory()
+    dec = hkv.dist.SeqSplitDecoder(hkv, hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD,
+                                                     slots=ctx_local, kernel_select=args.kernel,
+                                                     chunk_tiles=args.chunk_tiles), shard)
+    scale = 1.0 / math.sqrt(HD)
+
+    def step():
+        for l in range(L):
+            dec.step(q[l], kn[l], vn[l], k[l], v[l], out[l], d_tot, scale)
+        d_tot.add_(1).clamp_(max=logical)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    d_tot.copy_(h_tot)
+    sampler = ClockSampler(gpu_id)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    if dist is not None:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = float(ms.item()) / args.steps
+    assert dec.ctx.device_status() == 0
+    # algorithmic bytes over ALL ranks: the K/V rows of every sequence once, + new rows + q/out per rank
+    Ls = np.stack([np.minimum(pos0 + 1 + s, logical) for s in range(args.steps)]).astype(np.int64)
+    alg = float((4 * Ls * KVH * HD).sum(axis=1).mean() + world * B * (8 * KVH * HD + 4 * H * HD)) * L
+    if rank == 0:
+        cfgd = dict(base["config"], workload=f"{args.workload}-shaped long-context decode: {L} layers, logical ctx "
+                    f"{logical} split block-cyclically ({args.shard_block}) over {world} GPU(s) = {ctx_local} rows per "
+                    f"GPU, batch {B}", parallelism=f"sequence-split x{world}, NCCL all-gather of "
+                    f"{B * H * (HD + 2) * 4} B partials per layer", global_batch=B, ctx=logical)
+        line = dict(base, config=cfgd, impl="hkv", mode="seqsplit", value=B / (ms_per_step / 1e3),
+                    ms_per_step=ms_per_step, clocks=clocks, gpu_launches=args.steps * L * 4,
+                    hbm_gbs_step=alg / (ms_per_step * 1e-3) / 1e9,
+                    hbm_gbs_per_gpu=alg / world / (ms_per_step * 1e-3) / 1e9,
+                    hbm_frac_of_8TBs_per_gpu=alg / world / (ms_per_step * 1e-3) / 1e9 / 8000.0,
+                    e2e=None, roofline=None, cpu_baseline=None)
+        print(json.dumps(line))
+    dec.close()
+
+
 def main():
     args = parse_args()
     import torch
@@ -353,6 +432,12 @@ def main():
                                             f"this path): {nl} of {cfg['layers']} layers per step, one launch pair "
                                             f"per sequence as its batch-1 op does, time scaled to all layers"})
         print(json.dumps(line))
+        return 0
+
+    if args.mode == "seqsplit":
+        run_seqsplit(args, torch, hkv, dist, cfg, ctx, B, rank, n_gpus, base, gpu_id)
+        if dist is not None:
+            dist.destroy_process_group()
         return 0
 
     # ------------------------------------------------------------------ this library
