@@ -20,6 +20,7 @@
 #include "hkv_basic.cuh"
 #include "hkv_decode_tma.cuh"
 #include "hkv_prefill.cuh"
+#include "hkv_prefill_tc.cuh"
 
 using namespace hkv;
 
@@ -174,6 +175,29 @@ TmaKernel pick_tma(int HD, int nt, int groups) {
         case 256: return pick_tma_hd<256>(nt, groups);
     }
     return nullptr;
+}
+
+// Encodes a tiled fp16 tensor map with 128-byte swizzle (rank 3 or 4).
+int encode_f16_sw128(hkv_ctx* c, const void* base, int rank, const cuuint64_t* dims,
+                     const cuuint64_t* strides, const cuuint32_t* box, CUtensorMap* out) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(c, HKV_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+    const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank, const_cast<void*>(base), dims,
+                           strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char buf[96];
+        snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed (CUresult %d)", (int)r);
+        return fail(c, HKV_ERR_CUDA, buf);
+    }
+    return HKV_OK;
+}
+
+bool prefill_tc_ok(const hkv_geometry& g) {
+    const int G = g.num_heads / g.num_kv_heads;
+    return (g.head_dim == 64 || g.head_dim == 128) && G <= 128 && g.layout == HKV_LAYOUT_LINEAR &&
+           g.shard_count <= 1 && g.kernel_select != HKV_KERNEL_GENERIC;
 }
 
 int encode_map(hkv_ctx* c, const void* base, CUtensorMap* out) {
@@ -481,6 +505,13 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
         }
     }
 
+    if (prefill_tc_ok(*geometry)) {
+        const void* pk = geometry->head_dim == 64 ? (const void*)hkv_prefill_tc_kernel<64>
+                                                  : (const void*)hkv_prefill_tc_kernel<128>;
+        e = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)prefill_tc_smem_bytes(geometry->head_dim));
+        if (e != cudaSuccess) return fail_cuda(c, e, "cudaFuncSetAttribute(prefill shared memory)");
+    }
     c->workspace_bytes = workspace_bytes_for(*geometry, c->max_chunks);
     e = cudaMalloc(&c->workspace, c->workspace_bytes);
     if (e != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(workspace)");
@@ -626,6 +657,48 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
     if (c->g.layout != HKV_LAYOUT_LINEAR || c->g.shard_count > 1)
         return fail(c, HKV_ERR_GEOMETRY, "prefill: linear unsharded cache only");
     if (seq_new == 0) return HKV_OK;
+    if (prefill_tc_ok(c->g) && aligned(q, 16) && aligned(k_cache, 16) && aligned(v_cache, 16) && aligned(out, 16)) {
+        const hkv_geometry& g = c->g;
+        const int HD = g.head_dim, G = c->G;
+        PrefillTcArgs t;
+        t.out = (__half*)out;
+        t.status = c->d_status;
+        t.S_new = seq_new;
+        t.past_len = past_len;
+        t.H = g.num_heads;
+        t.KVH = g.num_kv_heads;
+        t.G = G;
+        t.QT = kPfRows / G;
+        t.n_qtiles = (seq_new + t.QT - 1) / t.QT;
+        t.slots = g.slots;
+        t.window = g.window_size;
+        t.scale_log2 = scale * 1.4426950408889634f;
+        CUtensorMap mq, mk, mv;
+        {
+            cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)g.num_heads, (cuuint64_t)seq_new};
+            cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)g.num_heads * HD * 2};
+            cuuint32_t box[3] = {64u, (cuuint32_t)G, (cuuint32_t)t.QT};
+            const int st = encode_f16_sw128(c, q, 3, dims, strides, box, &mq);
+            if (st) return st;
+        }
+        {
+            cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)g.num_kv_heads, (cuuint64_t)g.slots, 1};
+            cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)g.num_kv_heads * HD * 2,
+                                     (cuuint64_t)g.slots * g.num_kv_heads * HD * 2};
+            cuuint32_t box[4] = {64u, 1u, (cuuint32_t)kPfKeys, 1u};
+            int st = encode_f16_sw128(c, k_cache, 4, dims, strides, box, &mk);
+            if (st) return st;
+            st = encode_f16_sw128(c, v_cache, 4, dims, strides, box, &mv);
+            if (st) return st;
+        }
+        const long long items = (long long)t.n_qtiles * g.num_kv_heads;
+        const int grid = items < c->sm_count ? (int)items : c->sm_count;
+        const size_t smem = prefill_tc_smem_bytes(HD);
+        if (HD == 64) hkv_prefill_tc_kernel<64><<<grid, kPfThreads, smem, (cudaStream_t)stream>>>(mq, mk, mv, t);
+        else hkv_prefill_tc_kernel<128><<<grid, kPfThreads, smem, (cudaStream_t)stream>>>(mq, mk, mv, t);
+        const cudaError_t e = cudaPeekAtLastError();
+        return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "prefill launch");
+    }
     PrefillArgs a;
     a.q = (const __half*)q;
     a.k_cache = (const __half*)k_cache;

@@ -1,0 +1,391 @@
+// hkv_prefill_tc.cuh — attention of a chunk of new queries over the cache on the 5th-gen
+// tensor cores (tcgen05.mma, accumulators in tensor memory), batch 1.
+//
+// Replaces attention_prefill_cached_kernel (reference kernels/attention.cu:664-788), which
+// runs one CTA per (query, head) and re-reads the K/V rows once per query and per head of a
+// group. Semantics kept: query i attends cache rows [first_i, past_len + i] with
+// first_i = window > 0 ? max(0, past_len + i + 1 - window) : 0.
+//
+// Shape of the computation
+//   * Work item = (tile of QT queries, KV head). The G query heads of the KV head are stacked
+//     into the M dimension: row r of the 128-row tile is (query r / G, head r % G), QT = 128 / G
+//     queries per tile (18 for a group of 7: 126 of 128 rows used). One bulk-tensor load with
+//     box {64 halfs, G heads, QT queries} brings the tile in as 128-byte-swizzled K-major rows.
+//   * Warp 4 (one lane) is the TMA producer: Q tile per item, K/V tiles of 128 cache rows
+//     through a 2-stage ring (full/empty mbarriers).
+//   * Warp 5 (one lane) issues the MMAs:  S = Q·K^T  (M128 x N128 x K=HD, both operands K-major
+//     from shared memory) into one of two S buffers in tensor memory, and
+//     PV = P·V  (A = P from tensor memory as packed fp16, B = V straight from its row-major
+//     tile as an MN-major operand). S of tile t+1 is issued before PV of tile t, so the score
+//     contraction overlaps the softmax of the previous tile.
+//   * Warps 0-3: thread r owns row r. Two passes over its S row in tensor memory (max, then
+//     exp2 / sum / fp16 P written back with tcgen05.st), causal + window mask per element;
+//     then O_r = O_r * alpha + PV_r with O kept in registers (fp32).
+//   * All waits are bounded mbarrier waits; a wait that runs out sets the status word, the
+//     roles leave their loops, outstanding copies are drained and tensor memory is freed.
+#pragma once
+
+#include <cuda.h>
+
+#include "hkv_common.cuh"
+
+namespace hkv {
+
+struct PrefillTcArgs {
+    __half* out;      // [S_new, H, HD]
+    int32_t* status;
+    int S_new, past_len, H, KVH, G, QT, n_qtiles, slots, window;
+    float scale_log2;
+};
+
+constexpr int kPfRows = 128;   // M of the MMA = rows of a query tile
+constexpr int kPfKeys = 128;   // cache rows per K/V tile = N of the score MMA
+constexpr int kPfThreads = 192;
+
+__host__ __device__ constexpr size_t prefill_tc_smem_bytes(int HD) {
+    return 1024 + (size_t)kPfRows * HD * 2 + 2 * (2 * (size_t)kPfKeys * HD * 2) + 256;
+}
+
+// ---- tcgen05 wrappers -------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// Tensor-memory row access for the calling thread's lane: 32 consecutive 32-bit columns in,
+// 16 consecutive columns out. volatile + memory clobber: the same address is re-read after
+// the tensor core has rewritten it, so these must never be merged or hoisted.
+__device__ __forceinline__ void tmem_ld32(uint32_t (&v)[32], uint32_t taddr) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                 :
+                 : "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+                 : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart.
+// K-major operands ignore the leading-dimension offset; MN-major operands use it as the
+// distance between 64-element column blocks.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((1024u >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version for sm_100
+    d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+    return d;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cnt(uint32_t bar) { mbar_arrive(bar); }
+
+template <int HD>
+__global__ void __launch_bounds__(kPfThreads, 1)
+hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_v, const PrefillTcArgs a) {
+    static_assert(HD == 64 || HD == 128, "head_dim 64 or 128");
+    constexpr int NCH = HD / 64;                       // 64-half column blocks
+    constexpr int CHUNK_BYTES = kPfRows * 128;         // one column block of a 128-row tile
+    constexpr int TILE_BYTES = kPfRows * HD * 2;
+    constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr uint32_t COL_S0 = 0, COL_S1 = 128, COL_PV = 256, COL_P = 384;
+    constexpr uint32_t IDESC_QK = (1u << 4) | ((uint32_t)(kPfKeys >> 3) << 17) | ((uint32_t)(kPfRows >> 4) << 24);
+    constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(kPfRows >> 4) << 24);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_gen = smem;
+    uint8_t* kv_gen = smem + TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(kv_gen + 2 * STAGE_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    const uint32_t q_smem = smem_u32(q_gen), kv_smem = smem_u32(kv_gen);
+    const uint32_t bar0 = smem_u32(bars);
+    // barrier map
+    const uint32_t B_QFULL = bar0, B_QEMPTY = bar0 + 8;
+    const uint32_t B_KVFULL = bar0 + 16;    // [2]
+    const uint32_t B_KVEMPTY = bar0 + 32;   // [2]
+    const uint32_t B_SFULL = bar0 + 48;     // [2]
+    const uint32_t B_SFREE = bar0 + 64;     // [2]
+    const uint32_t B_PFULL = bar0 + 80, B_PVFULL = bar0 + 88, B_PVFREE = bar0 + 96, B_DONE = bar0 + 104;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        mbar_init(B_QFULL, 1); mbar_init(B_QEMPTY, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(B_KVFULL + 8 * s, 1); mbar_init(B_KVEMPTY + 8 * s, 1);
+            mbar_init(B_SFULL + 8 * s, 1); mbar_init(B_SFREE + 8 * s, 128);
+        }
+        mbar_init(B_PFULL, 128); mbar_init(B_PVFULL, 1); mbar_init(B_PVFREE, 128); mbar_init(B_DONE, 1);
+        fence_mbar_init();
+        tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
+    }
+    if (warp == 5) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    const int n_items = a.n_qtiles * a.KVH;
+    const int kv_valid = (a.past_len + a.S_new < a.slots) ? a.past_len + a.S_new : a.slots;
+
+    // Key-tile range of a query tile (identical in every role).
+    auto tile_span = [&](int qt, int& kt_lo, int& nt) {
+        const int q0 = qt * a.QT;
+        const int first_min = a.window > 0 ? (a.past_len + q0 + 1 - a.window > 0 ? a.past_len + q0 + 1 - a.window : 0) : 0;
+        int q_last = q0 + a.QT < a.S_new ? q0 + a.QT : a.S_new;
+        int last_max = a.past_len + q_last - 1;
+        if (last_max > a.slots - 1) last_max = a.slots - 1;
+        kt_lo = first_min / kPfKeys;
+        nt = last_max / kPfKeys - kt_lo + 1;
+        if (nt < 1) nt = 1;
+    };
+
+    if (warp == 4) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            uint32_t gt = 0, it = 0;
+            int issued_kv = 0;
+            bool ok = true, q_pending = false;
+            uint32_t q_it = 0;
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+                const int qt = a.n_qtiles - 1 - item / a.KVH, kvh = item % a.KVH;  // longest spans first
+                int kt_lo, nt;
+                tile_span(qt, kt_lo, nt);
+                if (!mbar_wait(B_QEMPTY, (it & 1) ^ 1, a.status)) { ok = false; break; }
+                mbar_expect_tx(B_QFULL, (uint32_t)(NCH * a.QT * a.G * 128));
+#pragma unroll
+                for (int c = 0; c < NCH; ++c)
+                    tma_load_3d(q_smem + c * CHUNK_BYTES, &tm_q, B_QFULL, c * 64, kvh * a.G, qt * a.QT);
+                q_pending = true;
+                q_it = it;
+                for (int t = 0; t < nt; ++t, ++gt) {
+                    const uint32_t st = gt & 1, use = gt >> 1;
+                    if (!mbar_wait(B_KVEMPTY + 8 * st, (use & 1) ^ 1, a.status)) { ok = false; break; }
+                    const uint32_t full = B_KVFULL + 8 * st, dst = kv_smem + st * STAGE_BYTES;
+                    mbar_expect_tx(full, STAGE_BYTES);
+                    const int row = (kt_lo + t) * kPfKeys;
+#pragma unroll
+                    for (int c = 0; c < NCH; ++c) tma_load_4d(dst + c * CHUNK_BYTES, &tm_k, full, c * 64, kvh, row, 0);
+#pragma unroll
+                    for (int c = 0; c < NCH; ++c)
+                        tma_load_4d(dst + TILE_BYTES + c * CHUNK_BYTES, &tm_v, full, c * 64, kvh, row, 0);
+                    ++issued_kv;
+                }
+            }
+            // drain this thread's outstanding copies before the CTA retires
+            if (q_pending) mbar_wait(B_QFULL, q_it & 1, a.status);
+            const int back = issued_kv < 2 ? issued_kv : 2;
+            for (int i = 1; i <= back; ++i) {
+                const uint32_t g = gt - i;
+                mbar_wait(B_KVFULL + 8 * (g & 1), (g >> 1) & 1, a.status);
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            uint32_t gt = 0, it = 0;
+            bool ok = true;
+            auto issue_qk = [&](uint32_t g) {
+                const uint32_t st = g & 1;
+                const uint32_t kbase = kv_smem + st * STAGE_BYTES;
+                const uint32_t d = tmem + (st ? COL_S1 : COL_S0);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const uint32_t off = (ks / 4) * CHUNK_BYTES + (ks % 4) * 32;
+                    tc_mma_ss(d, umma_desc_sw128(q_smem + off, 16), umma_desc_sw128(kbase + off, 16), IDESC_QK, ks > 0);
+                }
+                tc_commit(B_SFULL + 8 * st);
+            };
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+                const int qt = a.n_qtiles - 1 - item / a.KVH;
+                int kt_lo, nt;
+                tile_span(qt, kt_lo, nt);
+                if (!mbar_wait(B_QFULL, it & 1, a.status)) { ok = false; break; }
+                // scores of the first tile
+                if (!mbar_wait(B_KVFULL + 8 * (gt & 1), (gt >> 1) & 1, a.status) ||
+                    !mbar_wait(B_SFREE + 8 * (gt & 1), ((gt >> 1) & 1) ^ 1, a.status)) { ok = false; break; }
+                tc_fence_after();
+                issue_qk(gt);
+                for (int t = 0; t < nt && ok; ++t, ++gt) {
+                    if (t + 1 < nt) {
+                        const uint32_t g1 = gt + 1;
+                        if (!mbar_wait(B_KVFULL + 8 * (g1 & 1), (g1 >> 1) & 1, a.status) ||
+                            !mbar_wait(B_SFREE + 8 * (g1 & 1), ((g1 >> 1) & 1) ^ 1, a.status)) { ok = false; break; }
+                        tc_fence_after();
+                        issue_qk(g1);
+                    } else {
+                        tc_commit(B_QEMPTY);  // last score MMA of the item issued: Q tile may be replaced
+                    }
+                    if (!mbar_wait(B_PFULL, gt & 1, a.status) || !mbar_wait(B_PVFREE, (gt & 1) ^ 1, a.status)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t vbase = kv_smem + (gt & 1) * STAGE_BYTES + TILE_BYTES;
+#pragma unroll
+                    for (int ks = 0; ks < kPfKeys / 16; ++ks)
+                        tc_mma_ts(tmem + COL_PV, tmem + COL_P + ks * 8, umma_desc_sw128(vbase + ks * 2048, CHUNK_BYTES),
+                                  IDESC_PV, ks > 0);
+                    tc_commit(B_PVFULL);
+                    tc_commit(B_KVEMPTY + 8 * (gt & 1));
+                }
+            }
+            // every MMA issued above has completed before tensor memory is freed
+            tc_commit(B_DONE);
+            mbar_wait(B_DONE, 0, a.status);
+        }
+    } else {
+        // ------------------------------ softmax / output rows ------------------------------
+        const int r = tid;                         // row of the tile = lane of tensor memory
+        const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+        const int ql = r / a.G, g = r % a.G;
+        uint32_t gt = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+            const int qt = a.n_qtiles - 1 - item / a.KVH, kvh = item % a.KVH;
+            int kt_lo, nt;
+            tile_span(qt, kt_lo, nt);
+            const int qi = qt * a.QT + ql;
+            const bool row_valid = ql < a.QT && qi < a.S_new;
+            const int qpos = a.past_len + qi;
+            const int first_row = a.window > 0 ? (qpos + 1 - a.window > 0 ? qpos + 1 - a.window : 0) : 0;
+            const int qlim = qpos < a.slots ? qpos : a.slots - 1;  // never attend rows past the plane
+            float o[HD];
+#pragma unroll
+            for (int d = 0; d < HD; ++d) o[d] = 0.0f;
+            float m_run = kNegBig, l_run = 0.0f;
+
+            for (int t = 0; t < nt; ++t, ++gt) {
+                const uint32_t sb = gt & 1;
+                const uint32_t s_addr = tmem + lane_sel + (sb ? COL_S1 : COL_S0);
+                const int kstart = (kt_lo + t) * kPfKeys;
+                if (ok && !mbar_wait(B_SFULL + 8 * sb, (gt >> 1) & 1, a.status)) ok = false;
+                if (!ok) continue;
+                tc_fence_after();
+                // pass 1: row maximum
+                float mx = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < kPfKeys / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(v, s_addr + c * 32);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int key = kstart + c * 32 + j;
+                        const float s = __uint_as_float(v[j]) * a.scale_log2;
+                        if (key >= first_row && key <= qlim) mx = fmaxf(mx, s);
+                    }
+                }
+                const float m_new = fmaxf(m_run, mx);
+                const float alpha = exp2f(m_run - m_new);
+                // pass 2: probabilities, written back as packed fp16 (A operand of P·V)
+                float lsum = 0.0f;
+#pragma unroll
+                for (int c = 0; c < kPfKeys / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(v, s_addr + c * 32);
+                    tc_wait_ld();
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const int key = kstart + c * 32 + j;
+                        float p0 = exp2f(__uint_as_float(v[j]) * a.scale_log2 - m_new);
+                        float p1 = exp2f(__uint_as_float(v[j + 1]) * a.scale_log2 - m_new);
+                        if (!(key >= first_row && key <= qlim)) p0 = 0.0f;
+                        if (!(key + 1 >= first_row && key + 1 <= qlim)) p1 = 0.0f;
+                        lsum += p0 + p1;
+                        pk[j / 2] = pack_half2(p0, p1);
+                    }
+                    tmem_st16(tmem + lane_sel + COL_P + c * 16, pk);
+                }
+                tc_wait_st();
+                m_run = m_new;
+                l_run = l_run * alpha + lsum;
+                // cache rows of this tile past the last written position may hold stale bits:
+                // zero them in the staged V tile so that 0 * garbage cannot produce NaN
+                if (kstart + kPfKeys > kv_valid) {
+                    uint8_t* vt = kv_gen + (size_t)sb * STAGE_BYTES + TILE_BYTES;
+                    const int first_bad = kv_valid > kstart ? kv_valid - kstart : 0;
+                    for (int idx = first_bad * 8 * NCH + tid; idx < kPfKeys * 8 * NCH; idx += 128) {
+                        const int row = idx / (8 * NCH), u = idx % (8 * NCH);
+                        *reinterpret_cast<uint4*>(vt + (u / 8) * CHUNK_BYTES + row * 128 + (u % 8) * 16) =
+                            make_uint4(0, 0, 0, 0);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+                tc_fence_before();
+                mbar_arrive(B_SFREE + 8 * sb);
+                mbar_arrive(B_PFULL);
+                // accumulate P·V of this tile
+                if (!mbar_wait(B_PVFULL, gt & 1, a.status)) { ok = false; continue; }
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < HD / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(v, tmem + lane_sel + COL_PV + c * 32);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[c * 32 + j] = fmaf(o[c * 32 + j], alpha, __uint_as_float(v[j]));
+                }
+                tc_fence_before();
+                mbar_arrive(B_PVFREE);
+            }
+            if (ok && row_valid) {
+                const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+                __half* op = a.out + ((long long)qi * a.H + (long long)kvh * a.G + g) * HD;
+#pragma unroll
+                for (int d = 0; d < HD; d += 8) {
+                    uint4 w;
+                    w.x = pack_half2(o[d] * inv, o[d + 1] * inv);
+                    w.y = pack_half2(o[d + 2] * inv, o[d + 3] * inv);
+                    w.z = pack_half2(o[d + 4] * inv, o[d + 5] * inv);
+                    w.w = pack_half2(o[d + 6] * inv, o[d + 7] * inv);
+                    *reinterpret_cast<uint4*>(op + d) = w;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+}  // namespace hkv

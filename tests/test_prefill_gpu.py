@@ -1,0 +1,76 @@
+"""GPU parity of prefill-over-cache attention (hkv_prefill_attention) against the oracle:
+the tcgen05 tensor-core kernel (head_dim 64 / 128) and the any-geometry SIMT kernel, on the
+same seeded inputs. Tolerance: |x - ref| <= 2e-3 + 1e-2*|ref| per fp16 element."""
+import math
+
+import numpy as np
+import pytest
+
+from _util import assert_close, normal_f16, to_dev
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    # name, H, KVH, HD, slots, past_len, S_new, window
+    ("qwen7b_group7_multi_tile", 28, 4, 128, 2048, 1000, 200, 0),
+    ("qwen7b_from_empty_cache", 28, 4, 128, 512, 0, 300, 0),
+    ("qwen05b_hd64_group7", 14, 2, 64, 1024, 333, 77, 0),
+    ("mha_hd64", 8, 8, 64, 640, 100, 260, 0),
+    ("group2_window", 16, 8, 128, 1024, 500, 150, 96),
+    ("group16_window_small", 32, 2, 64, 512, 40, 90, 17),
+    ("single_query", 28, 4, 128, 256, 130, 1, 0),
+    ("fills_plane_exactly", 28, 4, 128, 384, 256, 128, 0),
+]
+
+
+@pytest.mark.parametrize("kernel", [0, 1], ids=["tensor_core", "simt"])
+@pytest.mark.parametrize("case", CASES, ids=lambda c: c[0])
+def test_prefill_matches_oracle(hkv, cuda, oracle, case, kernel):
+    torch = cuda
+    name, H, KVH, HD, slots, past, S_new, window = case
+    rng = np.random.default_rng(len(name) * 7919 + HD)
+    k = normal_f16(rng, 1, slots, KVH, HD)
+    v = normal_f16(rng, 1, slots, KVH, HD)
+    # rows past the chunk are stale memory in a real cache: poison them
+    k[0, past + S_new:] = np.float16(np.nan)
+    v[0, past + S_new:] = np.float16(np.inf)
+    q = normal_f16(rng, S_new, H, HD)
+    for scale in (1.0 / math.sqrt(HD), 1.0):
+        ref = oracle.prefill(q, k[0], v[0], past, scale, window=window, threads=8)
+        ctx = hkv.Context(hkv.Geometry(batch=1, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots,
+                                       window_size=window, kernel_select=kernel, max_seq_new=S_new))
+        out = torch.full((S_new, H, HD), float("nan"), dtype=torch.float16, device="cuda")
+        ctx.prefill_attention(to_dev(torch, q), to_dev(torch, k), to_dev(torch, v), out, S_new, past, scale)
+        assert ctx.device_status() == 0
+        got = out.cpu().numpy()
+        assert not np.isnan(got.astype(np.float32)).any()
+        assert_close(oracle, got, ref, f"{name} scale={scale:.3f}")
+        ctx.close()
+
+
+def test_chunked_prefill_then_decode_agree(hkv, cuda, oracle):
+    """Append a chunk, attend it with the prefill kernel, then decode the next token: the
+    last query of the chunk through prefill equals a decode call at that position."""
+    torch = cuda
+    H, KVH, HD, slots, past, S_new = 28, 4, 128, 1024, 300, 140
+    rng = np.random.default_rng(99)
+    kc = normal_f16(rng, 1, slots, KVH, HD)
+    vc = normal_f16(rng, 1, slots, KVH, HD)
+    nk, nv = normal_f16(rng, 1, S_new, KVH, HD), normal_f16(rng, 1, S_new, KVH, HD)
+    q = normal_f16(rng, S_new, H, HD)
+    scale = 1.0 / math.sqrt(HD)
+    ctx = hkv.Context(hkv.Geometry(batch=1, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots))
+    dk, dv = to_dev(torch, kc), to_dev(torch, vc)
+    ctx.append_at(to_dev(torch, nk), to_dev(torch, nv), dk, dv, past, S_new)      # KV_CACHE_UPDATE first
+    out = torch.zeros(S_new, H, HD, dtype=torch.float16, device="cuda")
+    ctx.prefill_attention(to_dev(torch, q), dk, dv, out, S_new, past, scale)      # then ATTENTION_PREFILL_CACHED
+    one = torch.zeros(1, H, HD, dtype=torch.float16, device="cuda")
+    ctx.decode_attention_len(to_dev(torch, q[-1:]), dk, dv, one, past + S_new, scale)
+    assert ctx.device_status() == 0
+    ref_k, ref_v = kc.copy(), vc.copy()
+    oracle.append(nk, nv, ref_k, ref_v, np.array([past], np.int32))
+    assert np.array_equal(dk.cpu().numpy().view(np.uint16), ref_k.view(np.uint16))
+    ref = oracle.prefill(q, ref_k[0], ref_v[0], past, scale, threads=8)
+    assert_close(oracle, out.cpu().numpy(), ref, "chunk through prefill")
+    assert_close(oracle, one.cpu().numpy()[0], ref[-1], "last query through decode")
+    ctx.close()
