@@ -60,7 +60,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--ref-layers", type=int, default=2, help="layers the reference arm runs per step")
-    ap.add_argument("--mode", default="batch", choices=["batch", "seqsplit"],
+    ap.add_argument("--past", type=int, default=30720, help="prefill mode: cache rows before the chunk")
+    ap.add_argument("--chunk", type=int, default=2048, help="prefill mode: new queries per chunk")
+    ap.add_argument("--mode", default="batch", choices=["batch", "seqsplit", "prefill"],
                     help="batch: sequences sharded over GPUs, no collective (default). seqsplit: every "
                          "sequence's cache split block-cyclically over the GPUs, partials all-gathered "
                          "over NCCL; --ctx is then the rows per sequence PER GPU")
@@ -361,6 +363,76 @@ def run_seqsplit(args, torch, hkv, dist, cfg, ctx_local, B, rank, world, base, g
     dec.close()
 
 
+def run_prefill(args, torch, hkv, oracle, cfg, rank, base, gpu_id):
+    """Chunked prefill over the cache (batch 1, one layer per call): append the chunk's K/V,
+    then attention of its --chunk queries over rows [0, past + chunk). Tensor-bound:
+    flops = 4*H*HD*sum_q(past + q + 1)."""
+    H, KVH, HD = cfg["H"], cfg["KVH"], cfg["HD"]
+    S, past = args.chunk, args.past
+    slots = past + S
+    dev = "cuda"
+    k = torch.empty((slots, KVH, HD), dtype=torch.float16, device=dev)
+    v = torch.empty((slots, KVH, HD), dtype=torch.float16, device=dev)
+    q = torch.empty((S, H, HD), dtype=torch.float16, device=dev)
+    kn = torch.empty((S, KVH, HD), dtype=torch.float16, device=dev)
+    vn = torch.empty((S, KVH, HD), dtype=torch.float16, device=dev)
+    out = torch.zeros((S, H, HD), dtype=torch.float16, device=dev)
+    for i, t in enumerate((k, v, q, kn, vn)):
+        hkv.fill_synthetic(t, SEED ^ (i << 20))
+    ctx = hkv.Context(hkv.Geometry(batch=1, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots,
+                                   kernel_select=args.kernel, max_seq_new=S))
+    scale = 1.0 / math.sqrt(HD)
+
+    def step():
+        ctx.append_at(kn, vn, k, v, past, S)
+        ctx.prefill_attention(q, k, v, out, S, past, scale)
+
+    step()
+    assert ctx.device_status() == 0
+    err = None
+    if not args.no_verify:  # sampled queries against the oracle
+        hk, hv, hq = k.cpu().numpy(), v.cpu().numpy(), q.cpu().numpy()
+        got = out.cpu().numpy()
+        err = 0.0
+        for lo in (0, S // 2, S - 4):
+            ref = oracle.prefill(hq, hk, hv, past, scale, q_begin=lo, q_end=lo + 4, threads=oracle.hardware_threads())
+            ok, e = oracle.within_tolerance(got[lo:lo + 4], ref[lo:lo + 4])
+            assert ok, f"prefill parity failed at query {lo}: {e:.3e}"
+            err = max(err, e)
+    for _ in range(args.warmup):
+        step()
+    sampler = ClockSampler(gpu_id)
+    torch.cuda.synchronize()
+    sampler.start()
+    e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    attn_ms = 0.0
+    evs = []
+    for _ in range(args.steps):
+        a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        a.record(); ctx.append_at(kn, vn, k, v, past, S)
+        b.record(); ctx.prefill_attention(q, k, v, out, S, past, scale)
+        c.record(); evs.append((a, b, c))
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    tot_ms = sum(a.elapsed_time(c) for a, b, c in evs) / args.steps
+    attn_ms = sum(b.elapsed_time(c) for a, b, c in evs) / args.steps
+    flops = 4.0 * H * HD * sum(past + i + 1 for i in range(S))
+    peaks_path = os.path.join(REPO, "MEASURED_PEAKS.json")
+    peak = float(json.load(open(peaks_path))["bf16_tflops"]) if os.path.exists(peaks_path) else 1590.0
+    achieved = flops / (attn_ms * 1e-3) / 1e12
+    cfgd = {"workload": f"{args.workload}-shaped chunked prefill over the cache: chunk {S} queries, {past} rows "
+                        f"already cached, {H}q/{KVH}kv heads, head_dim {HD}, one layer per step, batch 1",
+            "chunk": S, "past_len": past, "l2": "K/V planes of %.0f MB, re-read per query tile" % (slots * KVH * HD * 4 / 1e6)}
+    line = dict(base, config=cfgd, impl="hkv", mode="prefill", metric="prefill attention tokens/s (one layer)",
+                value=S / (tot_ms * 1e-3), ms_per_step=tot_ms, clocks=clocks, gpu_launches=args.steps * 2,
+                roofline={"bound": "tensor", "kernel": "hkv_prefill_tc_kernel", "achieved": achieved, "peak": peak,
+                          "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": "measured burst bf16 GEMM",
+                          "traffic": None, "algorithmic_flops_per_launch": flops, "avg_launch_ms": attn_ms},
+                e2e=None, cpu_baseline=None, parity_max_abs_err=err)
+    print(json.dumps(line))
+    ctx.close()
+
+
 def main():
     args = parse_args()
     import torch
@@ -387,7 +459,7 @@ def main():
     if args.layers:
         cfg["layers"] = args.layers
     ctx = args.ctx
-    B = pick_batch(torch, cfg, ctx, args.batch)
+    B = 1 if args.mode == "prefill" else pick_batch(torch, cfg, ctx, args.batch)
     n_gpus = world if args.impl != "reference" else 1
     try:
         gpu_id = str(torch.cuda.get_device_properties(local).uuid)
@@ -434,6 +506,12 @@ def main():
         print(json.dumps(line))
         return 0
 
+    if args.mode == "prefill":
+        if rank == 0:
+            run_prefill(args, torch, hkv, oracle, cfg, rank, base, gpu_id)
+        if dist is not None:
+            dist.destroy_process_group()
+        return 0
     if args.mode == "seqsplit":
         run_seqsplit(args, torch, hkv, dist, cfg, ctx, B, rank, n_gpus, base, gpu_id)
         if dist is not None:

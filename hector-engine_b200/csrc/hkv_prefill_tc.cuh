@@ -11,16 +11,18 @@
 //     into the M dimension: row r of the 128-row tile is (query r / G, head r % G), QT = 128 / G
 //     queries per tile (18 for a group of 7: 126 of 128 rows used). One bulk-tensor load with
 //     box {64 halfs, G heads, QT queries} brings the tile in as 128-byte-swizzled K-major rows.
-//   * Warp 4 (one lane) is the TMA producer: Q tile per item, K/V tiles of 128 cache rows
+//   * Warp 8 (one lane) is the TMA producer: Q tile per item, K/V tiles of 128 cache rows
 //     through a 2-stage ring (full/empty mbarriers).
-//   * Warp 5 (one lane) issues the MMAs:  S = Q·K^T  (M128 x N128 x K=HD, both operands K-major
+//   * Warp 9 (one lane) issues the MMAs:  S = Q·K^T  (M128 x N128 x K=HD, both operands K-major
 //     from shared memory) into one of two S buffers in tensor memory, and
 //     PV = P·V  (A = P from tensor memory as packed fp16, B = V straight from its row-major
 //     tile as an MN-major operand). S of tile t+1 is issued before PV of tile t, so the score
 //     contraction overlaps the softmax of the previous tile.
-//   * Warps 0-3: thread r owns row r. Two passes over its S row in tensor memory (max, then
-//     exp2 / sum / fp16 P written back with tcgen05.st), causal + window mask per element;
-//     then O_r = O_r * alpha + PV_r with O kept in registers (fp32).
+//   * Warps 0-7: two threads per row (each half of the score columns and of the output
+//     dimensions). The row's scores are read once from tensor memory, masked (causal +
+//     window), the two halves exchange their maxima through shared memory, exp2 / sum, and P
+//     goes back to tensor memory as packed fp16 (tcgen05.st); then O = O * alpha + PV with O
+//     kept in registers (fp32).
 //   * All waits are bounded mbarrier waits; a wait that runs out sets the status word, the
 //     roles leave their loops, outstanding copies are drained and tensor memory is freed.
 #pragma once
@@ -40,10 +42,10 @@ struct PrefillTcArgs {
 
 constexpr int kPfRows = 128;   // M of the MMA = rows of a query tile
 constexpr int kPfKeys = 128;   // cache rows per K/V tile = N of the score MMA
-constexpr int kPfThreads = 192;
+constexpr int kPfThreads = 320;  // 8 softmax warps + TMA producer + MMA issuer
 
 __host__ __device__ constexpr size_t prefill_tc_smem_bytes(int HD) {
-    return 1024 + (size_t)kPfRows * HD * 2 + 2 * (2 * (size_t)kPfKeys * HD * 2) + 256;
+    return 1024 + (size_t)kPfRows * HD * 2 + 2 * (2 * (size_t)kPfKeys * HD * 2) + 256 + 6 * kPfRows * 4;
 }
 
 // ---- tcgen05 wrappers -------------------------------------------------------------
@@ -136,6 +138,7 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     uint8_t* kv_gen = smem + TILE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(kv_gen + 2 * STAGE_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    float* xch = reinterpret_cast<float*>(bars + 32);   // [2 buffers][2 halves][128] maxima + [2][128] sums
     const uint32_t q_smem = smem_u32(q_gen), kv_smem = smem_u32(kv_gen);
     const uint32_t bar0 = smem_u32(bars);
     // barrier map
@@ -145,19 +148,20 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const uint32_t B_SFULL = bar0 + 48;     // [2]
     const uint32_t B_SFREE = bar0 + 64;     // [2]
     const uint32_t B_PFULL = bar0 + 80, B_PVFULL = bar0 + 88, B_PVFREE = bar0 + 96, B_DONE = bar0 + 104;
+    const uint32_t B_XCH = bar0 + 112;      // softmax threads exchanging row maxima / sums
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         mbar_init(B_QFULL, 1); mbar_init(B_QEMPTY, 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(B_KVFULL + 8 * s, 1); mbar_init(B_KVEMPTY + 8 * s, 1);
-            mbar_init(B_SFULL + 8 * s, 1); mbar_init(B_SFREE + 8 * s, 128);
+            mbar_init(B_SFULL + 8 * s, 1); mbar_init(B_SFREE + 8 * s, 256);
         }
-        mbar_init(B_PFULL, 128); mbar_init(B_PVFULL, 1); mbar_init(B_PVFREE, 128); mbar_init(B_DONE, 1);
+        mbar_init(B_PFULL, 256); mbar_init(B_PVFULL, 1); mbar_init(B_PVFREE, 256); mbar_init(B_DONE, 1); mbar_init(B_XCH, 256);
         fence_mbar_init();
         tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
     }
-    if (warp == 5) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    if (warp == 9) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -178,7 +182,7 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         if (nt < 1) nt = 1;
     };
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             uint32_t gt = 0, it = 0;
@@ -218,7 +222,7 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 mbar_wait(B_KVFULL + 8 * (g & 1), (g >> 1) & 1, a.status);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
             uint32_t gt = 0, it = 0;
@@ -274,11 +278,16 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         }
     } else {
         // ------------------------------ softmax / output rows ------------------------------
-        const int r = tid;                         // row of the tile = lane of tensor memory
-        const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+        // Two threads per row: warps 0-3 take columns [0, 64) of the score tile and the first
+        // half of the output dimensions, warps 4-7 the other halves. Tensor-memory lanes are
+        // reached through the warp's quadrant (warp % 4).
+        const int quad = warp & 3, half = warp >> 2;
+        const int r = quad * 32 + lane;            // row of the tile = lane of tensor memory
+        const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
+        constexpr int HH = HD / 2;                 // output dimensions per thread
         const int ql = r / a.G, g = r % a.G;
-        uint32_t gt = 0;
-        bool ok = true;
+        uint32_t gt = 0, xn = 0;   // tiles seen, exchanges done (barrier phases)
+        bool ok = true;            // kept warp-uniform: a wait that ran out for any lane stops the warp
         for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
             const int qt = a.n_qtiles - 1 - item / a.KVH, kvh = item % a.KVH;
             int kt_lo, nt;
@@ -288,91 +297,115 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             const int qpos = a.past_len + qi;
             const int first_row = a.window > 0 ? (qpos + 1 - a.window > 0 ? qpos + 1 - a.window : 0) : 0;
             const int qlim = qpos < a.slots ? qpos : a.slots - 1;  // never attend rows past the plane
-            float o[HD];
+            float o[HH];
 #pragma unroll
-            for (int d = 0; d < HD; ++d) o[d] = 0.0f;
+            for (int d = 0; d < HH; ++d) o[d] = 0.0f;
             float m_run = kNegBig, l_run = 0.0f;
 
             for (int t = 0; t < nt; ++t, ++gt) {
                 const uint32_t sb = gt & 1;
-                const uint32_t s_addr = tmem + lane_sel + (sb ? COL_S1 : COL_S0);
-                const int kstart = (kt_lo + t) * kPfKeys;
-                if (ok && !mbar_wait(B_SFULL + 8 * sb, (gt >> 1) & 1, a.status)) ok = false;
-                if (!ok) continue;
-                tc_fence_after();
-                // pass 1: row maximum
-                float mx = -INFINITY;
-#pragma unroll
-                for (int c = 0; c < kPfKeys / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32(v, s_addr + c * 32);
+                const uint32_t s_addr = tmem + lane_sel + (sb ? COL_S1 : COL_S0) + half * 64;
+                const int kstart = (kt_lo + t) * kPfKeys + half * 64;   // key of this thread's column 0
+                ok = __all_sync(0xffffffffu, ok && mbar_wait(B_SFULL + 8 * sb, (gt >> 1) & 1, a.status));
+                if (ok) {
+                    tc_fence_after();
+                    uint32_t s0[32], s1[32];
+                    tmem_ld32(s0, s_addr);
+                    tmem_ld32(s1, s_addr + 32);
                     tc_wait_ld();
+                    // columns [lo, hi] of this thread's 64 are attended (causal + window)
+                    const int lo = first_row - kstart, hi = qlim - kstart;
+                    const bool all_in = __all_sync(0xffffffffu, lo <= 0 && hi >= 63);
+                    float sc[64];
+                    float mx = -INFINITY;
+                    if (all_in) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int key = kstart + c * 32 + j;
-                        const float s = __uint_as_float(v[j]) * a.scale_log2;
-                        if (key >= first_row && key <= qlim) mx = fmaxf(mx, s);
+                        for (int j = 0; j < 32; ++j) {
+                            sc[j] = __uint_as_float(s0[j]) * a.scale_log2;
+                            sc[32 + j] = __uint_as_float(s1[j]) * a.scale_log2;
+                            mx = fmaxf(mx, fmaxf(sc[j], sc[32 + j]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            sc[j] = (j >= lo && j <= hi) ? __uint_as_float(s0[j]) * a.scale_log2 : -INFINITY;
+                            sc[32 + j] = (32 + j >= lo && 32 + j <= hi) ? __uint_as_float(s1[j]) * a.scale_log2 : -INFINITY;
+                            mx = fmaxf(mx, fmaxf(sc[j], sc[32 + j]));
+                        }
                     }
-                }
-                const float m_new = fmaxf(m_run, mx);
-                const float alpha = exp2f(m_run - m_new);
-                // pass 2: probabilities, written back as packed fp16 (A operand of P·V)
-                float lsum = 0.0f;
+                    // row maximum over both halves
+                    xch[(sb * 2 + half) * kPfRows + r] = mx;
+                    mbar_arrive(B_XCH);
+                    ok = __all_sync(0xffffffffu, mbar_wait(B_XCH, xn & 1, a.status));
+                    ++xn;
+                    if (!ok) continue;
+                    mx = fmaxf(mx, xch[(sb * 2 + (half ^ 1)) * kPfRows + r]);
+                    const float m_new = fmaxf(m_run, mx);
+                    const float alpha = exp2f(m_run - m_new);
+                    float lsum = 0.0f;
+                    uint32_t pk[32];
 #pragma unroll
-                for (int c = 0; c < kPfKeys / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32(v, s_addr + c * 32);
-                    tc_wait_ld();
-                    uint32_t pk[16];
-#pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        const int key = kstart + c * 32 + j;
-                        float p0 = exp2f(__uint_as_float(v[j]) * a.scale_log2 - m_new);
-                        float p1 = exp2f(__uint_as_float(v[j + 1]) * a.scale_log2 - m_new);
-                        if (!(key >= first_row && key <= qlim)) p0 = 0.0f;
-                        if (!(key + 1 >= first_row && key + 1 <= qlim)) p1 = 0.0f;
+                    for (int j = 0; j < 64; j += 2) {
+                        const float p0 = exp2f(sc[j] - m_new), p1 = exp2f(sc[j + 1] - m_new);
                         lsum += p0 + p1;
                         pk[j / 2] = pack_half2(p0, p1);
                     }
-                    tmem_st16(tmem + lane_sel + COL_P + c * 16, pk);
-                }
-                tc_wait_st();
-                m_run = m_new;
-                l_run = l_run * alpha + lsum;
-                // cache rows of this tile past the last written position may hold stale bits:
-                // zero them in the staged V tile so that 0 * garbage cannot produce NaN
-                if (kstart + kPfKeys > kv_valid) {
-                    uint8_t* vt = kv_gen + (size_t)sb * STAGE_BYTES + TILE_BYTES;
-                    const int first_bad = kv_valid > kstart ? kv_valid - kstart : 0;
-                    for (int idx = first_bad * 8 * NCH + tid; idx < kPfKeys * 8 * NCH; idx += 128) {
-                        const int row = idx / (8 * NCH), u = idx % (8 * NCH);
-                        *reinterpret_cast<uint4*>(vt + (u / 8) * CHUNK_BYTES + row * 128 + (u % 8) * 16) =
-                            make_uint4(0, 0, 0, 0);
+                    {
+                        uint32_t (&pa)[16] = *reinterpret_cast<uint32_t (*)[16]>(&pk[0]);
+                        uint32_t (&pb)[16] = *reinterpret_cast<uint32_t (*)[16]>(&pk[16]);
+                        tmem_st16(tmem + lane_sel + COL_P + half * 32, pa);
+                        tmem_st16(tmem + lane_sel + COL_P + half * 32 + 16, pb);
                     }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                }
-                tc_fence_before();
-                mbar_arrive(B_SFREE + 8 * sb);
-                mbar_arrive(B_PFULL);
-                // accumulate P·V of this tile
-                if (!mbar_wait(B_PVFULL, gt & 1, a.status)) { ok = false; continue; }
-                tc_fence_after();
+                    tc_wait_st();
+                    m_run = m_new;
+                    l_run = l_run * alpha + lsum;
+                    // cache rows of this tile past the last written position may hold stale bits:
+                    // zero them in the staged V tile so that 0 * garbage cannot produce NaN
+                    const int tile0 = (kt_lo + t) * kPfKeys;
+                    if (tile0 + kPfKeys > kv_valid) {
+                        uint8_t* vt = kv_gen + (size_t)sb * STAGE_BYTES + TILE_BYTES;
+                        const int first_bad = kv_valid > tile0 ? kv_valid - tile0 : 0;
+                        for (int idx = first_bad * 8 * NCH + tid; idx < kPfKeys * 8 * NCH; idx += 256) {
+                            const int row = idx / (8 * NCH), u = idx % (8 * NCH);
+                            *reinterpret_cast<uint4*>(vt + (u / 8) * CHUNK_BYTES + row * 128 + (u % 8) * 16) =
+                                make_uint4(0, 0, 0, 0);
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    }
+                    tc_fence_before();
+                    mbar_arrive(B_SFREE + 8 * sb);
+                    mbar_arrive(B_PFULL);
+                    // accumulate P·V of this tile (this thread's half of the output dimensions)
+                    ok = __all_sync(0xffffffffu, mbar_wait(B_PVFULL, gt & 1, a.status));
+                    if (ok) {
+                        tc_fence_after();
 #pragma unroll
-                for (int c = 0; c < HD / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32(v, tmem + lane_sel + COL_PV + c * 32);
-                    tc_wait_ld();
+                        for (int c = 0; c < HH / 32; ++c) {
+                            uint32_t v[32];
+                            tmem_ld32(v, tmem + lane_sel + COL_PV + half * HH + c * 32);
+                            tc_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) o[c * 32 + j] = fmaf(o[c * 32 + j], alpha, __uint_as_float(v[j]));
+                            for (int j = 0; j < 32; ++j) o[c * 32 + j] = fmaf(o[c * 32 + j], alpha, __uint_as_float(v[j]));
+                        }
+                        tc_fence_before();
+                        mbar_arrive(B_PVFREE);
+                    }
                 }
-                tc_fence_before();
-                mbar_arrive(B_PVFREE);
+            }
+            // total row sum = both halves' partial sums (same running maximum)
+            float l_tot = l_run;
+            if (ok) {
+                xch[4 * kPfRows + half * kPfRows + r] = l_run;
+                mbar_arrive(B_XCH);
+                ok = __all_sync(0xffffffffu, mbar_wait(B_XCH, xn & 1, a.status));
+                ++xn;
+                l_tot += xch[4 * kPfRows + (half ^ 1) * kPfRows + r];
             }
             if (ok && row_valid) {
-                const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-                __half* op = a.out + ((long long)qi * a.H + (long long)kvh * a.G + g) * HD;
+                const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
+                __half* op = a.out + ((long long)qi * a.H + (long long)kvh * a.G + g) * HD + half * HH;
 #pragma unroll
-                for (int d = 0; d < HD; d += 8) {
+                for (int d = 0; d < HH; d += 8) {
                     uint4 w;
                     w.x = pack_half2(o[d] * inv, o[d + 1] * inv);
                     w.y = pack_half2(o[d + 2] * inv, o[d + 3] * inv);
@@ -385,7 +418,7 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) tmem_dealloc(tmem, TMEM_COLS);
+    if (warp == 9) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 }  // namespace hkv
