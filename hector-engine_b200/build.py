@@ -81,10 +81,16 @@ def build_oracle() -> None:
     subprocess.run(["make", "-s", "-C", os.path.join(REPO, "oracle"), "all"], check=True)
 
 
+def build_dropin() -> None:
+    """Drop-in test binary against the real engine (only where the reference checkout exists)."""
+    subprocess.run(["make", "-s", "-C", os.path.join(REPO, "oracle"), "dropin"], check=True)
+
+
 def build_all(force: bool = False) -> None:
     build_lib(force=force)
     build_oracle()
     build_host_tests(force=force)
+    build_dropin()
 
 
 if __name__ == "__main__":
