@@ -39,8 +39,11 @@ DRAM_BYTES_PER_ALGORITHMIC_BYTE = 1.0172
 WORKLOADS = {
     # name: layers, H, KVH, HD, window pattern (None = all global)
     "qwen2-7b": dict(layers=28, H=28, KVH=4, HD=128),
-    "qwen2-0.5b": dict(layers=1, H=14, KVH=2, HD=64),
-    "phi3-mini": dict(layers=32, H=32, KVH=32, HD=96),
+    "qwen2-0.5b": dict(layers=1, H=14, KVH=2, HD=64, batch=1, ctx=2048),
+    "phi3-mini": dict(layers=32, H=32, KVH=32, HD=96, batch=16, ctx=4096),
+    # 5 sliding-window layers (window 1024) per global layer
+    "gemma-local-global": dict(layers=12, H=16, KVH=8, HD=256, window=1024, local_every=6, pos_rule="ctx-1-b",
+                               batch=8, ctx=32768),
 }
 
 
@@ -51,7 +54,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="hkv", choices=["hkv", "reference"])
     ap.add_argument("--workload", default="qwen2-7b", choices=sorted(WORKLOADS))
-    ap.add_argument("--ctx", type=int, default=32768)
+    ap.add_argument("--ctx", type=int, default=0, help="context (0 = the workload's own, 32768 for qwen2-7b)")
     ap.add_argument("--batch", type=int, default=0, help="sequences per GPU (0 = largest that fits)")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (parity/debug runs)")
     ap.add_argument("--kernel", type=int, default=0, help="0 auto, 1 generic, 2 tma")
@@ -67,6 +70,8 @@ def parse_args():
                          "sequence's cache split block-cyclically over the GPUs, partials all-gathered "
                          "over NCCL; --ctx is then the rows per sequence PER GPU")
     ap.add_argument("--shard-block", type=int, default=1024)
+    ap.add_argument("--linear-window", action="store_true",
+                    help="window layers keep a linear plane + mask (the reference's layout) instead of a ring")
     return ap.parse_args()
 
 
@@ -136,34 +141,62 @@ def pick_batch(torch, cfg, ctx, requested):
     free, _ = torch.cuda.mem_get_info()
     if requested:
         return requested
+    if cfg.get("batch"):
+        return cfg["batch"]
     for b in (64, 32, 8, 1):
         if b * per_seq + (6 << 30) < free:
             return b
     raise SystemExit("not enough free device memory for batch 1")
 
 
+def layer_specs(cfg, ctx, linear_window=False):
+    """Per layer: (rows per sequence, window, layout). Window layers use a ring plane of
+    `window` rows unless linear_window asks for the reference's layout (linear plane + mask)."""
+    specs = []
+    for l in range(cfg["layers"]):
+        w = cfg.get("window", 0) if cfg.get("local_every") and (l % cfg["local_every"]) != cfg["local_every"] - 1 else 0
+        if w and not linear_window:
+            specs.append((w, w, 1))
+        else:
+            specs.append((ctx, w, 0))
+    return specs
+
+
 class Workload:
-    def __init__(self, torch, hkv, cfg, ctx, B, rank, kernel=0, chunk_tiles=0):
+    def __init__(self, torch, hkv, cfg, ctx, B, rank, kernel=0, chunk_tiles=0, linear_window=False):
         self.torch, self.hkv, self.cfg, self.ctx_len, self.B, self.rank = torch, hkv, cfg, ctx, B, rank
         L, H, KVH, HD = cfg["layers"], cfg["H"], cfg["KVH"], cfg["HD"]
         self.scale = 1.0 / math.sqrt(HD)
+        self.specs = layer_specs(cfg, ctx, linear_window)
         dev = "cuda"
-        self.k = torch.empty((L, B, ctx, KVH, HD), dtype=torch.float16, device=dev)
-        self.v = torch.empty((L, B, ctx, KVH, HD), dtype=torch.float16, device=dev)
+        self.k = [torch.empty((B, s, KVH, HD), dtype=torch.float16, device=dev) for s, _, _ in self.specs]
+        self.v = [torch.empty((B, s, KVH, HD), dtype=torch.float16, device=dev) for s, _, _ in self.specs]
         self.q = torch.empty((L, B, H, HD), dtype=torch.float16, device=dev)
         self.kn = torch.empty((L, B, KVH, HD), dtype=torch.float16, device=dev)
         self.vn = torch.empty((L, B, KVH, HD), dtype=torch.float16, device=dev)
         self.out = torch.zeros((L, B, H, HD), dtype=torch.float16, device=dev)
         self.seeds = {n: SEED ^ (rank * 0x10001) ^ (i << 20) for i, n in enumerate(("k", "v", "q", "kn", "vn"))}
-        for n, t in (("k", self.k), ("v", self.v), ("q", self.q), ("kn", self.kn), ("vn", self.vn)):
+        for l in range(L):   # plane l is its own stream: element i of layer l = value(seed ^ (l << 8), i)
+            hkv.fill_synthetic(self.k[l], self.seeds["k"] ^ (l << 8))
+            hkv.fill_synthetic(self.v[l], self.seeds["v"] ^ (l << 8))
+        for n, t in (("q", self.q), ("kn", self.kn), ("vn", self.vn)):
             hkv.fill_synthetic(t, self.seeds[n])
-        rng = np.random.default_rng(SEED + rank)
-        self.pos0 = rng.integers(ctx // 2, ctx, size=B).astype(np.int32)  # per-sequence cache_pos
+        if cfg.get("pos_rule") == "ctx-1-b":      # distinct ring phases
+            self.pos0 = (ctx - 1 - np.arange(B)).astype(np.int32)
+        else:
+            self.pos0 = np.random.default_rng(SEED + rank).integers(ctx // 2, ctx, size=B).astype(np.int32)
         self.h_pos = torch.from_numpy(self.pos0.copy()).pin_memory()
         self.d_pos = torch.from_numpy(self.pos0.copy()).to(dev)
-        self.hctx = hkv.Context(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=ctx,
-                                             kernel_select=kernel, chunk_tiles=chunk_tiles))
+        self.ctxs = {}
+        for spec in dict.fromkeys(self.specs):
+            self.ctxs[spec] = hkv.Context(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD,
+                                                       slots=spec[0], window_size=spec[1], layout=spec[2],
+                                                       kernel_select=kernel, chunk_tiles=chunk_tiles))
+        self.hctx = self.ctxs[self.specs[0]]
         torch.cuda.synchronize()
+
+    def ctx_of(self, layer):
+        return self.ctxs[self.specs[layer]]
 
     def positions_at(self, step):
         return np.minimum(self.pos0 + step, self.ctx_len - 1)
@@ -175,69 +208,87 @@ class Workload:
         self.d_pos.add_(1).clamp_(max=self.ctx_len - 1)
 
     def step_device(self):
-        c = self.hctx
         for l in range(self.cfg["layers"]):
-            c.append_decode_attention(self.q[l], self.kn[l], self.vn[l], self.k[l], self.v[l], self.out[l],
-                                      self.d_pos, self.scale)
+            self.ctx_of(l).append_decode_attention(self.q[l], self.kn[l], self.vn[l], self.k[l], self.v[l],
+                                                   self.out[l], self.d_pos, self.scale)
         self.advance()
 
-    def algorithmic_bytes_per_layer(self, step):
+    def device_status(self):
+        return max(c.device_status() for c in self.ctxs.values())
+
+    def algorithmic_bytes_per_layer(self, step, layer=None):
         """Sum over sequences of 4*L*KVH*HD (read K and V) + 8*KVH*HD (new row in, row out)
-        + 4*H*HD (q in, out)."""
+        + 4*H*HD (q in, out); L = attended rows (window-limited on window layers). With
+        layer=None: mean over the layers."""
         H, KVH, HD = self.cfg["H"], self.cfg["KVH"], self.cfg["HD"]
-        Ls = self.positions_at(step).astype(np.int64) + 1
-        return int((4 * Ls * KVH * HD).sum() + self.B * (8 * KVH * HD + 4 * H * HD))
+        layers = range(self.cfg["layers"]) if layer is None else [layer]
+        tot = 0
+        for l in layers:
+            Ls = self.positions_at(step).astype(np.int64) + 1
+            if self.specs[l][1]:
+                Ls = np.minimum(Ls, self.specs[l][1])
+            tot += int((4 * Ls * KVH * HD).sum() + self.B * (8 * KVH * HD + 4 * H * HD))
+        return tot / len(layers)
+
+
+def _host_plane(w, oracle, name, layer, b, rows):
+    """Rows [0, rows) of sequence b of a layer's plane, regenerated on the CPU from the seed."""
+    KVH, HD = w.cfg["KVH"], w.cfg["HD"]
+    row = KVH * HD
+    slots = w.specs[layer][0]
+    return oracle.fill(w.seeds[name] ^ (layer << 8), (b * slots) * row, rows * row).reshape(1, rows, KVH, HD).copy()
 
 
 def verify(w: Workload, oracle, layer, seqs):
     """Full-size parity: regenerate the cache rows of (layer, b) on the CPU from the seed,
     append the new row, attend with the oracle, compare with the GPU's output."""
-    torch, cfg = w.torch, w.cfg
-    L, H, KVH, HD, ctx, B = cfg["layers"], cfg["H"], cfg["KVH"], cfg["HD"], w.ctx_len, w.B
+    cfg = w.cfg
+    H, KVH, HD, B = cfg["H"], cfg["KVH"], cfg["HD"], w.B
+    slots, window, layout = w.specs[layer]
     w.reset_positions()
-    w.hctx.append_decode_attention(w.q[layer], w.kn[layer], w.vn[layer], w.k[layer], w.v[layer],
-                                   w.out[layer], w.d_pos, w.scale)
-    status = w.hctx.device_status()
+    w.ctx_of(layer).append_decode_attention(w.q[layer], w.kn[layer], w.vn[layer], w.k[layer], w.v[layer],
+                                            w.out[layer], w.d_pos, w.scale)
+    status = w.ctx_of(layer).device_status()
     assert status == 0, f"device status word {status}"
     worst = 0.0
+    row = KVH * HD
     for b in seqs:
         pos = int(w.pos0[b])
-        row = KVH * HD
-        base = ((layer * B + b) * ctx) * row
-        kc = oracle.fill(w.seeds["k"], base, (pos + 1) * row).reshape(1, pos + 1, KVH, HD).copy()
-        vc = oracle.fill(w.seeds["v"], base, (pos + 1) * row).reshape(1, pos + 1, KVH, HD).copy()
+        rows = slots if layout == 1 else pos + 1
+        kc, vc = _host_plane(w, oracle, "k", layer, b, rows), _host_plane(w, oracle, "v", layer, b, rows)
         nb = (layer * B + b) * row
-        kc[0, pos] = oracle.fill(w.seeds["kn"], nb, row).reshape(KVH, HD)
-        vc[0, pos] = oracle.fill(w.seeds["vn"], nb, row).reshape(KVH, HD)
+        at = pos % slots if layout == 1 else pos
+        kc[0, at] = oracle.fill(w.seeds["kn"], nb, row).reshape(KVH, HD)
+        vc[0, at] = oracle.fill(w.seeds["vn"], nb, row).reshape(KVH, HD)
         q = oracle.fill(w.seeds["q"], (layer * B + b) * H * HD, H * HD).reshape(1, H, HD)
-        ref = oracle.decode(q, kc, vc, [pos + 1], w.scale, threads=oracle.hardware_threads())
+        ref = oracle.decode(q, kc, vc, [pos + 1], w.scale, window=window, layout=layout,
+                            threads=oracle.hardware_threads())
         got = w.out[layer, b].cpu().numpy()
         ok, err = oracle.within_tolerance(got, ref[0])
         assert ok, f"parity failed at layer {layer} seq {b}: max abs err {err:.3e}"
         # the appended row must be in the cache, bit-exact
-        assert np.array_equal(w.k[layer, b, pos].cpu().numpy().view(np.uint16), kc[0, pos].view(np.uint16))
-        assert np.array_equal(w.v[layer, b, pos].cpu().numpy().view(np.uint16), vc[0, pos].view(np.uint16))
+        assert np.array_equal(w.k[layer][b, at].cpu().numpy().view(np.uint16), kc[0, at].view(np.uint16))
+        assert np.array_equal(w.v[layer][b, at].cpu().numpy().view(np.uint16), vc[0, at].view(np.uint16))
         worst = max(worst, err)
     return worst
 
 
 def cpu_baseline(w: Workload, oracle, budget_s=12.0):
-    """Scalar CPU oracle on a bounded sample: whole sequences of ONE layer, all heads, all
-    host threads; tokens/s = sequences / (seconds * layers)."""
+    """Scalar CPU oracle on a bounded sample: whole (sequence, layer) units, all heads, all
+    host threads; tokens/s = units / (seconds * layers)."""
     cfg = w.cfg
-    H, KVH, HD, ctx, B = cfg["H"], cfg["KVH"], cfg["HD"], w.ctx_len, w.B
+    H, B = cfg["H"], w.B
     threads = oracle.hardware_threads()
-    row = KVH * HD
     done, secs, wall0 = 0, 0.0, time.perf_counter()
     for i in range(B * cfg["layers"]):
         l, b = divmod(i, B)
+        slots, window, layout = w.specs[l]
         pos = int(w.pos0[b])
-        base = ((l * B + b) * ctx) * row
-        kc = oracle.fill(w.seeds["k"], base, (pos + 1) * row).reshape(1, pos + 1, KVH, HD)
-        vc = oracle.fill(w.seeds["v"], base, (pos + 1) * row).reshape(1, pos + 1, KVH, HD)
-        q = oracle.fill(w.seeds["q"], (l * B + b) * H * HD, H * HD).reshape(1, H, HD)
+        rows = slots if layout == 1 else pos + 1
+        kc, vc = _host_plane(w, oracle, "k", l, b, rows), _host_plane(w, oracle, "v", l, b, rows)
+        q = oracle.fill(w.seeds["q"], (l * B + b) * H * cfg["HD"], H * cfg["HD"]).reshape(1, H, cfg["HD"])
         t0 = time.perf_counter()
-        oracle.decode(q, kc, vc, [pos + 1], w.scale, threads=threads)
+        oracle.decode(q, kc, vc, [pos + 1], w.scale, window=window, layout=layout, threads=threads)
         secs += time.perf_counter() - t0
         done += 1
         if secs > budget_s or time.perf_counter() - wall0 > 6 * budget_s:
@@ -255,7 +306,7 @@ def run_reference(args, torch, hkv, oracle, cfg, ctx, B, rank):
     ref = oracle.load_reference()
     if ref is None:
         return None
-    w = Workload(torch, hkv, cfg, ctx, B, rank)
+    w = Workload(torch, hkv, cfg, ctx, B, rank, linear_window=True)  # the reference has no ring layout
     L, H, KVH, HD = cfg["layers"], cfg["H"], cfg["KVH"], cfg["HD"]
     nl = max(1, min(args.ref_layers, L))
     d_total = (w.d_pos + 1).contiguous()
@@ -267,12 +318,12 @@ def run_reference(args, torch, hkv, oracle, cfg, ctx, B, rank):
         for l in range(nl):
             for b in range(B):
                 ref.hector_ref_kv_cache_update_dp(w.kn[l, b].data_ptr(), w.vn[l, b].data_ptr(),
-                                                  w.k[l, b].data_ptr(), w.v[l, b].data_ptr(), 1, 1, KVH, HD,
+                                                  w.k[l][b].data_ptr(), w.v[l][b].data_ptr(), 1, 1, KVH, HD,
                                                   ctx, w.d_pos.data_ptr() + 4 * b, stream)
-                ref.hector_ref_attention_cached_dp(w.q[l, b].data_ptr(), w.k[l, b].data_ptr(),
-                                                   w.v[l, b].data_ptr(), w.out[l, b].data_ptr(), 1,
-                                                   d_total.data_ptr() + 4 * b, H, KVH, HD, ctx, w.scale, 0,
-                                                   stream)
+                ref.hector_ref_attention_cached_dp(w.q[l, b].data_ptr(), w.k[l][b].data_ptr(),
+                                                   w.v[l][b].data_ptr(), w.out[l, b].data_ptr(), 1,
+                                                   d_total.data_ptr() + 4 * b, H, KVH, HD, ctx, w.scale,
+                                                   w.specs[l][1], stream)
         w.advance()
         torch.add(w.d_pos, 1, out=d_total)
 
@@ -458,7 +509,7 @@ def main():
     cfg = dict(WORKLOADS[args.workload])
     if args.layers:
         cfg["layers"] = args.layers
-    ctx = args.ctx
+    ctx = args.ctx or cfg.get("ctx", 32768)
     B = 1 if args.mode == "prefill" else pick_batch(torch, cfg, ctx, args.batch)
     n_gpus = world if args.impl != "reference" else 1
     try:
@@ -519,7 +570,7 @@ def main():
         return 0
 
     # ------------------------------------------------------------------ this library
-    w = Workload(torch, hkv, cfg, ctx, B, rank, args.kernel, args.chunk_tiles)
+    w = Workload(torch, hkv, cfg, ctx, B, rank, args.kernel, args.chunk_tiles, args.linear_window)
     L = cfg["layers"]
     verify_err = None
     if not args.no_verify:
@@ -533,7 +584,8 @@ def main():
     sampler = ClockSampler(gpu_id)
     barrier()
     sampler.start()
-    w.hctx.profile_begin(args.steps * L)
+    for c in w.ctxs.values():
+        c.profile_begin(args.steps * L)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
@@ -541,12 +593,16 @@ def main():
     e1.record()
     barrier()
     clocks = sampler.stop()
-    dec_ms, comb_ms, calls = w.hctx.profile_end()
+    dec_ms = comb_ms = 0.0
+    calls = 0
+    for c in w.ctxs.values():
+        d_, m_, n_ = c.profile_end()
+        dec_ms, comb_ms, calls = dec_ms + d_, comb_ms + m_, calls + n_
     ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
     if dist is not None:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms_per_step = float(ms.item()) / args.steps
-    status = w.hctx.device_status()
+    status = w.device_status()
     assert status == 0, f"device status word {status}"
     tok_s = B * n_gpus / (ms_per_step / 1e3)
 
@@ -582,7 +638,7 @@ def main():
         def e2e_step():
             w.d_pos.copy_(w.h_pos, non_blocking=True)  # this step's positions, host -> device
             for l in range(L):
-                w.hctx.append_decode_attention_host(hq[l], hk[l], hv[l], w.k[l], w.v[l], ho[l], w.d_pos, w.scale)
+                w.ctx_of(l).append_decode_attention_host(hq[l], hk[l], hv[l], w.k[l], w.v[l], ho[l], w.d_pos, w.scale)
             torch.cuda.current_stream().synchronize()   # the step's result is now readable on the host
             w.h_pos.add_(1).clamp_(max=ctx - 1)
 

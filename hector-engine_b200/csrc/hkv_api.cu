@@ -499,8 +499,10 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
         } else {
             if (!encode_tiled_fn()) return fail(c, HKV_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
             TmaKernel kern = pick_tma(geometry->head_dim, (c->G + 7) / 8, c->tma_groups);
+            // the attribute belongs to the kernel, not to this context: keep it at the device
+            // maximum so that contexts with different plans never lower it for each other
             e = cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)c->plan.bytes);
+                                     (int)c->smem_optin);
             if (e != cudaSuccess) return fail_cuda(c, e, "cudaFuncSetAttribute(shared memory)");
         }
     }

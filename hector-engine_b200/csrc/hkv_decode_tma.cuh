@@ -55,6 +55,12 @@ inline TmaSmemPlan tma_plan(int HD, int G, int ncw, int B, size_t budget) {
                          2 * kMaxStages * 8 + (size_t)(B + 1) * 4 + 64;
     int s = (int)((budget > fixed ? budget - fixed : 0) / stage);
     if (s > kMaxStages) s = kMaxStages;
+    // Tile i of a CTA's stream uses stage i % stages and belongs to consumer group
+    // i % groups. The stage count must be a multiple of the group count so that a stage
+    // (and its full barrier) always serves the same group: otherwise a group could run a
+    // whole barrier phase ahead of the other and a parity wait would pass on stale data.
+    const int groups = ncw / 4;
+    s -= s % groups;
     return TmaSmemPlan{s, fixed + (size_t)s * stage};
 }
 
