@@ -70,6 +70,8 @@ def parse_args():
                          "sequence's cache split block-cyclically over the GPUs, partials all-gathered "
                          "over NCCL; --ctx is then the rows per sequence PER GPU")
     ap.add_argument("--shard-block", type=int, default=1024)
+    ap.add_argument("--graph", action="store_true",
+                    help="also time the step as ONE captured CUDA graph replayed --steps times (adds graph_replay)")
     ap.add_argument("--linear-window", action="store_true",
                     help="window layers keep a linear plane + mask (the reference's layout) instead of a ring")
     return ap.parse_args()
@@ -593,6 +595,28 @@ def main():
     e1.record()
     barrier()
     clocks = sampler.stop()
+    graph_ms = None
+    if args.graph:
+        # The engine's own contract: the whole step captured ONCE, then replayed while only the
+        # device positions change (src/engine.cpp:151-269 of the reference). Timed separately:
+        # per-kernel events cannot be recorded inside a captured graph.
+        w.reset_positions()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side, capture_error_mode="global"):
+                w.step_device()
+            for _ in range(args.warmup):
+                graph.replay()
+            side.synchronize()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record(side)
+            for _ in range(args.steps):
+                graph.replay()
+            g1.record(side)
+            side.synchronize()
+        graph_ms = g0.elapsed_time(g1) / args.steps
     dec_ms = comb_ms = 0.0
     calls = 0
     for c in w.ctxs.values():
@@ -668,6 +692,9 @@ def main():
                     gpu_launches=args.steps * L * w.hctx.launches_per_decode, roofline=roofline,
                     cpu_baseline=cpu, hbm_gbs_step=step_gbs, hbm_frac_of_8TBs_step=step_gbs / 8000.0,
                     parity_max_abs_err=verify_err)
+        if graph_ms is not None:
+            line["graph_replay"] = {"ms_per_step": graph_ms, "value": B * n_gpus / (graph_ms / 1e3), "unit": "tokens/s",
+                                    "hbm_gbs_step": alg_bytes * L / (graph_ms * 1e-3) / 1e9}
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

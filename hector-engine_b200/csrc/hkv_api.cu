@@ -141,8 +141,13 @@ bool tma_geometry_ok(const hkv_geometry& g) {
 int auto_chunk_tiles(const hkv_geometry& g, int sm_count) {
     int rows = g.slots;
     if (g.window_size > 0 && g.window_size < rows) rows = g.window_size + kTileRows;
-    const long long tiles = (long long)g.batch * g.num_kv_heads * ((rows + kTileRows - 1) / kTileRows);
-    long long ct = tiles / ((long long)sm_count * 8);
+    // Work items of `ct` tiles: about four items per SM keeps the persistent CTAs balanced while
+    // the per-item cost (query fragments, warp merge, partial row) stays amortised; at most 128
+    // partials per sequence bounds the serial merge loop of the combine kernel.
+    const long long per_seq = (rows + kTileRows - 1) / kTileRows;
+    const long long tiles = (long long)g.batch * g.num_kv_heads * per_seq;
+    long long ct = tiles / ((long long)sm_count * 4);
+    if (ct < (per_seq + 127) / 128) ct = (per_seq + 127) / 128;
     if (ct < 1) ct = 1;
     if (ct > 16) ct = 16;
     return (int)ct;
