@@ -787,6 +787,15 @@ int hkv_ctx_profile_end(hkv_ctx* c, void* stream, float* decode_ms, float* combi
     return HKV_OK;
 }
 
+int hkv_ctx_selftest_bounded_wait(hkv_ctx* c, int32_t limit_ms, void* stream) {
+    HKV_CHECK_CTX(c);
+    if (limit_ms <= 0 || limit_ms > 1000) return fail(c, HKV_ERR_INVALID_ARG, "selftest: limit must be 1..1000 ms");
+    hkv_selftest_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(c->d_status, (unsigned long long)limit_ms * 1000000ull,
+                                                                nullptr);
+    const cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "selftest launch");
+}
+
 int32_t hkv_slot_of_position(const hkv_geometry* g, int32_t pos) {
     const char* why;
     if (validate_geometry(g, &why) != HKV_OK) return -1;

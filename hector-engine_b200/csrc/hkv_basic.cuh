@@ -227,6 +227,26 @@ __global__ void __launch_bounds__(128) hkv_combine_kernel(const CombineArgs a) {
 }
 
 // ---------------------------------------------------------------------------
+// Self-test of the bounded wait: one CTA waits on an mbarrier that nothing ever arrives on.
+// The wait must run out after `limit_ns`, set the status word and let the kernel return
+// normally, so the host can see how a lost producer would surface. No trap, no endless loop.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(32) hkv_selftest_wait_kernel(int32_t* status, unsigned long long limit_ns,
+                                                               int32_t* waited_ok) {
+    __shared__ uint64_t bar;
+    const uint32_t b = smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        mbar_init(b, 1);
+        fence_mbar_init();
+    }
+    __syncwarp();
+    if (threadIdx.x == 0) {
+        const bool ok = mbar_wait(b, 0, status, limit_ns);  // phase 0 never completes
+        if (waited_ok) *waited_ok = ok ? 1 : 0;
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Synthetic data (same bits as the CPU generator of the test oracle): the sum of
 // twelve 16-bit uniform fields of three splitmix64 outputs, centred and scaled by an
 // exact power of two (Irwin-Hall(12): mean 0, variance 1), rounded RN to fp16.

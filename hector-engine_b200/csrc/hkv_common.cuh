@@ -150,9 +150,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after ~2 s of wall time, records it in the status word and
+// Bounded wait: gives up after `limit_ns` (2 s by default) of wall time, records it in the status word and
 // returns false so the caller can leave its loops; the context stays usable.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t* status) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t* status,
+                                          unsigned long long limit_ns = 2000000000ull) {
     if (mbar_try_wait(bar, parity)) return true;
     unsigned long long t0 = 0;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
@@ -161,7 +162,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t
             if (mbar_try_wait(bar, parity)) return true;
         unsigned long long t1;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-        if (t1 - t0 > 2000000000ull) break;
+        if (t1 - t0 > limit_ns) break;
     }
     atomicOr(status, kStatusWaitRanOut);
     return false;

@@ -116,6 +116,10 @@ class Context:
             self._check(st)
         return out.value
 
+    def selftest_bounded_wait(self, limit_ms: int = 50, stream=None):
+        """Enqueues the bounded-wait self-test (a wait nothing satisfies); see device_status()."""
+        self._check(self.lib.hkv_ctx_selftest_bounded_wait(self._h, limit_ms, _stream(stream)))
+
     def profile_begin(self, max_calls: int):
         self._check(self.lib.hkv_ctx_profile_begin(self._h, max_calls))
 

@@ -199,6 +199,16 @@ int hkv_append_decode_attention_host(hkv_ctx* ctx, const void* h_q, const void* 
                                      void* h_out, const int32_t* d_cache_pos, float scale,
                                      void* stream);
 
+/* ---- failure reporting self-test ---------------------------------------------------- */
+
+/* Enqueues a one-warp kernel that waits, with the library's bounded wait, on a barrier that
+ * nothing ever signals. After `limit_ms` (1..1000) the wait gives up, sets bit 1 of the
+ * device status word and the kernel returns normally: hkv_ctx_device_status then reports
+ * HKV_ERR_DEVICE_FAULT with status 1 and clears it, and the context stays usable. This is how
+ * a lost producer inside the pipelined kernels surfaces: as a status, never as a hang or a
+ * trap. No counterpart in the reference (its kernels have no device-side waits). */
+int hkv_ctx_selftest_bounded_wait(hkv_ctx* ctx, int32_t limit_ms, void* stream);
+
 /* ---- per-kernel timing (benchmarks; not capturable) -------------------------------- */
 
 /* After hkv_ctx_profile_begin every decode call records CUDA events on its stream before
