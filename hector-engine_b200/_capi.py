@@ -55,6 +55,7 @@ SIGNATURES = {
     "hkv_decode_partials": (C.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, _F32P, _I32P, C.c_float, _VP]),
     "hkv_combine_partials": (C.c_int, [_VP, _F32P, C.c_int32, _VP, _VP]),
     "hkv_append_decode_attention_host": (C.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I32P, C.c_float, _VP]),
+    "hkv_qk_norm_rope_kv": (C.c_int, [_VP] * 8 + [_I32P, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_float, C.c_float, _VP]),
     "hkv_ctx_selftest_bounded_wait": (C.c_int, [_VP, C.c_int32, _VP]),
     "hkv_ctx_profile_begin": (C.c_int, [_VP, C.c_int32]),
     "hkv_ctx_profile_end": (C.c_int, [_VP, _VP, C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_int32)]),

@@ -21,6 +21,7 @@
 #include "hkv_decode_tma.cuh"
 #include "hkv_prefill.cuh"
 #include "hkv_prefill_tc.cuh"
+#include "hkv_rope.cuh"
 
 using namespace hkv;
 
@@ -785,6 +786,52 @@ int hkv_ctx_profile_end(hkv_ctx* c, void* stream, float* decode_ms, float* combi
     c->prof_max = 0;
     c->prof_calls = 0;
     return HKV_OK;
+}
+
+int hkv_qk_norm_rope_kv(hkv_ctx* c, void* q, void* k, const void* v, const void* q_norm_w,
+                        const void* k_norm_w, void* k_cache, void* v_cache, const int32_t* d_cache_pos,
+                        int32_t position, int32_t seq_new, int32_t rotary_dim, float eps, float theta,
+                        float scaling_factor, void* stream) {
+    HKV_CHECK_CTX(c);
+    if (!q || !k || !q_norm_w || !k_norm_w) return fail(c, HKV_ERR_INVALID_ARG, "qk_norm_rope: null tensor");
+    if ((k_cache == nullptr) != (v_cache == nullptr) || (k_cache && !v))
+        return fail(c, HKV_ERR_INVALID_ARG, "qk_norm_rope: k_cache, v_cache and v go together");
+    if (seq_new < 0 || (!d_cache_pos && position < 0)) return fail(c, HKV_ERR_INVALID_ARG, "qk_norm_rope: negative size");
+    if (!aligned(q, 2) || !aligned(k, 2) || !aligned(v, 2) || !aligned(k_cache, 2) || !aligned(v_cache, 2) ||
+        !aligned(q_norm_w, 2) || !aligned(k_norm_w, 2))
+        return fail(c, HKV_ERR_ALIGNMENT, "qk_norm_rope: fp16 pointer not 2-byte aligned");
+    if (seq_new == 0) return HKV_OK;
+    const hkv_geometry& g = c->g;
+    RopeArgs a;
+    a.q = (__half*)q;
+    a.k = (__half*)k;
+    a.v = (const __half*)v;
+    a.q_w = (const __half*)q_norm_w;
+    a.k_w = (const __half*)k_norm_w;
+    a.k_cache = (__half*)k_cache;
+    a.v_cache = (__half*)v_cache;
+    a.d_pos = d_cache_pos;
+    a.host_pos = position;
+    a.map = c->map;
+    a.B = g.batch;
+    a.S = seq_new;
+    a.H = g.num_heads;
+    a.KVH = g.num_kv_heads;
+    a.HD = g.head_dim;
+    // same defaults as the reference launcher (kernels/attention.cu:955-956)
+    a.rot = rotary_dim <= 0 ? g.head_dim : (rotary_dim / 2) * 2;
+    if (a.rot > g.head_dim) return fail(c, HKV_ERR_INVALID_ARG, "qk_norm_rope: rotary_dim exceeds head_dim");
+    a.batch_stride = c->batch_stride;
+    a.eps = eps;
+    a.theta = theta;
+    a.scaling = scaling_factor <= 0.0f ? 1.0f : scaling_factor;
+    const long long units = (long long)g.batch * seq_new * (g.num_heads + 2 * g.num_kv_heads);
+    long long blocks = (units + kRopeWarps - 1) / kRopeWarps;
+    const long long cap = (long long)c->sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    hkv_qk_norm_rope_kernel<<<(unsigned)blocks, kRopeWarps * 32, 0, (cudaStream_t)stream>>>(a);
+    const cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "qk_norm_rope launch");
 }
 
 int hkv_ctx_selftest_bounded_wait(hkv_ctx* c, int32_t limit_ms, void* stream) {

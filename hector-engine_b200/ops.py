@@ -168,6 +168,15 @@ class Context:
         self._check(self.lib.hkv_prefill_attention(self._h, _ptr(q), _ptr(k_cache), _ptr(v_cache),
                                                    _ptr(out), seq_new, past_len, scale, _stream(stream)))
 
+    def qk_norm_rope_kv(self, q, k, v, q_norm_w, k_norm_w, k_cache=None, v_cache=None, d_cache_pos=None,
+                        position=0, seq_new=1, rotary_dim=0, eps=1e-6, theta=10000.0, scaling_factor=1.0,
+                        stream=None):
+        """Per-head RMSNorm(q, k) + RoPE, K/V written into the cache when planes are given
+        (reference launch_qk_norm_rope_kv_fp16, kernels/attention.cu:947-973)."""
+        self._check(self.lib.hkv_qk_norm_rope_kv(
+            self._h, _ptr(q), _ptr(k), _ptr(v), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(k_cache), _ptr(v_cache),
+            _ptr(d_cache_pos), position, seq_new, rotary_dim, eps, theta, scaling_factor, _stream(stream)))
+
     def decode_partials(self, q, k_new, v_new, k_cache, v_cache, partial_out, d_total_seq,
                         scale=None, stream=None):
         scale = self.geometry.default_scale if scale is None else scale

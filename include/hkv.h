@@ -199,6 +199,23 @@ int hkv_append_decode_attention_host(hkv_ctx* ctx, const void* h_q, const void* 
                                      void* h_out, const int32_t* d_cache_pos, float scale,
                                      void* stream);
 
+/* ---- the step in front of the append (next row of the path) ------------------------ */
+
+/* Per-head RMSNorm of q and k + rotary embedding; with cache planes given, the rotated K and
+ * the V row are written straight into the cache at the device position (k itself is then left
+ * untouched), so the separate append disappears. Replaces launch_qk_norm_rope_kv_fp16,
+ * launch_qk_norm_rope_fp16 and launch_qk_norm_rope_fp16_dp (kernels/attention.cu:908-973,
+ * declared kernels/kernels.hpp:331-352).
+ *   q [batch, seq_new, num_heads, head_dim] in place; k, v [batch, seq_new, num_kv_heads, head_dim];
+ *   q_norm_w, k_norm_w [head_dim]; k_cache / v_cache may both be NULL (then k is rewritten in
+ *   place and v is ignored). Position of token s of sequence b = d_cache_pos[b] + s, or
+ *   `position` + s when d_cache_pos is NULL. rotary_dim <= 0 means head_dim; scaling_factor <= 0
+ *   means 1 (kernels/attention.cu:955-956). */
+int hkv_qk_norm_rope_kv(hkv_ctx* ctx, void* q, void* k, const void* v, const void* q_norm_w,
+                        const void* k_norm_w, void* k_cache, void* v_cache, const int32_t* d_cache_pos,
+                        int32_t position, int32_t seq_new, int32_t rotary_dim, float eps, float theta,
+                        float scaling_factor, void* stream);
+
 /* ---- failure reporting self-test ---------------------------------------------------- */
 
 /* Enqueues a one-warp kernel that waits, with the library's bounded wait, on a barrier that

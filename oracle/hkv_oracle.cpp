@@ -11,6 +11,7 @@
 //   prefill-cached    kernels/attention.cu:664-773    (attention_prefill_cached_kernel)
 //   op defaults       kernels/register_kernels.cpp:851-861, src/command.cpp:160
 //   cache layouts     src/kv_cache.hpp:175-199, src/gemma4_kv_cache.hpp:39-114
+//   QK-norm + RoPE    kernels/attention.cu:800-906 (with K/V cache write: :947-973)
 //
 // Parity pinning: the known-answer cases of the reference's own hot-path test
 // (tests/test_gemma4_kv.cu:110-347) are replayed against this file by the CPU test
@@ -317,6 +318,61 @@ void hkv_oracle_prefill(const uint16_t* q, const uint16_t* k_cache, const uint16
         attend_exact(q + o, k_cache, v_cache, out + o, out_f32 ? out_f32 + o : nullptr,
                      past_len + qi + 1, g, h);
     });
+}
+
+// Fused per-head RMSNorm(q, k) + RoPE with optional K/V cache write
+// (kernels/attention.cu:800-906, launcher :947-973). q: [B, S, H, HD] in place. k: [B, S, KVH, HD]:
+// with a cache the normalised + rotated K goes to the cache row pos[b] + s (k itself untouched)
+// and v is copied beside it; without a cache (k_cache null) k is rewritten in place.
+// x_norm[i] = x[i] * rsqrt(mean(x^2) + eps) * w[i]; pairs (i, i + rot/2) for i < rot/2 are rotated
+// by angle = ((s + pos) / scaling) / theta^(2i/rot); dims >= rot pass through normalised.
+// Rows whose position falls outside the plane are dropped (layout 0) or wrap (layout 1).
+void hkv_oracle_qk_norm_rope(uint16_t* q, uint16_t* k, const uint16_t* v, const uint16_t* q_w,
+                             const uint16_t* k_w, uint16_t* k_cache, uint16_t* v_cache, int B, int S,
+                             int H, int KVH, int HD, int rotary_dim, const int32_t* pos, int slots,
+                             int layout, float eps, float theta, float scaling) {
+    if (rotary_dim <= 0) rotary_dim = HD;
+    if (scaling <= 0.0f) scaling = 1.0f;
+    const int half_rot = rotary_dim / 2;
+    std::vector<float> x((size_t)HD), y((size_t)HD);
+    auto one = [&](const uint16_t* src, uint16_t* dst, const uint16_t* w, int p) {
+        float ssq = 0.0f;
+        for (int i = 0; i < HD; ++i) { x[i] = h2f(src[i]); ssq += x[i] * x[i]; }
+        const float inv = 1.0f / std::sqrt(ssq / (float)HD + eps);
+        for (int i = 0; i < HD; ++i) x[i] = x[i] * inv * h2f(w[i]);
+        const float fp = (float)p / scaling;
+        for (int i = 0; i < HD; ++i) y[i] = x[i];
+        for (int i = 0; i < half_rot; ++i) {
+            const float freq = 1.0f / std::pow(theta, (float)(2 * i) / (float)rotary_dim);
+            const float ang = fp * freq;
+            const float c = std::cos(ang), sn = std::sin(ang);
+            y[i] = x[i] * c - x[i + half_rot] * sn;
+            y[i + half_rot] = x[i] * sn + x[i + half_rot] * c;
+        }
+        for (int i = 0; i < HD; ++i) dst[i] = f2h(y[i]);
+    };
+    for (int b = 0; b < B; ++b)
+        for (int s = 0; s < S; ++s) {
+            const int p = pos[b] + s;
+            for (int h = 0; h < H; ++h) {
+                uint16_t* qp = q + (((int64_t)b * S + s) * H + h) * HD;
+                one(qp, qp, q_w, p);
+            }
+            int64_t row = p;
+            bool stored = true;
+            if (k_cache) {
+                if (layout == 1) row = p % slots;
+                else if (p >= slots || p < 0) stored = false;
+            }
+            for (int h = 0; h < KVH; ++h) {
+                uint16_t* kp = k + (((int64_t)b * S + s) * KVH + h) * HD;
+                if (!k_cache) { one(kp, kp, k_w, p); continue; }
+                if (!stored) continue;
+                const int64_t dst = (((int64_t)b * slots + row) * KVH + h) * HD;
+                one(kp, k_cache + dst, k_w, p);
+                std::memcpy(v_cache + dst, v + (((int64_t)b * S + s) * KVH + h) * HD, (size_t)HD * 2);
+            }
+        }
 }
 
 // Heterogeneous / shared KV layout (src/gemma4_kv_cache.hpp:39-114). Inputs per layer:

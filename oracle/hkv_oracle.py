@@ -45,6 +45,9 @@ def load() -> C.CDLL:
     lib.hkv_oracle_prefill.argtypes = [_u16p, _u16p, _u16p, _u16p, C.c_void_p, C.c_int, C.c_int,
                                        C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int,
                                        C.c_int, C.c_int, C.c_int]
+    lib.hkv_oracle_qk_norm_rope.argtypes = [_u16p, _u16p, C.c_void_p, _u16p, _u16p, C.c_void_p, C.c_void_p,
+                                            C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _i32p,
+                                            C.c_int, C.c_int, C.c_float, C.c_float, C.c_float]
     lib.hkv_oracle_gemma4_layout.restype = C.c_int64
     lib.hkv_oracle_gemma4_layout.argtypes = [C.c_int, C.c_int, _i32p, _i32p, C.c_int, C.c_int, C.c_int,
                                              C.c_int, _i32p, _i64p, _i32p]
@@ -105,6 +108,22 @@ def prefill(q, k_cache, v_cache, past_len, scale, window=0, q_begin=0, q_end=Non
     return out.view(np.float16)
 
 
+def qk_norm_rope(q, k, v, q_w, k_w, pos, k_cache=None, v_cache=None, rotary_dim=0, layout=0, eps=1e-6,
+                 theta=10000.0, scaling=1.0):
+    """In place: q [B,S,H,HD] normalised + rotated; k [B,S,KVH,HD] either rewritten in place
+    (no cache) or written, with v, into k_cache / v_cache [B, slots, KVH, HD] at pos[b] + s."""
+    B, S, H, HD = q.shape
+    KVH = k.shape[2]
+    qv, kv = as_u16(q), as_u16(k)
+    assert np.shares_memory(qv, q) and np.shares_memory(kv, k)
+    slots = k_cache.shape[1] if k_cache is not None else 0
+    kc = as_u16(k_cache).ctypes.data if k_cache is not None else None
+    vc = as_u16(v_cache).ctypes.data if v_cache is not None else None
+    vv = as_u16(v).ctypes.data if v is not None else None
+    load().hkv_oracle_qk_norm_rope(qv, kv, vv, as_u16(q_w), as_u16(k_w), kc, vc, B, S, H, KVH, HD, rotary_dim,
+                                   np.ascontiguousarray(pos, dtype=np.int32), slots, layout, eps, theta, scaling)
+
+
 def gemma4_layout(head_dim, is_global, shared, kvh, batch, max_seq, ring_window=0):
     n = len(head_dim)
     source = np.zeros(n, dtype=np.int32)
@@ -145,5 +164,8 @@ def load_reference():
     lib.hector_ref_attention_cached.argtypes = [vp, vp, vp, vp] + [C.c_int] * 6 + [C.c_float, C.c_int, vp]
     lib.hector_ref_attention_cached_dp.argtypes = [vp, vp, vp, vp, C.c_int, vp] + [C.c_int] * 4 + [C.c_float, C.c_int, vp]
     lib.hector_ref_attention_prefill_cached.argtypes = [vp, vp, vp, vp] + [C.c_int] * 6 + [C.c_float, C.c_int, vp]
+    if hasattr(lib, "hector_ref_qk_norm_rope_kv"):
+        lib.hector_ref_qk_norm_rope.argtypes = [vp, vp, vp, vp] + [C.c_int] * 7 + [C.c_float] * 3 + [vp]
+        lib.hector_ref_qk_norm_rope_kv.argtypes = ([vp] * 7 + [C.c_int] * 7 + [vp, C.c_int] + [C.c_float] * 3 + [vp])
     _ref = lib
     return lib

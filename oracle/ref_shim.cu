@@ -34,6 +34,16 @@ void launch_attention_prefill_cached_fp16(const half* q, const half* k_cache, co
                                           half* output, int seq_new, int past_len, int num_heads,
                                           int num_kv_heads, int head_dim, int max_seq_len,
                                           float scale, int window_size, cudaStream_t stream);
+// kernels/kernels.hpp:331-352
+void launch_qk_norm_rope_fp16(half* q, half* k, const half* q_norm_w, const half* k_norm_w, int batch_size,
+                              int seq_len, int num_heads, int num_kv_heads, int head_dim, int rotary_dim,
+                              int position_offset, float eps, float theta, float scaling_factor,
+                              cudaStream_t stream);
+void launch_qk_norm_rope_kv_fp16(half* q, half* k, const half* v, const half* q_norm_w, const half* k_norm_w,
+                                 half* k_cache, half* v_cache, int batch_size, int seq_len, int num_heads,
+                                 int num_kv_heads, int head_dim, int rotary_dim, int position_offset,
+                                 const int32_t* d_position_offset, int max_seq_len, float eps, float theta,
+                                 float scaling_factor, cudaStream_t stream);
 }  // namespace kernels
 }  // namespace helios
 
@@ -41,7 +51,27 @@ using namespace helios::kernels;
 
 extern "C" {
 
-int hector_ref_abi_version() { return 1; }
+int hector_ref_abi_version() { return 2; }
+
+int hector_ref_qk_norm_rope(void* q, void* k, const void* qw, const void* kw, int batch, int seq_len,
+                            int num_heads, int num_kv_heads, int head_dim, int rotary_dim, int position,
+                            float eps, float theta, float scaling, void* stream) {
+    launch_qk_norm_rope_fp16((half*)q, (half*)k, (const half*)qw, (const half*)kw, batch, seq_len, num_heads,
+                             num_kv_heads, head_dim, rotary_dim, position, eps, theta, scaling,
+                             (cudaStream_t)stream);
+    return (int)cudaGetLastError();
+}
+
+int hector_ref_qk_norm_rope_kv(void* q, void* k, const void* v, const void* qw, const void* kw, void* k_cache,
+                               void* v_cache, int batch, int seq_len, int num_heads, int num_kv_heads,
+                               int head_dim, int rotary_dim, int position, const int32_t* d_position,
+                               int max_seq_len, float eps, float theta, float scaling, void* stream) {
+    launch_qk_norm_rope_kv_fp16((half*)q, (half*)k, (const half*)v, (const half*)qw, (const half*)kw,
+                                (half*)k_cache, (half*)v_cache, batch, seq_len, num_heads, num_kv_heads,
+                                head_dim, rotary_dim, position, d_position, max_seq_len, eps, theta, scaling,
+                                (cudaStream_t)stream);
+    return (int)cudaGetLastError();
+}
 
 int hector_ref_kv_cache_update(const void* new_k, const void* new_v, void* k_cache, void* v_cache,
                                int batch, int seq_len, int kv_heads, int head_dim, int max_seq_len,
