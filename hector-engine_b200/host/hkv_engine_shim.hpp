@@ -32,6 +32,7 @@ namespace op {
 inline OpTypeID ATTENTION_CACHED() { return 1; }
 inline OpTypeID KV_CACHE_UPDATE() { return 2; }
 inline OpTypeID ATTENTION_PREFILL_CACHED() { return 3; }
+inline OpTypeID QK_NORM_ROPE() { return 4; }
 }  // namespace op
 
 enum class DType { INVALID, FP16, FP32, INT32 };

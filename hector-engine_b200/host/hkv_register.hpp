@@ -5,6 +5,7 @@
 //   ATTENTION_CACHED           kernels/register_kernels.cpp:841-887
 //   ATTENTION_PREFILL_CACHED   kernels/register_kernels.cpp:891-921
 //   KV_CACHE_UPDATE            kernels/register_kernels.cpp:924-980
+//   QK_NORM_ROPE               kernels/register_kernels.cpp:777-837 (the step in front of the append)
 // i.e. the same input order, parameter keys and defaults, the same geometry guard and
 // dtype check, std::runtime_error for every failure, work enqueued only on ctx.stream.
 // ATTENTION_CACHED additionally accepts the five-input form (Q, K_cache, V_cache, K_new,
@@ -18,6 +19,7 @@
 //       static uint32_t attention_cached()         { return helios::op::ATTENTION_CACHED(); }
 //       static uint32_t kv_cache_update()          { return helios::op::KV_CACHE_UPDATE(); }
 //       static uint32_t attention_prefill_cached() { return helios::op::ATTENTION_PREFILL_CACHED(); }
+//       static uint32_t qk_norm_rope()             { return helios::op::QK_NORM_ROPE(); }
 //       static bool is_fp16(const TensorInfo& t)   { return t.dtype == helios::dtype::FP16(); }
 //       static const char* dtype_name(const TensorInfo& t) { return helios::dtype_name(t.dtype); }
 //   };
@@ -137,6 +139,49 @@ public:
             ContextPool::check(c, hkv_prefill_attention(c, fp16(q), fp16(k_cache), fp16(v_cache), fp16(output),
                                                         (int32_t)seq_new, (int32_t)past_len, scale, ctx.stream),
                                "ATTENTION_PREFILL_CACHED");
+        });
+
+        // QK_NORM_ROPE (kernels/register_kernels.cpp:777-837): inputs q, k, q_norm_w, k_norm_w and,
+        // in the fused form, v, k_cache, v_cache; the fused form also writes the cache.
+        engine.register_kernel(Bind::qk_norm_rope(), [pool, eng](ExecContext& ctx, const Command& cmd) {
+            TensorInfo* q = ctx.in(0);
+            TensorInfo* k = ctx.in(1);
+            TensorInfo* qw = ctx.in(2);
+            TensorInfo* kw = ctx.in(3);
+            if (!q || !k || !qw || !kw) throw std::runtime_error("QK_NORM_ROPE: missing tensors");
+            const uint32_t H = cmd.template get<uint32_t>("num_heads", 32);
+            const uint32_t KVH = cmd.template get<uint32_t>("num_kv_heads", H);
+            const uint32_t HD = cmd.template get<uint32_t>("dim", 128);
+            const uint32_t seq_len = cmd.template get<uint32_t>("seq_len", 1);
+            const uint32_t offset = cmd.template get<uint32_t>("offset", 0);
+            const float eps = cmd.template get<float>("eps", 1e-6f);
+            const float theta = cmd.template get<float>("theta", 10000.0f);
+            const float partial_rotary = cmd.template get<float>("partial_rotary", 1.0f);
+            const float scaling_factor = cmd.template get<float>("rope_scaling_factor", 1.0f);
+            int rotary_dim = (int)(HD * partial_rotary);
+            rotary_dim = (rotary_dim / 2) * 2;
+            if (rotary_dim <= 0) rotary_dim = (int)HD;
+            if (HD == 0 || HD > 512 || KVH == 0 || H == 0 || H % KVH != 0)
+                throw std::runtime_error("QK_NORM_ROPE: unsupported head geometry");
+            const bool dev_pos = cmd.template get<uint32_t>("device_pos", 0) && eng->has_device_cache_pos();
+            const uint32_t max_seq_len = cmd.template get<uint32_t>("max_seq_len", 4096);
+            hkv_geometry g = geometry(1, H, KVH, HD, max_seq_len, 0);
+            hkv_ctx* c = pool->get(g);
+            void *v = nullptr, *kc = nullptr, *vc = nullptr;
+            if (ctx.num_inputs() >= 7) {
+                TensorInfo* tv = ctx.in(4);
+                TensorInfo* tkc = ctx.in(5);
+                TensorInfo* tvc = ctx.in(6);
+                if (!tv || !tkc || !tvc) throw std::runtime_error("QK_NORM_ROPE: missing kv cache tensors");
+                v = fp16(tv);
+                kc = fp16(tkc);
+                vc = fp16(tvc);
+            }
+            ContextPool::check(c, hkv_qk_norm_rope_kv(c, fp16(q), fp16(k), v, fp16(qw), fp16(kw), kc, vc,
+                                                      dev_pos ? eng->device_cache_pos() : nullptr, (int32_t)offset,
+                                                      (int32_t)seq_len, rotary_dim, eps, theta, scaling_factor,
+                                                      ctx.stream),
+                               "QK_NORM_ROPE");
         });
 
         engine.register_kernel(Bind::kv_cache_update(), [pool, eng](ExecContext& ctx, const Command& cmd) {

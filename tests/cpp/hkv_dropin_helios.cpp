@@ -47,6 +47,7 @@ struct HeliosBind {
     static uint32_t attention_cached() { return helios::op::ATTENTION_CACHED(); }
     static uint32_t kv_cache_update() { return helios::op::KV_CACHE_UPDATE(); }
     static uint32_t attention_prefill_cached() { return helios::op::ATTENTION_PREFILL_CACHED(); }
+    static uint32_t qk_norm_rope() { return helios::op::QK_NORM_ROPE(); }
     static bool is_fp16(const TensorInfo& t) { return t.dtype == helios::dtype::FP16(); }
     static const char* dtype_name(const TensorInfo& t) { return helios::dtype_name(t.dtype); }
 };

@@ -30,6 +30,10 @@ void hkv_oracle_append(const uint16_t* new_k, const uint16_t* new_v, uint16_t* k
 void hkv_oracle_decode(const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache, uint16_t* out,
                        float* out_f32, int B, const int32_t* total, int H, int KVH, int HD, int slots,
                        int64_t batch_stride, float scale, int window, int layout, int mode, int threads);
+void hkv_oracle_qk_norm_rope(uint16_t* q, uint16_t* k, const uint16_t* v, const uint16_t* q_w, const uint16_t* k_w,
+                             uint16_t* k_cache, uint16_t* v_cache, int B, int S, int H, int KVH, int HD,
+                             int rotary_dim, const int32_t* pos, int slots, int layout, float eps, float theta,
+                             float scaling);
 }
 
 namespace sh = hkv_shim;
@@ -42,6 +46,7 @@ struct ShimBind {
     static uint32_t attention_cached() { return sh::op::ATTENTION_CACHED(); }
     static uint32_t kv_cache_update() { return sh::op::KV_CACHE_UPDATE(); }
     static uint32_t attention_prefill_cached() { return sh::op::ATTENTION_PREFILL_CACHED(); }
+    static uint32_t qk_norm_rope() { return sh::op::QK_NORM_ROPE(); }
     static bool is_fp16(const TensorInfo& t) { return t.dtype == sh::DType::FP16; }
     static const char* dtype_name(const TensorInfo& t) { return sh::dtype_name(t.dtype); }
 };
@@ -263,6 +268,48 @@ static void test_error_behaviour() {
     std::printf("PASS: error behaviour (missing tensors, dtype, geometry, typed params)\n");
 }
 
+// QK_NORM_ROPE in its fused seven-input form (writes the cache), device position.
+static void test_qk_norm_rope_op() {
+    const int H = 8, KVH = 2, HD = 128, S = 256, pos = 37;
+    sh::Engine engine;
+    hkv::Registration<ShimBind> ops(engine);
+    engine.alloc_device_cache_pos();
+    auto& T = engine.tensors();
+    T.allocate_and_register("q", {1, 1, (uint32_t)(H * HD)}, sh::DType::FP16);
+    T.allocate_and_register("k", {1, 1, (uint32_t)(KVH * HD)}, sh::DType::FP16);
+    T.allocate_and_register("v", {1, 1, (uint32_t)(KVH * HD)}, sh::DType::FP16);
+    T.allocate_and_register("qw", {(uint32_t)HD}, sh::DType::FP16);
+    T.allocate_and_register("kw", {(uint32_t)HD}, sh::DType::FP16);
+    T.allocate_and_register("kc", {1, (uint32_t)S, (uint32_t)KVH, (uint32_t)HD}, sh::DType::FP16);
+    T.allocate_and_register("vc", {1, (uint32_t)S, (uint32_t)KVH, (uint32_t)HD}, sh::DType::FP16);
+    std::vector<uint16_t> q((size_t)H * HD), k((size_t)KVH * HD), v((size_t)KVH * HD), qw(HD), kw(HD);
+    hkv_oracle_fill(q.data(), 1, 0, q.size());
+    hkv_oracle_fill(k.data(), 2, 0, k.size());
+    hkv_oracle_fill(v.data(), 3, 0, v.size());
+    for (int i = 0; i < HD; ++i) { qw[i] = hkv_oracle_f2h(1.0f + 0.01f * i); kw[i] = hkv_oracle_f2h(1.5f - 0.005f * i); }
+    upload(T.at("q").ptr, q); upload(T.at("k").ptr, k); upload(T.at("v").ptr, v);
+    upload(T.at("qw").ptr, qw); upload(T.at("kw").ptr, kw);
+    sh::CommandBuffer cb;
+    cb.add_op(sh::op::QK_NORM_ROPE(), "q")
+        .in({"q", "k", "qw", "kw", "v", "kc", "vc"})
+        .set("num_heads", uint32_t(H)).set("num_kv_heads", uint32_t(KVH)).set("dim", uint32_t(HD))
+        .set("seq_len", uint32_t{1}).set("theta", 1000000.0f).set("max_seq_len", uint32_t(S))
+        .set("device_pos", uint32_t{1});
+    engine.update_device_cache_pos(pos, 1);
+    engine.execute(cb);
+    engine.sync();
+    std::vector<uint16_t> rq = q, rk = k, rkc((size_t)S * KVH * HD, 0), rvc((size_t)S * KVH * HD, 0);
+    const int32_t p32 = pos;
+    hkv_oracle_qk_norm_rope(rq.data(), rk.data(), v.data(), qw.data(), kw.data(), rkc.data(), rvc.data(), 1, 1, H, KVH,
+                            HD, HD, &p32, S, 0, 1e-6f, 1000000.0f, 1.0f);
+    float worst;
+    REQUIRE(close_enough(download(T.at("q").ptr, q.size()), rq, &worst), "rotated q differs from the oracle");
+    REQUIRE(close_enough(download(T.at("kc").ptr, rkc.size()), rkc, &worst), "cache K differs from the oracle");
+    REQUIRE(download(T.at("vc").ptr, rvc.size()) == rvc, "cache V must be bit-exact");
+    REQUIRE(download(T.at("k").ptr, k.size()) == k, "k must stay untouched in the fused form");
+    std::printf("PASS: QK_NORM_ROPE fused op (norm + rope + cache write)\n");
+}
+
 static void test_cache_owner() {
     hkv::KVCache cache;
     REQUIRE(!cache.allocate(hkv::KVCacheConfig{}), "zero dims refused");
@@ -291,7 +338,8 @@ int main(int argc, char** argv) {
     struct Case { const char* name; void (*fn)(); };
     const Case cases[] = {{"known_answers", test_known_answers}, {"graph_contract", test_graph_contract},
                           {"graph_contract_fused", test_graph_contract_fused},
-                          {"error_behaviour", test_error_behaviour}, {"cache_owner", test_cache_owner}};
+                          {"error_behaviour", test_error_behaviour}, {"qk_norm_rope_op", test_qk_norm_rope_op},
+                          {"cache_owner", test_cache_owner}};
     if (argc > 1 && std::strcmp(argv[1], "--list") == 0) {
         for (const auto& c : cases) std::printf("%s\n", c.name);
         return 0;

@@ -20,7 +20,8 @@ def _ensure_built():
 def test_host_tests_binary_links_and_lists_cases():
     _ensure_built()
     out = subprocess.run([BIN, "--list"], capture_output=True, text=True, check=True).stdout.split()
-    assert out == ["known_answers", "graph_contract", "graph_contract_fused", "error_behaviour", "cache_owner"]
+    assert out == ["known_answers", "graph_contract", "graph_contract_fused", "error_behaviour", "qk_norm_rope_op",
+                   "cache_owner"]
 
 
 @pytest.mark.gpu
@@ -29,4 +30,4 @@ def test_host_adapter_cases_on_gpu():
     res = subprocess.run([BIN], capture_output=True, text=True, timeout=300)
     print(res.stdout, res.stderr)
     assert res.returncode == 0, res.stdout + res.stderr
-    assert res.stdout.count("PASS:") == 5 and "ALL PASSED" in res.stdout
+    assert res.stdout.count("PASS:") == 6 and "ALL PASSED" in res.stdout
