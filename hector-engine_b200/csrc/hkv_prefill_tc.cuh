@@ -11,8 +11,8 @@
 //     into the M dimension: row r of the 128-row tile is (query r / G, head r % G), QT = 128 / G
 //     queries per tile (18 for a group of 7: 126 of 128 rows used). One bulk-tensor load with
 //     box {64 halfs, G heads, QT queries} brings the tile in as 128-byte-swizzled K-major rows.
-//   * Warp 8 (one lane) is the TMA producer: Q tile per item, K/V tiles of 128 cache rows
-//     through a 2-stage ring (full/empty mbarriers).
+//   * Warp 8 (one lane) is the TMA producer: Q tile per item; K tiles of 128 cache rows through
+//     a 2-stage ring and V tiles through a 3-stage ring (full/empty mbarriers each).
 //   * Warp 9 (one lane) issues the MMAs:  S = Q·K^T  (M128 x N128 x K=HD, both operands K-major
 //     from shared memory) into one of two S buffers in tensor memory, and
 //     PV = P·V  (A = P from tensor memory as packed fp16, B = V straight from its row-major
@@ -21,8 +21,9 @@
 //   * Warps 0-7: two threads per row (each half of the score columns and of the output
 //     dimensions). The row's scores are read once from tensor memory, masked (causal +
 //     window), the two halves exchange their maxima through shared memory, exp2 / sum, and P
-//     goes back to tensor memory as packed fp16 (tcgen05.st); then O = O * alpha + PV with O
-//     kept in registers (fp32).
+//     goes back to tensor memory as packed fp16 (tcgen05.st, two P buffers). O accumulates in
+//     tensor memory across the whole item; it is rescaled in place only when a row's maximum
+//     outgrows its reference by more than 2^8, so the softmax of tile t+1 overlaps P·V of tile t.
 //   * All waits are bounded mbarrier waits; a wait that runs out sets the status word, the
 //     roles leave their loops, outstanding copies are drained and tensor memory is freed.
 #pragma once
@@ -44,8 +45,11 @@ constexpr int kPfRows = 128;   // M of the MMA = rows of a query tile
 constexpr int kPfKeys = 128;   // cache rows per K/V tile = N of the score MMA
 constexpr int kPfThreads = 320;  // 8 softmax warps + TMA producer + MMA issuer
 
+constexpr int kPfKStages = 2;  // K tiles in flight (freed right after the score MMA)
+constexpr int kPfVStages = 3;  // V tiles in flight (freed after the output MMA)
+
 __host__ __device__ constexpr size_t prefill_tc_smem_bytes(int HD) {
-    return 1024 + (size_t)kPfRows * HD * 2 + 2 * (2 * (size_t)kPfKeys * HD * 2) + 256 + 6 * kPfRows * 4;
+    return 1024 + (size_t)(1 + kPfKStages + kPfVStages) * kPfRows * HD * 2 + 40 * 8 + 6 * kPfRows * 4;
 }
 
 // ---- tcgen05 wrappers -------------------------------------------------------------
@@ -77,6 +81,12 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16
     asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
                  :
                  : "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                 :
+                 : "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
                  : "memory");
 }
 // D[tmem] (+)= A[smem] * B[smem]
@@ -116,7 +126,19 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint
         ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
-__device__ __forceinline__ void mbar_arrive_cnt(uint32_t bar) { mbar_arrive(bar); }
+// Rare path of the softmax warps: scale this thread's n32*32 columns of O (tensor memory) by
+// alpha. Kept out of line so that its registers do not weigh on the per-tile loop.
+__device__ __noinline__ void tmem_scale_columns(uint32_t addr, int n32, float alpha) {
+    for (int c = 0; c < n32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(v, addr + c * 32);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+        tmem_st32(addr + c * 32, v);
+    }
+    tc_wait_st();
+}
 
 template <int HD>
 __global__ void __launch_bounds__(kPfThreads, 1)
@@ -126,38 +148,39 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     constexpr int NCH = HD / 64;                       // 64-half column blocks
     constexpr int CHUNK_BYTES = kPfRows * 128;         // one column block of a 128-row tile
     constexpr int TILE_BYTES = kPfRows * HD * 2;
-    constexpr int STAGE_BYTES = 2 * TILE_BYTES;
     constexpr uint32_t TMEM_COLS = 512;
-    constexpr uint32_t COL_S0 = 0, COL_S1 = 128, COL_PV = 256, COL_P = 384;
+    constexpr uint32_t COL_S0 = 0, COL_S1 = 128, COL_PV = 256, COL_P0 = 384, COL_P1 = 448;
     constexpr uint32_t IDESC_QK = (1u << 4) | ((uint32_t)(kPfKeys >> 3) << 17) | ((uint32_t)(kPfRows >> 4) << 24);
     constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(kPfRows >> 4) << 24);
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t* q_gen = smem;
-    uint8_t* kv_gen = smem + TILE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(kv_gen + 2 * STAGE_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-    float* xch = reinterpret_cast<float*>(bars + 32);   // [2 buffers][2 halves][128] maxima + [2][128] sums
-    const uint32_t q_smem = smem_u32(q_gen), kv_smem = smem_u32(kv_gen);
+    uint8_t* q_gen = smem;                                   // Q tile
+    uint8_t* k_gen = smem + TILE_BYTES;                      // kPfKStages K tiles
+    uint8_t* v_gen = k_gen + kPfKStages * TILE_BYTES;        // kPfVStages V tiles
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_gen + kPfVStages * TILE_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
+    float* xch = reinterpret_cast<float*>(bars + 40);   // [2 buffers][2 halves][128] maxima + [2][128] sums
+    const uint32_t q_smem = smem_u32(q_gen), k_smem = smem_u32(k_gen), v_smem = smem_u32(v_gen);
     const uint32_t bar0 = smem_u32(bars);
-    // barrier map
+    // barrier map (8 bytes each)
     const uint32_t B_QFULL = bar0, B_QEMPTY = bar0 + 8;
-    const uint32_t B_KVFULL = bar0 + 16;    // [2]
-    const uint32_t B_KVEMPTY = bar0 + 32;   // [2]
-    const uint32_t B_SFULL = bar0 + 48;     // [2]
-    const uint32_t B_SFREE = bar0 + 64;     // [2]
-    const uint32_t B_PFULL = bar0 + 80, B_PVFULL = bar0 + 88, B_PVFREE = bar0 + 96, B_DONE = bar0 + 104;
-    const uint32_t B_XCH = bar0 + 112;      // softmax threads exchanging row maxima / sums
+    const uint32_t B_KFULL = bar0 + 16;     // [2]
+    const uint32_t B_KEMPTY = bar0 + 32;    // [2]
+    const uint32_t B_VFULL = bar0 + 48;     // [3]
+    const uint32_t B_VEMPTY = bar0 + 72;    // [3]
+    const uint32_t B_SFULL = bar0 + 96;     // [2]
+    const uint32_t B_SFREE = bar0 + 112;    // [2]
+    const uint32_t B_PFULL = bar0 + 128, B_PVFULL = bar0 + 136, B_DONE = bar0 + 144;
+    const uint32_t B_XCH = bar0 + 152;      // softmax threads exchanging row maxima / sums
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         mbar_init(B_QFULL, 1); mbar_init(B_QEMPTY, 1);
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(B_KVFULL + 8 * s, 1); mbar_init(B_KVEMPTY + 8 * s, 1);
-            mbar_init(B_SFULL + 8 * s, 1); mbar_init(B_SFREE + 8 * s, 256);
-        }
-        mbar_init(B_PFULL, 256); mbar_init(B_PVFULL, 1); mbar_init(B_PVFREE, 256); mbar_init(B_DONE, 1); mbar_init(B_XCH, 256);
+        for (int s = 0; s < kPfKStages; ++s) { mbar_init(B_KFULL + 8 * s, 1); mbar_init(B_KEMPTY + 8 * s, 1); }
+        for (int s = 0; s < kPfVStages; ++s) { mbar_init(B_VFULL + 8 * s, 1); mbar_init(B_VEMPTY + 8 * s, 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(B_SFULL + 8 * s, 1); mbar_init(B_SFREE + 8 * s, 256); }
+        mbar_init(B_PFULL, 256); mbar_init(B_PVFULL, 1); mbar_init(B_DONE, 1); mbar_init(B_XCH, 256);
         fence_mbar_init();
         tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
     }
@@ -184,11 +207,12 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
     if (warp == 8) {
         // ------------------------------ TMA producer ------------------------------
+        // K and V travel through separate rings: a K tile is free again as soon as its score MMA
+        // has run (long before P·V of the same tile), and V has one more stage than K, so the
+        // loads of tile t+2 never wait for the output MMA of tile t.
         if (lane == 0) {
-            uint32_t gt = 0, it = 0;
-            int issued_kv = 0;
+            uint32_t gt = 0, it = 0, q_it = 0;
             bool ok = true, q_pending = false;
-            uint32_t q_it = 0;
             for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
                 const int qt = a.n_qtiles - 1 - item / a.KVH, kvh = item % a.KVH;  // longest spans first
                 int kt_lo, nt;
@@ -201,75 +225,90 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 q_pending = true;
                 q_it = it;
                 for (int t = 0; t < nt; ++t, ++gt) {
-                    const uint32_t st = gt & 1, use = gt >> 1;
-                    if (!mbar_wait(B_KVEMPTY + 8 * st, (use & 1) ^ 1, a.status)) { ok = false; break; }
-                    const uint32_t full = B_KVFULL + 8 * st, dst = kv_smem + st * STAGE_BYTES;
-                    mbar_expect_tx(full, STAGE_BYTES);
                     const int row = (kt_lo + t) * kPfKeys;
-#pragma unroll
-                    for (int c = 0; c < NCH; ++c) tma_load_4d(dst + c * CHUNK_BYTES, &tm_k, full, c * 64, kvh, row, 0);
+                    const uint32_t ks = gt % kPfKStages, ku = gt / kPfKStages;
+                    if (!mbar_wait(B_KEMPTY + 8 * ks, (ku & 1) ^ 1, a.status)) { ok = false; break; }
+                    mbar_expect_tx(B_KFULL + 8 * ks, TILE_BYTES);
 #pragma unroll
                     for (int c = 0; c < NCH; ++c)
-                        tma_load_4d(dst + TILE_BYTES + c * CHUNK_BYTES, &tm_v, full, c * 64, kvh, row, 0);
-                    ++issued_kv;
+                        tma_load_4d(k_smem + ks * TILE_BYTES + c * CHUNK_BYTES, &tm_k, B_KFULL + 8 * ks, c * 64, kvh,
+                                    row, 0);
+                    const uint32_t vs = gt % kPfVStages, vu = gt / kPfVStages;
+                    if (!mbar_wait(B_VEMPTY + 8 * vs, (vu & 1) ^ 1, a.status)) {
+                        // the K copy above is in flight: wait for it before giving up
+                        mbar_wait(B_KFULL + 8 * ks, ku & 1, a.status);
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(B_VFULL + 8 * vs, TILE_BYTES);
+#pragma unroll
+                    for (int c = 0; c < NCH; ++c)
+                        tma_load_4d(v_smem + vs * TILE_BYTES + c * CHUNK_BYTES, &tm_v, B_VFULL + 8 * vs, c * 64, kvh,
+                                    row, 0);
                 }
             }
-            // drain this thread's outstanding copies before the CTA retires
+            // drain this thread's outstanding copies before the CTA retires (tiles 0..gt-1 were issued)
             if (q_pending) mbar_wait(B_QFULL, q_it & 1, a.status);
-            const int back = issued_kv < 2 ? issued_kv : 2;
-            for (int i = 1; i <= back; ++i) {
+            for (uint32_t i = 1; i <= (uint32_t)kPfKStages && i <= gt; ++i) {
                 const uint32_t g = gt - i;
-                mbar_wait(B_KVFULL + 8 * (g & 1), (g >> 1) & 1, a.status);
+                mbar_wait(B_KFULL + 8 * (g % kPfKStages), (g / kPfKStages) & 1, a.status);
+            }
+            for (uint32_t i = 1; i <= (uint32_t)kPfVStages && i <= gt; ++i) {
+                const uint32_t g = gt - i;
+                mbar_wait(B_VFULL + 8 * (g % kPfVStages), (g / kPfVStages) & 1, a.status);
             }
         }
     } else if (warp == 9) {
         // ------------------------------ MMA issuer ------------------------------
+        // Issue order per item: QK(0), QK(1), PV(0), QK(2), PV(1), ... — the score MMA of tile t+1
+        // runs while the softmax warps work on tile t.
         if (lane == 0) {
             uint32_t gt = 0, it = 0;
             bool ok = true;
-            auto issue_qk = [&](uint32_t g) {
-                const uint32_t st = g & 1;
-                const uint32_t kbase = kv_smem + st * STAGE_BYTES;
-                const uint32_t d = tmem + (st ? COL_S1 : COL_S0);
+            auto issue_qk = [&](uint32_t g) -> bool {
+                const uint32_t ks = g % kPfKStages, sb = g & 1;
+                if (!mbar_wait(B_KFULL + 8 * ks, (g / kPfKStages) & 1, a.status) ||
+                    !mbar_wait(B_SFREE + 8 * sb, ((g >> 1) & 1) ^ 1, a.status))
+                    return false;
+                tc_fence_after();
+                const uint32_t kbase = k_smem + ks * TILE_BYTES;
+                const uint32_t d = tmem + (sb ? COL_S1 : COL_S0);
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {
-                    const uint32_t off = (ks / 4) * CHUNK_BYTES + (ks % 4) * 32;
-                    tc_mma_ss(d, umma_desc_sw128(q_smem + off, 16), umma_desc_sw128(kbase + off, 16), IDESC_QK, ks > 0);
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint32_t off = (kk / 4) * CHUNK_BYTES + (kk % 4) * 32;
+                    tc_mma_ss(d, umma_desc_sw128(q_smem + off, 16), umma_desc_sw128(kbase + off, 16), IDESC_QK, kk > 0);
                 }
-                tc_commit(B_SFULL + 8 * st);
+                tc_commit(B_SFULL + 8 * sb);
+                tc_commit(B_KEMPTY + 8 * ks);   // the K tile is free once these MMAs have run
+                return true;
             };
             for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
                 const int qt = a.n_qtiles - 1 - item / a.KVH;
                 int kt_lo, nt;
                 tile_span(qt, kt_lo, nt);
-                if (!mbar_wait(B_QFULL, it & 1, a.status)) { ok = false; break; }
-                // scores of the first tile
-                if (!mbar_wait(B_KVFULL + 8 * (gt & 1), (gt >> 1) & 1, a.status) ||
-                    !mbar_wait(B_SFREE + 8 * (gt & 1), ((gt >> 1) & 1) ^ 1, a.status)) { ok = false; break; }
-                tc_fence_after();
-                issue_qk(gt);
+                if (!mbar_wait(B_QFULL, it & 1, a.status) || !issue_qk(gt)) { ok = false; break; }
                 for (int t = 0; t < nt && ok; ++t, ++gt) {
                     if (t + 1 < nt) {
-                        const uint32_t g1 = gt + 1;
-                        if (!mbar_wait(B_KVFULL + 8 * (g1 & 1), (g1 >> 1) & 1, a.status) ||
-                            !mbar_wait(B_SFREE + 8 * (g1 & 1), ((g1 >> 1) & 1) ^ 1, a.status)) { ok = false; break; }
-                        tc_fence_after();
-                        issue_qk(g1);
+                        if (!issue_qk(gt + 1)) { ok = false; break; }
                     } else {
                         tc_commit(B_QEMPTY);  // last score MMA of the item issued: Q tile may be replaced
                     }
-                    if (!mbar_wait(B_PFULL, gt & 1, a.status) || !mbar_wait(B_PVFREE, (gt & 1) ^ 1, a.status)) {
+                    const uint32_t vs = gt % kPfVStages;
+                    if (!mbar_wait(B_PFULL, gt & 1, a.status) ||
+                        !mbar_wait(B_VFULL + 8 * vs, (gt / kPfVStages) & 1, a.status)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t vbase = kv_smem + (gt & 1) * STAGE_BYTES + TILE_BYTES;
+                    // O accumulates in tensor memory over the whole item (the first tile overwrites)
+                    const uint32_t vbase = v_smem + vs * TILE_BYTES;
+                    const uint32_t pbase = tmem + ((gt & 1) ? COL_P1 : COL_P0);
 #pragma unroll
-                    for (int ks = 0; ks < kPfKeys / 16; ++ks)
-                        tc_mma_ts(tmem + COL_PV, tmem + COL_P + ks * 8, umma_desc_sw128(vbase + ks * 2048, CHUNK_BYTES),
-                                  IDESC_PV, ks > 0);
+                    for (int kk = 0; kk < kPfKeys / 16; ++kk)
+                        tc_mma_ts(tmem + COL_PV, pbase + kk * 8, umma_desc_sw128(vbase + kk * 2048, CHUNK_BYTES),
+                                  IDESC_PV, (t > 0 || kk > 0) ? 1u : 0u);
                     tc_commit(B_PVFULL);
-                    tc_commit(B_KVEMPTY + 8 * (gt & 1));
+                    tc_commit(B_VEMPTY + 8 * vs);
                 }
             }
             // every MMA issued above has completed before tensor memory is freed
@@ -297,102 +336,114 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             const int qpos = a.past_len + qi;
             const int first_row = a.window > 0 ? (qpos + 1 - a.window > 0 ? qpos + 1 - a.window : 0) : 0;
             const int qlim = qpos < a.slots ? qpos : a.slots - 1;  // never attend rows past the plane
-            float o[HH];
-#pragma unroll
-            for (int d = 0; d < HH; ++d) o[d] = 0.0f;
-            float m_run = kNegBig, l_run = 0.0f;
+            // m_ref: the reference maximum the probabilities and O are scaled by. It only moves
+            // when a tile's maximum exceeds it by more than 2^8 (then O is rescaled in tensor
+            // memory); otherwise P simply carries the factor, which fp16 holds comfortably.
+            float m_ref = kNegBig, l_run = 0.0f;
 
             for (int t = 0; t < nt; ++t, ++gt) {
                 const uint32_t sb = gt & 1;
                 const uint32_t s_addr = tmem + lane_sel + (sb ? COL_S1 : COL_S0) + half * 64;
                 const int kstart = (kt_lo + t) * kPfKeys + half * 64;   // key of this thread's column 0
                 ok = __all_sync(0xffffffffu, ok && mbar_wait(B_SFULL + 8 * sb, (gt >> 1) & 1, a.status));
-                if (ok) {
-                    tc_fence_after();
-                    uint32_t s0[32], s1[32];
-                    tmem_ld32(s0, s_addr);
-                    tmem_ld32(s1, s_addr + 32);
-                    tc_wait_ld();
-                    // columns [lo, hi] of this thread's 64 are attended (causal + window)
-                    const int lo = first_row - kstart, hi = qlim - kstart;
-                    const bool all_in = __all_sync(0xffffffffu, lo <= 0 && hi >= 63);
-                    float sc[64];
-                    float mx = -INFINITY;
-                    if (all_in) {
+                if (!ok) continue;
+                tc_fence_after();
+                uint32_t sv[64];
+                tmem_ld32(*reinterpret_cast<uint32_t (*)[32]>(&sv[0]), s_addr);
+                tmem_ld32(*reinterpret_cast<uint32_t (*)[32]>(&sv[32]), s_addr + 32);
+                tc_wait_ld();
+                // columns [lo, hi] of this thread's 64 are attended (causal + window)
+                const int lo = first_row - kstart, hi = qlim - kstart;
+                const bool all_in = __all_sync(0xffffffffu, lo <= 0 && hi >= 63);
+                float mx = -INFINITY;
+                if (all_in) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            sc[j] = __uint_as_float(s0[j]) * a.scale_log2;
-                            sc[32 + j] = __uint_as_float(s1[j]) * a.scale_log2;
-                            mx = fmaxf(mx, fmaxf(sc[j], sc[32 + j]));
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            sc[j] = (j >= lo && j <= hi) ? __uint_as_float(s0[j]) * a.scale_log2 : -INFINITY;
-                            sc[32 + j] = (32 + j >= lo && 32 + j <= hi) ? __uint_as_float(s1[j]) * a.scale_log2 : -INFINITY;
-                            mx = fmaxf(mx, fmaxf(sc[j], sc[32 + j]));
-                        }
+                    for (int j = 0; j < 64; ++j) {
+                        const float s = __uint_as_float(sv[j]) * a.scale_log2;
+                        sv[j] = __float_as_uint(s);
+                        mx = fmaxf(mx, s);
                     }
-                    // row maximum over both halves
-                    xch[(sb * 2 + half) * kPfRows + r] = mx;
-                    mbar_arrive(B_XCH);
-                    ok = __all_sync(0xffffffffu, mbar_wait(B_XCH, xn & 1, a.status));
-                    ++xn;
-                    if (!ok) continue;
-                    mx = fmaxf(mx, xch[(sb * 2 + (half ^ 1)) * kPfRows + r]);
-                    const float m_new = fmaxf(m_run, mx);
-                    const float alpha = exp2f(m_run - m_new);
-                    float lsum = 0.0f;
-                    uint32_t pk[32];
+                } else {
 #pragma unroll
-                    for (int j = 0; j < 64; j += 2) {
-                        const float p0 = exp2f(sc[j] - m_new), p1 = exp2f(sc[j + 1] - m_new);
-                        lsum += p0 + p1;
-                        pk[j / 2] = pack_half2(p0, p1);
-                    }
-                    {
-                        uint32_t (&pa)[16] = *reinterpret_cast<uint32_t (*)[16]>(&pk[0]);
-                        uint32_t (&pb)[16] = *reinterpret_cast<uint32_t (*)[16]>(&pk[16]);
-                        tmem_st16(tmem + lane_sel + COL_P + half * 32, pa);
-                        tmem_st16(tmem + lane_sel + COL_P + half * 32 + 16, pb);
-                    }
-                    tc_wait_st();
-                    m_run = m_new;
-                    l_run = l_run * alpha + lsum;
-                    // cache rows of this tile past the last written position may hold stale bits:
-                    // zero them in the staged V tile so that 0 * garbage cannot produce NaN
-                    const int tile0 = (kt_lo + t) * kPfKeys;
-                    if (tile0 + kPfKeys > kv_valid) {
-                        uint8_t* vt = kv_gen + (size_t)sb * STAGE_BYTES + TILE_BYTES;
-                        const int first_bad = kv_valid > tile0 ? kv_valid - tile0 : 0;
-                        for (int idx = first_bad * 8 * NCH + tid; idx < kPfKeys * 8 * NCH; idx += 256) {
-                            const int row = idx / (8 * NCH), u = idx % (8 * NCH);
-                            *reinterpret_cast<uint4*>(vt + (u / 8) * CHUNK_BYTES + row * 128 + (u % 8) * 16) =
-                                make_uint4(0, 0, 0, 0);
-                        }
-                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    }
-                    tc_fence_before();
-                    mbar_arrive(B_SFREE + 8 * sb);
-                    mbar_arrive(B_PFULL);
-                    // accumulate P·V of this tile (this thread's half of the output dimensions)
-                    ok = __all_sync(0xffffffffu, mbar_wait(B_PVFULL, gt & 1, a.status));
-                    if (ok) {
-                        tc_fence_after();
-#pragma unroll
-                        for (int c = 0; c < HH / 32; ++c) {
-                            uint32_t v[32];
-                            tmem_ld32(v, tmem + lane_sel + COL_PV + half * HH + c * 32);
-                            tc_wait_ld();
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) o[c * 32 + j] = fmaf(o[c * 32 + j], alpha, __uint_as_float(v[j]));
-                        }
-                        tc_fence_before();
-                        mbar_arrive(B_PVFREE);
+                    for (int j = 0; j < 64; ++j) {
+                        const float s = (j >= lo && j <= hi) ? __uint_as_float(sv[j]) * a.scale_log2 : -INFINITY;
+                        sv[j] = __float_as_uint(s);
+                        mx = fmaxf(mx, s);
                     }
                 }
+                // row maximum over both halves
+                xch[(sb * 2 + half) * kPfRows + r] = mx;
+                mbar_arrive(B_XCH);
+                ok = __all_sync(0xffffffffu, mbar_wait(B_XCH, xn & 1, a.status));
+                ++xn;
+                if (!ok) continue;
+                mx = fmaxf(mx, xch[(sb * 2 + (half ^ 1)) * kPfRows + r]);
+                const bool move = mx > m_ref + 8.0f;
+                if (__any_sync(0xffffffffu, move)) {
+                    const float m_to = move ? mx : m_ref;
+                    const float alpha = exp2f(m_ref - m_to);   // 1 for rows that keep their reference
+                    if (t > 0) {
+                        // rescale this thread's half of O in place; every earlier P·V must have landed
+                        ok = __all_sync(0xffffffffu, mbar_wait(B_PVFULL, (gt - 1) & 1, a.status));
+                        if (!ok) continue;
+                        tc_fence_after();
+                        tmem_scale_columns(tmem + lane_sel + COL_PV + half * HH, HH / 32, alpha);
+                    }
+                    l_run *= alpha;
+                    m_ref = m_to;
+                }
+                float lsum = 0.0f;
+                uint32_t pk[32];
+#pragma unroll
+                for (int j = 0; j < 64; j += 2) {
+                    const float p0 = exp2f(__uint_as_float(sv[j]) - m_ref);
+                    const float p1 = exp2f(__uint_as_float(sv[j + 1]) - m_ref);
+                    lsum += p0 + p1;
+                    pk[j / 2] = pack_half2(p0, p1);
+                }
+                {
+                    const uint32_t pcol = (sb ? COL_P1 : COL_P0) + half * 32;
+                    tmem_st16(tmem + lane_sel + pcol, *reinterpret_cast<uint32_t (*)[16]>(&pk[0]));
+                    tmem_st16(tmem + lane_sel + pcol + 16, *reinterpret_cast<uint32_t (*)[16]>(&pk[16]));
+                }
+                tc_wait_st();
+                l_run += lsum;
+                // cache rows of this tile past the last written position may hold stale bits:
+                // zero them in the staged V tile so that 0 * garbage cannot produce NaN
+                const int tile0 = (kt_lo + t) * kPfKeys;
+                if (tile0 + kPfKeys > kv_valid) {
+                    const uint32_t vs = gt % kPfVStages;
+                    ok = __all_sync(0xffffffffu, mbar_wait(B_VFULL + 8 * vs, (gt / kPfVStages) & 1, a.status));
+                    if (!ok) continue;
+                    uint8_t* vt = v_gen + (size_t)vs * TILE_BYTES;
+                    const int first_bad = kv_valid > tile0 ? kv_valid - tile0 : 0;
+                    for (int idx = first_bad * 8 * NCH + tid; idx < kPfKeys * 8 * NCH; idx += 256) {
+                        const int row = idx / (8 * NCH), u = idx % (8 * NCH);
+                        *reinterpret_cast<uint4*>(vt + (u / 8) * CHUNK_BYTES + row * 128 + (u % 8) * 16) =
+                            make_uint4(0, 0, 0, 0);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+                tc_fence_before();
+                mbar_arrive(B_SFREE + 8 * sb);
+                mbar_arrive(B_PFULL);
             }
-            // total row sum = both halves' partial sums (same running maximum)
+            // the item's last P·V has landed: read this thread's half of O
+            float o[HH];
+            ok = __all_sync(0xffffffffu, ok && mbar_wait(B_PVFULL, (gt - 1) & 1, a.status));
+            if (ok) {
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < HH / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(v, tmem + lane_sel + COL_PV + half * HH + c * 32);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[c * 32 + j] = __uint_as_float(v[j]);
+                }
+                tc_fence_before();
+            }
+            // total row sum = both halves' partial sums (same reference maximum)
             float l_tot = l_run;
             if (ok) {
                 xch[4 * kPfRows + half * kPfRows + r] = l_run;
