@@ -6,6 +6,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -48,6 +49,7 @@ struct hkv_ctx {
     size_t workspace_bytes = 0;
     int32_t* d_status = nullptr;
     int32_t* d_len = nullptr;       // [B] for the host-length / host-position twins
+    float* prefill_ws = nullptr;    // [max_seq_new][kPrefillMaxSplits][H][HD+2] key-split partials of the prefill kernel
     int32_t* h_len = nullptr;       // pinned staging for d_len
     // host-buffer entry point staging
     __half *st_q = nullptr, *st_k = nullptr, *st_v = nullptr, *st_out = nullptr;
@@ -198,6 +200,54 @@ int encode_f16_sw128(hkv_ctx* c, const void* base, int rank, const cuuint64_t* d
         return fail(c, HKV_ERR_CUDA, buf);
     }
     return HKV_OK;
+}
+
+constexpr int kPrefillMaxSplits = 4;
+
+// Number of key ranges each (query tile, kv head) is cut into: the smallest count whose work
+// items fill at least 92 % of the SM waves they occupy, never more than the shortest span.
+// Key-range split count of the tensor-core prefill kernel. The kernel deals its work items
+// (query tile, kv head, split) round-robin to one CTA per SM, so the launch lasts as long as the
+// most loaded CTA; this replays that deal with a per-item overhead (pipeline fill, Q load, output)
+// and adds what the split costs (fp32 partials written and read back by the merge kernel).
+// Costs are in microseconds, from timings of the kernel on B200: ~1.55 us per 128-key tile at
+// head_dim 128, ~6 tiles' worth of overhead per item.
+int prefill_splits(const PrefillTcArgs& t, int HD, int sm_count, int min_span_tiles, bool have_ws) {
+    if (!have_ws) return 1;
+    if (const char* e = getenv("HKV_PREFILL_SPLITS")) {  // tuning override
+        const int v = atoi(e);
+        if (v >= 1) return v < kPrefillMaxSplits ? (v < min_span_tiles ? v : min_span_tiles) : kPrefillMaxSplits;
+    }
+    const double tile_us = 0.60 + 0.95 * HD / 128.0, item_tiles = 6.0;
+    const double row_bytes = (double)t.S_new * t.H * (HD + 2) * 4.0;
+    int best = 1;
+    double best_cost = 0.0;
+    std::vector<double> load((size_t)sm_count);
+    for (int s = 1; s <= kPrefillMaxSplits && s <= min_span_tiles; ++s) {
+        const long long items = (long long)t.n_qtiles * t.KVH * s;
+        const int grid = items < sm_count ? (int)items : sm_count;
+        std::fill(load.begin(), load.end(), 0.0);
+        long long item = 0;
+        for (int qt = t.n_qtiles - 1; qt >= 0; --qt) {
+            const int q0 = qt * t.QT;
+            const int lo = t.window > 0 ? (t.past_len + q0 + 1 - t.window > 0 ? t.past_len + q0 + 1 - t.window : 0) : 0;
+            const int q_last = q0 + t.QT < t.S_new ? q0 + t.QT : t.S_new;
+            int hi = t.past_len + q_last - 1;
+            if (hi > t.slots - 1) hi = t.slots - 1;
+            int ntot = hi / kPfKeys - lo / kPfKeys + 1;
+            if (ntot < 1) ntot = 1;
+            const int base = ntot / s, rem = ntot % s;
+            for (int kvh = 0; kvh < t.KVH; ++kvh)
+                for (int sp = 0; sp < s; ++sp, ++item)
+                    load[(size_t)(item % grid)] += (base + (sp < rem ? 1 : 0)) + item_tiles;
+        }
+        double mx = 0.0;
+        for (int i = 0; i < grid; ++i) mx = load[(size_t)i] > mx ? load[(size_t)i] : mx;
+        double cost = mx * tile_us;
+        if (s > 1) cost += 4.0 + 2.0 * s * row_bytes / 3.0e6;   // partials out and back at ~3 TB/s
+        if (s == 1 || cost < 0.97 * best_cost) { best = s; best_cost = cost; }
+    }
+    return best;
 }
 
 bool prefill_tc_ok(const hkv_geometry& g) {
@@ -520,6 +570,12 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
                                  (int)prefill_tc_smem_bytes(geometry->head_dim));
         if (e != cudaSuccess) return fail_cuda(c, e, "cudaFuncSetAttribute(prefill shared memory)");
     }
+    if (prefill_tc_ok(*geometry) && geometry->max_seq_new > 0) {
+        const size_t nb = (size_t)geometry->max_seq_new * kPrefillMaxSplits * geometry->num_heads *
+                          (geometry->head_dim + 2) * sizeof(float);
+        e = cudaMalloc(&c->prefill_ws, nb);
+        if (e != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(prefill workspace)");
+    }
     c->workspace_bytes = workspace_bytes_for(*geometry, c->max_chunks);
     e = cudaMalloc(&c->workspace, c->workspace_bytes);
     if (e != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(workspace)");
@@ -539,6 +595,7 @@ int hkv_ctx_destroy(hkv_ctx* c) {
     if (c->workspace) cudaFree(c->workspace);
     if (c->d_status) cudaFree(c->d_status);
     if (c->d_len) cudaFree(c->d_len);
+    if (c->prefill_ws) cudaFree(c->prefill_ws);
     if (c->h_len) cudaFreeHost(c->h_len);
     if (c->st_q) cudaFree(c->st_q);
     if (c->st_k) cudaFree(c->st_k);
@@ -681,6 +738,17 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
         t.slots = g.slots;
         t.window = g.window_size;
         t.scale_log2 = scale * 1.4426950408889634f;
+        {
+            // shortest key span over the query tiles = that of the first tile (window-limited)
+            const int q_last = t.QT < seq_new ? t.QT : seq_new;
+            const int first_min = g.window_size > 0 ? (past_len + 1 - g.window_size > 0 ? past_len + 1 - g.window_size : 0) : 0;
+            int last_max = past_len + q_last - 1;
+            if (last_max > g.slots - 1) last_max = g.slots - 1;
+            const int min_span = last_max / kPfKeys - first_min / kPfKeys + 1;
+            const bool have_ws = c->prefill_ws != nullptr && seq_new <= g.max_seq_new;
+            t.splits = prefill_splits(t, HD, c->sm_count, min_span, have_ws);
+            t.part = c->prefill_ws;
+        }
         CUtensorMap mq, mk, mv;
         {
             cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)g.num_heads, (cuuint64_t)seq_new};
@@ -699,11 +767,22 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
             st = encode_f16_sw128(c, v_cache, 4, dims, strides, box, &mv);
             if (st) return st;
         }
-        const long long items = (long long)t.n_qtiles * g.num_kv_heads;
+        const long long items = (long long)t.n_qtiles * g.num_kv_heads * t.splits;
         const int grid = items < c->sm_count ? (int)items : c->sm_count;
         const size_t smem = prefill_tc_smem_bytes(HD);
         if (HD == 64) hkv_prefill_tc_kernel<64><<<grid, kPfThreads, smem, (cudaStream_t)stream>>>(mq, mk, mv, t);
         else hkv_prefill_tc_kernel<128><<<grid, kPfThreads, smem, (cudaStream_t)stream>>>(mq, mk, mv, t);
+        if (t.splits > 1) {
+            // merge the key-range partials of every (query, head)
+            const long long rows = (long long)seq_new * g.num_heads;
+            const unsigned cgrid = (unsigned)((rows + 7) / 8);
+            if (HD == 64)
+                hkv_prefill_combine_kernel<64><<<cgrid, 256, 0, (cudaStream_t)stream>>>(c->prefill_ws, (__half*)out, rows,
+                                                                                       g.num_heads, t.splits);
+            else
+                hkv_prefill_combine_kernel<128><<<cgrid, 256, 0, (cudaStream_t)stream>>>(c->prefill_ws, (__half*)out, rows,
+                                                                                        g.num_heads, t.splits);
+        }
         const cudaError_t e = cudaPeekAtLastError();
         return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "prefill launch");
     }

@@ -39,6 +39,12 @@ struct PrefillTcArgs {
     int32_t* status;
     int S_new, past_len, H, KVH, G, QT, n_qtiles, slots, window;
     float scale_log2;
+    // Key-range split: every (query tile, kv head) is cut into `splits` consecutive key ranges
+    // so that the work items fill the last wave of SMs; with splits > 1 each range writes an
+    // un-normalised partial row (o[HD], reference maximum, sum) to `part`
+    // [S_new][splits][H][HD+2] and the combine kernel merges them.
+    int splits;
+    float* part;
 };
 
 constexpr int kPfRows = 128;   // M of the MMA = rows of a query tile
@@ -173,6 +179,7 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const uint32_t B_SFREE = bar0 + 112;    // [2]
     const uint32_t B_PFULL = bar0 + 128, B_PVFULL = bar0 + 136, B_DONE = bar0 + 144;
     const uint32_t B_XCH = bar0 + 152;      // softmax threads exchanging row maxima / sums
+    const uint32_t B_OFULL = bar0 + 160;    // last P·V of an item has completed
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
@@ -181,6 +188,7 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         for (int s = 0; s < kPfVStages; ++s) { mbar_init(B_VFULL + 8 * s, 1); mbar_init(B_VEMPTY + 8 * s, 1); }
         for (int s = 0; s < 2; ++s) { mbar_init(B_SFULL + 8 * s, 1); mbar_init(B_SFREE + 8 * s, 256); }
         mbar_init(B_PFULL, 256); mbar_init(B_PVFULL, 1); mbar_init(B_DONE, 1); mbar_init(B_XCH, 256);
+        mbar_init(B_OFULL, 1);
         fence_mbar_init();
         tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
     }
@@ -190,19 +198,23 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    const int n_items = a.n_qtiles * a.KVH;
+    const int n_items = a.n_qtiles * a.KVH * a.splits;
     const int kv_valid = (a.past_len + a.S_new < a.slots) ? a.past_len + a.S_new : a.slots;
 
     // Key-tile range of a query tile (identical in every role).
-    auto tile_span = [&](int qt, int& kt_lo, int& nt) {
+    auto tile_span = [&](int qt, int sp, int& kt_lo, int& nt) {
         const int q0 = qt * a.QT;
         const int first_min = a.window > 0 ? (a.past_len + q0 + 1 - a.window > 0 ? a.past_len + q0 + 1 - a.window : 0) : 0;
         int q_last = q0 + a.QT < a.S_new ? q0 + a.QT : a.S_new;
         int last_max = a.past_len + q_last - 1;
         if (last_max > a.slots - 1) last_max = a.slots - 1;
-        kt_lo = first_min / kPfKeys;
-        nt = last_max / kPfKeys - kt_lo + 1;
-        if (nt < 1) nt = 1;
+        const int kt0 = first_min / kPfKeys;
+        int ntot = last_max / kPfKeys - kt0 + 1;
+        if (ntot < 1) ntot = 1;
+        // this split's share of the span (the host guarantees splits <= shortest span)
+        const int base = ntot / a.splits, rem = ntot % a.splits;
+        kt_lo = kt0 + sp * base + (sp < rem ? sp : rem);
+        nt = base + (sp < rem ? 1 : 0);
     };
 
     if (warp == 8) {
@@ -214,9 +226,10 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             uint32_t gt = 0, it = 0, q_it = 0;
             bool ok = true, q_pending = false;
             for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
-                const int qt = a.n_qtiles - 1 - item / a.KVH, kvh = item % a.KVH;  // longest spans first
+                const int sp = item % a.splits, rest = item / a.splits;
+                const int qt = a.n_qtiles - 1 - rest / a.KVH, kvh = rest % a.KVH;  // longest spans first
                 int kt_lo, nt;
-                tile_span(qt, kt_lo, nt);
+                tile_span(qt, sp, kt_lo, nt);
                 if (!mbar_wait(B_QEMPTY, (it & 1) ^ 1, a.status)) { ok = false; break; }
                 mbar_expect_tx(B_QFULL, (uint32_t)(NCH * a.QT * a.G * 128));
 #pragma unroll
@@ -283,9 +296,10 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 return true;
             };
             for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
-                const int qt = a.n_qtiles - 1 - item / a.KVH;
+                const int sp = item % a.splits, rest = item / a.splits;
+                const int qt = a.n_qtiles - 1 - rest / a.KVH;
                 int kt_lo, nt;
-                tile_span(qt, kt_lo, nt);
+                tile_span(qt, sp, kt_lo, nt);
                 if (!mbar_wait(B_QFULL, it & 1, a.status) || !issue_qk(gt)) { ok = false; break; }
                 for (int t = 0; t < nt && ok; ++t, ++gt) {
                     if (t + 1 < nt) {
@@ -308,6 +322,7 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                         tc_mma_ts(tmem + COL_PV, pbase + kk * 8, umma_desc_sw128(vbase + kk * 2048, CHUNK_BYTES),
                                   IDESC_PV, (t > 0 || kk > 0) ? 1u : 0u);
                     tc_commit(B_PVFULL);
+                    if (t + 1 == nt) tc_commit(B_OFULL);   // the item's output is complete
                     tc_commit(B_VEMPTY + 8 * vs);
                 }
             }
@@ -325,12 +340,13 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
         constexpr int HH = HD / 2;                 // output dimensions per thread
         const int ql = r / a.G, g = r % a.G;
-        uint32_t gt = 0, xn = 0;   // tiles seen, exchanges done (barrier phases)
+        uint32_t gt = 0, xn = 0, si = 0;   // tiles seen, exchanges done, items done (barrier phases)
         bool ok = true;            // kept warp-uniform: a wait that ran out for any lane stops the warp
         for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-            const int qt = a.n_qtiles - 1 - item / a.KVH, kvh = item % a.KVH;
+            const int sp = item % a.splits, rest = item / a.splits;
+            const int qt = a.n_qtiles - 1 - rest / a.KVH, kvh = rest % a.KVH;
             int kt_lo, nt;
-            tile_span(qt, kt_lo, nt);
+            tile_span(qt, sp, kt_lo, nt);
             const int qi = qt * a.QT + ql;
             const bool row_valid = ql < a.QT && qi < a.S_new;
             const int qpos = a.past_len + qi;
@@ -383,7 +399,9 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     const float m_to = move ? mx : m_ref;
                     const float alpha = exp2f(m_ref - m_to);   // 1 for rows that keep their reference
                     if (t > 0) {
-                        // rescale this thread's half of O in place; every earlier P·V must have landed
+                        // rescale this thread's half of O in place; every earlier P·V must have landed.
+                        // (The parity wait is sound here: the score MMA of this tile was issued after
+                        // P·V of tile t-2, so the barrier is at most one phase behind.)
                         ok = __all_sync(0xffffffffu, mbar_wait(B_PVFULL, (gt - 1) & 1, a.status));
                         if (!ok) continue;
                         tc_fence_after();
@@ -428,9 +446,13 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 mbar_arrive(B_SFREE + 8 * sb);
                 mbar_arrive(B_PFULL);
             }
-            // the item's last P·V has landed: read this thread's half of O
+            // Wait for the item's last P·V, then read this thread's half of O. This is a barrier of
+            // its own with one phase per item: the per-tile barrier may still be two phases behind
+            // here (nothing orders P·V of tile nt-2 before this point), where a parity wait passes
+            // a phase early.
             float o[HH];
-            ok = __all_sync(0xffffffffu, ok && mbar_wait(B_PVFULL, (gt - 1) & 1, a.status));
+            ok = __all_sync(0xffffffffu, ok && mbar_wait(B_OFULL, si & 1, a.status));
+            ++si;
             if (ok) {
                 tc_fence_after();
 #pragma unroll
@@ -452,7 +474,17 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 ++xn;
                 l_tot += xch[4 * kPfRows + (half ^ 1) * kPfRows + r];
             }
-            if (ok && row_valid) {
+            if (ok && row_valid && a.splits > 1) {
+                float* prow = a.part + (((long long)qi * a.splits + sp) * a.H + (long long)kvh * a.G + g) * (HD + 2);
+#pragma unroll
+                for (int d = 0; d < HH; d += 4)
+                    *reinterpret_cast<float2*>(prow + half * HH + d) = make_float2(o[d], o[d + 1]),
+                    *reinterpret_cast<float2*>(prow + half * HH + d + 2) = make_float2(o[d + 2], o[d + 3]);
+                if (half == 0) {
+                    prow[HD] = m_ref;
+                    prow[HD + 1] = l_tot;
+                }
+            } else if (ok && row_valid) {
                 const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
                 __half* op = a.out + ((long long)qi * a.H + (long long)kvh * a.G + g) * HD + half * HH;
 #pragma unroll
@@ -470,6 +502,50 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     tc_fence_before();
     __syncthreads();
     if (warp == 9) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
+// Merge of the key-range partials written by the kernel above: one warp per (query, head) row,
+// each lane HD/32 output dimensions. The partial rows are [o(HD), m (log2 domain), l] in fp32.
+// ---------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(256) hkv_prefill_combine_kernel(const float* __restrict__ part,
+                                                                  __half* __restrict__ out, long long rows,
+                                                                  int H, int splits) {
+    constexpr int EPL = HD / 32;   // 2 or 4 floats per lane; rows are 8-byte aligned
+    const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const long long qi = row / H;
+    const int head = (int)(row % H);
+    const long long stride = (long long)H * (HD + 2);
+    const float* base = part + (qi * splits * H + head) * (HD + 2);
+    float M = kNegBig;
+    for (int sp = 0; sp < splits; ++sp) M = fmaxf(M, __ldg(base + sp * stride + HD));
+    float L = 0.0f, acc[EPL];
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) acc[j] = 0.0f;
+    for (int sp = 0; sp < splits; ++sp) {
+        const float* r = base + sp * stride;
+        const float w = exp2f(__ldg(r + HD) - M);
+        L = fmaf(__ldg(r + HD + 1), w, L);
+#pragma unroll
+        for (int j = 0; j < EPL; j += 2) {
+            const float2 v = __ldg(reinterpret_cast<const float2*>(r + lane * EPL + j));
+            acc[j] = fmaf(v.x, w, acc[j]);
+            acc[j + 1] = fmaf(v.y, w, acc[j + 1]);
+        }
+    }
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    __half* op = out + row * HD + lane * EPL;
+    if constexpr (EPL == 4) {
+        uint2 w;
+        w.x = pack_half2(acc[0] * inv, acc[1] * inv);
+        w.y = pack_half2(acc[2] * inv, acc[3] * inv);
+        *reinterpret_cast<uint2*>(op) = w;
+    } else {
+        *reinterpret_cast<uint32_t*>(op) = pack_half2(acc[0] * inv, acc[1] * inv);
+    }
 }
 
 }  // namespace hkv

@@ -81,7 +81,8 @@ typedef struct hkv_geometry {
     int32_t shard_count;
     int32_t shard_block;  /* multiple of 64                                              */
     int32_t kernel_select; /* hkv_kernel_select                                          */
-    int32_t max_seq_new;  /* largest seq_new for hkv_prefill_attention; 0 = decode only   */
+    int32_t max_seq_new;  /* largest seq_new hkv_prefill_attention may split by key range
+                             (allocates seq_new*4*H*(HD+2)*4 bytes of partials); 0 = no split */
     int32_t reserved[3];
 } hkv_geometry;
 
