@@ -722,7 +722,8 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
     if (c->g.layout != HKV_LAYOUT_LINEAR || c->g.shard_count > 1)
         return fail(c, HKV_ERR_GEOMETRY, "prefill: linear unsharded cache only");
     if (seq_new == 0) return HKV_OK;
-    if (prefill_tc_ok(c->g) && aligned(q, 16) && aligned(k_cache, 16) && aligned(v_cache, 16) && aligned(out, 16)) {
+    // (the tensor-core kernel takes row maxima before scaling, which needs a positive scale)
+    if (prefill_tc_ok(c->g) && scale > 0.0f && aligned(q, 16) && aligned(k_cache, 16) && aligned(v_cache, 16) && aligned(out, 16)) {
         const hkv_geometry& g = c->g;
         const int HD = g.head_dim, G = c->G;
         PrefillTcArgs t;

@@ -132,6 +132,35 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint
         ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
+// ---- softmax arithmetic: the softmax warps are issue-bound, so every element costs as few
+// instructions as sm_100 allows: 3-input max, packed two-lane fp32 FMA/ADD, bare ex2.approx.
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// (d0, d1) = (a0, a1) * (b, b) + (c, c)
+__device__ __forceinline__ void ffma2_bcast(float& d0, float& d1, float a0, float a1, float b, float c) {
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+// (d0, d1) += (a0, a1)
+__device__ __forceinline__ void fadd2_acc(float& d0, float& d1, float a0, float a1) {
+    asm("{\n\t.reg .b64 ra, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rd, {%0, %1};\n\t"
+        "add.rn.f32x2 rd, rd, ra;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "+f"(d0), "+f"(d1)
+        : "f"(a0), "f"(a1));
+}
+
 // Rare path of the softmax warps: scale this thread's n32*32 columns of O (tensor memory) by
 // alpha. Kept out of line so that its registers do not weigh on the per-tile loop.
 __device__ __noinline__ void tmem_scale_columns(uint32_t addr, int n32, float alpha) {
@@ -371,22 +400,21 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 // columns [lo, hi] of this thread's 64 are attended (causal + window)
                 const int lo = first_row - kstart, hi = qlim - kstart;
                 const bool all_in = __all_sync(0xffffffffu, lo <= 0 && hi >= 63);
+                // the maximum is taken on the raw scores (the scale is positive) and scaled once
                 float mx = -INFINITY;
                 if (all_in) {
 #pragma unroll
-                    for (int j = 0; j < 64; ++j) {
-                        const float s = __uint_as_float(sv[j]) * a.scale_log2;
-                        sv[j] = __float_as_uint(s);
-                        mx = fmaxf(mx, s);
-                    }
+                    for (int j = 0; j < 64; j += 2)
+                        mx = fmax3(mx, __uint_as_float(sv[j]), __uint_as_float(sv[j + 1]));
                 } else {
 #pragma unroll
                     for (int j = 0; j < 64; ++j) {
-                        const float s = (j >= lo && j <= hi) ? __uint_as_float(sv[j]) * a.scale_log2 : -INFINITY;
+                        const float s = (j >= lo && j <= hi) ? __uint_as_float(sv[j]) : -INFINITY;
                         sv[j] = __float_as_uint(s);
                         mx = fmaxf(mx, s);
                     }
                 }
+                mx *= a.scale_log2;
                 // row maximum over both halves
                 xch[(sb * 2 + half) * kPfRows + r] = mx;
                 mbar_arrive(B_XCH);
@@ -410,15 +438,19 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     l_run *= alpha;
                     m_ref = m_to;
                 }
-                float lsum = 0.0f;
+                // p = 2^(s*scale - m_ref): one packed FMA, two ex2, one packed add, one pack per pair
+                float lsum0 = 0.0f, lsum1 = 0.0f;
+                const float neg_m = -m_ref;
                 uint32_t pk[32];
 #pragma unroll
                 for (int j = 0; j < 64; j += 2) {
-                    const float p0 = exp2f(__uint_as_float(sv[j]) - m_ref);
-                    const float p1 = exp2f(__uint_as_float(sv[j + 1]) - m_ref);
-                    lsum += p0 + p1;
+                    float x0, x1;
+                    ffma2_bcast(x0, x1, __uint_as_float(sv[j]), __uint_as_float(sv[j + 1]), a.scale_log2, neg_m);
+                    const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+                    fadd2_acc(lsum0, lsum1, p0, p1);
                     pk[j / 2] = pack_half2(p0, p1);
                 }
+                const float lsum = lsum0 + lsum1;
                 {
                     const uint32_t pcol = (sb ? COL_P1 : COL_P0) + half * 32;
                     tmem_st16(tmem + lane_sel + pcol, *reinterpret_cast<uint32_t (*)[16]>(&pk[0]));

@@ -17,6 +17,7 @@
 
 #include "hkv.h"
 #include "hkv_engine_shim.hpp"
+#include "hkv_decode_loop.hpp"
 #include "hkv_kv_cache.hpp"
 #include "hkv_register.hpp"
 
@@ -334,12 +335,113 @@ static void test_cache_owner() {
     std::printf("PASS: C++ cache owner\n");
 }
 
+// ---------------------------------------------------------------------------
+// Batched decode loop: sessions join and leave batch slots between tokens while ONE captured
+// graph keeps replaying; every active slot must match its own batch-1 oracle history, a free slot
+// must produce zeros and leave its planes untouched.
+static void test_decode_loop() {
+    const uint32_t L = 3, B = 4, H = 8, KVH = 2, HD = 64, S = 256;
+    cudaStream_t stream;
+    cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking);
+    {
+        hkv::DecodeLoopConfig cfg;
+        cfg.layers = L; cfg.batch = B; cfg.heads = H; cfg.kv_heads = KVH; cfg.head_dim = HD; cfg.max_seq_len = S;
+        hkv::BatchedDecodeLoop loop(cfg, stream);
+        const size_t qn = (size_t)B * H * HD, kn = (size_t)B * KVH * HD, row = (size_t)KVH * HD;
+        const size_t plane = (size_t)B * S * row;   // one layer
+        half *d_q, *d_k, *d_v, *d_out;
+        cudaMalloc(&d_q, L * qn * 2); cudaMalloc(&d_k, L * kn * 2); cudaMalloc(&d_v, L * kn * 2); cudaMalloc(&d_out, L * qn * 2);
+        int hook_calls = 0;
+        loop.bind(d_q, d_k, d_v, d_out, [&](uint32_t, cudaStream_t) { ++hook_calls; });
+
+        // host mirror of the planes, [layer][slot][S][row]
+        std::vector<uint16_t> hk(L * plane, 0), hv(L * plane, 0);
+        int32_t mirror_pos[B];
+        for (auto& p : mirror_pos) p = -1;
+        auto attach = [&](uint32_t start) {
+            const int slot = loop.board().attach(start);
+            if (slot < 0) return slot;
+            mirror_pos[slot] = (int32_t)start;
+            // a new tenant starts from a prefix of `start` rows (zero rows here: only what it appends counts)
+            return slot;
+        };
+        REQUIRE(attach(0) == 0, "first session takes slot 0");
+        const float scale = 1.0f / std::sqrt(float(HD));
+        const int steps = 40;
+        int replays = 0;
+        for (int s = 0; s < steps; ++s) {
+            if (s == 3) REQUIRE(attach(0) == 1, "second session takes slot 1");
+            if (s == 5) { REQUIRE(attach(0) == 2, "slot 2"); REQUIRE(attach(0) == 3, "slot 3"); REQUIRE(attach(0) == -1, "batch full"); }
+            if (s == 12) { loop.board().detach(1); mirror_pos[1] = -1; }
+            if (s == 20) {
+                // slot 1 is re-let: the new tenant starts at row 0 and overwrites the old rows as it goes;
+                // rows beyond its position are never attended
+                REQUIRE(attach(0) == 1, "freed slot is reused");
+            }
+            if (s == 30) { loop.board().detach(0); mirror_pos[0] = -1; loop.board().detach(3); mirror_pos[3] = -1; }
+            std::vector<uint16_t> q(L * qn), nk(L * kn), nv(L * kn);
+            hkv_oracle_fill(q.data(), 1000 + s, 0, q.size());
+            hkv_oracle_fill(nk.data(), 2000 + s, 0, nk.size());
+            hkv_oracle_fill(nv.data(), 3000 + s, 0, nv.size());
+            upload(d_q, q, stream); upload(d_k, nk, stream); upload(d_v, nv, stream);
+            replays += loop.step() ? 1 : 0;
+            cudaStreamSynchronize(stream);
+            const auto out = download(d_out, L * qn);
+            for (uint32_t l = 0; l < L; ++l)
+                for (uint32_t b = 0; b < B; ++b) {
+                    const uint16_t* o = out.data() + l * qn + (size_t)b * H * HD;
+                    if (mirror_pos[b] < 0) {
+                        for (size_t i = 0; i < (size_t)H * HD; ++i) REQUIRE(o[i] == 0, "free slot output is not zero");
+                        continue;
+                    }
+                    uint16_t* pk = hk.data() + l * plane + (size_t)b * S * row;
+                    uint16_t* pv = hv.data() + l * plane + (size_t)b * S * row;
+                    const int32_t p = mirror_pos[b], tot = p + 1;
+                    hkv_oracle_append(nk.data() + l * kn + b * row, nv.data() + l * kn + b * row, pk, pv, 1, 1, KVH, HD,
+                                      S, 0, &p, 0);
+                    std::vector<uint16_t> ref((size_t)H * HD), got(o, o + (size_t)H * HD);
+                    hkv_oracle_decode(q.data() + l * qn + (size_t)b * H * HD, pk, pv, ref.data(), nullptr, 1, &tot, H,
+                                      KVH, HD, S, 0, scale, 0, 0, 0, 1);
+                    float worst;
+                    REQUIRE(close_enough(got, ref, &worst), "slot output differs from its batch-1 oracle history");
+                }
+            for (auto& p : mirror_pos) if (p >= 0 && p < (int32_t)S) ++p;
+            for (uint32_t b = 0; b < B; ++b)
+                REQUIRE((mirror_pos[b] < 0 && !loop.board().active((int)b)) ||
+                        (uint32_t)mirror_pos[b] == loop.board().position((int)b), "board position");
+        }
+        REQUIRE(loop.graph().valid(), "graph was not captured");
+        REQUIRE(replays == steps, "every step, the first included, replays the captured graph");
+        REQUIRE(loop.graph().capture_failures() == 0, "capture failed");
+        REQUIRE(hook_calls == (int)L, "the per-layer hook runs at capture only");
+        REQUIRE(loop.device_status() == 0, "device status word");
+        // planes: bit-identical to the mirror (free slots included: nothing was written for them)
+        for (uint32_t l = 0; l < L; ++l) {
+            REQUIRE(download(loop.cache().k_cache(l), plane) == std::vector<uint16_t>(hk.begin() + l * plane, hk.begin() + (l + 1) * plane), "K plane differs");
+            REQUIRE(download(loop.cache().v_cache(l), plane) == std::vector<uint16_t>(hv.begin() + l * plane, hv.begin() + (l + 1) * plane), "V plane differs");
+        }
+        // capture failure → per-token fallback, sticky error cleared
+        hkv::GraphReplay g2(1);
+        int direct = 0;
+        const bool r = g2.run(stream, [&](cudaStream_t st) {
+            ++direct;
+            if (direct == 1) cudaStreamSynchronize(st);   // illegal during capture: invalidates it
+        });
+        REQUIRE(!r && direct == 2 && g2.capture_failures() == 1 && !g2.valid(), "failed capture falls back to direct enqueue");
+        REQUIRE(cudaGetLastError() == cudaSuccess, "sticky error left behind");
+        REQUIRE(!g2.run(stream, [&](cudaStream_t) { ++direct; }) && direct == 3, "gives up capturing after the limit");
+        cudaFree(d_q); cudaFree(d_k); cudaFree(d_v); cudaFree(d_out);
+    }
+    cudaStreamDestroy(stream);
+    std::printf("PASS: batched decode loop (sessions join/leave under one captured graph)\n");
+}
+
 int main(int argc, char** argv) {
     struct Case { const char* name; void (*fn)(); };
     const Case cases[] = {{"known_answers", test_known_answers}, {"graph_contract", test_graph_contract},
                           {"graph_contract_fused", test_graph_contract_fused},
                           {"error_behaviour", test_error_behaviour}, {"qk_norm_rope_op", test_qk_norm_rope_op},
-                          {"cache_owner", test_cache_owner}};
+                          {"cache_owner", test_cache_owner}, {"decode_loop", test_decode_loop}};
     if (argc > 1 && std::strcmp(argv[1], "--list") == 0) {
         for (const auto& c : cases) std::printf("%s\n", c.name);
         return 0;
