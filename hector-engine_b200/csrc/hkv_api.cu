@@ -22,6 +22,7 @@
 #include "hkv_decode_tma.cuh"
 #include "hkv_prefill.cuh"
 #include "hkv_prefill_tc.cuh"
+#include "hkv_prefill_tc2.cuh"
 #include "hkv_rope.cuh"
 
 using namespace hkv;
@@ -212,13 +213,14 @@ constexpr int kPrefillMaxSplits = 4;
 // and adds what the split costs (fp32 partials written and read back by the merge kernel).
 // Costs are in microseconds, from timings of the kernel on B200: ~1.55 us per 128-key tile at
 // head_dim 128, ~6 tiles' worth of overhead per item.
-int prefill_splits(const PrefillTcArgs& t, int HD, int sm_count, int min_span_tiles, bool have_ws) {
+int prefill_splits(const PrefillTcArgs& t, int HD, int q_item, double tile_us, int sm_count, int min_span_tiles,
+                   bool have_ws) {
     if (!have_ws) return 1;
     if (const char* e = getenv("HKV_PREFILL_SPLITS")) {  // tuning override
         const int v = atoi(e);
-        if (v >= 1) return v < kPrefillMaxSplits ? (v < min_span_tiles ? v : min_span_tiles) : kPrefillMaxSplits;
+        if (v >= 1) return std::min(v, std::min(kPrefillMaxSplits, min_span_tiles));
     }
-    const double tile_us = 0.60 + 0.95 * HD / 128.0, item_tiles = 6.0;
+    const double item_tiles = 6.0;
     const double row_bytes = (double)t.S_new * t.H * (HD + 2) * 4.0;
     int best = 1;
     double best_cost = 0.0;
@@ -229,9 +231,9 @@ int prefill_splits(const PrefillTcArgs& t, int HD, int sm_count, int min_span_ti
         std::fill(load.begin(), load.end(), 0.0);
         long long item = 0;
         for (int qt = t.n_qtiles - 1; qt >= 0; --qt) {
-            const int q0 = qt * t.QT;
+            const int q0 = qt * q_item;
             const int lo = t.window > 0 ? (t.past_len + q0 + 1 - t.window > 0 ? t.past_len + q0 + 1 - t.window : 0) : 0;
-            const int q_last = q0 + t.QT < t.S_new ? q0 + t.QT : t.S_new;
+            const int q_last = q0 + q_item < t.S_new ? q0 + q_item : t.S_new;
             int hi = t.past_len + q_last - 1;
             if (hi > t.slots - 1) hi = t.slots - 1;
             int ntot = hi / kPfKeys - lo / kPfKeys + 1;
@@ -569,6 +571,11 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
         e = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)prefill_tc_smem_bytes(geometry->head_dim));
         if (e != cudaSuccess) return fail_cuda(c, e, "cudaFuncSetAttribute(prefill shared memory)");
+        const void* pk2 = geometry->head_dim == 64 ? (const void*)hkv_prefill_tc2_kernel<64>
+                                                   : (const void*)hkv_prefill_tc2_kernel<128>;
+        e = cudaFuncSetAttribute(pk2, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)prefill_tc2_smem_bytes(geometry->head_dim));
+        if (e != cudaSuccess) return fail_cuda(c, e, "cudaFuncSetAttribute(prefill shared memory)");
     }
     if (prefill_tc_ok(*geometry) && geometry->max_seq_new > 0) {
         const size_t nb = (size_t)geometry->max_seq_new * kPrefillMaxSplits * geometry->num_heads *
@@ -735,19 +742,25 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
         t.KVH = g.num_kv_heads;
         t.G = G;
         t.QT = kPfRows / G;
-        t.n_qtiles = (seq_new + t.QT - 1) / t.QT;
+        // two query tiles per work item (hkv_prefill_tc2_kernel) unless the chunk is too short to
+        // give every SM an item that way
+        int pair = 1;
+        if (const char* e = getenv("HKV_PREFILL_KERNEL")) pair = atoi(e) == 1 ? 0 : 1;   // tuning override
+        const int q_item = pair ? 2 * t.QT : t.QT;
+        t.n_qtiles = (seq_new + q_item - 1) / q_item;
         t.slots = g.slots;
         t.window = g.window_size;
         t.scale_log2 = scale * 1.4426950408889634f;
         {
-            // shortest key span over the query tiles = that of the first tile (window-limited)
-            const int q_last = t.QT < seq_new ? t.QT : seq_new;
+            // shortest key span over the items = that of the first one (window-limited)
+            const int q_last = q_item < seq_new ? q_item : seq_new;
             const int first_min = g.window_size > 0 ? (past_len + 1 - g.window_size > 0 ? past_len + 1 - g.window_size : 0) : 0;
             int last_max = past_len + q_last - 1;
             if (last_max > g.slots - 1) last_max = g.slots - 1;
             const int min_span = last_max / kPfKeys - first_min / kPfKeys + 1;
             const bool have_ws = c->prefill_ws != nullptr && seq_new <= g.max_seq_new;
-            t.splits = prefill_splits(t, HD, c->sm_count, min_span, have_ws);
+            const double tile_us = pair ? 2.0 * (0.35 + 0.45 * HD / 128.0) : 0.60 + 0.95 * HD / 128.0;
+            t.splits = prefill_splits(t, HD, q_item, tile_us, c->sm_count, min_span, have_ws);
             t.part = c->prefill_ws;
         }
         CUtensorMap mq, mk, mv;
@@ -770,9 +783,15 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
         }
         const long long items = (long long)t.n_qtiles * g.num_kv_heads * t.splits;
         const int grid = items < c->sm_count ? (int)items : c->sm_count;
-        const size_t smem = prefill_tc_smem_bytes(HD);
-        if (HD == 64) hkv_prefill_tc_kernel<64><<<grid, kPfThreads, smem, (cudaStream_t)stream>>>(mq, mk, mv, t);
-        else hkv_prefill_tc_kernel<128><<<grid, kPfThreads, smem, (cudaStream_t)stream>>>(mq, mk, mv, t);
+        if (pair) {
+            const size_t smem = prefill_tc2_smem_bytes(HD);
+            if (HD == 64) hkv_prefill_tc2_kernel<64><<<grid, kPf2Threads, smem, (cudaStream_t)stream>>>(mq, mk, mv, t);
+            else hkv_prefill_tc2_kernel<128><<<grid, kPf2Threads, smem, (cudaStream_t)stream>>>(mq, mk, mv, t);
+        } else {
+            const size_t smem = prefill_tc_smem_bytes(HD);
+            if (HD == 64) hkv_prefill_tc_kernel<64><<<grid, kPfThreads, smem, (cudaStream_t)stream>>>(mq, mk, mv, t);
+            else hkv_prefill_tc_kernel<128><<<grid, kPfThreads, smem, (cudaStream_t)stream>>>(mq, mk, mv, t);
+        }
         if (t.splits > 1) {
             // merge the key-range partials of every (query, head)
             const long long rows = (long long)seq_new * g.num_heads;
@@ -1100,3 +1119,9 @@ extern "C" int hkv_decode_attention_static(const hkv_geometry* geometry, const v
     hkv_combine_kernel<<<dim3((unsigned)g.num_heads, (unsigned)g.batch), 128, 0, st>>>(c);
     return cudaPeekAtLastError() == cudaSuccess ? HKV_OK : HKV_ERR_CUDA;
 }
+
+#ifdef HKV_PF_TRACE
+extern "C" int hkv_debug_prefill_trace(long long* out, int n) {
+    return (int)cudaMemcpyFromSymbol(out, hkv::g_pf_trace, sizeof(long long) * (size_t)n);
+}
+#endif

@@ -1,0 +1,460 @@
+// hkv_prefill_tc2.cuh — the tensor-core prefill kernel with TWO query tiles in flight per CTA.
+//
+// Same contract as hkv_prefill_tc_kernel (reference kernels/attention.cu:664-788: query i attends
+// cache rows [first_i, past_len + i]), different shape of the pipeline:
+//   * Work item = (pair of query tiles A and B = 2 x QT consecutive queries, KV head, key split).
+//     Both tiles are contracted against the SAME staged K and V tiles, so shared-memory and L2
+//     traffic per flop halve.
+//   * Softmax group A (warps 0-3) owns the rows of tile A, group B (warps 4-7) those of tile B:
+//     one thread per row, all 128 score columns — no exchange between threads. The two groups
+//     are a tile-phase apart by construction: while A runs exp2 on its scores the tensor core
+//     runs  O_B += P_B·V  and  S_B = Q_B·K^T  for the other tile, and vice versa, so neither the
+//     tensor pipe nor the MUFU pipe waits for the other's latency chain.
+//   * Tensor memory (512 columns): S_A [0,128)  S_B [128,256)  O_A [256,384)  O_B [384,512).
+//     P (packed fp16, 64 columns) is written over the first half of its own S: the score MMA of
+//     the next tile is issued after P·V of this one on the same in-order pipe, so S is dead by
+//     the time P lands, and P is dead by the time the next S lands.
+//   * Issue order of warp 9 per key tile j:  PV_A(j) QK_A(j+1)  PV_B(j) QK_B(j+1).
+//   * O accumulates in tensor memory for the whole item; a row is rescaled in place (by its own
+//     thread) only when its maximum outgrows the reference by more than 2^8.
+//   * All waits are bounded mbarrier waits reporting through the status word; tensor memory is
+//     freed on every path.
+#pragma once
+
+#include "hkv_prefill_tc.cuh"
+
+namespace hkv {
+
+#ifdef HKV_PF_TRACE
+// Development aid (never compiled into the shipped library): SM-clock timestamps of the roles of
+// CTA 0, [role][tile][event].
+__device__ long long g_pf_trace[3 * 64 * 4];
+#define PF_TRACE(role, tile, k)                                                                      \
+    do {                                                                                             \
+        if (blockIdx.x == 0 && (tile) < 64u) g_pf_trace[((role) * 64 + (tile)) * 4 + (k)] = clock64(); \
+    } while (0)
+#else
+#define PF_TRACE(role, tile, k) do { } while (0)
+#endif
+
+constexpr int kPf2KStages = 2;
+constexpr int kPf2VStages = 2;
+// 12 warps: 0-3 softmax group A, 4-7 group B, 8 TMA producer, 9 MMA issuer, 10-11 only complete the
+// third warpgroup so that it can hand its registers to the softmax warps (setmaxnreg works on whole
+// warpgroups): 168 registers per thread at launch, 192 for the softmax rows, 120 for the rest.
+constexpr int kPf2Threads = 384;
+#ifndef HKV_PF2_EMU
+#define HKV_PF2_EMU 0
+#endif
+constexpr int kPf2EmuOf8 = HKV_PF2_EMU;   // pairs of every 8 whose exp2 runs on the FMA pipe
+
+__host__ __device__ constexpr size_t prefill_tc2_smem_bytes(int HD) {
+    return 1024 + (size_t)(2 + kPf2KStages + kPf2VStages) * kPfRows * HD * 2 + 32 * 8 + 64;
+}
+
+// tcgen05.wait::ld that also names the registers of the load it completes, so that no use of
+// them can be scheduled above the wait.
+__device__ __forceinline__ void tc_wait_ld_dep(uint32_t (&v)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                   "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
+                   "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]),
+                   "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+                 :
+                 : "memory");
+}
+
+// MMA wrappers with the accumulate flag as an immediate (no predicate set-up from a register).
+template <bool ACC>
+__device__ __forceinline__ void tc_mma_ss_i(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "n"(ACC ? 1 : 0)
+        : "memory");
+}
+template <bool ACC>
+__device__ __forceinline__ void tc_mma_ts_i(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "n"(ACC ? 1 : 0)
+        : "memory");
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kPf2Threads, 1)
+hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                       const __grid_constant__ CUtensorMap tm_v, const PrefillTcArgs a) {
+    static_assert(HD == 64 || HD == 128, "head_dim 64 or 128");
+    constexpr int NCH = HD / 64;                       // 64-half column blocks
+    constexpr int CHUNK_BYTES = kPfRows * 128;         // one column block of a 128-row tile
+    constexpr int TILE_BYTES = kPfRows * HD * 2;
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr uint32_t COL_S = 0, COL_O = 256;         // + 128 * group
+    constexpr uint32_t IDESC_QK = (1u << 4) | ((uint32_t)(kPfKeys >> 3) << 17) | ((uint32_t)(kPfRows >> 4) << 24);
+    constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(kPfRows >> 4) << 24);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_gen = smem;                                    // Q tiles A, B
+    uint8_t* k_gen = smem + 2 * TILE_BYTES;                   // kPf2KStages K tiles
+    uint8_t* v_gen = k_gen + kPf2KStages * TILE_BYTES;        // kPf2VStages V tiles
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_gen + kPf2VStages * TILE_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
+    const uint32_t q_smem = smem_u32(q_gen), k_smem = smem_u32(k_gen), v_smem = smem_u32(v_gen);
+    const uint32_t bar0 = smem_u32(bars);
+    // barrier map (8 bytes each)
+    const uint32_t B_QFULL = bar0, B_QEMPTY = bar0 + 8;
+    const uint32_t B_KFULL = bar0 + 16;     // [2]
+    const uint32_t B_KEMPTY = bar0 + 32;    // [2]
+    const uint32_t B_VFULL = bar0 + 48;     // [2]
+    const uint32_t B_VEMPTY = bar0 + 64;    // [2]
+    const uint32_t B_SFULL = bar0 + 80;     // [group]
+    const uint32_t B_PFULL = bar0 + 96;     // [group]
+    const uint32_t B_OFULL = bar0 + 112;    // [group] last P·V of an item has completed
+    const uint32_t B_DONE = bar0 + 128;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        mbar_init(B_QFULL, 1); mbar_init(B_QEMPTY, 1);
+        for (int s = 0; s < kPf2KStages; ++s) { mbar_init(B_KFULL + 8 * s, 1); mbar_init(B_KEMPTY + 8 * s, 1); }
+        for (int s = 0; s < kPf2VStages; ++s) { mbar_init(B_VFULL + 8 * s, 1); mbar_init(B_VEMPTY + 8 * s, 1); }
+        for (int g = 0; g < 2; ++g) { mbar_init(B_SFULL + 8 * g, 1); mbar_init(B_PFULL + 8 * g, 128); mbar_init(B_OFULL + 8 * g, 1); }
+        mbar_init(B_DONE, 1);
+        fence_mbar_init();
+        tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
+    }
+    if (warp == 9) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    // a.QT = queries per 128-row tile; a.n_qtiles counts PAIRS of tiles here
+    const int QT2 = 2 * a.QT;
+    const int n_items = a.n_qtiles * a.KVH * a.splits;
+    const int kv_valid = (a.past_len + a.S_new < a.slots) ? a.past_len + a.S_new : a.slots;
+
+    // Key-tile range of a tile pair and split (identical in every role).
+    auto tile_span = [&](int qt, int sp, int& kt_lo, int& nt) {
+        const int q0 = qt * QT2;
+        const int first_min = a.window > 0 ? (a.past_len + q0 + 1 - a.window > 0 ? a.past_len + q0 + 1 - a.window : 0) : 0;
+        int q_last = q0 + QT2 < a.S_new ? q0 + QT2 : a.S_new;
+        int last_max = a.past_len + q_last - 1;
+        if (last_max > a.slots - 1) last_max = a.slots - 1;
+        const int kt0 = first_min / kPfKeys;
+        int ntot = last_max / kPfKeys - kt0 + 1;
+        if (ntot < 1) ntot = 1;
+        const int base = ntot / a.splits, rem = ntot % a.splits;   // the host guarantees splits <= shortest span
+        kt_lo = kt0 + sp * base + (sp < rem ? sp : rem);
+        nt = base + (sp < rem ? 1 : 0);
+    };
+    auto decode_item = [&](int item, int& qt, int& kvh, int& sp) {
+        sp = item % a.splits;
+        const int rest = item / a.splits;
+        qt = a.n_qtiles - 1 - rest / a.KVH;   // longest spans first
+        kvh = rest % a.KVH;
+    };
+
+    if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 120;");
+    if (warp == 8) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            uint32_t gt = 0, it = 0, q_it = 0;
+            bool ok = true, q_pending = false;
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+                int qt, kvh, sp, kt_lo, nt;
+                decode_item(item, qt, kvh, sp);
+                tile_span(qt, sp, kt_lo, nt);
+                if (!mbar_wait(B_QEMPTY, (it & 1) ^ 1, a.status)) { ok = false; break; }
+                mbar_expect_tx(B_QFULL, (uint32_t)(2 * NCH * a.QT * a.G * 128));
+#pragma unroll
+                for (int t2 = 0; t2 < 2; ++t2)
+#pragma unroll
+                    for (int c = 0; c < NCH; ++c)
+                        tma_load_3d(q_smem + t2 * TILE_BYTES + c * CHUNK_BYTES, &tm_q, B_QFULL, c * 64, kvh * a.G,
+                                    qt * QT2 + t2 * a.QT);
+                q_pending = true;
+                q_it = it;
+                for (int t = 0; t < nt; ++t, ++gt) {
+                    const int row = (kt_lo + t) * kPfKeys;
+                    const uint32_t ks = gt % kPf2KStages, ku = gt / kPf2KStages;
+                    if (!mbar_wait(B_KEMPTY + 8 * ks, (ku & 1) ^ 1, a.status)) { ok = false; break; }
+                    mbar_expect_tx(B_KFULL + 8 * ks, TILE_BYTES);
+#pragma unroll
+                    for (int c = 0; c < NCH; ++c)
+                        tma_load_4d(k_smem + ks * TILE_BYTES + c * CHUNK_BYTES, &tm_k, B_KFULL + 8 * ks, c * 64, kvh,
+                                    row, 0);
+                    const uint32_t vs = gt % kPf2VStages, vu = gt / kPf2VStages;
+                    if (!mbar_wait(B_VEMPTY + 8 * vs, (vu & 1) ^ 1, a.status)) {
+                        mbar_wait(B_KFULL + 8 * ks, ku & 1, a.status);   // the K copy above is in flight
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(B_VFULL + 8 * vs, TILE_BYTES);
+#pragma unroll
+                    for (int c = 0; c < NCH; ++c)
+                        tma_load_4d(v_smem + vs * TILE_BYTES + c * CHUNK_BYTES, &tm_v, B_VFULL + 8 * vs, c * 64, kvh,
+                                    row, 0);
+                }
+            }
+            // drain this thread's outstanding copies before the CTA retires (tiles 0..gt-1 were issued)
+            if (q_pending) mbar_wait(B_QFULL, q_it & 1, a.status);
+            for (uint32_t i = 1; i <= (uint32_t)kPf2KStages && i <= gt; ++i) {
+                const uint32_t g = gt - i;
+                mbar_wait(B_KFULL + 8 * (g % kPf2KStages), (g / kPf2KStages) & 1, a.status);
+            }
+            for (uint32_t i = 1; i <= (uint32_t)kPf2VStages && i <= gt; ++i) {
+                const uint32_t g = gt - i;
+                mbar_wait(B_VFULL + 8 * (g % kPf2VStages), (g / kPf2VStages) & 1, a.status);
+            }
+        }
+    } else if (warp == 9) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            uint32_t gt = 0, it = 0;
+            bool ok = true;
+            // Descriptors differ only in the 14-bit start-address field (bytes >> 4): build one per
+            // tile base and add the in-tile offset per instruction.
+            const uint64_t qdesc0 = umma_desc_sw128(q_smem, 16), kdesc0 = umma_desc_sw128(k_smem, 16);
+            const uint64_t vdesc0 = umma_desc_sw128(v_smem, CHUNK_BYTES);
+            // S_grp = Q_grp · K(g)^T   (the K tile must have been waited for)
+            auto issue_qk = [&](uint32_t g, int grp) {
+                const uint64_t kd = kdesc0 + (uint64_t)(((g % kPf2KStages) * TILE_BYTES) >> 4);
+                const uint64_t qd = qdesc0 + (uint64_t)((grp * TILE_BYTES) >> 4);
+                const uint32_t d = tmem + COL_S + 128u * grp;
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint64_t off = (uint64_t)(((kk / 4) * CHUNK_BYTES + (kk % 4) * 32) >> 4);
+                    if (kk == 0) tc_mma_ss_i<false>(d, qd + off, kd + off, IDESC_QK);
+                    else tc_mma_ss_i<true>(d, qd + off, kd + off, IDESC_QK);
+                }
+                tc_commit(B_SFULL + 8 * grp);
+            };
+            // O_grp (+)= P_grp · V(g)   (P lives in the first 64 columns of S_grp)
+            auto issue_pv = [&](uint32_t g, int grp, bool accumulate) {
+                const uint64_t vd = vdesc0 + (uint64_t)(((g % kPf2VStages) * TILE_BYTES) >> 4);
+                const uint32_t pbase = tmem + COL_S + 128u * grp, d = tmem + COL_O + 128u * grp;
+                if (accumulate) tc_mma_ts_i<true>(d, pbase, vd, IDESC_PV);
+                else tc_mma_ts_i<false>(d, pbase, vd, IDESC_PV);
+#pragma unroll
+                for (int kk = 1; kk < kPfKeys / 16; ++kk)
+                    tc_mma_ts_i<true>(d, pbase + kk * 8, vd + (uint64_t)((kk * 2048) >> 4), IDESC_PV);
+            };
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+                int qt, kvh, sp, kt_lo, nt;
+                decode_item(item, qt, kvh, sp);
+                tile_span(qt, sp, kt_lo, nt);
+                if (!mbar_wait(B_QFULL, it & 1, a.status) ||
+                    !mbar_wait(B_KFULL + 8 * (gt % kPf2KStages), (gt / kPf2KStages) & 1, a.status)) { ok = false; break; }
+                tc_fence_after();
+                issue_qk(gt, 0);
+                issue_qk(gt, 1);
+                tc_commit(B_KEMPTY + 8 * (gt % kPf2KStages));
+                if (nt == 1) tc_commit(B_QEMPTY);
+                for (int t = 0; t < nt && ok; ++t, ++gt) {
+                    const bool more = t + 1 < nt;
+                    const uint32_t vs = gt % kPf2VStages, ks1 = (gt + 1) % kPf2KStages;
+#pragma unroll
+                    for (int grp = 0; grp < 2; ++grp) {
+                        if (!mbar_wait(B_PFULL + 8 * grp, gt & 1, a.status)) { ok = false; break; }
+                        if (grp == 0) {
+                            if (!mbar_wait(B_VFULL + 8 * vs, (gt / kPf2VStages) & 1, a.status)) { ok = false; break; }
+                            if (more && !mbar_wait(B_KFULL + 8 * ks1, ((gt + 1) / kPf2KStages) & 1, a.status)) { ok = false; break; }
+                        }
+                        tc_fence_after();
+                        PF_TRACE(2, gt, grp * 2);
+                        issue_pv(gt, grp, t > 0);
+                        if (!more) tc_commit(B_OFULL + 8 * grp);        // the item's output of this tile is complete
+                        if (grp == 1) tc_commit(B_VEMPTY + 8 * vs);     // both tiles have consumed V(g)
+                        if (more) {
+                            issue_qk(gt + 1, grp);
+                            if (grp == 1) {
+                                tc_commit(B_KEMPTY + 8 * ks1);
+                                if (t + 2 == nt) tc_commit(B_QEMPTY);   // last score MMAs of the item issued
+                            }
+                        }
+                        PF_TRACE(2, gt, grp * 2 + 1);
+                    }
+                }
+            }
+            // every MMA issued above has completed before tensor memory is freed
+            tc_commit(B_DONE);
+            mbar_wait(B_DONE, 0, a.status);
+        }
+    }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 192;");
+        // ------------------------------ softmax / output rows ------------------------------
+        const int quad = warp & 3, grp = warp >> 2;
+        const int r = quad * 32 + lane;            // row of the tile = lane of tensor memory
+        const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
+        const uint32_t s_addr = tmem + lane_sel + COL_S + 128u * grp;
+        const uint32_t o_addr = tmem + lane_sel + COL_O + 128u * grp;
+        const uint32_t b_sfull = B_SFULL + 8 * grp, b_pfull = B_PFULL + 8 * grp, b_ofull = B_OFULL + 8 * grp;
+        const int ql = r / a.G, g = r % a.G;
+        uint32_t gt = 0, si = 0;   // tiles seen, items done (barrier phases)
+        bool ok = true;            // kept warp-uniform: a wait that ran out for any lane stops the warp
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+            int qt, kvh, sp, kt_lo, nt;
+            decode_item(item, qt, kvh, sp);
+            tile_span(qt, sp, kt_lo, nt);
+            const int qi = qt * QT2 + grp * a.QT + ql;
+            const bool row_valid = ql < a.QT && qi < a.S_new;
+            const int qpos = a.past_len + qi;
+            const int first_row = a.window > 0 ? (qpos + 1 - a.window > 0 ? qpos + 1 - a.window : 0) : 0;
+            const int qlim = qpos < a.slots ? qpos : a.slots - 1;  // never attend rows past the plane
+            // m_ref: the reference maximum P and O are scaled by; it moves (and O is rescaled) only
+            // when a tile's maximum exceeds it by more than 2^8 — fp16 holds P up to that factor.
+            float m_ref = kNegBig, l_run = 0.0f;
+
+            for (int t = 0; t < nt; ++t, ++gt) {
+                ok = __all_sync(0xffffffffu, ok && mbar_wait(b_sfull, gt & 1, a.status));
+                if (!ok) continue;
+                tc_fence_after();
+                if (lane == 0 && quad == 0) PF_TRACE(grp, gt, 0);
+                const int kstart = (kt_lo + t) * kPfKeys;
+                const int lo = first_row - kstart, hi = qlim - kstart;   // attended columns [lo, hi]
+                const bool all_in = __all_sync(0xffffffffu, lo <= 0 && hi >= kPfKeys - 1);
+                // ---- the row's 128 scores, read once ----
+                uint32_t sv[4][32];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld32(sv[c], s_addr + c * 32);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tc_wait_ld_dep(sv[c]);
+                // ---- row maximum of the raw scores (the scale is positive) ----
+                float mx;
+                {
+                    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;   // independent chains
+                    if (all_in) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                m0 = fmax3(m0, __uint_as_float(sv[c][j]), __uint_as_float(sv[c][j + 1]));
+                                m1 = fmax3(m1, __uint_as_float(sv[c][j + 2]), __uint_as_float(sv[c][j + 3]));
+                                m2 = fmax3(m2, __uint_as_float(sv[c][j + 4]), __uint_as_float(sv[c][j + 5]));
+                                m3 = fmax3(m3, __uint_as_float(sv[c][j + 6]), __uint_as_float(sv[c][j + 7]));
+                            }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const int col = c * 32 + j;
+                                const float sc = (col >= lo && col <= hi) ? __uint_as_float(sv[c][j]) : -INFINITY;
+                                sv[c][j] = __float_as_uint(sc);
+                                m0 = fmaxf(m0, sc);
+                            }
+                    }
+                    mx = fmaxf(fmax3(m0, m1, m2), m3);
+                }
+                mx *= a.scale_log2;
+                if (lane == 0 && quad == 0) PF_TRACE(grp, gt, 1);
+                const bool move = mx > m_ref + 8.0f;
+                if (__any_sync(0xffffffffu, move)) {
+                    const float m_to = move ? mx : m_ref;
+                    const float alpha = ex2_approx(m_ref - m_to);   // 1 for rows that keep their reference
+                    // The score MMA of this tile was issued after P·V of the previous one, so O is
+                    // complete up to tile t-1 here.
+                    if (t > 0) tmem_scale_columns(o_addr, HD / 32, alpha);
+                    l_run *= alpha;
+                    m_ref = m_to;
+                }
+                // ---- p = 2^(s*scale - m_ref), row sum, P back to tensor memory as packed fp16 ----
+                float lsum0 = 0.0f, lsum1 = 0.0f, lsum2 = 0.0f, lsum3 = 0.0f;
+                const float neg_m = -m_ref;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        float x0, x1, x2, x3;
+                        ffma2_bcast(x0, x1, __uint_as_float(sv[c][j]), __uint_as_float(sv[c][j + 1]), a.scale_log2, neg_m);
+                        ffma2_bcast(x2, x3, __uint_as_float(sv[c][j + 2]), __uint_as_float(sv[c][j + 3]), a.scale_log2, neg_m);
+                        // kPf2EmuOf8 of every 8 pairs take the FMA-pipe exp2, the rest the MUFU pipe
+                        float p0, p1, p2, p3;
+                        if (((j / 4) * 2) % 8 < kPf2EmuOf8) ex2_emu2(p0, p1, x0, x1);
+                        else { p0 = ex2_approx(x0); p1 = ex2_approx(x1); }
+                        if (((j / 4) * 2 + 1) % 8 < kPf2EmuOf8) ex2_emu2(p2, p3, x2, x3);
+                        else { p2 = ex2_approx(x2); p3 = ex2_approx(x3); }
+                        fadd2_acc(lsum0, lsum1, p0, p1);
+                        fadd2_acc(lsum2, lsum3, p2, p3);
+                        pk[j / 2] = pack_half2(p0, p1);
+                        pk[j / 2 + 1] = pack_half2(p2, p3);
+                    }
+                    // P columns [16c, 16c+16) of this row overwrite its scores, all of which are in registers
+                    tmem_st16(s_addr + c * 16, pk);
+                }
+                tc_wait_st();
+                if (lane == 0 && quad == 0) PF_TRACE(grp, gt, 2);
+                l_run += (lsum0 + lsum1) + (lsum2 + lsum3);
+                // cache rows of this tile past the last written position may hold stale bits: group A
+                // zeroes them in the staged V tile (before its arrival below, which precedes both
+                // output MMAs of the tile) so that 0 * garbage cannot produce NaN
+                const int tile0 = (kt_lo + t) * kPfKeys;
+                if (grp == 0 && tile0 + kPfKeys > kv_valid) {
+                    const uint32_t vs = gt % kPf2VStages;
+                    ok = __all_sync(0xffffffffu, mbar_wait(B_VFULL + 8 * vs, (gt / kPf2VStages) & 1, a.status));
+                    if (!ok) continue;
+                    uint8_t* vt = v_gen + (size_t)vs * TILE_BYTES;
+                    const int first_bad = kv_valid > tile0 ? kv_valid - tile0 : 0;
+                    for (int idx = first_bad * 8 * NCH + tid; idx < kPfKeys * 8 * NCH; idx += 128) {
+                        const int row = idx / (8 * NCH), u = idx % (8 * NCH);
+                        *reinterpret_cast<uint4*>(vt + (u / 8) * CHUNK_BYTES + row * 128 + (u % 8) * 16) =
+                            make_uint4(0, 0, 0, 0);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+                tc_fence_before();
+                mbar_arrive(b_pfull);
+                if (lane == 0 && quad == 0) PF_TRACE(grp, gt, 3);
+            }
+            // Wait for the item's last P·V of this tile, then write the row out.
+            ok = __all_sync(0xffffffffu, ok && mbar_wait(b_ofull, si & 1, a.status));
+            ++si;
+            if (!ok) continue;
+            tc_fence_after();
+            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+            float* prow = nullptr;
+            __half* op = nullptr;
+            if (row_valid) {
+                if (a.splits > 1) prow = a.part + (((long long)qi * a.splits + sp) * a.H + (long long)kvh * a.G + g) * (HD + 2);
+                else op = a.out + ((long long)qi * a.H + (long long)kvh * a.G + g) * HD;
+            }
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(v, o_addr + c * 32);
+                tc_wait_ld_dep(v);
+                if (prow) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2)
+                        *reinterpret_cast<float2*>(prow + c * 32 + j) = make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                } else if (op) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint4 w;
+                        w.x = pack_half2(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv);
+                        w.y = pack_half2(__uint_as_float(v[j + 2]) * inv, __uint_as_float(v[j + 3]) * inv);
+                        w.z = pack_half2(__uint_as_float(v[j + 4]) * inv, __uint_as_float(v[j + 5]) * inv);
+                        w.w = pack_half2(__uint_as_float(v[j + 6]) * inv, __uint_as_float(v[j + 7]) * inv);
+                        *reinterpret_cast<uint4*>(op + c * 32 + j) = w;
+                    }
+                }
+            }
+            if (prow) {
+                prow[HD] = m_ref;
+                prow[HD + 1] = l_run;
+            }
+            tc_fence_before();
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+}  // namespace hkv
