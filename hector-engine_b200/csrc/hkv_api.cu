@@ -220,7 +220,7 @@ int prefill_splits(const PrefillTcArgs& t, int HD, int q_item, double tile_us, i
         const int v = atoi(e);
         if (v >= 1) return std::min(v, std::min(kPrefillMaxSplits, min_span_tiles));
     }
-    const double item_tiles = 6.0;
+    const double item_tiles = q_item > t.QT ? 3.0 : 6.0;
     const double row_bytes = (double)t.S_new * t.H * (HD + 2) * 4.0;
     int best = 1;
     double best_cost = 0.0;
@@ -742,10 +742,9 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
         t.KVH = g.num_kv_heads;
         t.G = G;
         t.QT = kPfRows / G;
-        // two query tiles per work item (hkv_prefill_tc2_kernel) unless the chunk is too short to
-        // give every SM an item that way
-        int pair = 1;
-        if (const char* e = getenv("HKV_PREFILL_KERNEL")) pair = atoi(e) == 1 ? 0 : 1;   // tuning override
+        // two query tiles per work item (hkv_prefill_tc2_kernel) unless the whole chunk fits one tile
+        int pair = seq_new > t.QT ? 1 : 0;
+        if (const char* e = getenv("HKV_PREFILL_KERNEL")) pair = atoi(e) == 1 ? 0 : 1;   // A/B override
         const int q_item = pair ? 2 * t.QT : t.QT;
         t.n_qtiles = (seq_new + q_item - 1) / q_item;
         t.slots = g.slots;
@@ -759,7 +758,7 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
             if (last_max > g.slots - 1) last_max = g.slots - 1;
             const int min_span = last_max / kPfKeys - first_min / kPfKeys + 1;
             const bool have_ws = c->prefill_ws != nullptr && seq_new <= g.max_seq_new;
-            const double tile_us = pair ? 2.0 * (0.35 + 0.45 * HD / 128.0) : 0.60 + 0.95 * HD / 128.0;
+            const double tile_us = pair ? 1.0 + 0.9 * HD / 128.0 : 0.60 + 0.95 * HD / 128.0;   // per key tile of an item
             t.splits = prefill_splits(t, HD, q_item, tile_us, c->sm_count, min_span, have_ws);
             t.part = c->prefill_ws;
         }

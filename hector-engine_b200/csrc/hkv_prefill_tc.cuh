@@ -161,36 +161,6 @@ __device__ __forceinline__ void fadd2_acc(float& d0, float& d1, float a0, float 
         : "f"(a0), "f"(a1));
 }
 
-// 2^x for two values on the FMA pipe (the MUFU pipe is the narrowest unit of the softmax: 16
-// ex2 per clock per SM). x is clamped to [-100, +inf); callers keep x <= ~9. Round-to-nearest
-// split x = n + f, f in [-0.5, 0.5], by adding 1.5*2^23; 2^f by a degree-3 minimax polynomial
-// (max relative error 7.5e-5, below half an ulp of the fp16 the result is rounded to); 2^n by
-// adding n to the exponent field.
-__device__ __forceinline__ void ex2_emu2(float& p0, float& p1, float x0, float x1) {
-    x0 = fmaxf(x0, -100.0f);
-    x1 = fmaxf(x1, -100.0f);
-    uint32_t t0, t1, q0, q1;
-    asm("{\n\t.reg .b64 rx, rt, rr, rf, rp, rc;\n\t"
-        "mov.b64 rx, {%4, %5};\n\t"
-        "mov.b64 rc, {0f4B400000, 0f4B400000};\n\t"      // 12582912.0
-        "add.rn.f32x2 rt, rx, rc;\n\t"                    // n in the low mantissa bits
-        "sub.rn.f32x2 rr, rt, rc;\n\t"                    // n as a float
-        "sub.rn.f32x2 rf, rx, rr;\n\t"                    // f = x - n
-        "mov.b64 rp, {0f3D61FB59, 0f3D61FB59};\n\t"      // 0.055171344
-        "mov.b64 rc, {0f3E786ED8, 0f3E786ED8};\n\t"      // 0.24261034
-        "fma.rn.f32x2 rp, rp, rf, rc;\n\t"
-        "mov.b64 rc, {0f3F31798D, 0f3F31798D};\n\t"      // 0.69326097
-        "fma.rn.f32x2 rp, rp, rf, rc;\n\t"
-        "mov.b64 rc, {0f3F7FFB4A, 0f3F7FFB4A};\n\t"      // 0.9999281
-        "fma.rn.f32x2 rp, rp, rf, rc;\n\t"
-        "mov.b64 {%0, %1}, rt;\n\t"
-        "mov.b64 {%2, %3}, rp;\n\t}"
-        : "=r"(t0), "=r"(t1), "=r"(q0), "=r"(q1)
-        : "f"(x0), "f"(x1));
-    p0 = __uint_as_float(q0 + (t0 << 23));
-    p1 = __uint_as_float(q1 + (t1 << 23));
-}
-
 // Rare path of the softmax warps: scale this thread's n32*32 columns of O (tensor memory) by
 // alpha. Kept out of line so that its registers do not weigh on the per-tile loop.
 __device__ __noinline__ void tmem_scale_columns(uint32_t addr, int n32, float alpha) {

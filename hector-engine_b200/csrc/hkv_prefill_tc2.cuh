@@ -43,10 +43,7 @@ constexpr int kPf2VStages = 2;
 // third warpgroup so that it can hand its registers to the softmax warps (setmaxnreg works on whole
 // warpgroups): 168 registers per thread at launch, 192 for the softmax rows, 120 for the rest.
 constexpr int kPf2Threads = 384;
-#ifndef HKV_PF2_EMU
-#define HKV_PF2_EMU 0
-#endif
-constexpr int kPf2EmuOf8 = HKV_PF2_EMU;   // pairs of every 8 whose exp2 runs on the FMA pipe
+
 
 __host__ __device__ constexpr size_t prefill_tc2_smem_bytes(int HD) {
     return 1024 + (size_t)(2 + kPf2KStages + kPf2VStages) * kPfRows * HD * 2 + 32 * 8 + 64;
@@ -257,13 +254,13 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 for (int t = 0; t < nt && ok; ++t, ++gt) {
                     const bool more = t + 1 < nt;
                     const uint32_t vs = gt % kPf2VStages, ks1 = (gt + 1) % kPf2KStages;
+                    // the operand tiles of this step first (they land long before P does), so that
+                    // nothing stands between the arrival of P and the first MMA
+                    if (!mbar_wait(B_VFULL + 8 * vs, (gt / kPf2VStages) & 1, a.status) ||
+                        (more && !mbar_wait(B_KFULL + 8 * ks1, ((gt + 1) / kPf2KStages) & 1, a.status))) { ok = false; break; }
 #pragma unroll
                     for (int grp = 0; grp < 2; ++grp) {
                         if (!mbar_wait(B_PFULL + 8 * grp, gt & 1, a.status)) { ok = false; break; }
-                        if (grp == 0) {
-                            if (!mbar_wait(B_VFULL + 8 * vs, (gt / kPf2VStages) & 1, a.status)) { ok = false; break; }
-                            if (more && !mbar_wait(B_KFULL + 8 * ks1, ((gt + 1) / kPf2KStages) & 1, a.status)) { ok = false; break; }
-                        }
                         tc_fence_after();
                         PF_TRACE(2, gt, grp * 2);
                         issue_pv(gt, grp, t > 0);
@@ -315,13 +312,13 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 if (!ok) continue;
                 tc_fence_after();
                 if (lane == 0 && quad == 0) PF_TRACE(grp, gt, 0);
-                const int kstart = (kt_lo + t) * kPfKeys;
-                const int lo = first_row - kstart, hi = qlim - kstart;   // attended columns [lo, hi]
-                const bool all_in = __all_sync(0xffffffffu, lo <= 0 && hi >= kPfKeys - 1);
-                // ---- the row's 128 scores, read once ----
+                // ---- the row's 128 scores, read once (mask bounds are computed under the loads) ----
                 uint32_t sv[4][32];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) tmem_ld32(sv[c], s_addr + c * 32);
+                const int kstart = (kt_lo + t) * kPfKeys;
+                const int lo = first_row - kstart, hi = qlim - kstart;   // attended columns [lo, hi]
+                const bool all_in = __all_sync(0xffffffffu, lo <= 0 && hi >= kPfKeys - 1);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) tc_wait_ld_dep(sv[c]);
                 // ---- row maximum of the raw scores (the scale is positive) ----
@@ -374,12 +371,7 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                         float x0, x1, x2, x3;
                         ffma2_bcast(x0, x1, __uint_as_float(sv[c][j]), __uint_as_float(sv[c][j + 1]), a.scale_log2, neg_m);
                         ffma2_bcast(x2, x3, __uint_as_float(sv[c][j + 2]), __uint_as_float(sv[c][j + 3]), a.scale_log2, neg_m);
-                        // kPf2EmuOf8 of every 8 pairs take the FMA-pipe exp2, the rest the MUFU pipe
-                        float p0, p1, p2, p3;
-                        if (((j / 4) * 2) % 8 < kPf2EmuOf8) ex2_emu2(p0, p1, x0, x1);
-                        else { p0 = ex2_approx(x0); p1 = ex2_approx(x1); }
-                        if (((j / 4) * 2 + 1) % 8 < kPf2EmuOf8) ex2_emu2(p2, p3, x2, x3);
-                        else { p2 = ex2_approx(x2); p3 = ex2_approx(x3); }
+                        const float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
                         fadd2_acc(lsum0, lsum1, p0, p1);
                         fadd2_acc(lsum2, lsum3, p2, p3);
                         pk[j / 2] = pack_half2(p0, p1);
