@@ -81,53 +81,86 @@ def parse_args():
 # clocks
 # ---------------------------------------------------------------------------
 class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU while the timed region runs.
+
+    The query process is started before warm-up (it needs ~0.1 s to come up) and streams a sample
+    every 20 ms; a reader thread stamps each line on receipt and only the samples received between
+    begin() and end() count. A region too short to catch three samples is followed by extra,
+    untimed steps of the same work (`keep_loaded`) until three have been taken; the record says so."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, gpu_id: str):
         self.gpu_id = gpu_id
         self.proc = None
-        self.path = None
+        self.samples = []   # (receipt time, [fields])
+        self.t0 = self.t1 = None
+        self.thread = None
 
     def start(self):
+        import threading
         try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", self.gpu_id, f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+                 "--format=csv,noheader,nounits", "-lms", "20"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, bufsize=1)
         except Exception:
             self.proc = None
+            return
 
-    def stop(self) -> dict:
+        def reader():
+            try:
+                for line in self.proc.stdout:
+                    self.samples.append((time.monotonic(), [p.strip() for p in line.split(",")]))
+            except Exception:
+                pass
+        self.thread = threading.Thread(target=reader, daemon=True)
+        self.thread.start()
+
+    def begin(self):
+        self.t0 = time.monotonic()
+
+    def end(self):
+        self.t1 = time.monotonic()
+
+    def _in_region(self):
+        if self.t0 is None:
+            return list(self.samples)
+        t1 = self.t1 if self.t1 is not None else time.monotonic()
+        return [f for (t, f) in list(self.samples) if self.t0 <= t <= t1 and len(f) >= 7]
+
+    def stop(self, keep_loaded=None) -> dict:
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
             return out
-        time.sleep(0.15)
+        if self.t1 is None:
+            self.end()
+        if keep_loaded is not None and len(self._in_region()) < 3:
+            # the timed region was shorter than the sampling period: same load, untimed
+            out["sampled_under"] = "extra untimed steps of the same work after the timed region"
+            self.t0 = time.monotonic()
+            self.t1 = None
+            deadline = time.monotonic() + 2.0
+            while len(self._in_region()) < 3 and time.monotonic() < deadline:
+                keep_loaded()
+            self.end()
+        rows = self._in_region()
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
         sm, smax, reasons, power = [], [], set(), []
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        try:
-            for line in open(self.path):
-                parts = [p.strip() for p in line.split(",")]
-                if len(parts) < 7:
-                    continue
-                try:
-                    sm.append(float(parts[0])); smax.append(float(parts[1])); power.append(float(parts[2]))
-                except ValueError:
-                    continue
-                for n, v in zip(names, parts[3:7]):
-                    if v.lower().startswith("active"):
-                        reasons.add(n)
-            os.unlink(self.path)
-        except Exception:
-            pass
+        for parts in rows:
+            try:
+                sm.append(float(parts[0])); smax.append(float(parts[1])); power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for n, v in zip(self.NAMES, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
         if sm:
             out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=float(max(smax)), samples=len(sm),
                        power_w_max=float(max(power)))
@@ -380,23 +413,37 @@ def run_seqsplit(args, torch, hkv, dist, cfg, ctx_local, B, rank, world, base, g
             dist.barrier()
             torch.cuda.synchronize()
 
+    sampler = ClockSampler(gpu_id)
+    sampler.start()
     for _ in range(args.warmup):
         step()
     d_tot.copy_(h_tot)
-    sampler = ClockSampler(gpu_id)
     barrier()
-    sampler.start()
+    sampler.begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
         step()
     e1.record()
     barrier()
-    clocks = sampler.stop()
+    sampler.end()
     ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
     if dist is not None:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms_per_step = float(ms.item()) / args.steps
+    extended = None
+    if float(ms.item()) < 150.0:
+        # shorter than a few sampling periods: every rank runs the same number of extra, untimed
+        # steps (the step holds a collective) and the clocks are sampled under that same load
+        sampler.begin()
+        for _ in range(int(math.ceil(150.0 / max(ms_per_step, 1e-3)))):
+            step()
+        barrier()
+        sampler.end()
+        extended = "extra untimed steps of the same work after the timed region"
+    clocks = sampler.stop()
+    if extended:
+        clocks["sampled_under"] = extended
     assert dec.ctx.device_status() == 0
     # algorithmic bytes over ALL ranks: the K/V rows of every sequence once, + new rows + q/out per rank
     Ls = np.stack([np.minimum(pos0 + 1 + s, logical) for s in range(args.steps)]).astype(np.int64)
@@ -452,11 +499,12 @@ def run_prefill(args, torch, hkv, oracle, cfg, rank, base, gpu_id):
             ok, e = oracle.within_tolerance(got[lo:lo + 4], ref[lo:lo + 4])
             assert ok, f"prefill parity failed at query {lo}: {e:.3e}"
             err = max(err, e)
+    sampler = ClockSampler(gpu_id)
+    sampler.start()
     for _ in range(args.warmup):
         step()
-    sampler = ClockSampler(gpu_id)
     torch.cuda.synchronize()
-    sampler.start()
+    sampler.begin()
     e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
     attn_ms = 0.0
     evs = []
@@ -466,7 +514,8 @@ def run_prefill(args, torch, hkv, oracle, cfg, rank, base, gpu_id):
         b.record(); ctx.prefill_attention(q, k, v, out, S, past, scale)
         c.record(); evs.append((a, b, c))
     torch.cuda.synchronize()
-    clocks = sampler.stop()
+    sampler.end()
+    clocks = sampler.stop(keep_loaded=lambda: (step(), torch.cuda.synchronize()))
     tot_ms = sum(a.elapsed_time(c) for a, b, c in evs) / args.steps
     attn_ms = sum(b.elapsed_time(c) for a, b, c in evs) / args.steps
     flops = 4.0 * H * HD * sum(past + i + 1 for i in range(S))
@@ -540,7 +589,9 @@ def main():
     if args.impl == "reference":
         sampler = ClockSampler(gpu_id)
         sampler.start()
+        sampler.begin()
         res = run_reference(args, torch, hkv, oracle, cfg, ctx, B, rank)
+        sampler.end()
         clocks = sampler.stop()
         if res is None:
             print(json.dumps({"impl": "reference", "unavailable":
@@ -579,22 +630,30 @@ def main():
         verify_err = verify(w, oracle, layer=L // 2, seqs=sorted({0, B // 2, B - 1}))
 
     # device-resident timing
+    sampler = ClockSampler(gpu_id)
+    sampler.start()
     w.reset_positions()
     for _ in range(args.warmup):
         w.step_device()
     w.reset_positions()
-    sampler = ClockSampler(gpu_id)
     barrier()
-    sampler.start()
     for c in w.ctxs.values():
         c.profile_begin(args.steps * L)
+    sampler.begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
         w.step_device()
     e1.record()
     barrier()
-    clocks = sampler.stop()
+    sampler.end()
+    dec_ms = comb_ms = 0.0
+    calls = 0
+    for c in w.ctxs.values():
+        d_, m_, n_ = c.profile_end()
+        dec_ms, comb_ms, calls = dec_ms + d_, comb_ms + m_, calls + n_
+    # (no collective inside the extra steps: every rank extends its own load independently)
+    clocks = sampler.stop(keep_loaded=lambda: (w.step_device(), torch.cuda.synchronize()))
     graph_ms = None
     if args.graph:
         # The engine's own contract: the whole step captured ONCE, then replayed while only the
@@ -617,11 +676,6 @@ def main():
             g1.record(side)
             side.synchronize()
         graph_ms = g0.elapsed_time(g1) / args.steps
-    dec_ms = comb_ms = 0.0
-    calls = 0
-    for c in w.ctxs.values():
-        d_, m_, n_ = c.profile_end()
-        dec_ms, comb_ms, calls = dec_ms + d_, comb_ms + m_, calls + n_
     ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
     if dist is not None:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
