@@ -425,7 +425,7 @@ int launch_combine(hkv_ctx* c, const float* part, long long stride_b, long long 
     a.out = (__half*)out;
     a.out_partial = out_partial;
     dim3 grid((unsigned)c->g.num_heads, (unsigned)c->g.batch);
-    hkv_combine_kernel<<<grid, 128, 0, st>>>(a);
+    hkv_combine_kernel<<<grid, kCombineThreads, 0, st>>>(a);
     return HKV_OK;
 }
 
@@ -1115,7 +1115,7 @@ extern "C" int hkv_decode_attention_static(const hkv_geometry* geometry, const v
     c.HD = g.head_dim;
     c.out = (__half*)out;
     c.out_partial = nullptr;
-    hkv_combine_kernel<<<dim3((unsigned)g.num_heads, (unsigned)g.batch), 128, 0, st>>>(c);
+    hkv_combine_kernel<<<dim3((unsigned)g.num_heads, (unsigned)g.batch), kCombineThreads, 0, st>>>(c);
     return cudaPeekAtLastError() == cudaSuccess ? HKV_OK : HKV_ERR_CUDA;
 }
 

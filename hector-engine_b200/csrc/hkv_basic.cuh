@@ -161,7 +161,15 @@ struct CombineArgs {
     float* out_partial;  // [B, H, HD+2] or null
 };
 
-__global__ void __launch_bounds__(128) hkv_combine_kernel(const CombineArgs a) {
+constexpr int kCombineWarps = 8;
+constexpr int kCombineThreads = kCombineWarps * 32;
+
+// One CTA per (head, sequence). The partials are dealt to the warps (warp w takes c = w, w+8, ...);
+// a warp reads one partial row at a time, lane l the output dimensions l, l+32, ... — coalesced
+// 128-byte pieces, several rows in flight — so the merge is bandwidth- rather than latency-bound
+// even when a single sequence has 128 partials and only `heads` CTAs exist. Warps then reduce
+// through shared memory.
+__global__ void __launch_bounds__(kCombineThreads) hkv_combine_kernel(const CombineArgs a) {
     const int h = blockIdx.x, b = blockIdx.y;
     int n = a.fixed_count;
     if (a.total) {
@@ -171,55 +179,55 @@ __global__ void __launch_bounds__(128) hkv_combine_kernel(const CombineArgs a) {
     const int PW = a.HD + 2;
     const float* base = a.part + b * a.stride_b + (long long)h * PW;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    __shared__ float s_red[4];
-    __shared__ float s_w[128];
-    // M = max over partials: the chunks are spread over the threads, so the loads overlap
+    __shared__ float s_red[kCombineWarps];
+    __shared__ float s_acc[kCombineWarps][512];   // head_dim <= 512
+    // M = max over partials
     float M = kNegBig;
-    for (int c = tid; c < n; c += 128) M = fmaxf(M, base[c * a.stride_c + a.HD]);
+    for (int c = tid; c < n; c += kCombineThreads) M = fmaxf(M, base[c * a.stride_c + a.HD]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
     if (lane == 0) s_red[warp] = M;
     __syncthreads();
-    M = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
-    float L = 0.0f;        // thread-partial sum of weights * l, reduced at the end
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // output dims tid, tid+128, ... (head_dim <= 512)
-    for (int c0 = 0; c0 < n; c0 += 128) {
-        const int nb = n - c0 < 128 ? n - c0 : 128;
-        __syncthreads();
-        if (tid < nb) {
-            const float* row = base + (long long)(c0 + tid) * a.stride_c;
-            const float w = exp2f(row[a.HD] - M);
-            s_w[tid] = w;
-            L = fmaf(row[a.HD + 1], w, L);
-        }
-        __syncthreads();
+    M = s_red[0];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int d = tid + 128 * i;
-            if (d < a.HD) {
-                float o = acc[i];
-#pragma unroll 8
-                for (int c = 0; c < nb; ++c) o = fmaf(base[(long long)(c0 + c) * a.stride_c + d], s_w[c], o);
-                acc[i] = o;
-            }
+    for (int w = 1; w < kCombineWarps; ++w) M = fmaxf(M, s_red[w]);
+    __syncthreads();   // s_red is reused below
+    // this warp's share
+    const int ndim = (a.HD + 31) >> 5;   // dimensions per lane, <= 16
+    float acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
+    float L = 0.0f;
+#pragma unroll 4
+    for (int c = warp; c < n; c += kCombineWarps) {   // unrolled: four rows' loads in flight per warp
+        const float* row = base + (long long)c * a.stride_c;
+        const float w = exp2f(row[a.HD] - M);
+        L = fmaf(row[a.HD + 1], w, L);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int d = lane + 32 * i;
+            if (i < ndim && d < a.HD) acc[i] = fmaf(row[d], w, acc[i]);
         }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
-    __syncthreads();
+    for (int i = 0; i < 16; ++i) {
+        const int d = lane + 32 * i;
+        if (i < ndim && d < a.HD) s_acc[warp][d] = acc[i];
+    }
     if (lane == 0) s_red[warp] = L;
     __syncthreads();
-    L = s_red[0] + s_red[1] + s_red[2] + s_red[3];
-    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    L = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int d = tid + 128 * i;
-        if (d < a.HD) {
-            if (a.out) a.out[((long long)b * a.H + h) * a.HD + d] = __float2half_rn(acc[i] * inv);
-            if (a.out_partial) a.out_partial[((long long)b * a.H + h) * PW + d] = acc[i];
-        }
+    for (int w = 0; w < kCombineWarps; ++w) L += s_red[w];
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    for (int d = tid; d < a.HD; d += kCombineThreads) {
+        float o = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kCombineWarps; ++w) o += s_acc[w][d];
+        if (a.out) a.out[((long long)b * a.H + h) * a.HD + d] = __float2half_rn(o * inv);
+        if (a.out_partial) a.out_partial[((long long)b * a.H + h) * PW + d] = o;
     }
-    if (a.out_partial && threadIdx.x == 0) {
+    if (a.out_partial && tid == 0) {
         float* row = a.out_partial + ((long long)b * a.H + h) * PW;
         row[a.HD] = M;
         row[a.HD + 1] = L;
