@@ -43,6 +43,10 @@ constexpr int kPf2VStages = 2;
 // third warpgroup so that it can hand its registers to the softmax warps (setmaxnreg works on whole
 // warpgroups): 168 registers per thread at launch, 192 for the softmax rows, 120 for the rest.
 constexpr int kPf2Threads = 384;
+#ifndef HKV_PF2_EMU
+#define HKV_PF2_EMU 3
+#endif
+constexpr int kPf2EmuOf8 = HKV_PF2_EMU;   // pairs of every 8 whose exp2 runs on the FMA pipe
 
 
 __host__ __device__ constexpr size_t prefill_tc2_smem_bytes(int HD) {
@@ -61,21 +65,71 @@ __device__ __forceinline__ void tc_wait_ld_dep(uint32_t (&v)[32]) {
                  : "memory");
 }
 
-// MMA wrappers with the accumulate flag as an immediate (no predicate set-up from a register).
-template <bool ACC>
-__device__ __forceinline__ void tc_mma_ss_i(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+// 2^x for two values on the FMA pipe (the MUFU pipe is the narrowest unit of the softmax: 16
+// ex2 per clock per SM). x is clamped to [-100, +inf); callers keep x <= ~9. Round-to-nearest
+// split x = n + f, f in [-0.5, 0.5], by adding 1.5*2^23; 2^f by a degree-3 minimax polynomial
+// (max relative error 7.5e-5, below half an ulp of the fp16 the result is rounded to); 2^n by
+// adding n to the exponent field.
+__device__ __forceinline__ void ex2_emu2(float& p0, float& p1, float x0, float x1) {
+    x0 = fmaxf(x0, -100.0f);
+    x1 = fmaxf(x1, -100.0f);
+    uint32_t t0, t1, q0, q1;
+    asm("{\n\t.reg .b64 rx, rt, rr, rf, rp, rc;\n\t"
+        "mov.b64 rx, {%4, %5};\n\t"
+        "mov.b64 rc, {0f4B400000, 0f4B400000};\n\t"      // 12582912.0
+        "add.rn.f32x2 rt, rx, rc;\n\t"                    // n in the low mantissa bits
+        "sub.rn.f32x2 rr, rt, rc;\n\t"                    // n as a float
+        "sub.rn.f32x2 rf, rx, rr;\n\t"                    // f = x - n
+        "mov.b64 rp, {0f3D61FB59, 0f3D61FB59};\n\t"      // 0.055171344
+        "mov.b64 rc, {0f3E786ED8, 0f3E786ED8};\n\t"      // 0.24261034
+        "fma.rn.f32x2 rp, rp, rf, rc;\n\t"
+        "mov.b64 rc, {0f3F31798D, 0f3F31798D};\n\t"      // 0.69326097
+        "fma.rn.f32x2 rp, rp, rf, rc;\n\t"
+        "mov.b64 rc, {0f3F7FFB4A, 0f3F7FFB4A};\n\t"      // 0.9999281
+        "fma.rn.f32x2 rp, rp, rf, rc;\n\t"
+        "mov.b64 {%0, %1}, rt;\n\t"
+        "mov.b64 {%2, %3}, rp;\n\t}"
+        : "=r"(t0), "=r"(t1), "=r"(q0), "=r"(q1)
+        : "f"(x0), "f"(x1));
+    p0 = __uint_as_float(q0 + (t0 << 23));
+    p1 = __uint_as_float(q1 + (t1 << 23));
+}
+
+// One lane of a converged warp, chosen by the hardware. Unlike `lane == 0` this tells the compiler
+// that the guarded code is executed by a single thread of a converged warp, so descriptors and
+// addresses of the issue loops can live in uniform registers instead of being moved there per
+// instruction.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred = 0;
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "n"(ACC ? 1 : 0)
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "@p mov.s32 %0, 1;\n\t}"
+        : "+r"(pred));
+    return pred != 0;
+}
+
+// MMA wrappers for the issuing thread's inner loops: the accumulate flag is an immediate and the
+// 64-bit shared-memory descriptors are passed as (low, high) words — every descriptor of this kernel
+// has the same high word (8-row group stride 1024 B, version, 128-byte swizzle), and the low word
+// (start address, leading-dimension offset) moves by a compile-time constant per instruction, so
+// the loop costs one 32-bit add per operand instead of 64-bit descriptor arithmetic.
+template <bool ACC>
+__device__ __forceinline__ void tc_mma_ss_i(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(ACC ? 1 : 0)
         : "memory");
 }
 template <bool ACC>
-__device__ __forceinline__ void tc_mma_ts_i(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+__device__ __forceinline__ void tc_mma_ts_i(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "n"(ACC ? 1 : 0)
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(ACC ? 1 : 0)
         : "memory");
 }
 
@@ -158,7 +212,7 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     asm volatile("setmaxnreg.dec.sync.aligned.u32 120;");
     if (warp == 8) {
         // ------------------------------ TMA producer ------------------------------
-        if (lane == 0) {
+        if (elect_one()) {
             uint32_t gt = 0, it = 0, q_it = 0;
             bool ok = true, q_pending = false;
             for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
@@ -210,35 +264,35 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
     } else if (warp == 9) {
         // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
+        if (elect_one()) {
             uint32_t gt = 0, it = 0;
             bool ok = true;
-            // Descriptors differ only in the 14-bit start-address field (bytes >> 4): build one per
-            // tile base and add the in-tile offset per instruction.
             const uint64_t qdesc0 = umma_desc_sw128(q_smem, 16), kdesc0 = umma_desc_sw128(k_smem, 16);
             const uint64_t vdesc0 = umma_desc_sw128(v_smem, CHUNK_BYTES);
+            const uint32_t desc_hi = (uint32_t)(qdesc0 >> 32);
+            const uint32_t q_lo = (uint32_t)qdesc0, k_lo = (uint32_t)kdesc0, v_lo = (uint32_t)vdesc0;
             // S_grp = Q_grp · K(g)^T   (the K tile must have been waited for)
             auto issue_qk = [&](uint32_t g, int grp) {
-                const uint64_t kd = kdesc0 + (uint64_t)(((g % kPf2KStages) * TILE_BYTES) >> 4);
-                const uint64_t qd = qdesc0 + (uint64_t)((grp * TILE_BYTES) >> 4);
+                const uint32_t kd = k_lo + (((g % kPf2KStages) * TILE_BYTES) >> 4);
+                const uint32_t qd = q_lo + ((grp * TILE_BYTES) >> 4);
                 const uint32_t d = tmem + COL_S + 128u * grp;
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
-                    const uint64_t off = (uint64_t)(((kk / 4) * CHUNK_BYTES + (kk % 4) * 32) >> 4);
-                    if (kk == 0) tc_mma_ss_i<false>(d, qd + off, kd + off, IDESC_QK);
-                    else tc_mma_ss_i<true>(d, qd + off, kd + off, IDESC_QK);
+                    const uint32_t off = (uint32_t)(((kk / 4) * CHUNK_BYTES + (kk % 4) * 32) >> 4);
+                    if (kk == 0) tc_mma_ss_i<false>(d, qd + off, kd + off, desc_hi, IDESC_QK);
+                    else tc_mma_ss_i<true>(d, qd + off, kd + off, desc_hi, IDESC_QK);
                 }
                 tc_commit(B_SFULL + 8 * grp);
             };
             // O_grp (+)= P_grp · V(g)   (P lives in the first 64 columns of S_grp)
             auto issue_pv = [&](uint32_t g, int grp, bool accumulate) {
-                const uint64_t vd = vdesc0 + (uint64_t)(((g % kPf2VStages) * TILE_BYTES) >> 4);
+                const uint32_t vd = v_lo + (((g % kPf2VStages) * TILE_BYTES) >> 4);
                 const uint32_t pbase = tmem + COL_S + 128u * grp, d = tmem + COL_O + 128u * grp;
-                if (accumulate) tc_mma_ts_i<true>(d, pbase, vd, IDESC_PV);
-                else tc_mma_ts_i<false>(d, pbase, vd, IDESC_PV);
+                if (accumulate) tc_mma_ts_i<true>(d, pbase, vd, desc_hi, IDESC_PV);
+                else tc_mma_ts_i<false>(d, pbase, vd, desc_hi, IDESC_PV);
 #pragma unroll
                 for (int kk = 1; kk < kPfKeys / 16; ++kk)
-                    tc_mma_ts_i<true>(d, pbase + kk * 8, vd + (uint64_t)((kk * 2048) >> 4), IDESC_PV);
+                    tc_mma_ts_i<true>(d, pbase + kk * 8, vd + (uint32_t)((kk * 2048) >> 4), desc_hi, IDESC_PV);
             };
             for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
                 int qt, kvh, sp, kt_lo, nt;
@@ -371,7 +425,11 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                         float x0, x1, x2, x3;
                         ffma2_bcast(x0, x1, __uint_as_float(sv[c][j]), __uint_as_float(sv[c][j + 1]), a.scale_log2, neg_m);
                         ffma2_bcast(x2, x3, __uint_as_float(sv[c][j + 2]), __uint_as_float(sv[c][j + 3]), a.scale_log2, neg_m);
-                        const float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
+                        float p0, p1, p2, p3;
+                        if (((j / 4) * 2) % 8 < kPf2EmuOf8) ex2_emu2(p0, p1, x0, x1);
+                        else { p0 = ex2_approx(x0); p1 = ex2_approx(x1); }
+                        if (((j / 4) * 2 + 1) % 8 < kPf2EmuOf8) ex2_emu2(p2, p3, x2, x3);
+                        else { p2 = ex2_approx(x2); p3 = ex2_approx(x3); }
                         fadd2_acc(lsum0, lsum1, p0, p1);
                         fadd2_acc(lsum2, lsum3, p2, p3);
                         pk[j / 2] = pack_half2(p0, p1);
