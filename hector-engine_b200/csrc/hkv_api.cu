@@ -758,7 +758,7 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
             if (last_max > g.slots - 1) last_max = g.slots - 1;
             const int min_span = last_max / kPfKeys - first_min / kPfKeys + 1;
             const bool have_ws = c->prefill_ws != nullptr && seq_new <= g.max_seq_new;
-            const double tile_us = pair ? 1.0 + 0.9 * HD / 128.0 : 0.60 + 0.95 * HD / 128.0;   // per key tile of an item
+            const double tile_us = pair ? 0.85 + 0.85 * HD / 128.0 : 0.60 + 0.95 * HD / 128.0;   // per key tile of an item
             t.splits = prefill_splits(t, HD, q_item, tile_us, c->sm_count, min_span, have_ws);
             t.part = c->prefill_ws;
         }
