@@ -168,6 +168,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t
     return false;
 }
 
+// One lane of a converged warp, chosen by the hardware. Unlike `lane == 0` this tells the compiler
+// that the guarded code is executed by a single thread of a converged warp, so descriptors and
+// addresses of the issue loops can live in uniform registers instead of being moved there per
+// instruction.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred = 0;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "@p mov.s32 %0, 1;\n\t}"
+        : "+r"(pred));
+    return pred != 0;
+}
+
 // 4-D bulk-tensor load global -> shared (no multicast), completion on an mbarrier.
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint32_t bar, int c0,
                                             int c1, int c2, int c3) {

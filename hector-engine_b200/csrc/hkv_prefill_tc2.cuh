@@ -95,20 +95,6 @@ __device__ __forceinline__ void ex2_emu2(float& p0, float& p1, float x0, float x
     p1 = __uint_as_float(q1 + (t1 << 23));
 }
 
-// One lane of a converged warp, chosen by the hardware. Unlike `lane == 0` this tells the compiler
-// that the guarded code is executed by a single thread of a converged warp, so descriptors and
-// addresses of the issue loops can live in uniform registers instead of being moved there per
-// instruction.
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred = 0;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "elect.sync _|p, 0xffffffff;\n\t"
-        "@p mov.s32 %0, 1;\n\t}"
-        : "+r"(pred));
-    return pred != 0;
-}
-
 // MMA wrappers for the issuing thread's inner loops: the accumulate flag is an immediate and the
 // 64-bit shared-memory descriptors are passed as (low, high) words — every descriptor of this kernel
 // has the same high word (8-row group stride 1024 B, version, 128-byte swizzle), and the low word
