@@ -205,17 +205,29 @@ int encode_f16_sw128(hkv_ctx* c, const void* base, int rank, const cuuint64_t* d
 
 constexpr int kPrefillMaxSplits = 4;
 
-// Number of key ranges each (query tile, kv head) is cut into: the smallest count whose work
-// items fill at least 92 % of the SM waves they occupy, never more than the shortest span.
-// Key-range split count of the tensor-core prefill kernel. The kernel deals its work items
-// (query tile, kv head, split) round-robin to one CTA per SM, so the launch lasts as long as the
-// most loaded CTA; this replays that deal with a per-item overhead (pipeline fill, Q load, output)
-// and adds what the split costs (fp32 partials written and read back by the merge kernel).
-// Costs are in microseconds, from timings of the kernel on B200: ~1.55 us per 128-key tile at
-// head_dim 128, ~6 tiles' worth of overhead per item.
-int prefill_splits(const PrefillTcArgs& t, int HD, int q_item, double tile_us, int sm_count, int min_span_tiles,
-                   bool have_ws) {
+// Key tiles an item of `q_item` queries starting at query q0 spans (the kernels' tile_span).
+int prefill_span_tiles(const PrefillTcArgs& t, int q_item, int qt) {
+    const int q0 = qt * q_item;
+    const int lo = t.window > 0 ? (t.past_len + q0 + 1 - t.window > 0 ? t.past_len + q0 + 1 - t.window : 0) : 0;
+    const int q_last = q0 + q_item < t.S_new ? q0 + q_item : t.S_new;
+    int hi = t.past_len + q_last - 1;
+    if (hi > t.slots - 1) hi = t.slots - 1;
+    const int ntot = hi / kPfKeys - lo / kPfKeys + 1;
+    return ntot < 1 ? 1 : ntot;
+}
+
+// Key-range split count of the tensor-core prefill kernels. A kernel deals its work items
+// (query tile or pair, kv head, split) round-robin to one CTA per SM, so the launch lasts as long
+// as the most loaded CTA; this replays that deal with a per-item overhead (pipeline fill, Q load,
+// output) and adds what the split costs (fp32 partials written and read back by the merge kernel).
+// Costs are in microseconds, from timings of the kernels on B200.
+int prefill_splits(const PrefillTcArgs& t, int HD, int q_item, double tile_us, int sm_count, bool have_ws) {
     if (!have_ws) return 1;
+    // No split may be empty: the split count is bounded by the SHORTEST span of any item. (With a
+    // sliding window the spans differ by one tile from item to item, depending on how the window
+    // falls on the tile grid; without one the first item has the shortest.)
+    int min_span_tiles = 1 << 30;
+    for (int qt = 0; qt < t.n_qtiles; ++qt) min_span_tiles = std::min(min_span_tiles, prefill_span_tiles(t, q_item, qt));
     if (const char* e = getenv("HKV_PREFILL_SPLITS")) {  // tuning override
         const int v = atoi(e);
         if (v >= 1) return std::min(v, std::min(kPrefillMaxSplits, min_span_tiles));
@@ -231,13 +243,7 @@ int prefill_splits(const PrefillTcArgs& t, int HD, int q_item, double tile_us, i
         std::fill(load.begin(), load.end(), 0.0);
         long long item = 0;
         for (int qt = t.n_qtiles - 1; qt >= 0; --qt) {
-            const int q0 = qt * q_item;
-            const int lo = t.window > 0 ? (t.past_len + q0 + 1 - t.window > 0 ? t.past_len + q0 + 1 - t.window : 0) : 0;
-            const int q_last = q0 + q_item < t.S_new ? q0 + q_item : t.S_new;
-            int hi = t.past_len + q_last - 1;
-            if (hi > t.slots - 1) hi = t.slots - 1;
-            int ntot = hi / kPfKeys - lo / kPfKeys + 1;
-            if (ntot < 1) ntot = 1;
+            const int ntot = prefill_span_tiles(t, q_item, qt);
             const int base = ntot / s, rem = ntot % s;
             for (int kvh = 0; kvh < t.KVH; ++kvh)
                 for (int sp = 0; sp < s; ++sp, ++item)
@@ -250,6 +256,31 @@ int prefill_splits(const PrefillTcArgs& t, int HD, int q_item, double tile_us, i
         if (s == 1 || cost < 0.97 * best_cost) { best = s; best_cost = cost; }
     }
     return best;
+}
+
+// Host-side plan of one tensor-core prefill launch: which kernel, how the chunk is cut into
+// work items, how many key splits. Fills the shape fields of `t` (not the pointers). Pure
+// arithmetic: no device is touched.
+void plan_prefill_tc(const hkv_geometry& g, int seq_new, int past_len, int sm_count, bool have_ws,
+                     PrefillTcArgs& t, int& pair, int& min_span) {
+    const int G = g.num_heads / g.num_kv_heads, HD = g.head_dim;
+    t.S_new = seq_new;
+    t.past_len = past_len;
+    t.H = g.num_heads;
+    t.KVH = g.num_kv_heads;
+    t.G = G;
+    t.QT = kPfRows / G;
+    // two query tiles per work item (hkv_prefill_tc2_kernel) unless the whole chunk fits one tile
+    pair = seq_new > t.QT ? 1 : 0;
+    if (const char* e = getenv("HKV_PREFILL_KERNEL")) pair = atoi(e) == 1 ? 0 : 1;   // A/B override
+    const int q_item = pair ? 2 * t.QT : t.QT;
+    t.n_qtiles = (seq_new + q_item - 1) / q_item;
+    t.slots = g.slots;
+    t.window = g.window_size;
+    const double tile_us = pair ? 0.85 + 0.85 * HD / 128.0 : 0.60 + 0.95 * HD / 128.0;   // per key tile of an item
+    t.splits = prefill_splits(t, HD, q_item, tile_us, sm_count, have_ws);
+    min_span = 1 << 30;
+    for (int qt = 0; qt < t.n_qtiles; ++qt) min_span = std::min(min_span, prefill_span_tiles(t, q_item, qt));
 }
 
 bool prefill_tc_ok(const hkv_geometry& g) {
@@ -736,32 +767,12 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
         PrefillTcArgs t;
         t.out = (__half*)out;
         t.status = c->d_status;
-        t.S_new = seq_new;
-        t.past_len = past_len;
-        t.H = g.num_heads;
-        t.KVH = g.num_kv_heads;
-        t.G = G;
-        t.QT = kPfRows / G;
-        // two query tiles per work item (hkv_prefill_tc2_kernel) unless the whole chunk fits one tile
-        int pair = seq_new > t.QT ? 1 : 0;
-        if (const char* e = getenv("HKV_PREFILL_KERNEL")) pair = atoi(e) == 1 ? 0 : 1;   // A/B override
-        const int q_item = pair ? 2 * t.QT : t.QT;
-        t.n_qtiles = (seq_new + q_item - 1) / q_item;
-        t.slots = g.slots;
-        t.window = g.window_size;
+        int pair = 0, min_span = 0;
+        plan_prefill_tc(g, seq_new, past_len, c->sm_count, c->prefill_ws != nullptr && seq_new <= g.max_seq_new, t, pair,
+                        min_span);
+        if (t.splits > min_span) return fail(c, HKV_ERR_INVALID_ARG, "prefill: internal plan error (a key split would be empty)");
         t.scale_log2 = scale * 1.4426950408889634f;
-        {
-            // shortest key span over the items = that of the first one (window-limited)
-            const int q_last = q_item < seq_new ? q_item : seq_new;
-            const int first_min = g.window_size > 0 ? (past_len + 1 - g.window_size > 0 ? past_len + 1 - g.window_size : 0) : 0;
-            int last_max = past_len + q_last - 1;
-            if (last_max > g.slots - 1) last_max = g.slots - 1;
-            const int min_span = last_max / kPfKeys - first_min / kPfKeys + 1;
-            const bool have_ws = c->prefill_ws != nullptr && seq_new <= g.max_seq_new;
-            const double tile_us = pair ? 0.85 + 0.85 * HD / 128.0 : 0.60 + 0.95 * HD / 128.0;   // per key tile of an item
-            t.splits = prefill_splits(t, HD, q_item, tile_us, c->sm_count, min_span, have_ws);
-            t.part = c->prefill_ws;
-        }
+        t.part = c->prefill_ws;
         CUtensorMap mq, mk, mv;
         {
             cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)g.num_heads, (cuuint64_t)seq_new};
@@ -966,6 +977,29 @@ int hkv_plan_sequence(const hkv_geometry* g, int32_t total_seq, int32_t chunk_ti
     if (tile_lo) *tile_lo = tl;
     if (n_tiles) *n_tiles = nt;
     if (n_chunks) *n_chunks = (nt + chunk_tiles - 1) / chunk_tiles;
+    return HKV_OK;
+}
+
+int hkv_plan_prefill(const hkv_geometry* g, int32_t seq_new, int32_t past_len, int32_t sm_count,
+                     int32_t* tiles_in_flight, int32_t* items, int32_t* splits, int32_t* min_span_tiles) {
+    const char* why;
+    const int st = validate_geometry(g, &why);
+    if (st) return st;
+    if (seq_new <= 0 || past_len < 0 || sm_count <= 0) return HKV_ERR_INVALID_ARG;
+    if (!prefill_tc_ok(*g)) {   // the SIMT kernel: one CTA per (query, head), no split
+        if (tiles_in_flight) *tiles_in_flight = 0;
+        if (items) *items = seq_new * g->num_heads;
+        if (splits) *splits = 1;
+        if (min_span_tiles) *min_span_tiles = 0;
+        return HKV_OK;
+    }
+    PrefillTcArgs t{};
+    int pair = 0, min_span = 0;
+    plan_prefill_tc(*g, seq_new, past_len, sm_count, g->max_seq_new >= seq_new, t, pair, min_span);
+    if (tiles_in_flight) *tiles_in_flight = pair ? 2 : 1;
+    if (items) *items = t.n_qtiles * t.KVH * t.splits;
+    if (splits) *splits = t.splits;
+    if (min_span_tiles) *min_span_tiles = min_span;
     return HKV_OK;
 }
 

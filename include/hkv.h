@@ -253,6 +253,13 @@ int32_t hkv_position_of_slot(const hkv_geometry* geometry, int32_t slot, int32_t
 int hkv_plan_sequence(const hkv_geometry* geometry, int32_t total_seq, int32_t chunk_tiles,
                       int32_t* first_pos, int32_t* tile_lo, int32_t* n_tiles, int32_t* n_chunks);
 
+/* Plan of one hkv_prefill_attention call on a device with `sm_count` SMs (host arithmetic, no
+ * device needed): query tiles in flight per CTA (2 or 1 for the tensor-core kernels, 0 = SIMT
+ * kernel), number of work items, key-range splits per item and the shortest key span (in
+ * 128-row tiles) of any item. splits <= min_span_tiles always holds: no split is ever empty. */
+int hkv_plan_prefill(const hkv_geometry* geometry, int32_t seq_new, int32_t past_len, int32_t sm_count,
+                     int32_t* tiles_in_flight, int32_t* items, int32_t* splits, int32_t* min_span_tiles);
+
 /* ---- utilities ------------------------------------------------------------------- */
 
 /* Deterministic synthetic fp16 data, bit-identical to the CPU generator used by the

@@ -171,3 +171,53 @@ def test_cache_owner_position_bookkeeping(hkv):
     cfg = hkv.KVCacheConfig(num_layers=28, num_kv_heads=4, head_dim=128, max_batch_size=64, max_seq_len=32768)
     assert cfg.total_bytes() == 28 * 2 * 64 * 32768 * 4 * 128 * 2
     assert not hkv.KVCache().allocate(hkv.KVCacheConfig())  # zero dims refused like the reference
+
+
+def _plan_prefill(hkv, g, seq_new, past, sms=148):
+    lib = hkv._capi.load()
+    vals = [C.c_int32() for _ in range(4)]
+    st = lib.hkv_plan_prefill(C.byref(g.to_c()), seq_new, past, sms, *[C.byref(v) for v in vals])
+    assert st == 0
+    return [v.value for v in vals]   # tiles in flight, items, splits, min span
+
+
+def test_prefill_plan_never_leaves_a_key_split_empty(hkv, monkeypatch):
+    """Host plan of the tensor-core prefill launch (no device needed): kernel choice, work items and
+    key-range splits. With a sliding window the key span differs from item to item by a tile
+    depending on how the window falls on the 128-row tile grid, so the split count must be bounded
+    by the SHORTEST span over all items — a plan with an empty split makes the kernel wait for a
+    tile that is never loaded."""
+    monkeypatch.delenv("HKV_PREFILL_SPLITS", raising=False)
+    monkeypatch.delenv("HKV_PREFILL_KERNEL", raising=False)
+    # the headline shape: long pasts get split (148 SMs, 228 pair items x 4 kv heads... ), short ones do not
+    g = hkv.Geometry(num_heads=28, num_kv_heads=4, head_dim=128, slots=131072, max_seq_new=2048)
+    tif, items, splits, span = _plan_prefill(hkv, g, 2048, 129024)
+    assert tif == 2 and splits > 1 and splits <= span and items == 57 * 4 * splits
+    tif, items, splits, span = _plan_prefill(hkv, g, 2048, 0)
+    assert tif == 2 and splits == 1 and span == 1
+    # a chunk that fits one query tile takes the one-tile kernel
+    assert _plan_prefill(hkv, g, 18, 5000)[0] == 1 and _plan_prefill(hkv, g, 19, 5000)[0] == 2
+    # without a workspace for partials there is no split
+    g0 = hkv.Geometry(num_heads=28, num_kv_heads=4, head_dim=128, slots=131072, max_seq_new=0)
+    assert _plan_prefill(hkv, g0, 2048, 129024)[2] == 1
+    # geometries the tensor-core kernels do not take: SIMT, one CTA per (query, head)
+    g96 = hkv.Geometry(num_heads=32, num_kv_heads=32, head_dim=96, slots=4096, max_seq_new=256)
+    assert _plan_prefill(hkv, g96, 256, 100) == [0, 256 * 32, 1, 0]
+    # window 119 over 36-query items: spans of 2 and 3 tiles alternate; forcing 3 or 4 splits must clamp to 2
+    gw = hkv.Geometry(num_heads=7, num_kv_heads=1, head_dim=128, slots=1231, window_size=119, max_seq_new=345)
+    for forced in (1, 2, 3, 4):
+        monkeypatch.setenv("HKV_PREFILL_SPLITS", str(forced))
+        tif, items, splits, span = _plan_prefill(hkv, gw, 345, 734)
+        assert span == 2 and splits == min(forced, 2), (forced, splits, span)
+    monkeypatch.delenv("HKV_PREFILL_SPLITS")
+    # and whatever the cost model picks on its own, over many shapes
+    import numpy as np
+    rng = np.random.default_rng(5)
+    for _ in range(300):
+        G = int(rng.choice([1, 2, 4, 7, 8])); KVH = int(rng.choice([1, 2, 4, 8]))
+        S = int(rng.integers(1, 4000)); past = int(rng.integers(0, 200000))
+        win = int(rng.choice([0, int(rng.integers(1, 5000))]))
+        gg = hkv.Geometry(num_heads=G * KVH, num_kv_heads=KVH, head_dim=int(rng.choice([64, 128])),
+                          slots=past + S + int(rng.integers(0, 300)), window_size=win, max_seq_new=S)
+        tif, items, splits, span = _plan_prefill(hkv, gg, S, past, sms=int(rng.choice([132, 148])))
+        assert 1 <= splits <= min(span, 4) and tif in (1, 2) and items >= 1

@@ -228,6 +228,55 @@ def test_fused_append_decode(hkv, cuda, oracle, shape, kernel):
     ctx.close()
 
 
+def test_fused_decode_seeded_random_shapes(hkv, cuda, oracle):
+    """Forty seeded random geometries of the fused append + decode op: group sizes 1..16, every
+    TMA head_dim and two that only the generic kernel takes, linear and ring planes, windows,
+    ragged positions (first row, tile edges, last row, past the plane = dropped append), forced
+    split sizes, inactive sequences (position -1). Cache planes bit-exact, outputs within
+    tolerance, rows beyond each position poisoned."""
+    torch = cuda
+    rng = np.random.default_rng(31415)
+    for i in range(40):
+        HD = int(rng.choice([64, 96, 128, 256, 80, 32]))
+        KVH = int(rng.choice([1, 2, 4, 8]))
+        G = int(rng.choice([1, 2, 4, 7, 8, 16]))
+        H = KVH * G
+        B = int(rng.integers(1, 7))
+        ring = bool(rng.integers(0, 3) == 0)
+        slots = int(rng.integers(1, 9)) * 64 if ring else int(rng.integers(1, 900))
+        window = slots if ring else int(rng.choice([0, 0, int(rng.integers(1, 300))]))
+        layout = 1 if ring else 0
+        hi = 4 * slots if ring else slots + 2          # linear: up to two positions past the plane
+        pos = rng.integers(-1, hi, size=B).astype(np.int32)
+        pos[rng.integers(0, B)] = int(rng.choice([0, 63, 64, slots - 1]))
+        ct = int(rng.choice([0, 0, 1, 2, 5]))
+        q, nk, nv, kc, vc = make_case(int(rng.integers(1 << 30)), B, H, KVH, HD, slots, fill="garbage")
+        if not ring:
+            for b, p_ in enumerate(pos):   # rows at and past the append position are stale memory
+                kc[b, max(int(p_), 0) + 1:] = np.float16(np.nan)
+                vc[b, max(int(p_), 0) + 1:] = np.float16(np.inf)
+        scale = float(rng.choice([1.0 / math.sqrt(HD), 1.0]))
+        ref_k, ref_v = kc.copy(), vc.copy()
+        oracle.append(nk, nv, ref_k, ref_v, pos, layout=layout)
+        totals = np.where(pos >= 0, pos + 1, 0).astype(np.int32)
+        ref = oracle.decode(q, ref_k, ref_v, totals, scale, window=window, layout=layout, threads=8)
+        ctx = hkv.Context(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots,
+                                       window_size=window, layout=layout, chunk_tiles=ct))
+        dk, dv = to_dev(torch, kc), to_dev(torch, vc)
+        out = torch.full((B, H, HD), float("nan"), dtype=torch.float16, device="cuda")
+        ctx.append_decode_attention(to_dev(torch, q), to_dev(torch, nk), to_dev(torch, nv), dk, dv, out,
+                                    to_dev(torch, pos), scale)
+        what = (f"case {i}: B={B} H={H} KVH={KVH} HD={HD} slots={slots} window={window} ring={ring} "
+                f"pos={pos.tolist()} chunk_tiles={ct} kernel={ctx.kernel}")
+        assert ctx.device_status() == 0, what
+        assert np.array_equal(dk.cpu().numpy().view(np.uint16), ref_k.view(np.uint16)), what + ": K plane"
+        assert np.array_equal(dv.cpu().numpy().view(np.uint16), ref_v.view(np.uint16)), what + ": V plane"
+        got = out.cpu().numpy()
+        assert not np.isnan(got.astype(np.float32)).any(), what + ": NaN"
+        assert_close(oracle, got, ref, what)
+        ctx.close()
+
+
 def test_strided_batch_and_engine_scalar_position(hkv, cuda, oracle):
     """batch = 1 with scalar device positions is the engine's own contract; a batch stride
     larger than one sequence's plane addresses sequences inside a bigger allocation."""

@@ -131,3 +131,39 @@ def test_prefill_row_maxima_that_keep_growing(hkv, cuda, oracle, monkeypatch, ti
     assert not np.isnan(got.astype(np.float32)).any()
     assert_close(oracle, got, ref, f"growing maxima, kernel={tiles_in_flight}")
     ctx.close()
+
+
+def test_prefill_seeded_random_shapes(hkv, cuda, oracle, monkeypatch):
+    """Thirty seeded random geometries (group size, head_dim 64/128, chunk and past lengths that are
+    not multiples of any tile, windows, forced key splits, both tensor-core kernels): every one must
+    match the oracle. Catches protocol slips that only show for particular tile counts per item."""
+    torch = cuda
+    rng = np.random.default_rng(20241125)
+    for i in range(30):
+        HD = int(rng.choice([64, 128]))
+        KVH = int(rng.choice([1, 2, 4]))
+        G = int(rng.choice([1, 2, 4, 7, 8]))
+        H = KVH * G
+        S_new = int(rng.integers(1, 420))
+        past = int(rng.integers(0, 1500))
+        slots = int(past + S_new + rng.integers(0, 200))
+        window = int(rng.choice([0, 0, int(rng.integers(1, 700))]))
+        monkeypatch.setenv("HKV_PREFILL_KERNEL", str(int(rng.choice([1, 2]))))
+        monkeypatch.setenv("HKV_PREFILL_SPLITS", str(int(rng.choice([1, 1, 2, 3, 4]))))
+        k = normal_f16(rng, 1, slots, KVH, HD)
+        v = normal_f16(rng, 1, slots, KVH, HD)
+        k[0, past + S_new:] = np.float16(np.nan)
+        v[0, past + S_new:] = np.float16(np.inf)
+        q = normal_f16(rng, S_new, H, HD)
+        scale = float(rng.choice([1.0 / math.sqrt(HD), 0.5]))
+        ref = oracle.prefill(q, k[0], v[0], past, scale, window=window, threads=8)
+        ctx = hkv.Context(hkv.Geometry(batch=1, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots,
+                                       window_size=window, max_seq_new=S_new))
+        out = torch.full((S_new, H, HD), float("nan"), dtype=torch.float16, device="cuda")
+        ctx.prefill_attention(to_dev(torch, q), to_dev(torch, k), to_dev(torch, v), out, S_new, past, scale)
+        assert ctx.device_status() == 0, f"case {i}"
+        got = out.cpu().numpy()
+        assert not np.isnan(got.astype(np.float32)).any(), f"case {i}: NaN"
+        assert_close(oracle, got, ref, f"case {i}: H={H} KVH={KVH} HD={HD} S_new={S_new} past={past} "
+                                        f"slots={slots} window={window}")
+        ctx.close()
