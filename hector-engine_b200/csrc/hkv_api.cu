@@ -456,7 +456,14 @@ int launch_combine(hkv_ctx* c, const float* part, long long stride_b, long long 
     a.out = (__half*)out;
     a.out_partial = out_partial;
     dim3 grid((unsigned)c->g.num_heads, (unsigned)c->g.batch);
-    hkv_combine_kernel<<<grid, kCombineThreads, 0, st>>>(a);
+    // Two merge kernels, chosen by host constants of the context (so a captured graph never changes
+    // kernel): with few (sequence, head) rows and many partials per row the merge is latency-bound
+    // and the warp-dealt kernel wins (batch 1-8: +5 %); with many rows the one-thread-per-dimension
+    // kernel does (batch 32-64: +2 % of the step).
+    const int most = d_total ? c->max_chunks : fixed_count;
+    const long long rows = (long long)grid.x * grid.y;
+    if (rows <= 2LL * c->sm_count && most > 8) hkv_combine_kernel<<<grid, kCombineThreads, 0, st>>>(a);
+    else hkv_combine_few_kernel<<<grid, 128, 0, st>>>(a);
     return HKV_OK;
 }
 

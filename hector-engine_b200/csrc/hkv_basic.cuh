@@ -234,6 +234,74 @@ __global__ void __launch_bounds__(kCombineThreads) hkv_combine_kernel(const Comb
     }
 }
 
+// The merge for many (sequence, head) rows: one thread per output dimension walks the row's
+// partials directly; no cross-warp reduction, half the threads and a fraction of the shared memory
+// of the kernel above, which only pays when few rows each have many partials (small batches).
+__global__ void __launch_bounds__(128) hkv_combine_few_kernel(const CombineArgs a) {
+    const int h = blockIdx.x, b = blockIdx.y;
+    int n = a.fixed_count;
+    if (a.total) {
+        const int t = a.total[b] + a.pos_is_index;
+        n = num_chunks(a.map, t > 0 ? t : 0, a.chunk_tiles);
+    }
+    const int PW = a.HD + 2;
+    const float* base = a.part + b * a.stride_b + (long long)h * PW;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ float s_red[4];
+    __shared__ float s_w[128];
+    // M = max over partials: the chunks are spread over the threads, so the loads overlap
+    float M = kNegBig;
+    for (int c = tid; c < n; c += 128) M = fmaxf(M, base[c * a.stride_c + a.HD]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    if (lane == 0) s_red[warp] = M;
+    __syncthreads();
+    M = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+    float L = 0.0f;        // thread-partial sum of weights * l, reduced at the end
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // output dims tid, tid+128, ... (head_dim <= 512)
+    for (int c0 = 0; c0 < n; c0 += 128) {
+        const int nb = n - c0 < 128 ? n - c0 : 128;
+        __syncthreads();
+        if (tid < nb) {
+            const float* row = base + (long long)(c0 + tid) * a.stride_c;
+            const float w = exp2f(row[a.HD] - M);
+            s_w[tid] = w;
+            L = fmaf(row[a.HD + 1], w, L);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int d = tid + 128 * i;
+            if (d < a.HD) {
+                float o = acc[i];
+#pragma unroll 8
+                for (int c = 0; c < nb; ++c) o = fmaf(base[(long long)(c0 + c) * a.stride_c + d], s_w[c], o);
+                acc[i] = o;
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    __syncthreads();
+    if (lane == 0) s_red[warp] = L;
+    __syncthreads();
+    L = s_red[0] + s_red[1] + s_red[2] + s_red[3];
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int d = tid + 128 * i;
+        if (d < a.HD) {
+            if (a.out) a.out[((long long)b * a.H + h) * a.HD + d] = __float2half_rn(acc[i] * inv);
+            if (a.out_partial) a.out_partial[((long long)b * a.H + h) * PW + d] = acc[i];
+        }
+    }
+    if (a.out_partial && threadIdx.x == 0) {
+        float* row = a.out_partial + ((long long)b * a.H + h) * PW;
+        row[a.HD] = M;
+        row[a.HD + 1] = L;
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Self-test of the bounded wait: one CTA waits on an mbarrier that nothing ever arrives on.
 // The wait must run out after `limit_ns`, set the status word and let the kernel return
