@@ -51,6 +51,7 @@ struct hkv_ctx {
     int32_t* d_status = nullptr;
     int32_t* d_len = nullptr;       // [B] for the host-length / host-position twins
     float* prefill_ws = nullptr;    // [max_seq_new][kPrefillMaxSplits][H][HD+2] key-split partials of the prefill kernel
+    int* prefill_counter = nullptr; // work counter of the two-tile prefill kernel (zeroed on the stream before each launch)
     int32_t* h_len = nullptr;       // pinned staging for d_len
     // host-buffer entry point staging
     __half *st_q = nullptr, *st_k = nullptr, *st_v = nullptr, *st_out = nullptr;
@@ -232,7 +233,7 @@ int prefill_splits(const PrefillTcArgs& t, int HD, int q_item, double tile_us, i
         const int v = atoi(e);
         if (v >= 1) return std::min(v, std::min(kPrefillMaxSplits, min_span_tiles));
     }
-    const double item_tiles = q_item > t.QT ? 3.0 : 6.0;
+    const double item_tiles = q_item > t.QT ? 5.0 : 6.0;
     const double row_bytes = (double)t.S_new * t.H * (HD + 2) * 4.0;
     int best = 1;
     double best_cost = 0.0;
@@ -240,20 +241,32 @@ int prefill_splits(const PrefillTcArgs& t, int HD, int q_item, double tile_us, i
     for (int s = 1; s <= kPrefillMaxSplits && s <= min_span_tiles; ++s) {
         const long long items = (long long)t.n_qtiles * t.KVH * s;
         const int grid = items < sm_count ? (int)items : sm_count;
-        std::fill(load.begin(), load.end(), 0.0);
+        // The one-tile kernel deals items round-robin: replay the deal. The two-tile kernel hands
+        // the next item (longest first) to whichever CTA is free: the full rounds even out, the
+        // remainder lands on top — estimated in one pass, this runs on the host before every launch.
+        const bool greedy = q_item > t.QT;
+        if (!greedy) std::fill(load.begin(), load.end(), 0.0);
+        const long long full = (items / grid) * grid;
         long long item = 0;
+        double mx = 0.0, sum_full = 0.0, rem_first = 0.0;
         for (int qt = t.n_qtiles - 1; qt >= 0; --qt) {
             const int ntot = prefill_span_tiles(t, q_item, qt);
             const int base = ntot / s, rem = ntot % s;
             for (int kvh = 0; kvh < t.KVH; ++kvh)
-                for (int sp = 0; sp < s; ++sp, ++item)
-                    load[(size_t)(item % grid)] += (base + (sp < rem ? 1 : 0)) + item_tiles;
+                for (int sp = 0; sp < s; ++sp, ++item) {
+                    const double w = (base + (sp < rem ? 1 : 0)) + item_tiles;
+                    if (!greedy) load[(size_t)(item % grid)] += w;
+                    else if (item < full) sum_full += w;
+                    else if (w > rem_first) rem_first = w;
+                }
         }
-        double mx = 0.0;
-        for (int i = 0; i < grid; ++i) mx = load[(size_t)i] > mx ? load[(size_t)i] : mx;
+        if (greedy) mx = sum_full / grid + rem_first;
+        else for (int i = 0; i < grid; ++i) mx = load[(size_t)i] > mx ? load[(size_t)i] : mx;
         double cost = mx * tile_us;
         if (s > 1) cost += 4.0 + 2.0 * s * row_bytes / 3.0e6;   // partials out and back at ~3 TB/s
-        if (s == 1 || cost < 0.97 * best_cost) { best = s; best_cost = cost; }
+        // (a split must promise 10 % with the self-balancing kernel: it runs its items a little less
+        // efficiently than the model says, and the merge pass is pure overhead)
+        if (s == 1 || cost < (greedy ? 0.90 : 0.97) * best_cost) { best = s; best_cost = cost; }
     }
     return best;
 }
@@ -615,6 +628,10 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
                                  (int)prefill_tc2_smem_bytes(geometry->head_dim));
         if (e != cudaSuccess) return fail_cuda(c, e, "cudaFuncSetAttribute(prefill shared memory)");
     }
+    if (prefill_tc_ok(*geometry)) {
+        e = cudaMalloc(&c->prefill_counter, sizeof(int));
+        if (e != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(prefill work counter)");
+    }
     if (prefill_tc_ok(*geometry) && geometry->max_seq_new > 0) {
         const size_t nb = (size_t)geometry->max_seq_new * kPrefillMaxSplits * geometry->num_heads *
                           (geometry->head_dim + 2) * sizeof(float);
@@ -641,6 +658,7 @@ int hkv_ctx_destroy(hkv_ctx* c) {
     if (c->d_status) cudaFree(c->d_status);
     if (c->d_len) cudaFree(c->d_len);
     if (c->prefill_ws) cudaFree(c->prefill_ws);
+    if (c->prefill_counter) cudaFree(c->prefill_counter);
     if (c->h_len) cudaFreeHost(c->h_len);
     if (c->st_q) cudaFree(c->st_q);
     if (c->st_k) cudaFree(c->st_k);
@@ -800,7 +818,10 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
         }
         const long long items = (long long)t.n_qtiles * g.num_kv_heads * t.splits;
         const int grid = items < c->sm_count ? (int)items : c->sm_count;
+        t.item_counter = c->prefill_counter;
         if (pair) {
+            const cudaError_t me = cudaMemsetAsync(c->prefill_counter, 0, sizeof(int), (cudaStream_t)stream);
+            if (me != cudaSuccess) return fail_cuda(c, me, "cudaMemsetAsync(prefill work counter)");
             const size_t smem = prefill_tc2_smem_bytes(HD);
             if (HD == 64) hkv_prefill_tc2_kernel<64><<<grid, kPf2Threads, smem, (cudaStream_t)stream>>>(mq, mk, mv, t);
             else hkv_prefill_tc2_kernel<128><<<grid, kPf2Threads, smem, (cudaStream_t)stream>>>(mq, mk, mv, t);

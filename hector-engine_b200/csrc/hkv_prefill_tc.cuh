@@ -45,6 +45,7 @@ struct PrefillTcArgs {
     // [S_new][splits][H][HD+2] and the combine kernel merges them.
     int splits;
     float* part;
+    int* item_counter;   // two-tile kernel: zeroed before the launch; items beyond the first of each CTA come from it
 };
 
 constexpr int kPfRows = 128;   // M of the MMA = rows of a query tile

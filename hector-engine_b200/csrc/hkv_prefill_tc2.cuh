@@ -156,6 +156,12 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const uint32_t B_PFULL = bar0 + 96;     // [group]
     const uint32_t B_OFULL = bar0 + 112;    // [group] last P·V of an item has completed
     const uint32_t B_DONE = bar0 + 128;
+    // Work queue: the producer takes items off a global counter (whichever CTA is free takes the
+    // next, longest first: greedy balance instead of a fixed deal) and hands each index to the
+    // other roles through four shared-memory slots.
+    const uint32_t B_QF = bar0 + 144;       // [4] slot holds an item index (or -1 = no more work)
+    const uint32_t B_QE = bar0 + 176;       // [4] slot read by the MMA issuer and the 8 softmax warps
+    volatile int* q_items = reinterpret_cast<volatile int*>(tmem_slot + 4);   // [4]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
@@ -164,6 +170,7 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         for (int s = 0; s < kPf2VStages; ++s) { mbar_init(B_VFULL + 8 * s, 1); mbar_init(B_VEMPTY + 8 * s, 1); }
         for (int g = 0; g < 2; ++g) { mbar_init(B_SFULL + 8 * g, 1); mbar_init(B_PFULL + 8 * g, 128); mbar_init(B_OFULL + 8 * g, 1); }
         mbar_init(B_DONE, 1);
+        for (int i = 0; i < 4; ++i) { mbar_init(B_QF + 8 * i, 1); mbar_init(B_QE + 8 * i, 9); }
         fence_mbar_init();
         tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
     }
@@ -199,14 +206,27 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         kvh = rest % a.KVH;
     };
 
+    // Consumers of the queue: entry k lives in slot k % 4, phase k / 4.
+    auto queue_wait = [&](uint32_t k) -> bool { return mbar_wait(B_QF + 8 * (k & 3), (k >> 2) & 1, a.status); };
+
     if (warp >= 8) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 120;");
     if (warp == 8) {
         // ------------------------------ TMA producer ------------------------------
         if (elect_one()) {
-            uint32_t gt = 0, it = 0, q_it = 0;
+            uint32_t gt = 0, it = 0, q_it = 0, qk = 0;
             bool ok = true, q_pending = false;
-            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+            auto publish = [&](int item) -> bool {
+                const uint32_t slot = qk & 3;
+                if (qk >= 4 && !mbar_wait(B_QE + 8 * slot, ((qk >> 2) - 1) & 1, a.status)) return false;
+                q_items[slot] = item;
+                mbar_arrive(B_QF + 8 * slot);
+                ++qk;
+                return true;
+            };
+            // first item = this CTA's index, then whatever the shared counter hands out
+            for (int item = blockIdx.x; item < n_items && ok; item = (int)gridDim.x + atomicAdd(a.item_counter, 1), ++it) {
+                if (!publish(item)) { ok = false; break; }
                 int qt, kvh, sp, kt_lo, nt;
                 decode_item(item, qt, kvh, sp);
                 tile_span(qt, sp, kt_lo, nt);
@@ -242,6 +262,7 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                                     row, 0);
                 }
             }
+            publish(-1);   // no more work (also after a wait that ran out: the other roles leave at once)
             // drain this thread's outstanding copies before the CTA retires (tiles 0..gt-1 were issued)
             if (q_pending) mbar_wait(B_QFULL, q_it & 1, a.status);
             for (uint32_t i = 1; i <= (uint32_t)kPf2KStages && i <= gt; ++i) {
@@ -285,7 +306,11 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 for (int kk = 1; kk < kPfKeys / 16; ++kk)
                     tc_mma_ts_i<true>(d, pbase + kk * 8, vd + (uint32_t)((kk * 2048) >> 4), desc_hi, IDESC_PV);
             };
-            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+            for (; ok; ++it) {
+                if (!queue_wait(it)) { ok = false; break; }
+                const int item = q_items[it & 3];
+                mbar_arrive(B_QE + 8 * (it & 3));
+                if (item < 0) break;
                 int qt, kvh, sp, kt_lo, nt;
                 decode_item(item, qt, kvh, sp);
                 tile_span(qt, sp, kt_lo, nt);
@@ -339,7 +364,13 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const int ql = r / a.G, g = r % a.G;
         uint32_t gt = 0, si = 0;   // tiles seen, items done (barrier phases)
         bool ok = true;            // kept warp-uniform: a wait that ran out for any lane stops the warp
-        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+        for (uint32_t qk = 0; ok; ++qk) {
+            ok = __all_sync(0xffffffffu, queue_wait(qk));
+            if (!ok) break;
+            const int item = q_items[qk & 3];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(B_QE + 8 * (qk & 3));
+            if (item < 0) break;
             int qt, kvh, sp, kt_lo, nt;
             decode_item(item, qt, kvh, sp);
             tile_span(qt, sp, kt_lo, nt);
