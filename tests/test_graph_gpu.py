@@ -64,3 +64,46 @@ def test_capture_once_replay_many(hkv, cuda, oracle, shape):
         assert np.array_equal(dv[l].cpu().numpy().view(np.uint16), hv[l].view(np.uint16))
     assert ctx.device_status() == 0
     ctx.close()
+
+
+@pytest.mark.parametrize("splits", ["auto", "3"])
+def test_prefill_chunk_captured_and_replayed(hkv, cuda, oracle, monkeypatch, splits):
+    """A prefill chunk (append of its rows + the tensor-core attention, incl. the reset of the
+    kernel's work counter and the merge of key splits) is captured once and replayed with new
+    contents at the same addresses: every replay must match the oracle. The chunk geometry
+    (seq_new, past_len) is frozen in the graph, as an engine replaying a fixed-shape chunk would."""
+    torch = cuda
+    if splits != "auto":
+        monkeypatch.setenv("HKV_PREFILL_SPLITS", splits)
+    H, KVH, HD, slots, past, S_new = 28, 4, 128, 1024, 600, 150
+    rng = np.random.default_rng(7)
+    scale = 1.0 / math.sqrt(HD)
+    hk, hv = normal_f16(rng, 1, slots, KVH, HD), normal_f16(rng, 1, slots, KVH, HD)
+    dk, dv = to_dev(torch, hk), to_dev(torch, hv)
+    dq = torch.zeros(S_new, H, HD, dtype=torch.float16, device="cuda")
+    dkn = torch.zeros(1, S_new, KVH, HD, dtype=torch.float16, device="cuda")
+    dvn = torch.zeros(1, S_new, KVH, HD, dtype=torch.float16, device="cuda")
+    out = torch.zeros(S_new, H, HD, dtype=torch.float16, device="cuda")
+    ctx = hkv.Context(hkv.Geometry(batch=1, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots,
+                                   max_seq_new=S_new))
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    for s in range(4):
+        q = normal_f16(rng, S_new, H, HD)
+        kn, vn = normal_f16(rng, 1, S_new, KVH, HD), normal_f16(rng, 1, S_new, KVH, HD)
+        with torch.cuda.stream(side):
+            dq.copy_(to_dev(torch, q)); dkn.copy_(to_dev(torch, kn)); dvn.copy_(to_dev(torch, vn))
+            if s == 0:
+                with torch.cuda.graph(graph, stream=side, capture_error_mode="global"):
+                    ctx.append_at(dkn, dvn, dk, dv, past, S_new)
+                    ctx.prefill_attention(dq, dk, dv, out, S_new, past, scale)
+            graph.replay()
+        side.synchronize()
+        hk[0, past:past + S_new] = kn[0]
+        hv[0, past:past + S_new] = vn[0]
+        ref = oracle.prefill(q, hk[0], hv[0], past, scale, threads=8)
+        assert_close(oracle, out.cpu().numpy(), ref, f"replay {s}")
+    assert np.array_equal(dk.cpu().numpy().view(np.uint16), hk.view(np.uint16))
+    assert ctx.device_status() == 0
+    ctx.close()
