@@ -55,7 +55,7 @@ public:
     static void check(hkv_ctx* c, int status, const char* op);
 
 private:
-    using Key = std::tuple<int, int, int, int, int, int, int, long long>;
+    using Key = std::tuple<int, int, int, int, int, int, int, long long, int>;
     std::map<Key, hkv_ctx*> ctxs_;
 };
 
@@ -135,6 +135,10 @@ public:
                 num_heads % num_kv_heads != 0)
                 throw std::runtime_error("ATTENTION_PREFILL_CACHED: unsupported head geometry");
             hkv_geometry g = geometry(1, num_heads, num_kv_heads, head_dim, max_seq_len, window_size);
+            // chunks up to this size may be cut by key range to fill the SMs (the engine's chunk of 512
+            // queries makes fewer work items than a B200 has SMs); rounded so that a ragged last
+            // chunk shares the context of the full ones
+            g.max_seq_new = (int32_t)(((seq_new + 511u) / 512u) * 512u);
             hkv_ctx* c = pool->get(g);
             ContextPool::check(c, hkv_prefill_attention(c, fp16(q), fp16(k_cache), fp16(v_cache), fp16(output),
                                                         (int32_t)seq_new, (int32_t)past_len, scale, ctx.stream),
