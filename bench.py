@@ -463,6 +463,68 @@ def run_seqsplit(args, torch, hkv, dist, cfg, ctx_local, B, rank, world, base, g
     dec.close()
 
 
+def run_prefill_reference(args, torch, oracle, cfg, base, gpu_id, q, k, v, out, S, past, slots, scale, ctx):
+    """Reference arm of the prefill metric: the reference's own attention_prefill_cached kernel
+    (kernels/attention.cu:664-788, rebuilt for sm_100a in oracle/_ref) on the same chunk. Its grid is
+    one CTA per (query, head), each streaming its whole key range, so time is additive over queries:
+    three slices of 32 queries (start, middle, end of the chunk) are timed and scaled to the chunk.
+    The slices are also compared with this library's output for the same queries."""
+    ref = oracle.load_reference()
+    if ref is None:
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "oracle/_ref/libhector_ref_attention.so not built (reference checkout absent at build time)"}))
+        ctx.close()
+        return
+    H, KVH, HD = cfg["H"], cfg["KVH"], cfg["HD"]
+    n = min(32, S)
+    los = sorted({0, max(0, S // 2 - n // 2), S - n})
+    rout = torch.zeros((n, H, HD), dtype=torch.float16, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def ref_slice(lo):
+        st = ref.hector_ref_attention_prefill_cached(q[lo:].data_ptr(), k.data_ptr(), v.data_ptr(), rout.data_ptr(), n,
+                                                     past + lo, H, KVH, HD, slots, scale, 0, stream)
+        assert st == 0, f"reference prefill kernel failed: {st}"
+
+    worst = 0.0
+    for lo in los:   # warm-up + agreement with this library (both within tolerance of the oracle)
+        ref_slice(lo)
+        torch.cuda.synchronize()
+        ok, e = oracle.within_tolerance(out[lo:lo + n].cpu().numpy(), rout.cpu().numpy())
+        assert ok, f"reference and hkv prefill disagree at query {lo}: {e:.3e}"
+        worst = max(worst, e)
+    sampler = ClockSampler(gpu_id)
+    sampler.start()
+    for _ in range(max(args.warmup, 1)):
+        ref_slice(los[-1])
+    torch.cuda.synchronize()
+    sampler.begin()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        for lo in los:
+            ref_slice(lo)
+    e1.record()
+    torch.cuda.synchronize()
+    sampler.end()
+    clocks = sampler.stop(keep_loaded=lambda: (ref_slice(los[-1]), torch.cuda.synchronize()))
+    ms = e0.elapsed_time(e1) / args.steps * (S / float(n * len(los)))
+    flops = 4.0 * H * HD * sum(past + i + 1 for i in range(S))
+    cfgd = {"workload": f"{args.workload}-shaped chunked prefill over the cache: chunk {S} queries, {past} rows "
+                        f"already cached, {H}q/{KVH}kv heads, head_dim {HD}, one layer per step, batch 1",
+            "chunk": S, "past_len": past}
+    sample = (f"the reference's attention_prefill_cached kernel rebuilt for sm_100a, run on the GPU: {len(los)} slices of "
+              f"{n} queries of the chunk per step, time scaled to {S} queries (one CTA per (query, head): additive)")
+    val = S / (ms * 1e-3)
+    line = dict(base, config=cfgd, impl="reference", mode="prefill", metric="prefill attention tokens/s (one layer)",
+                value=val, ms_per_step=ms, clocks=clocks, gpu_launches=args.steps * len(los),
+                tflops=flops / (ms * 1e-3) / 1e12, agreement_max_abs_err=worst,
+                e2e={"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                cpu_baseline={"value": val, "unit": "tokens/s", "cores": 0, "kind": "reference", "sample": sample})
+    print(json.dumps(line))
+    ctx.close()
+
+
 def run_prefill(args, torch, hkv, oracle, cfg, rank, base, gpu_id):
     """Chunked prefill over the cache (batch 1, one layer per call): append the chunk's K/V,
     then attention of its --chunk queries over rows [0, past + chunk). Tensor-bound:
@@ -489,6 +551,8 @@ def run_prefill(args, torch, hkv, oracle, cfg, rank, base, gpu_id):
 
     step()
     assert ctx.device_status() == 0
+    if args.impl == "reference":
+        return run_prefill_reference(args, torch, oracle, cfg, base, gpu_id, q, k, v, out, S, past, slots, scale, ctx)
     err = None
     if not args.no_verify:  # sampled queries against the oracle
         hk, hv, hq = k.cpu().numpy(), v.cpu().numpy(), q.cpu().numpy()
@@ -586,6 +650,9 @@ def main():
             "config": config}
 
     # ------------------------------------------------------------------ reference arm
+    if args.impl == "reference" and args.mode == "prefill":
+        run_prefill(args, torch, hkv, oracle, cfg, rank, base, gpu_id)
+        return 0
     if args.impl == "reference":
         sampler = ClockSampler(gpu_id)
         sampler.start()
