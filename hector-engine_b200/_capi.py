@@ -63,6 +63,7 @@ SIGNATURES = {
     "hkv_position_of_slot": (C.c_int32, [C.POINTER(HkvGeometry), C.c_int32, C.c_int32]),
     "hkv_plan_sequence": (C.c_int, [C.POINTER(HkvGeometry), C.c_int32, C.c_int32] + [C.POINTER(C.c_int32)] * 4),
     "hkv_plan_prefill": (C.c_int, [C.POINTER(HkvGeometry), C.c_int32, C.c_int32, C.c_int32] + [C.POINTER(C.c_int32)] * 4),
+    "hkv_preferred_prefill_chunk": (C.c_int32, [C.POINTER(HkvGeometry), C.c_int32, C.c_int32]),
     "hkv_fill_synthetic": (C.c_int, [_VP, C.c_uint64, C.c_uint64, C.c_uint64, _VP]),
 }
 

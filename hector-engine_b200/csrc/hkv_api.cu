@@ -1031,6 +1031,20 @@ int hkv_plan_prefill(const hkv_geometry* g, int32_t seq_new, int32_t past_len, i
     return HKV_OK;
 }
 
+int32_t hkv_preferred_prefill_chunk(const hkv_geometry* g, int32_t sm_count, int32_t target) {
+    const char* why;
+    if (validate_geometry(g, &why) || sm_count <= 0 || target <= 0) return -1;
+    if (!prefill_tc_ok(*g)) return target;
+    const int G = g->num_heads / g->num_kv_heads;
+    const int q_pair = 2 * (kPfRows / G);
+    int a = sm_count, b = g->num_kv_heads;
+    while (b) { const int r = a % b; a = b; b = r; }   // a = gcd
+    const long long unit = (long long)(sm_count / a) * q_pair;   // queries per whole round of items
+    const long long k = target / unit;
+    const long long best = (k > 0 ? k : 1) * unit;
+    return best > 0x7fffffffLL ? target : (int32_t)best;
+}
+
 int hkv_fill_synthetic(void* dst, uint64_t seed, uint64_t first_index, uint64_t count, void* stream) {
     if (!dst && count) return HKV_ERR_INVALID_ARG;
     if (!aligned(dst, 2)) return HKV_ERR_ALIGNMENT;

@@ -221,3 +221,20 @@ def test_prefill_plan_never_leaves_a_key_split_empty(hkv, monkeypatch):
                           slots=past + S + int(rng.integers(0, 300)), window_size=win, max_seq_new=S)
         tif, items, splits, span = _plan_prefill(hkv, gg, S, past, sms=int(rng.choice([132, 148])))
         assert 1 <= splits <= min(span, 4) and tif in (1, 2) and items >= 1
+
+
+def test_preferred_prefill_chunk_makes_items_a_multiple_of_the_sms(hkv):
+    lib = hkv._capi.load()
+    g = hkv.Geometry(num_heads=28, num_kv_heads=4, head_dim=128, slots=131072, max_seq_new=4096)
+    gc = g.to_c()
+    assert lib.hkv_preferred_prefill_chunk(C.byref(gc), 148, 2048) == 1332     # 37 pairs x 36 queries
+    assert lib.hkv_preferred_prefill_chunk(C.byref(gc), 148, 3000) == 2664
+    assert lib.hkv_preferred_prefill_chunk(C.byref(gc), 148, 100) == 1332      # never below one round
+    for target in (1332, 2664, 3996):
+        tif, items, splits, span = _plan_prefill(hkv, g, target, 30720)
+        assert tif == 2 and (items // splits) % 148 == 0
+    mha = hkv.Geometry(num_heads=8, num_kv_heads=8, head_dim=64, slots=4096, max_seq_new=4096)
+    assert lib.hkv_preferred_prefill_chunk(C.byref(mha.to_c()), 148, 10000) == 9472   # 37 pairs x 256
+    simt = hkv.Geometry(num_heads=32, num_kv_heads=32, head_dim=96, slots=4096)
+    assert lib.hkv_preferred_prefill_chunk(C.byref(simt.to_c()), 148, 777) == 777
+    assert lib.hkv_preferred_prefill_chunk(C.byref(gc), 0, 2048) < 0
