@@ -3,8 +3,8 @@ the Héctor / HELIOS engine) behind a C ABI. This package is the host-side harne
 libhkv.so: a ctypes binding, operator wrappers named like the reference's launchers and
 cache owners mirroring the reference's cache objects. It has no CPU compute path."""
 from . import _capi
-from ._capi import (HkvError, HkvGeometry, KERNEL_AUTO, KERNEL_GENERIC, KERNEL_TMA,
-                    LAYOUT_LINEAR, LAYOUT_RING)
+from ._capi import (FLAG_APPEND_ONLY, FLAG_SCALAR_POSITION, HkvError, HkvGeometry, KERNEL_AUTO,
+                    KERNEL_GENERIC, KERNEL_TMA, LAYOUT_LINEAR, LAYOUT_RING)
 from .cache import (Gemma4KVCache, Gemma4Layer, Gemma4Layout, KVCache, KVCacheConfig,
                     gemma4_layout)
 from . import dist, ops

@@ -18,6 +18,8 @@ STATUS_NAMES = {
     8: "HKV_ERR_DEVICE_FAULT",
 }
 LAYOUT_LINEAR, LAYOUT_RING = 0, 1
+FLAG_SCALAR_POSITION, FLAG_APPEND_ONLY = 1, 2
+ABI_VERSION = 2
 KERNEL_AUTO, KERNEL_GENERIC, KERNEL_TMA = 0, 1, 2
 
 
@@ -28,7 +30,9 @@ class HkvGeometry(C.Structure):
         ("head_dim", C.c_int32), ("slots", C.c_int32), ("window_size", C.c_int32),
         ("layout", C.c_int32), ("chunk_tiles", C.c_int32), ("batch_stride_elems", C.c_int64),
         ("shard_rank", C.c_int32), ("shard_count", C.c_int32), ("shard_block", C.c_int32),
-        ("kernel_select", C.c_int32), ("max_seq_new", C.c_int32), ("reserved", C.c_int32 * 3),
+        ("kernel_select", C.c_int32), ("max_seq_new", C.c_int32), ("flags", C.c_int32),
+        ("tune_prefill_splits", C.c_int32), ("tune_prefill_kernel", C.c_int32), ("tune_tma_groups", C.c_int32),
+        ("reserved", C.c_int32 * 3),
     ]
 
 

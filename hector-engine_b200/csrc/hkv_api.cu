@@ -14,7 +14,8 @@
 #include <mutex>
 #include <new>
 #include <string>
-#include <unordered_map>
+#include <map>
+#include <utility>
 #include <vector>
 
 #include "../../include/hkv.h"
@@ -49,14 +50,15 @@ struct hkv_ctx {
     float* workspace = nullptr;
     size_t workspace_bytes = 0;
     int32_t* d_status = nullptr;
-    int32_t* d_len = nullptr;       // [B] for the host-length / host-position twins
+    bool ready = false;             // hkv_ctx_create completed
+    int pos_stride = 1;             // 0 with HKV_FLAG_SCALAR_POSITION
     float* prefill_ws = nullptr;    // [max_seq_new][kPrefillMaxSplits][H][HD+2] key-split partials of the prefill kernel
     int* prefill_counter = nullptr; // work counter of the two-tile prefill kernel (zeroed on the stream before each launch)
-    int32_t* h_len = nullptr;       // pinned staging for d_len
     // host-buffer entry point staging
     __half *st_q = nullptr, *st_k = nullptr, *st_v = nullptr, *st_out = nullptr;
-    std::unordered_map<unsigned long long, TmapPair> tmaps;
+    std::map<std::pair<const void*, const void*>, TmapPair> tmaps;   // keyed on the (k, v) plane pair
     std::string err;
+    std::vector<double> plan_scratch;   // per-SM loads of the prefill split cost model
     // per-kernel timing (hkv_ctx_profile_begin/end)
     std::vector<cudaEvent_t> prof_events;  // 3 per timed call
     int prof_calls = 0, prof_max = 0;
@@ -113,6 +115,11 @@ int validate_geometry(const hkv_geometry* g, const char** why) {
     }
     if (g->kernel_select < 0 || g->kernel_select > 2) {
         *why = "unknown kernel_select";
+        return HKV_ERR_INVALID_ARG;
+    }
+    if ((g->flags & ~(HKV_FLAG_SCALAR_POSITION | HKV_FLAG_APPEND_ONLY)) != 0 || g->tune_prefill_splits < 0 ||
+        g->tune_prefill_kernel < 0 || g->tune_prefill_kernel > 2 || g->tune_tma_groups < 0 || g->tune_tma_groups > 2) {
+        *why = "unknown flag or tuning override";
         return HKV_ERR_INVALID_ARG;
     }
     if (g->batch > 65535) { *why = "batch exceeds 65535"; return HKV_ERR_TOO_LARGE; }
@@ -222,22 +229,20 @@ int prefill_span_tiles(const PrefillTcArgs& t, int q_item, int qt) {
 // as the most loaded CTA; this replays that deal with a per-item overhead (pipeline fill, Q load,
 // output) and adds what the split costs (fp32 partials written and read back by the merge kernel).
 // Costs are in microseconds, from timings of the kernels on B200.
-int prefill_splits(const PrefillTcArgs& t, int HD, int q_item, double tile_us, int sm_count, bool have_ws) {
+int prefill_splits(const PrefillTcArgs& t, int HD, int q_item, double tile_us, int sm_count, bool have_ws,
+                   int tune_splits, std::vector<double>& load) {
     if (!have_ws) return 1;
     // No split may be empty: the split count is bounded by the SHORTEST span of any item. (With a
     // sliding window the spans differ by one tile from item to item, depending on how the window
     // falls on the tile grid; without one the first item has the shortest.)
     int min_span_tiles = 1 << 30;
     for (int qt = 0; qt < t.n_qtiles; ++qt) min_span_tiles = std::min(min_span_tiles, prefill_span_tiles(t, q_item, qt));
-    if (const char* e = getenv("HKV_PREFILL_SPLITS")) {  // tuning override
-        const int v = atoi(e);
-        if (v >= 1) return std::min(v, std::min(kPrefillMaxSplits, min_span_tiles));
-    }
+    if (tune_splits >= 1) return std::min(tune_splits, std::min(kPrefillMaxSplits, min_span_tiles));
     const double item_tiles = q_item > t.QT ? 5.0 : 6.0;
     const double row_bytes = (double)t.S_new * t.H * (HD + 2) * 4.0;
     int best = 1;
     double best_cost = 0.0;
-    std::vector<double> load((size_t)sm_count);
+    if (load.size() < (size_t)sm_count) load.resize((size_t)sm_count);   // grows once per context
     for (int s = 1; s <= kPrefillMaxSplits && s <= min_span_tiles; ++s) {
         const long long items = (long long)t.n_qtiles * t.KVH * s;
         const int grid = items < sm_count ? (int)items : sm_count;
@@ -245,7 +250,7 @@ int prefill_splits(const PrefillTcArgs& t, int HD, int q_item, double tile_us, i
         // the next item (longest first) to whichever CTA is free: the full rounds even out, the
         // remainder lands on top — estimated in one pass, this runs on the host before every launch.
         const bool greedy = q_item > t.QT;
-        if (!greedy) std::fill(load.begin(), load.end(), 0.0);
+        if (!greedy) std::fill(load.begin(), load.begin() + sm_count, 0.0);
         const long long full = (items / grid) * grid;
         long long item = 0;
         double mx = 0.0, sum_full = 0.0, rem_first = 0.0;
@@ -275,7 +280,7 @@ int prefill_splits(const PrefillTcArgs& t, int HD, int q_item, double tile_us, i
 // work items, how many key splits. Fills the shape fields of `t` (not the pointers). Pure
 // arithmetic: no device is touched.
 void plan_prefill_tc(const hkv_geometry& g, int seq_new, int past_len, int sm_count, bool have_ws,
-                     PrefillTcArgs& t, int& pair, int& min_span) {
+                     PrefillTcArgs& t, int& pair, int& min_span, std::vector<double>& scratch) {
     const int G = g.num_heads / g.num_kv_heads, HD = g.head_dim;
     t.S_new = seq_new;
     t.past_len = past_len;
@@ -285,13 +290,13 @@ void plan_prefill_tc(const hkv_geometry& g, int seq_new, int past_len, int sm_co
     t.QT = kPfRows / G;
     // two query tiles per work item (hkv_prefill_tc2_kernel) unless the whole chunk fits one tile
     pair = seq_new > t.QT ? 1 : 0;
-    if (const char* e = getenv("HKV_PREFILL_KERNEL")) pair = atoi(e) == 1 ? 0 : 1;   // A/B override
+    if (g.tune_prefill_kernel) pair = g.tune_prefill_kernel == 1 ? 0 : 1;
     const int q_item = pair ? 2 * t.QT : t.QT;
     t.n_qtiles = (seq_new + q_item - 1) / q_item;
     t.slots = g.slots;
     t.window = g.window_size;
     const double tile_us = pair ? 0.85 + 0.85 * HD / 128.0 : 0.60 + 0.95 * HD / 128.0;   // per key tile of an item
-    t.splits = prefill_splits(t, HD, q_item, tile_us, sm_count, have_ws);
+    t.splits = prefill_splits(t, HD, q_item, tile_us, sm_count, have_ws, g.tune_prefill_splits, scratch);
     min_span = 1 << 30;
     for (int qt = 0; qt < t.n_qtiles; ++qt) min_span = std::min(min_span, prefill_span_tiles(t, q_item, qt));
 }
@@ -326,9 +331,7 @@ int encode_map(hkv_ctx* c, const void* base, CUtensorMap* out) {
 }
 
 int get_maps(hkv_ctx* c, const void* k, const void* v, const TmapPair** out) {
-    const unsigned long long key =
-        (unsigned long long)reinterpret_cast<uintptr_t>(k) * 0x9E3779B97F4A7C15ull ^
-        (unsigned long long)reinterpret_cast<uintptr_t>(v);
+    const std::pair<const void*, const void*> key(k, v);
     auto it = c->tmaps.find(key);
     if (it == c->tmaps.end()) {
         TmapPair p;
@@ -367,6 +370,7 @@ int launch_append(hkv_ctx* c, const void* k_new, const void* v_new, void* k_cach
     a.k_cache = (__half*)k_cache;
     a.v_cache = (__half*)v_cache;
     a.d_pos = d_pos;
+    a.pos_stride = c->pos_stride;
     a.host_pos = host_pos;
     a.pos_bias = pos_bias;
     a.map = c->map;
@@ -388,10 +392,10 @@ int launch_append(hkv_ctx* c, const void* k_new, const void* v_new, void* k_cach
 
 // Decode into the workspace; `fused` appends k_new/v_new at position total-1.
 int launch_decode(hkv_ctx* c, const void* q, const void* k_new, const void* v_new, void* k_cache,
-                  void* v_cache, const int32_t* d_total, int pos_is_index, float scale,
+                  void* v_cache, const int32_t* d_total, int pos_is_index, int host_len, float scale,
                   cudaStream_t st) {
     const hkv_geometry& g = c->g;
-    if (!q || !k_cache || !v_cache || !d_total) return fail(c, HKV_ERR_INVALID_ARG, "decode: null tensor");
+    if (!q || !k_cache || !v_cache) return fail(c, HKV_ERR_INVALID_ARG, "decode: null tensor");
     if (!aligned(q, 2) || !aligned(k_cache, 2) || !aligned(v_cache, 2))
         return fail(c, HKV_ERR_ALIGNMENT, "decode: fp16 pointer not 2-byte aligned");
     if (!std::isfinite(scale)) return fail(c, HKV_ERR_INVALID_ARG, "decode: scale is not finite");
@@ -417,6 +421,8 @@ int launch_decode(hkv_ctx* c, const void* q, const void* k_new, const void* v_ne
     a.chunk_tiles = c->chunk_tiles;
     a.max_chunks = c->max_chunks;
     a.pos_is_index = pos_is_index;
+    a.pos_stride = c->pos_stride;
+    a.host_len = host_len;
     a.batch_stride = c->batch_stride;
     a.scale_log2 = scale * 1.4426950408889634f;
 
@@ -440,10 +446,10 @@ int launch_decode(hkv_ctx* c, const void* q, const void* k_new, const void* v_ne
         kern<<<grid, threads, c->plan.bytes, st>>>(maps->k, maps->v, a, c->plan.stages);
     } else {
         if (fused) {
-            // generic path: append first (its own launch), then attend
-            const int32_t* d_pos = d_total;
-            if (!pos_is_index) return fail(c, HKV_ERR_INVALID_ARG, "fused decode needs cache positions");
-            const int stt = launch_append(c, k_new, v_new, k_cache, v_cache, d_pos, 0, 0, 1, st);
+            // generic path: append first (its own launch), then attend; the new row sits at
+            // position total - 1 when the array holds attended lengths
+            if (!d_total) return fail(c, HKV_ERR_INVALID_ARG, "fused decode needs device positions");
+            const int stt = launch_append(c, k_new, v_new, k_cache, v_cache, d_total, pos_is_index ? 0 : -1, 0, 1, st);
             if (stt) return stt;
         }
         dim3 grid((unsigned)c->max_chunks, (unsigned)g.num_heads, (unsigned)g.batch);
@@ -453,7 +459,7 @@ int launch_decode(hkv_ctx* c, const void* q, const void* k_new, const void* v_ne
 }
 
 int launch_combine(hkv_ctx* c, const float* part, long long stride_b, long long stride_c,
-                   const int32_t* d_total, int pos_is_index, int fixed_count, void* out,
+                   const int32_t* d_total, int pos_is_index, int host_len, int fixed_count, void* out,
                    float* out_partial, cudaStream_t st) {
     CombineArgs a;
     a.part = part;
@@ -461,6 +467,8 @@ int launch_combine(hkv_ctx* c, const float* part, long long stride_b, long long 
     a.stride_c = stride_c;
     a.total = d_total;
     a.pos_is_index = pos_is_index;
+    a.pos_stride = c->pos_stride;
+    a.host_len = host_len;
     a.fixed_count = fixed_count;
     a.map = c->map;
     a.chunk_tiles = c->chunk_tiles;
@@ -473,7 +481,7 @@ int launch_combine(hkv_ctx* c, const float* part, long long stride_b, long long 
     // kernel): with few (sequence, head) rows and many partials per row the merge is latency-bound
     // and the warp-dealt kernel wins (batch 1-8: +5 %); with many rows the one-thread-per-dimension
     // kernel does (batch 32-64: +2 % of the step).
-    const int most = d_total ? c->max_chunks : fixed_count;
+    const int most = fixed_count > 0 ? fixed_count : c->max_chunks;
     const long long rows = (long long)grid.x * grid.y;
     if (rows <= 2LL * c->sm_count && most > 8) hkv_combine_kernel<<<grid, kCombineThreads, 0, st>>>(a);
     else hkv_combine_few_kernel<<<grid, 128, 0, st>>>(a);
@@ -482,18 +490,19 @@ int launch_combine(hkv_ctx* c, const float* part, long long stride_b, long long 
 
 int decode_full(hkv_ctx* c, const void* q, const void* k_new, const void* v_new, void* k_cache,
                 void* v_cache, void* out, float* out_partial, const int32_t* d_total,
-                int pos_is_index, float scale, cudaStream_t st) {
+                int pos_is_index, int host_len, float scale, cudaStream_t st) {
+    if (!c->workspace) return fail(c, HKV_ERR_WORKSPACE, "decode: the context was created append-only");
     if (!out && !out_partial) return fail(c, HKV_ERR_INVALID_ARG, "decode: null output");
     if (out && !aligned(out, 2)) return fail(c, HKV_ERR_ALIGNMENT, "decode: out not 2-byte aligned");
     const bool timed = c->prof_calls < c->prof_max;
     cudaEvent_t* ev = timed ? &c->prof_events[(size_t)c->prof_calls * 3] : nullptr;
     if (timed) cudaEventRecord(ev[0], st);
-    int stt = launch_decode(c, q, k_new, v_new, k_cache, v_cache, d_total, pos_is_index, scale, st);
+    int stt = launch_decode(c, q, k_new, v_new, k_cache, v_cache, d_total, pos_is_index, host_len, scale, st);
     if (stt) return stt;
     if (timed) cudaEventRecord(ev[1], st);
     const long long PW = c->g.head_dim + 2;
     stt = launch_combine(c, c->workspace, (long long)c->max_chunks * c->g.num_heads * PW,
-                         (long long)c->g.num_heads * PW, d_total, pos_is_index, 0, out, out_partial,
+                         (long long)c->g.num_heads * PW, d_total, pos_is_index, host_len, 0, out, out_partial,
                          st);
     if (stt) return stt;
     if (timed) {
@@ -503,13 +512,6 @@ int decode_full(hkv_ctx* c, const void* q, const void* k_new, const void* v_new,
     const cudaError_t e = cudaPeekAtLastError();
     if (e != cudaSuccess) return fail_cuda(c, e, "decode launch");
     return HKV_OK;
-}
-
-int set_host_len(hkv_ctx* c, int32_t v, cudaStream_t st) {
-    for (int b = 0; b < c->g.batch; ++b) c->h_len[b] = v;
-    const cudaError_t e = cudaMemcpyAsync(c->d_len, c->h_len, sizeof(int32_t) * c->g.batch,
-                                          cudaMemcpyHostToDevice, st);
-    return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "cudaMemcpyAsync(length)");
 }
 
 }  // namespace
@@ -585,7 +587,16 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
                           ? geometry->batch_stride_elems
                           : (long long)geometry->slots * geometry->num_kv_heads * geometry->head_dim;
     c->map = make_map(*geometry);
+    c->pos_stride = (geometry->flags & HKV_FLAG_SCALAR_POSITION) ? 0 : 1;
     fill_plan(*geometry, sm, c->chunk_tiles, c->max_chunks);
+    e = cudaMalloc(&c->d_status, sizeof(int32_t));
+    if (e != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(status)");
+    e = cudaMemset(c->d_status, 0, sizeof(int32_t));
+    if (e != cudaSuccess) return fail_cuda(c, e, "cudaMemset(status)");
+    if (geometry->flags & HKV_FLAG_APPEND_ONLY) {   // no attention: no workspaces, no kernel opt-ins
+        c->ready = true;
+        return HKV_OK;
+    }
 
     // kernel choice
     const bool tma_ok = tma_geometry_ok(*geometry);
@@ -594,8 +605,7 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
     c->kernel = (geometry->kernel_select != HKV_KERNEL_GENERIC && tma_ok) ? HKV_KERNEL_TMA
                                                                            : HKV_KERNEL_GENERIC;
     if (c->kernel == HKV_KERNEL_TMA) {
-        const char* env = getenv("HKV_TMA_GROUPS");
-        c->tma_groups = (env && atoi(env) == 1) ? 1 : 2;
+        c->tma_groups = geometry->tune_tma_groups == 1 ? 1 : 2;
         c->plan = tma_plan(geometry->head_dim, c->G, c->tma_groups * 4, geometry->batch, c->smem_optin);
         if (c->plan.stages < 2 && c->tma_groups == 2) {
             c->tma_groups = 1;
@@ -641,14 +651,7 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
     c->workspace_bytes = workspace_bytes_for(*geometry, c->max_chunks);
     e = cudaMalloc(&c->workspace, c->workspace_bytes);
     if (e != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(workspace)");
-    e = cudaMalloc(&c->d_status, sizeof(int32_t));
-    if (e != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(status)");
-    e = cudaMemset(c->d_status, 0, sizeof(int32_t));
-    if (e != cudaSuccess) return fail_cuda(c, e, "cudaMemset(status)");
-    e = cudaMalloc(&c->d_len, sizeof(int32_t) * geometry->batch);
-    if (e != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(length)");
-    e = cudaMallocHost(&c->h_len, sizeof(int32_t) * geometry->batch);
-    if (e != cudaSuccess) return fail_cuda(c, e, "cudaMallocHost(length)");
+    c->ready = true;
     return HKV_OK;
 }
 
@@ -656,10 +659,8 @@ int hkv_ctx_destroy(hkv_ctx* c) {
     if (!c) return HKV_OK;
     if (c->workspace) cudaFree(c->workspace);
     if (c->d_status) cudaFree(c->d_status);
-    if (c->d_len) cudaFree(c->d_len);
     if (c->prefill_ws) cudaFree(c->prefill_ws);
     if (c->prefill_counter) cudaFree(c->prefill_counter);
-    if (c->h_len) cudaFreeHost(c->h_len);
     if (c->st_q) cudaFree(c->st_q);
     if (c->st_k) cudaFree(c->st_k);
     if (c->st_v) cudaFree(c->st_v);
@@ -673,9 +674,32 @@ const char* hkv_ctx_last_error(const hkv_ctx* c) { return c ? c->err.c_str() : "
 int hkv_ctx_kernel(const hkv_ctx* c) { return c ? c->kernel : 0; }
 int hkv_ctx_launches_per_decode(const hkv_ctx* c) { return c ? 2 : 0; }
 
+// Every launch entry point: the context must be complete and the CURRENT device must be the one
+// it was created on (its workspace, status word, tensor maps and shared-memory opt-ins live there).
+static int check_ctx(hkv_ctx* c) {
+    if (!c) return HKV_ERR_INVALID_ARG;
+    if (!c->ready) return fail(c, HKV_ERR_INVALID_ARG, "context not initialised");
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(c, HKV_ERR_CUDA, "cudaGetDevice failed");
+    }
+    if (dev != c->device) {
+        char buf[96];
+        snprintf(buf, sizeof buf, "context belongs to device %d, current device is %d", c->device, dev);
+        return fail(c, HKV_ERR_INVALID_ARG, buf);
+    }
+    return HKV_OK;
+}
+#define HKV_CHECK_CTX(c)                        \
+    do {                                        \
+        const int chk_ = check_ctx(c);          \
+        if (chk_ != HKV_OK) return chk_;        \
+    } while (0)
+
 int hkv_ctx_device_status(hkv_ctx* c, void* stream, int32_t* status_out) {
     if (!c || !status_out) return HKV_ERR_INVALID_ARG;
-    if (!c->d_status) return fail(c, HKV_ERR_INVALID_ARG, "context not initialised");
+    HKV_CHECK_CTX(c);
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return fail_cuda(c, e, "cudaStreamSynchronize");
@@ -688,11 +712,6 @@ int hkv_ctx_device_status(hkv_ctx* c, void* stream, int32_t* status_out) {
     return HKV_OK;
 }
 
-#define HKV_CHECK_CTX(c)                                                        \
-    do {                                                                        \
-        if (!(c)) return HKV_ERR_INVALID_ARG;                                   \
-        if (!(c)->workspace) return fail((c), HKV_ERR_INVALID_ARG, "context not initialised"); \
-    } while (0)
 
 int hkv_append(hkv_ctx* c, const void* k_new, const void* v_new, void* k_cache, void* v_cache,
                const int32_t* d_cache_pos, int32_t seq_new, void* stream) {
@@ -719,18 +738,18 @@ int hkv_append_at(hkv_ctx* c, const void* k_new, const void* v_new, void* k_cach
 int hkv_decode_attention(hkv_ctx* c, const void* q, const void* k_cache, const void* v_cache,
                          void* out, const int32_t* d_total_seq, float scale, void* stream) {
     HKV_CHECK_CTX(c);
+    if (!d_total_seq) return fail(c, HKV_ERR_INVALID_ARG, "decode: null length array");
     return decode_full(c, q, nullptr, nullptr, const_cast<void*>(k_cache), const_cast<void*>(v_cache),
-                       out, nullptr, d_total_seq, 0, scale, (cudaStream_t)stream);
+                       out, nullptr, d_total_seq, 0, 0, scale, (cudaStream_t)stream);
 }
 
 int hkv_decode_attention_len(hkv_ctx* c, const void* q, const void* k_cache, const void* v_cache,
                              void* out, int32_t seq_len, float scale, void* stream) {
     HKV_CHECK_CTX(c);
     if (seq_len < 0) return fail(c, HKV_ERR_INVALID_ARG, "decode: negative seq_len");
-    const int st = set_host_len(c, seq_len, (cudaStream_t)stream);
-    if (st) return st;
+    // the length is a kernel argument: nothing shared between calls, nothing to copy
     return decode_full(c, q, nullptr, nullptr, const_cast<void*>(k_cache), const_cast<void*>(v_cache),
-                       out, nullptr, c->d_len, 0, scale, (cudaStream_t)stream);
+                       out, nullptr, nullptr, 0, seq_len, scale, (cudaStream_t)stream);
 }
 
 int hkv_append_decode_attention(hkv_ctx* c, const void* q, const void* k_new, const void* v_new,
@@ -740,7 +759,8 @@ int hkv_append_decode_attention(hkv_ctx* c, const void* q, const void* k_new, co
     if (!k_new || !v_new) return fail(c, HKV_ERR_INVALID_ARG, "fused decode: null k_new/v_new");
     if (!aligned(k_new, 2) || !aligned(v_new, 2))
         return fail(c, HKV_ERR_ALIGNMENT, "fused decode: fp16 pointer not 2-byte aligned");
-    return decode_full(c, q, k_new, v_new, k_cache, v_cache, out, nullptr, d_cache_pos, 1, scale,
+    if (!d_cache_pos) return fail(c, HKV_ERR_INVALID_ARG, "fused decode: null position array");
+    return decode_full(c, q, k_new, v_new, k_cache, v_cache, out, nullptr, d_cache_pos, 1, 0, scale,
                        (cudaStream_t)stream);
 }
 
@@ -749,16 +769,15 @@ int hkv_decode_partials(hkv_ctx* c, const void* q, const void* k_new, const void
                         const int32_t* d_total_seq, float scale, void* stream) {
     HKV_CHECK_CTX(c);
     if (!partial_out) return fail(c, HKV_ERR_INVALID_ARG, "decode_partials: null output");
-    cudaStream_t st = (cudaStream_t)stream;
-    if (k_new) {
-        // d_total_seq holds attended lengths, so the new row sits at position total - 1.
-        // Only the rank that owns that position stores it (slot_of_pos is -1 elsewhere).
-        if (!v_new) return fail(c, HKV_ERR_INVALID_ARG, "decode_partials: k_new without v_new");
-        const int stt = launch_append(c, k_new, v_new, k_cache, v_cache, d_total_seq, -1, 0, 1, st);
-        if (stt) return stt;
-    }
-    return decode_full(c, q, nullptr, nullptr, k_cache, v_cache, nullptr, partial_out, d_total_seq, 0,
-                       scale, st);
+    if (!d_total_seq) return fail(c, HKV_ERR_INVALID_ARG, "decode_partials: null length array");
+    if (k_new && !v_new) return fail(c, HKV_ERR_INVALID_ARG, "decode_partials: k_new without v_new");
+    if (k_new && (!aligned(k_new, 2) || !aligned(v_new, 2)))
+        return fail(c, HKV_ERR_ALIGNMENT, "decode_partials: fp16 pointer not 2-byte aligned");
+    // d_total_seq holds attended lengths, so the new row sits at position total - 1. Only the rank
+    // that owns that position stages and stores it (slot_of_pos is -1 elsewhere): the decode kernel
+    // patches its tile, exactly as in hkv_append_decode_attention — no separate append launch.
+    return decode_full(c, q, k_new, v_new, k_cache, v_cache, nullptr, partial_out, d_total_seq, 0, 0,
+                       scale, (cudaStream_t)stream);
 }
 
 int hkv_combine_partials(hkv_ctx* c, const float* partials, int32_t num_parts, void* out,
@@ -768,7 +787,7 @@ int hkv_combine_partials(hkv_ctx* c, const float* partials, int32_t num_parts, v
     if (!aligned(out, 2)) return fail(c, HKV_ERR_ALIGNMENT, "combine: out not 2-byte aligned");
     const long long PW = c->g.head_dim + 2;
     const int st = launch_combine(c, partials, (long long)c->g.num_heads * PW,
-                                  (long long)c->g.batch * c->g.num_heads * PW, nullptr, 0, num_parts,
+                                  (long long)c->g.batch * c->g.num_heads * PW, nullptr, 0, 0, num_parts,
                                   out, nullptr, (cudaStream_t)stream);
     if (st) return st;
     const cudaError_t e = cudaPeekAtLastError();
@@ -782,6 +801,8 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
     if (seq_new < 0 || past_len < 0) return fail(c, HKV_ERR_INVALID_ARG, "prefill: negative length");
     if (!aligned(q, 2) || !aligned(k_cache, 2) || !aligned(v_cache, 2) || !aligned(out, 2))
         return fail(c, HKV_ERR_ALIGNMENT, "prefill: fp16 pointer not 2-byte aligned");
+    if (c->g.batch != 1) return fail(c, HKV_ERR_GEOMETRY, "prefill: the op is batch 1 (kernels/attention.cu:709)");
+    if (!c->workspace) return fail(c, HKV_ERR_WORKSPACE, "prefill: the context was created append-only");
     if (c->g.layout != HKV_LAYOUT_LINEAR || c->g.shard_count > 1)
         return fail(c, HKV_ERR_GEOMETRY, "prefill: linear unsharded cache only");
     if (seq_new == 0) return HKV_OK;
@@ -794,7 +815,7 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
         t.status = c->d_status;
         int pair = 0, min_span = 0;
         plan_prefill_tc(g, seq_new, past_len, c->sm_count, c->prefill_ws != nullptr && seq_new <= g.max_seq_new, t, pair,
-                        min_span);
+                        min_span, c->plan_scratch);
         if (t.splits > min_span) return fail(c, HKV_ERR_INVALID_ARG, "prefill: internal plan error (a key split would be empty)");
         t.scale_log2 = scale * 1.4426950408889634f;
         t.part = c->prefill_ws;
@@ -883,8 +904,9 @@ int hkv_append_decode_attention_host(hkv_ctx* c, const void* h_q, const void* h_
         (e = cudaMemcpyAsync(c->st_k, h_k_new, kb, cudaMemcpyHostToDevice, st)) != cudaSuccess ||
         (e = cudaMemcpyAsync(c->st_v, h_v_new, kb, cudaMemcpyHostToDevice, st)) != cudaSuccess)
         return fail_cuda(c, e, "cudaMemcpyAsync(H2D)");
+    if (!d_cache_pos) return fail(c, HKV_ERR_INVALID_ARG, "host op: null position array");
     const int stt = decode_full(c, c->st_q, c->st_k, c->st_v, k_cache, v_cache, c->st_out, nullptr,
-                                d_cache_pos, 1, scale, st);
+                                d_cache_pos, 1, 0, scale, st);
     if (stt) return stt;
     if ((e = cudaMemcpyAsync(h_out, c->st_out, qb, cudaMemcpyDeviceToHost, st)) != cudaSuccess)
         return fail_cuda(c, e, "cudaMemcpyAsync(D2H)");
@@ -948,6 +970,7 @@ int hkv_qk_norm_rope_kv(hkv_ctx* c, void* q, void* k, const void* v, const void*
     a.k_cache = (__half*)k_cache;
     a.v_cache = (__half*)v_cache;
     a.d_pos = d_cache_pos;
+    a.pos_stride = c->pos_stride;
     a.host_pos = position;
     a.map = c->map;
     a.B = g.batch;
@@ -1023,7 +1046,8 @@ int hkv_plan_prefill(const hkv_geometry* g, int32_t seq_new, int32_t past_len, i
     }
     PrefillTcArgs t{};
     int pair = 0, min_span = 0;
-    plan_prefill_tc(*g, seq_new, past_len, sm_count, g->max_seq_new >= seq_new, t, pair, min_span);
+    std::vector<double> scratch;
+    plan_prefill_tc(*g, seq_new, past_len, sm_count, g->max_seq_new >= seq_new, t, pair, min_span, scratch);
     if (tiles_in_flight) *tiles_in_flight = pair ? 2 : 1;
     if (items) *items = t.n_qtiles * t.KVH * t.splits;
     if (splits) *splits = t.splits;
@@ -1170,6 +1194,8 @@ extern "C" int hkv_decode_attention_static(const hkv_geometry* geometry, const v
     a.chunk_tiles = chunk_tiles;
     a.max_chunks = max_chunks;
     a.pos_is_index = 0;
+    a.pos_stride = (g.flags & HKV_FLAG_SCALAR_POSITION) ? 0 : 1;
+    a.host_len = 0;
     a.batch_stride = g.batch_stride_elems ? g.batch_stride_elems
                                           : (long long)g.slots * g.num_kv_heads * g.head_dim;
     a.scale_log2 = scale * 1.4426950408889634f;
@@ -1184,6 +1210,8 @@ extern "C" int hkv_decode_attention_static(const hkv_geometry* geometry, const v
     c.stride_c = (long long)g.num_heads * PW;
     c.total = d_total_seq;
     c.pos_is_index = 0;
+    c.pos_stride = a.pos_stride;
+    c.host_len = 0;
     c.fixed_count = 0;
     c.map = a.map;
     c.chunk_tiles = chunk_tiles;
@@ -1194,9 +1222,3 @@ extern "C" int hkv_decode_attention_static(const hkv_geometry* geometry, const v
     hkv_combine_kernel<<<dim3((unsigned)g.num_heads, (unsigned)g.batch), kCombineThreads, 0, st>>>(c);
     return cudaPeekAtLastError() == cudaSuccess ? HKV_OK : HKV_ERR_CUDA;
 }
-
-#ifdef HKV_PF_TRACE
-extern "C" int hkv_debug_prefill_trace(long long* out, int n) {
-    return (int)cudaMemcpyFromSymbol(out, hkv::g_pf_trace, sizeof(long long) * (size_t)n);
-}
-#endif

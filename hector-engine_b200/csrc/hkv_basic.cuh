@@ -19,6 +19,7 @@ struct AppendArgs {
     __half* k_cache;
     __half* v_cache;
     const int32_t* d_pos;  // [B] or null -> host_pos
+    int pos_stride;        // 1: d_pos[b]; 0: every sequence reads d_pos[0] (the reference's scalar)
     int host_pos;
     int pos_bias;          // added to the position read from d_pos (e.g. -1: length -> index)
     SeqMap map;
@@ -39,7 +40,7 @@ __global__ void __launch_bounds__(256) hkv_append_kernel(const AppendArgs a) {
         r >>= 1;
         const int s = (int)(r % a.S);
         const int b = (int)(r / a.S);
-        const int pos = (a.d_pos ? a.d_pos[b] + a.pos_bias : a.host_pos) + s;
+        const int pos = (a.d_pos ? a.d_pos[b * a.pos_stride] + a.pos_bias : a.host_pos) + s;
         const int slot = slot_of_pos(a.map, pos);
         if (slot < 0) continue;
         const __half* src = (plane ? a.v_new : a.k_new) + ((long long)b * a.S + s) * a.row_elems;
@@ -151,9 +152,11 @@ __global__ void __launch_bounds__(kGenWarps * 32) hkv_decode_generic_kernel(cons
 struct CombineArgs {
     const float* part;
     long long stride_b, stride_c;  // floats
-    const int32_t* total;          // null -> fixed_count
+    const int32_t* total;          // null -> host_len (or fixed_count when that is > 0)
     int pos_is_index;
-    int fixed_count;
+    int pos_stride;                // as DecodeArgs
+    int host_len;
+    int fixed_count;               // > 0: that many partials per row, whatever the length
     SeqMap map;
     int chunk_tiles;
     int H, HD;
@@ -171,11 +174,10 @@ constexpr int kCombineThreads = kCombineWarps * 32;
 // through shared memory.
 __global__ void __launch_bounds__(kCombineThreads) hkv_combine_kernel(const CombineArgs a) {
     const int h = blockIdx.x, b = blockIdx.y;
-    int n = a.fixed_count;
-    if (a.total) {
-        const int t = a.total[b] + a.pos_is_index;
-        n = num_chunks(a.map, t > 0 ? t : 0, a.chunk_tiles);
-    }
+    const int n = a.fixed_count > 0
+                      ? a.fixed_count
+                      : num_chunks(a.map, length_of(a.total, a.pos_stride, a.pos_is_index, a.host_len, b),
+                                   a.chunk_tiles);
     const int PW = a.HD + 2;
     const float* base = a.part + b * a.stride_b + (long long)h * PW;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -239,11 +241,10 @@ __global__ void __launch_bounds__(kCombineThreads) hkv_combine_kernel(const Comb
 // of the kernel above, which only pays when few rows each have many partials (small batches).
 __global__ void __launch_bounds__(128) hkv_combine_few_kernel(const CombineArgs a) {
     const int h = blockIdx.x, b = blockIdx.y;
-    int n = a.fixed_count;
-    if (a.total) {
-        const int t = a.total[b] + a.pos_is_index;
-        n = num_chunks(a.map, t > 0 ? t : 0, a.chunk_tiles);
-    }
+    const int n = a.fixed_count > 0
+                      ? a.fixed_count
+                      : num_chunks(a.map, length_of(a.total, a.pos_stride, a.pos_is_index, a.host_len, b),
+                                   a.chunk_tiles);
     const int PW = a.HD + 2;
     const float* base = a.part + b * a.stride_b + (long long)h * PW;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;

@@ -102,19 +102,28 @@ struct DecodeArgs {
     __half* k_cache_w;      // writable aliases of the planes (fused append)
     __half* v_cache_w;
     float* part;            // [B, max_chunks, H, HD+2]: o[HD], m (log2 domain), l
-    const int32_t* total;   // [B] attended length, or cache position when pos_is_index
+    const int32_t* total;   // [B] attended length, or cache position when pos_is_index; null -> host_len
     int32_t* status;        // device status word
     SeqMap map;
     int B, H, KVH, HD;
     int chunk_tiles, max_chunks;
     int pos_is_index;       // 1: total[b] holds cache_pos, attended length = cache_pos + 1
+    int pos_stride;         // 1: one position per sequence; 0: every sequence reads total[0]
+                            //    (the reference's scalar, kernels/attention.cu:351)
+    int host_len;           // attended length of every sequence when total is null
     long long batch_stride; // elements
     float scale_log2;       // scale * log2(e)
 };
 
-__device__ __forceinline__ int attended_len(const DecodeArgs& a, int b) {
-    const int t = a.total[b] + a.pos_is_index;
+// Attended length of sequence b from a device position array (one entry per sequence, or one
+// shared entry when pos_stride == 0) or, when the array is null, from a value passed by the host.
+__device__ __forceinline__ int length_of(const int32_t* total, int pos_stride, int pos_is_index,
+                                         int host_len, int b) {
+    const int t = total ? total[b * pos_stride] + pos_is_index : host_len;
     return t > 0 ? t : 0;
+}
+__device__ __forceinline__ int attended_len(const DecodeArgs& a, int b) {
+    return length_of(a.total, a.pos_stride, a.pos_is_index, a.host_len, b);
 }
 
 // ---------------------------------------------------------------------------

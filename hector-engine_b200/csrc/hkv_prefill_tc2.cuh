@@ -30,18 +30,6 @@
 
 namespace hkv {
 
-#ifdef HKV_PF_TRACE
-// Development aid (never compiled into the shipped library): SM-clock timestamps of the roles of
-// CTA 0, [role][tile][event].
-__device__ long long g_pf_trace[3 * 64 * 4];
-#define PF_TRACE(role, tile, k)                                                                      \
-    do {                                                                                             \
-        if (blockIdx.x == 0 && (tile) < 64u) g_pf_trace[((role) * 64 + (tile)) * 4 + (k)] = clock64(); \
-    } while (0)
-#else
-#define PF_TRACE(role, tile, k) do { } while (0)
-#endif
-
 constexpr int kPf2KStages = 2;
 constexpr int kPf2VStages = 2;
 // 12 warps: 0-3 softmax group A, 4-7 group B, 8 TMA producer, 9 MMA issuer, 10-11 only complete the
@@ -332,7 +320,6 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     for (int grp = 0; grp < 2; ++grp) {
                         if (!mbar_wait(B_PFULL + 8 * grp, gt & 1, a.status)) { ok = false; break; }
                         tc_fence_after();
-                        PF_TRACE(2, gt, grp * 2);
                         issue_pv(gt, grp, t > 0);
                         if (!more) tc_commit(B_OFULL + 8 * grp);        // the item's output of this tile is complete
                         if (grp == 1) tc_commit(B_VEMPTY + 8 * vs);     // both tiles have consumed V(g)
@@ -343,7 +330,6 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                                 if (t + 2 == nt) tc_commit(B_QEMPTY);   // last score MMAs of the item issued
                             }
                         }
-                        PF_TRACE(2, gt, grp * 2 + 1);
                     }
                 }
             }
@@ -387,7 +373,6 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 ok = __all_sync(0xffffffffu, ok && mbar_wait(b_sfull, gt & 1, a.status));
                 if (!ok) continue;
                 tc_fence_after();
-                if (lane == 0 && quad == 0) PF_TRACE(grp, gt, 0);
                 // ---- the row's 128 scores, read once (mask bounds are computed under the loads) ----
                 uint32_t sv[4][32];
 #pragma unroll
@@ -425,7 +410,6 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     mx = fmaxf(fmax3(m0, m1, m2), m3);
                 }
                 mx *= a.scale_log2;
-                if (lane == 0 && quad == 0) PF_TRACE(grp, gt, 1);
                 const bool move = mx > m_ref + 8.0f;
                 if (__any_sync(0xffffffffu, move)) {
                     const float m_to = move ? mx : m_ref;
@@ -461,7 +445,6 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     tmem_st16(s_addr + c * 16, pk);
                 }
                 tc_wait_st();
-                if (lane == 0 && quad == 0) PF_TRACE(grp, gt, 2);
                 l_run += (lsum0 + lsum1) + (lsum2 + lsum3);
                 // cache rows of this tile past the last written position may hold stale bits: group A
                 // zeroes them in the staged V tile (before its arrival below, which precedes both
@@ -482,7 +465,6 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 }
                 tc_fence_before();
                 mbar_arrive(b_pfull);
-                if (lane == 0 && quad == 0) PF_TRACE(grp, gt, 3);
             }
             // Wait for the item's last P·V of this tile, then write the row out.
             ok = __all_sync(0xffffffffu, ok && mbar_wait(b_ofull, si & 1, a.status));

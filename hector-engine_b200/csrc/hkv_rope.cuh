@@ -24,6 +24,7 @@ struct RopeArgs {
     __half* k_cache;        // [B, slots, KVH, HD] or null
     __half* v_cache;
     const int32_t* d_pos;   // [B] or null -> host_pos
+    int pos_stride;         // 1: d_pos[b]; 0: every sequence reads d_pos[0]
     int host_pos;
     SeqMap map;
     int B, S, H, KVH, HD, rot;
@@ -45,7 +46,7 @@ __global__ void __launch_bounds__(kRopeWarps * 32) hkv_qk_norm_rope_kernel(const
         const int j = (int)(u % per_tok);
         const long long tok = u / per_tok;
         const int s = (int)(tok % a.S), b = (int)(tok / a.S);
-        const int pos = (a.d_pos ? a.d_pos[b] : a.host_pos) + s;
+        const int pos = (a.d_pos ? a.d_pos[b * a.pos_stride] : a.host_pos) + s;
         const bool is_q = j < a.H, is_k = !is_q && j < a.H + a.KVH;
         const int kvh = is_q ? 0 : (is_k ? j - a.H : j - a.H - a.KVH);
         int slot = -1;

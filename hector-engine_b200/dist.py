@@ -12,11 +12,17 @@ Two ways the path shards (the reference is single-GPU and has neither):
   K/V row is stored only by the rank that owns its position.
 
 The arithmetic here (ownership, local row indices, buffer layout) is plain Python so that it
-can be tested with gloo ranks on CPU; the compute is in libhkv's kernels.
+can be tested with gloo ranks on CPU; the compute is in libhkv's kernels and the step's host
+(context, NCCL communicator, graph capture, failure detection) is C++ (libhkv_dist.so), of which
+SeqSplitDecoder below is only a binding.
 """
 from __future__ import annotations
 
+import ctypes as C
+import os
 from dataclasses import dataclass
+
+from . import _capi
 
 
 def shard_batch(batch: int, world: int, rank: int) -> range:
@@ -66,34 +72,143 @@ class SeqShard:
         return -(-blocks // self.world) * self.block
 
 
-class SeqSplitDecoder:
-    """One layer-geometry's sequence-split decode step on this rank.
+# ---------------------------------------------------------------------------
+# libhkv_dist: the C++ host of the sequence-split step (include/hkv_dist.h)
+# ---------------------------------------------------------------------------
+DIST_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libhkv_dist.so")
+UNIQUE_ID_BYTES = 128
+ERR_PEER, ERR_TIMEOUT, ERR_ROSTER, ERR_HOST = 101, 102, 103, 104
+_dist_lib = None
 
-    step(q, k_new, v_new, k_cache, v_cache, out, d_total_seq):
-        local partials -> all_gather -> merge. `out` is replicated on every rank.
+
+def load_dist() -> C.CDLL:
+    """Loads libhkv_dist.so (once); raises if it was not built. It links libhkv and NCCL."""
+    global _dist_lib
+    if _dist_lib is not None:
+        return _dist_lib
+    if not os.path.exists(DIST_LIB_PATH):
+        raise ImportError(f"{DIST_LIB_PATH} is missing. Build it with `python hector-engine_b200/build.py`.")
+    _capi.load()
+    # Order matters in a process that also uses PyTorch: torch ships its own libnccl.so.2 and must be
+    # the one to load it; libhkv_dist then binds to that copy (same SONAME). Loaded the other way
+    # round, torch would find an older system NCCL already mapped and fail to import.
+    import torch  # noqa: F401
+    lib = C.CDLL(DIST_LIB_PATH)
+    vp, i32, f32p, i32p = C.c_void_p, C.c_int32, C.POINTER(C.c_float), C.POINTER(C.c_int32)
+    sigs = {
+        "hkvd_unique_id": (C.c_int, [vp]),
+        "hkvd_create": (C.c_int, [C.POINTER(vp), C.POINTER(_capi.HkvGeometry), i32, vp, C.c_float, vp]),
+        "hkvd_destroy": (C.c_int, [vp]),
+        "hkvd_last_error": (C.c_char_p, [vp]),
+        "hkvd_bind": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, C.c_uint64, vp]),
+        "hkvd_step": (C.c_int, [vp, i32, i32p]),
+        "hkvd_step_profiled": (C.c_int, [vp, f32p, f32p, f32p]),
+        "hkvd_wait": (C.c_int, [vp, i32]),
+        "hkvd_device_status": (C.c_int, [vp, i32p]),
+        "hkvd_attach_roster": (C.c_int, [vp, C.c_char_p, i32, i32]),
+        "hkvd_leave": (C.c_int, [vp]),
+    }
+    for name, (res, args) in sigs.items():
+        fn = getattr(lib, name)   # AttributeError here = header and library disagree
+        fn.restype, fn.argtypes = res, args
+    lib._hkvd_symbols = tuple(sigs)
+    _dist_lib = lib
+    return lib
+
+
+class SeqSplitError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"hkvd status {status}: {message}")
+        self.status = status
+
+
+def _ptr(x) -> int:
+    return 0 if x is None else (x if isinstance(x, int) else x.data_ptr())
+
+
+class SeqSplitDecoder:
+    """Binding of the C++ sequence-split decoder (host/hkv_seqsplit.hpp behind include/hkv_dist.h):
+    per layer  local split-K partials -> NCCL all-gather -> merge, all layers captured once into a
+    CUDA graph and replayed. The communicator is the C++ object's own; torch.distributed is used
+    only to hand rank 0's communicator id to the other ranks.
+
+        dec = SeqSplitDecoder(geometry, shard, layers, stream=s)
+        dec.bind(q, k_new, v_new, out, k_planes, v_planes, layer_stride_elems, d_total_seq)
+        dec.step()            # enqueue one token (graph replay from the third call on)
+        dec.wait(5000)        # host-side wait with a deadline; raises on a stuck or failed peer
     """
 
-    def __init__(self, hkv, geometry, shard: SeqShard, group=None):
+    def __init__(self, geometry, shard: SeqShard, layers: int, scale: float = 0.0, stream=None, group=None):
         import torch
-        import torch.distributed as dist
-        self.torch, self.dist, self.group, self.shard = torch, dist, group, shard
+        self.lib = load_dist()
+        self.shard = shard
         geometry.shard_rank, geometry.shard_count, geometry.shard_block = shard.rank, shard.world, shard.block
-        self.ctx = hkv.Context(geometry)
-        g = geometry
-        kvh = g.num_heads if g.num_kv_heads is None else g.num_kv_heads
-        del kvh
-        self.part = torch.empty((g.batch, g.num_heads, g.head_dim + 2), dtype=torch.float32, device="cuda")
-        # rank-major concatenation = [num_parts, batch, heads, head_dim + 2]
-        self.gathered = torch.empty((shard.world * g.batch, g.num_heads, g.head_dim + 2), dtype=torch.float32,
-                                    device="cuda")
+        self.geometry = geometry
+        self._g = geometry.to_c()
+        uid = None
+        if shard.world > 1:
+            import torch.distributed as dist
+            box = [None]
+            if dist.get_rank(group) == 0:
+                buf = C.create_string_buffer(UNIQUE_ID_BYTES)
+                st = self.lib.hkvd_unique_id(buf)
+                if st:
+                    raise SeqSplitError(st, "hkvd_unique_id")
+                box[0] = buf.raw
+            dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+            uid = C.create_string_buffer(box[0], UNIQUE_ID_BYTES)
+        self.stream = stream if stream is not None else torch.cuda.current_stream()
+        handle = C.c_void_p()
+        st = self.lib.hkvd_create(C.byref(handle), C.byref(self._g), layers, uid, scale, self.stream.cuda_stream)
+        self._h = handle
+        if st:
+            msg = self.lib.hkvd_last_error(handle).decode() if handle else "allocation failed"
+            self.close()
+            raise SeqSplitError(st, msg)
 
-    def step(self, q, k_new, v_new, k_cache, v_cache, out, d_total_seq, scale=None):
-        self.ctx.decode_partials(q, k_new, v_new, k_cache, v_cache, self.part, d_total_seq, scale)
-        if self.shard.world > 1:
-            self.dist.all_gather_into_tensor(self.gathered, self.part, group=self.group)
-            self.ctx.combine_partials(self.gathered, self.shard.world, out)
-        else:
-            self.ctx.combine_partials(self.part, 1, out)
+    def _check(self, st: int):
+        if st:
+            raise SeqSplitError(st, self.lib.hkvd_last_error(self._h).decode())
+
+    def bind(self, q, k_new, v_new, out, k_planes, v_planes, layer_stride_elems: int, d_total_seq):
+        self._check(self.lib.hkvd_bind(self._h, _ptr(q), _ptr(k_new), _ptr(v_new), _ptr(out), _ptr(k_planes),
+                                       _ptr(v_planes), layer_stride_elems, _ptr(d_total_seq)))
+
+    def step(self, eager: bool = False) -> bool:
+        """Enqueues one step on the decoder's stream; True when it was a graph replay."""
+        r = C.c_int32(0)
+        self._check(self.lib.hkvd_step(self._h, 1 if eager else 0, C.byref(r)))
+        return bool(r.value)
+
+    def step_profiled(self):
+        """One step with CUDA events around every phase -> (decode, all-gather, merge) ms summed over layers."""
+        d, g, m = C.c_float(0), C.c_float(0), C.c_float(0)
+        self._check(self.lib.hkvd_step_profiled(self._h, C.byref(d), C.byref(g), C.byref(m)))
+        return d.value, g.value, m.value
+
+    def wait(self, timeout_ms: int = 10000):
+        self._check(self.lib.hkvd_wait(self._h, timeout_ms))
+
+    def device_status(self) -> int:
+        w = C.c_int32(0)
+        st = self.lib.hkvd_device_status(self._h, C.byref(w))
+        if st not in (0, 8):
+            self._check(st)
+        return w.value
+
+    def attach_roster(self, name: str, fresh: bool, grace_ms: int = 1000):
+        self._check(self.lib.hkvd_attach_roster(self._h, name.encode(), 1 if fresh else 0, grace_ms))
+
+    def leave(self):
+        self._check(self.lib.hkvd_leave(self._h))
 
     def close(self):
-        self.ctx.close()
+        if getattr(self, "_h", None):
+            self.lib.hkvd_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -9,7 +9,7 @@ ContextPool::~ContextPool() {
 
 hkv_ctx* ContextPool::get(const hkv_geometry& g) {
     const Key key{g.batch, g.num_heads, g.num_kv_heads, g.head_dim, g.slots, g.window_size, g.layout,
-                  (long long)g.batch_stride_elems, g.max_seq_new};
+                  (long long)g.batch_stride_elems, g.max_seq_new, g.flags};
     auto it = ctxs_.find(key);
     if (it != ctxs_.end()) return it->second;
     hkv_ctx* c = nullptr;

@@ -55,7 +55,7 @@ public:
     static void check(hkv_ctx* c, int status, const char* op);
 
 private:
-    using Key = std::tuple<int, int, int, int, int, int, int, long long, int>;
+    using Key = std::tuple<int, int, int, int, int, int, int, long long, int, int>;
     std::map<Key, hkv_ctx*> ctxs_;
 };
 
@@ -135,10 +135,14 @@ public:
                 num_heads % num_kv_heads != 0)
                 throw std::runtime_error("ATTENTION_PREFILL_CACHED: unsupported head geometry");
             hkv_geometry g = geometry(1, num_heads, num_kv_heads, head_dim, max_seq_len, window_size);
-            // chunks up to this size may be cut by key range to fill the SMs (the engine's chunk of 512
-            // queries makes fewer work items than a B200 has SMs); rounded so that a ragged last
-            // chunk shares the context of the full ones
-            g.max_seq_new = (int32_t)(((seq_new + 511u) / 512u) * 512u);
+            // Chunks may be cut by key range to fill the SMs (the engine's chunk of 512 queries makes
+            // fewer work items than a B200 has SMs), which needs a workspace of partials sized by the
+            // chunk. The size is rounded up to 512, 1024, 2048 or 4096 so that ragged chunks share a
+            // context and at most four exist per geometry; longer chunks have enough work items
+            // without a split and get none.
+            g.max_seq_new = 0;
+            for (uint32_t cap = 512; cap <= 4096; cap *= 2)
+                if (seq_new <= cap) { g.max_seq_new = (int32_t)cap; break; }
             hkv_ctx* c = pool->get(g);
             ContextPool::check(c, hkv_prefill_attention(c, fp16(q), fp16(k_cache), fp16(v_cache), fp16(output),
                                                         (int32_t)seq_new, (int32_t)past_len, scale, ctx.stream),
@@ -170,6 +174,7 @@ public:
             const bool dev_pos = cmd.template get<uint32_t>("device_pos", 0) && eng->has_device_cache_pos();
             const uint32_t max_seq_len = cmd.template get<uint32_t>("max_seq_len", 4096);
             hkv_geometry g = geometry(1, H, KVH, HD, max_seq_len, 0);
+            g.flags = HKV_FLAG_APPEND_ONLY;   // norm + rope + cache write: no attention workspace
             hkv_ctx* c = pool->get(g);
             void *v = nullptr, *kc = nullptr, *vc = nullptr;
             if (ctx.num_inputs() >= 7) {
@@ -217,10 +222,11 @@ public:
                 batch = (int)k_new->shape[0];
             }
             hkv_geometry g = geometry(batch, kv_heads, kv_heads, head_dim, max_seq_len, 0);
+            // The engine's device position is ONE scalar that every sequence of the batch writes at
+            // (kernels/register_kernels.cpp:959-968 forwards `batch` with it): same here.
+            g.flags = HKV_FLAG_APPEND_ONLY | HKV_FLAG_SCALAR_POSITION;
             hkv_ctx* c = pool->get(g);
             if (cmd.template get<uint32_t>("device_pos", 0) && eng->has_device_cache_pos()) {
-                if (batch != 1)
-                    throw std::runtime_error("KV_CACHE_UPDATE: the engine's device position is a scalar (batch 1)");
                 ContextPool::check(c, hkv_append(c, fp16(k_new), fp16(v_new), fp16(k_cache), fp16(v_cache),
                                                  eng->device_cache_pos(), seq_len, ctx.stream),
                                    "KV_CACHE_UPDATE");

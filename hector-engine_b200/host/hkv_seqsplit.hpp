@@ -1,0 +1,273 @@
+// hkv_seqsplit.hpp — sequence-split decode over the GPUs of one node, hosted in C++.
+//
+// One logical KV cache per sequence is dealt block-cyclically over `world` ranks (one process per
+// GPU): logical block j of `shard_block` positions lives on rank j % world as local block j / world
+// (hkv_geometry.shard_*). Per layer, on the compute stream:
+//     hkv_decode_partials     split-K decode over THIS rank's rows, one fp32 partial
+//                             (o[head_dim], m, l) per (sequence, head); the rank that owns the new
+//                             token's position stages and stores its K/V row inside the same kernel
+//     ncclAllGather           batch*heads*(head_dim+2)*4 bytes per rank, NVLink/NVSwitch
+//     hkv_combine_partials    merges the `world` partials, fp16 output replicated on every rank
+// The whole multi-layer step is captured ONCE into a CUDA graph (NCCL collectives are capturable)
+// and replayed while only the device-side length array changes, under the same capture rules as
+// the engine's own graph (reference src/engine.cpp:206-231: work only on the capture stream, no
+// allocation, no synchronisation, no host reads). Partials arrive in local memory through NCCL
+// before any kernel reads them: no kernel here loads from a peer or waits on one.
+//
+// Failure handling is host-side only (hkv_step_watch.hpp): wait() polls the stream and
+// ncclCommGetAsyncError against a deadline and aborts the communicator when a peer is stuck or
+// gone; an optional NodeRoster lets a rank that left between steps be noticed before the launch.
+//
+// The reference engine has no multi-GPU path (its README lists it as absent); this is new work
+// behind the same C ABI (include/hkv.h).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <nccl.h>
+
+#include <chrono>
+#include <cmath>
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "hkv.h"
+#include "hkv_decode_loop.hpp"
+#include "hkv_step_watch.hpp"
+
+namespace hkv {
+
+struct SeqSplitConfig {
+    uint32_t layers = 0, batch = 1, heads = 0, kv_heads = 0, head_dim = 0;
+    uint32_t local_slots = 0;    // rows per sequence held by THIS rank
+    uint32_t shard_block = 1024; // positions per dealt block (multiple of 64)
+    int rank = 0, world = 1;
+    float scale = 0.0f;          // 0 = 1/sqrt(head_dim) (reference default, src/command.cpp:160)
+    int32_t chunk_tiles = 0, kernel_select = 0;
+};
+
+struct SeqSplitTimes {
+    float decode_ms = 0, gather_ms = 0, combine_ms = 0;   // summed over the layers of one step
+};
+
+class SeqSplitDecoder {
+public:
+    // `id` is the communicator's unique id (ncclGetUniqueId on one rank, handed to the others by
+    // the launcher's own means); ignored when world == 1. Allocates: construct before any capture.
+    SeqSplitDecoder(const SeqSplitConfig& cfg, const ncclUniqueId* id, cudaStream_t stream)
+        : cfg_(cfg), stream_(stream) {
+        if (!cfg.layers || !cfg.batch || !cfg.heads || !cfg.kv_heads || !cfg.head_dim || !cfg.local_slots)
+            throw std::runtime_error("SeqSplitDecoder: incomplete configuration");
+        if (cfg.world < 1 || cfg.rank < 0 || cfg.rank >= cfg.world)
+            throw std::runtime_error("SeqSplitDecoder: rank/world out of range");
+        if (cfg_.scale == 0.0f) cfg_.scale = 1.0f / std::sqrt((float)cfg.head_dim);
+        hkv_geometry g{};
+        g.batch = (int32_t)cfg.batch; g.num_heads = (int32_t)cfg.heads; g.num_kv_heads = (int32_t)cfg.kv_heads;
+        g.head_dim = (int32_t)cfg.head_dim; g.slots = (int32_t)cfg.local_slots; g.layout = HKV_LAYOUT_LINEAR;
+        g.shard_rank = cfg.rank; g.shard_count = cfg.world; g.shard_block = (int32_t)cfg.shard_block;
+        g.chunk_tiles = cfg.chunk_tiles; g.kernel_select = cfg.kernel_select;
+        const int st = hkv_ctx_create(&ctx_, &g);
+        if (st != HKV_OK) {
+            std::string msg = std::string("SeqSplitDecoder: hkv_ctx_create: ") + hkv_status_string(st);
+            if (ctx_) { msg += std::string(" (") + hkv_ctx_last_error(ctx_) + ")"; hkv_ctx_destroy(ctx_); ctx_ = nullptr; }
+            throw std::runtime_error(msg);
+        }
+        part_floats_ = (size_t)cfg.batch * cfg.heads * (cfg.head_dim + 2);
+        cuda_check(cudaMalloc(&part_, part_floats_ * sizeof(float)), "cudaMalloc(partial)");
+        cuda_check(cudaMalloc(&gathered_, part_floats_ * sizeof(float) * cfg.world), "cudaMalloc(gathered)");
+        if (cfg.world > 1) {
+            if (!id) throw std::runtime_error("SeqSplitDecoder: world > 1 needs a communicator id");
+            const ncclResult_t r = ncclCommInitRank(&comm_, cfg.world, *id, cfg.rank);
+            if (r != ncclSuccess) throw std::runtime_error(std::string("SeqSplitDecoder: ncclCommInitRank: ") + ncclGetErrorString(r));
+        }
+    }
+    ~SeqSplitDecoder() {
+        graph_.invalidate();
+        for (cudaEvent_t e : events_) cudaEventDestroy(e);
+        if (comm_) ncclCommDestroy(comm_);
+        if (part_) cudaFree(part_);
+        if (gathered_) cudaFree(gathered_);
+        if (ctx_) hkv_ctx_destroy(ctx_);
+    }
+    SeqSplitDecoder(const SeqSplitDecoder&) = delete;
+    SeqSplitDecoder& operator=(const SeqSplitDecoder&) = delete;
+
+    const SeqSplitConfig& config() const { return cfg_; }
+    hkv_ctx* context() { return ctx_; }
+    GraphReplay& graph() { return graph_; }
+    uint64_t steps() const { return steps_; }
+    size_t partial_bytes() const { return part_floats_ * sizeof(float); }
+
+    // Buffers the step reads and writes; they keep their addresses for as long as the graph lives
+    // (rebinding drops it). Per layer l:
+    //   q + l*batch*heads*head_dim, k_new/v_new + l*batch*kv_heads*head_dim, out like q,
+    //   k_planes/v_planes + l*layer_stride_elems  ([batch][local_slots][kv_heads][head_dim] each).
+    // k_new/v_new may be null (attention only). d_total_seq[b] = attended length of sequence b in
+    // LOGICAL positions (the new token included), identical on every rank.
+    void bind(const half* q, const half* k_new, const half* v_new, half* out, half* k_planes, half* v_planes,
+              size_t layer_stride_elems, const int32_t* d_total_seq) {
+        q_ = q; k_new_ = k_new; v_new_ = v_new; out_ = out; k_ = k_planes; v_ = v_planes;
+        layer_stride_ = layer_stride_elems; d_total_ = d_total_seq;
+        graph_.invalidate();
+    }
+    void attach_roster(NodeRoster* roster, std::chrono::milliseconds grace = std::chrono::milliseconds(1000)) {
+        roster_ = roster;
+        grace_ = grace;
+    }
+
+    // One token for every sequence: all layers, captured once and replayed. Only enqueues. Returns
+    // true when the step was a graph replay. With a roster attached the step is announced and the
+    // peers are checked first; a peer that left or fell behind throws BEFORE anything is enqueued.
+    bool step() {
+        require_bound();
+        pre_launch();
+        // The first step runs un-captured, as the engine's first token does: NCCL sets up its
+        // channels (and allocates) on a communicator's first collective, which must not happen
+        // inside a capture.
+        if (!warmed_) {
+            enqueue_layers(stream_, nullptr);
+            warmed_ = true;
+            ++steps_;
+            return false;
+        }
+        const bool replayed = graph_.run(stream_, [this](cudaStream_t s) { enqueue_layers(s, nullptr); });
+        ++steps_;
+        return replayed;
+    }
+    // The same step enqueued call by call (no graph).
+    void step_eager() {
+        require_bound();
+        pre_launch();
+        enqueue_layers(stream_, nullptr);
+        warmed_ = true;
+        ++steps_;
+    }
+    // The same step with CUDA events around every phase of every layer; synchronises the stream.
+    SeqSplitTimes step_profiled() {
+        require_bound();
+        pre_launch();
+        while (events_.size() < (size_t)cfg_.layers * 4) {
+            cudaEvent_t e;
+            cuda_check(cudaEventCreate(&e), "cudaEventCreate");
+            events_.push_back(e);
+        }
+        enqueue_layers(stream_, events_.data());
+        warmed_ = true;
+        ++steps_;
+        cuda_check(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+        SeqSplitTimes t;
+        for (uint32_t l = 0; l < cfg_.layers; ++l) {
+            float a = 0, b = 0, c = 0;
+            cudaEventElapsedTime(&a, events_[l * 4], events_[l * 4 + 1]);
+            cudaEventElapsedTime(&b, events_[l * 4 + 1], events_[l * 4 + 2]);
+            cudaEventElapsedTime(&c, events_[l * 4 + 2], events_[l * 4 + 3]);
+            t.decode_ms += a; t.gather_ms += b; t.combine_ms += c;
+        }
+        return t;
+    }
+
+    // Host-side wait for everything enqueued so far, with a deadline. On PeerError / TimedOut the
+    // communicator is aborted (its pending collectives are cancelled; the object then only serves
+    // destruction). Never blocks longer than `timeout`.
+    WatchResult wait(std::chrono::milliseconds timeout) {
+        const WatchResult r = watch_step(
+            [this] { return cudaStreamQuery(stream_) == cudaSuccess; },
+            [this] {
+                if (!comm_) return false;
+                ncclResult_t async = ncclSuccess;
+                return ncclCommGetAsyncError(comm_, &async) != ncclSuccess || (async != ncclSuccess && async != ncclInProgress);
+            },
+            timeout);
+        if (r != WatchResult::Done && comm_ && !aborted_) {
+            ncclCommAbort(comm_);
+            comm_ = nullptr;
+            aborted_ = true;
+            graph_.invalidate();
+        }
+        cudaGetLastError();
+        return r;
+    }
+    // Tears the communicator down without the peers (ncclCommAbort): for a rank that leaves, and
+    // for the ranks it leaves behind. Call with nothing of this rank in flight. The object then
+    // only serves destruction.
+    void abandon() {
+        if (comm_) ncclCommAbort(comm_);
+        comm_ = nullptr;
+        aborted_ = true;
+        graph_.invalidate();
+    }
+    bool aborted() const { return aborted_; }
+    int device_status() { int32_t w = 0; hkv_ctx_device_status(ctx_, stream_, &w); return w; }
+
+private:
+    static void cuda_check(cudaError_t e, const char* what) {
+        if (e != cudaSuccess) throw std::runtime_error(std::string("SeqSplitDecoder: ") + what + ": " + cudaGetErrorString(e));
+    }
+    void require_bound() const {
+        if (!q_ || !out_ || !k_ || !v_ || !d_total_) throw std::runtime_error("SeqSplitDecoder: bind() first");
+        if (aborted_) throw std::runtime_error("SeqSplitDecoder: the communicator was aborted");
+    }
+    void pre_launch() {
+        if (!roster_) return;
+        roster_->announce(steps_ + 1);
+        int who = -1;
+        const NodeRoster::Check c = roster_->check_before_launch(steps_ + 1, grace_, &who);
+        if (c == NodeRoster::Check::PeerLeft)
+            throw std::runtime_error("SeqSplitDecoder: rank " + std::to_string(who) + " has left; step not launched");
+        if (c == NodeRoster::Check::PeerBehind)
+            throw std::runtime_error("SeqSplitDecoder: rank " + std::to_string(who) + " is not keeping up; step not launched");
+    }
+    void hkv_check(int st, const char* what, uint32_t layer) const {
+        if (st != HKV_OK)
+            throw std::runtime_error(std::string("SeqSplitDecoder: ") + what + " (layer " + std::to_string(layer) + "): " +
+                                     hkv_ctx_last_error(ctx_));
+    }
+    void enqueue_layers(cudaStream_t s, cudaEvent_t* ev) {
+        const size_t qn = (size_t)cfg_.batch * cfg_.heads * cfg_.head_dim;
+        const size_t kn = (size_t)cfg_.batch * cfg_.kv_heads * cfg_.head_dim;
+        for (uint32_t l = 0; l < cfg_.layers; ++l) {
+            if (ev) cudaEventRecord(ev[l * 4], s);
+            hkv_check(hkv_decode_partials(ctx_, q_ + l * qn, k_new_ ? k_new_ + l * kn : nullptr,
+                                          v_new_ ? v_new_ + l * kn : nullptr, k_ + l * layer_stride_, v_ + l * layer_stride_,
+                                          part_, d_total_, cfg_.scale, s),
+                      "hkv_decode_partials", l);
+            if (ev) cudaEventRecord(ev[l * 4 + 1], s);
+            const float* merged = part_;
+            if (comm_) {
+                const ncclResult_t r = ncclAllGather(part_, gathered_, part_floats_, ncclFloat, comm_, s);
+                if (r != ncclSuccess) throw std::runtime_error(std::string("SeqSplitDecoder: ncclAllGather: ") + ncclGetErrorString(r));
+                merged = gathered_;
+            }
+            if (ev) cudaEventRecord(ev[l * 4 + 2], s);
+            hkv_check(hkv_combine_partials(ctx_, merged, comm_ ? cfg_.world : 1, out_ + l * qn, s), "hkv_combine_partials", l);
+            if (ev) cudaEventRecord(ev[l * 4 + 3], s);
+        }
+    }
+
+    SeqSplitConfig cfg_;
+    cudaStream_t stream_;
+    hkv_ctx* ctx_ = nullptr;
+    ncclComm_t comm_ = nullptr;
+    bool aborted_ = false;
+    bool warmed_ = false;   // a collective has run outside capture
+    float* part_ = nullptr;       // [batch][heads][head_dim + 2]
+    float* gathered_ = nullptr;   // [world][batch][heads][head_dim + 2]
+    size_t part_floats_ = 0;
+    GraphReplay graph_;
+    std::vector<cudaEvent_t> events_;
+    NodeRoster* roster_ = nullptr;
+    std::chrono::milliseconds grace_{1000};
+    const half* q_ = nullptr;
+    const half* k_new_ = nullptr;
+    const half* v_new_ = nullptr;
+    half* out_ = nullptr;
+    half* k_ = nullptr;
+    half* v_ = nullptr;
+    size_t layer_stride_ = 0;
+    const int32_t* d_total_ = nullptr;
+    uint64_t steps_ = 0;
+};
+
+}  // namespace hkv

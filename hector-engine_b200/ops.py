@@ -48,6 +48,10 @@ class Geometry:
     shard_block: int = 1024
     kernel_select: int = _capi.KERNEL_AUTO
     max_seq_new: int = 0
+    flags: int = 0                 # FLAG_SCALAR_POSITION | FLAG_APPEND_ONLY
+    tune_prefill_splits: int = 0   # 0 = the library's own choice (parity tests force each variant)
+    tune_prefill_kernel: int = 0
+    tune_tma_groups: int = 0
 
     def to_c(self) -> HkvGeometry:
         g = HkvGeometry()
@@ -57,7 +61,9 @@ class Geometry:
         g.layout, g.chunk_tiles = self.layout, self.chunk_tiles
         g.batch_stride_elems = self.batch_stride_elems
         g.shard_rank, g.shard_count, g.shard_block = self.shard_rank, self.shard_count, self.shard_block
-        g.kernel_select, g.max_seq_new = self.kernel_select, self.max_seq_new
+        g.kernel_select, g.max_seq_new, g.flags = self.kernel_select, self.max_seq_new, self.flags
+        g.tune_prefill_splits, g.tune_prefill_kernel = self.tune_prefill_splits, self.tune_prefill_kernel
+        g.tune_tma_groups = self.tune_tma_groups
         return g
 
     @property
@@ -168,6 +174,16 @@ class Context:
         self._check(self.lib.hkv_prefill_attention(self._h, _ptr(q), _ptr(k_cache), _ptr(v_cache),
                                                    _ptr(out), seq_new, past_len, scale, _stream(stream)))
 
+    def plan_prefill(self, seq_new: int, past_len: int, sm_count: int | None = None):
+        """Host plan of one prefill_attention call -> (query tiles in flight per CTA: 2, 1, or 0 for the
+        SIMT kernel; work items; key-range splits; shortest key span in tiles)."""
+        if sm_count is None:
+            import torch
+            sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        vals = [C.c_int32() for _ in range(4)]
+        self._check(self.lib.hkv_plan_prefill(C.byref(self._g), seq_new, past_len, sm_count, *[C.byref(v) for v in vals]))
+        return tuple(v.value for v in vals)
+
     def qk_norm_rope_kv(self, q, k, v, q_norm_w, k_norm_w, k_cache=None, v_cache=None, d_cache_pos=None,
                         position=0, seq_new=1, rotary_dim=0, eps=1e-6, theta=10000.0, scaling_factor=1.0,
                         stream=None):
@@ -218,6 +234,9 @@ def fill_synthetic(dst, seed: int, first_index: int = 0, count: int | None = Non
 # ---------------------------------------------------------------------------
 # Reference-named launchers (kernels/kernels.hpp:414-483): one-shot forms that build a
 # context per call signature and cache it, for tests that read like the reference's.
+# They keep the reference's position convention: `d_position` / `d_seq_len` is ONE int32
+# on the device that every sequence of the batch reads (kernels/attention.cu:351, :1129),
+# not the per-sequence arrays of Context.append / Context.decode_attention.
 # ---------------------------------------------------------------------------
 _ctx_cache: dict[tuple, Context] = {}
 
@@ -233,14 +252,14 @@ def _ctx_for(**kw) -> Context:
 def launch_kv_cache_update(new_k, new_v, k_cache, v_cache, batch_size, seq_len, kv_heads, head_dim,
                            max_seq_len, position, stream=None, **geom):
     ctx = _ctx_for(batch=batch_size, num_heads=kv_heads, num_kv_heads=kv_heads, head_dim=head_dim,
-                   slots=max_seq_len, **geom)
+                   slots=max_seq_len, flags=_capi.FLAG_APPEND_ONLY, **geom)
     ctx.append_at(new_k, new_v, k_cache, v_cache, position, seq_len, stream)
 
 
 def launch_kv_cache_update_dp(new_k, new_v, k_cache, v_cache, batch_size, seq_len, kv_heads,
                               head_dim, max_seq_len, d_position, stream=None, **geom):
     ctx = _ctx_for(batch=batch_size, num_heads=kv_heads, num_kv_heads=kv_heads, head_dim=head_dim,
-                   slots=max_seq_len, **geom)
+                   slots=max_seq_len, flags=_capi.FLAG_APPEND_ONLY | _capi.FLAG_SCALAR_POSITION, **geom)
     ctx.append(new_k, new_v, k_cache, v_cache, d_position, seq_len, stream)
 
 
@@ -256,15 +275,19 @@ def launch_attention_cached_fp16_dp(q, k_cache, v_cache, output, batch_size, d_s
                                     num_kv_heads, head_dim, max_seq_len, scale, window_size,
                                     stream=None, **geom):
     ctx = _ctx_for(batch=batch_size, num_heads=num_heads, num_kv_heads=num_kv_heads,
-                   head_dim=head_dim, slots=max_seq_len, window_size=window_size, **geom)
+                   head_dim=head_dim, slots=max_seq_len, window_size=window_size,
+                   flags=_capi.FLAG_SCALAR_POSITION, **geom)
     ctx.decode_attention(q, k_cache, v_cache, output, d_seq_len, scale, stream)
 
 
 def launch_attention_prefill_cached_fp16(q, k_cache, v_cache, output, seq_new, past_len, num_heads,
                                          num_kv_heads, head_dim, max_seq_len, scale, window_size,
                                          stream=None, **geom):
+    # key-split workspace rounded to 512..4096 queries (as the C++ adapter does): ragged chunk
+    # lengths share a context; longer chunks have enough work items without a split
+    cap = next((c for c in (512, 1024, 2048, 4096) if seq_new <= c), 0)
     ctx = _ctx_for(batch=1, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
-                   slots=max_seq_len, window_size=window_size, max_seq_new=seq_new, **geom)
+                   slots=max_seq_len, window_size=window_size, max_seq_new=cap, **geom)
     ctx.prefill_attention(q, k_cache, v_cache, output, seq_new, past_len, scale, stream)
 
 

@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define HKV_ABI_VERSION 1
+#define HKV_ABI_VERSION 2
 
 typedef enum hkv_status {
     HKV_OK = 0,
@@ -83,8 +83,24 @@ typedef struct hkv_geometry {
     int32_t kernel_select; /* hkv_kernel_select                                          */
     int32_t max_seq_new;  /* largest seq_new hkv_prefill_attention may split by key range
                              (allocates seq_new*4*H*(HD+2)*4 bytes of partials); 0 = no split */
+    int32_t flags;        /* HKV_FLAG_* bits                                             */
+    /* Overrides of choices the library otherwise makes itself (parity tests run every
+     * variant through them); 0 = automatic.                                             */
+    int32_t tune_prefill_splits; /* key-range splits of a prefill work item, 1..4; clamped to
+                                    what the plan allows                                 */
+    int32_t tune_prefill_kernel; /* 1 = one query tile in flight per CTA, 2 = two        */
+    int32_t tune_tma_groups;     /* consumer groups of the TMA decode kernel, 1 or 2     */
     int32_t reserved[3];
 } hkv_geometry;
+
+/* hkv_geometry.flags */
+/* The device position arrays hold ONE int32 that every sequence of the batch reads, as the
+ * reference's kernels do (`*d_position`, `*d_seq_len`: kernels/attention.cu:351, :1129),
+ * instead of one entry per sequence. With batch 1 both conventions coincide.            */
+#define HKV_FLAG_SCALAR_POSITION 1
+/* The context only appends (hkv_append, hkv_append_at, hkv_qk_norm_rope_kv): no split-K or
+ * prefill workspace is allocated; the attention entry points return HKV_ERR_WORKSPACE.  */
+#define HKV_FLAG_APPEND_ONLY 2
 
 typedef struct hkv_ctx hkv_ctx;
 
@@ -114,7 +130,8 @@ int hkv_ctx_launches_per_decode(const hkv_ctx* ctx);
 
 /* KV append. Replaces launch_kv_cache_update_dp (kernels/attention.cu:1153-1170,
  * declared kernels/kernels.hpp:428-440) — K and V in one launch, 16-byte accesses.
- * d_cache_pos[b] is the write index of token 0 of sequence b. */
+ * d_cache_pos[b] is the write index of token 0 of sequence b: one entry PER SEQUENCE, where
+ * the reference reads one scalar for the whole batch (HKV_FLAG_SCALAR_POSITION restores that). */
 int hkv_append(hkv_ctx* ctx, const void* k_new, const void* v_new, void* k_cache, void* v_cache,
                const int32_t* d_cache_pos, int32_t seq_new, void* stream);
 
@@ -125,13 +142,15 @@ int hkv_append_at(hkv_ctx* ctx, const void* k_new, const void* v_new, void* k_ca
 
 /* Cached decode attention. Replaces launch_attention_cached_fp16_dp
  * (kernels/attention.cu:496-510, declared kernels/kernels.hpp:468-482).
- * d_total_seq[b] = attended length (cache position + 1). */
+ * d_total_seq[b] = attended length (cache position + 1), one entry PER SEQUENCE (the reference
+ * reads one scalar for the whole batch; HKV_FLAG_SCALAR_POSITION restores that). */
 int hkv_decode_attention(hkv_ctx* ctx, const void* q, const void* k_cache, const void* v_cache,
                          void* out, const int32_t* d_total_seq, float scale, void* stream);
 
 /* Host-length twin. Replaces launch_attention_cached_fp16 (kernels/attention.cu:318-334):
- * every sequence attends `seq_len` positions. Uses a context-owned device int32[batch]
- * that is refreshed with an async copy on `stream` (so: not for graph replay). */
+ * every sequence attends `seq_len` positions. The length travels as a kernel argument, so
+ * back-to-back calls with different lengths need no synchronisation between them; a captured
+ * graph freezes the length it was captured with. */
 int hkv_decode_attention_len(hkv_ctx* ctx, const void* q, const void* k_cache,
                              const void* v_cache, void* out, int32_t seq_len, float scale,
                              void* stream);
@@ -144,8 +163,10 @@ int hkv_append_decode_attention(hkv_ctx* ctx, const void* q, const void* k_new, 
                                 void* k_cache, void* v_cache, void* out,
                                 const int32_t* d_cache_pos, float scale, void* stream);
 
-/* Prefill over the cache, batch 1. Replaces launch_attention_prefill_cached_fp16
- * (kernels/attention.cu:775-788). The cache must already hold the chunk. */
+/* Prefill over the cache, batch 1 (a context of any other batch gets HKV_ERR_GEOMETRY).
+ * Replaces launch_attention_prefill_cached_fp16 (kernels/attention.cu:775-788). The cache must
+ * already hold the chunk. In a ring plane (HKV_LAYOUT_RING) the chunk must fit the plane together
+ * with the window it attends: seq_new + window_size - 1 <= slots when past_len > 0. */
 int hkv_prefill_attention(hkv_ctx* ctx, const void* q, const void* k_cache, const void* v_cache,
                           void* out, int32_t seq_new, int32_t past_len, float scale, void* stream);
 

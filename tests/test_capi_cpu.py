@@ -24,14 +24,32 @@ def test_library_exports_every_declared_symbol(hkv):
     for name in names:
         assert hasattr(lib, name), f"{name} declared in include/hkv.h but not exported"
     assert set(names) == set(hkv._capi.SIGNATURES), "ctypes table and header disagree"
-    assert hkv._capi.load().hkv_abi_version() == 1
+    assert hkv._capi.load().hkv_abi_version() == hkv._capi.ABI_VERSION == 2
+
+
+def test_dist_library_exports_every_declared_symbol(hkv):
+    """libhkv_dist.so (the C++ multi-GPU host) exports what include/hkv_dist.h declares and the
+    Python binding binds exactly those. Loading it needs no GPU."""
+    text = open(os.path.join(REPO, "include", "hkv_dist.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = sorted(set(re.findall(r"\b(hkvd_[a-z0-9_]+)\s*\(", text)))
+    lib = hkv.dist.load_dist()
+    assert len(names) == 11
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in include/hkv_dist.h but not exported"
+    assert set(names) == set(lib._hkvd_symbols)
+    buf = C.create_string_buffer(hkv.dist.UNIQUE_ID_BYTES)
+    assert lib.hkvd_unique_id(None) == 1          # HKV_ERR_INVALID_ARG, before NCCL is touched
+    assert lib.hkvd_step(None, 0, None) == 1 and lib.hkvd_wait(None, 10) == 1
+    del buf
 
 
 def test_product_library_has_no_oracle_or_torch_dependency(hkv):
-    """The shipped library must not link the test oracle or PyTorch."""
+    """The shipped libraries must not link the test oracle or PyTorch."""
     import subprocess
-    out = subprocess.run(["ldd", hkv._capi.LIB_PATH], capture_output=True, text=True).stdout
-    assert "oracle" not in out and "torch" not in out and "libc10" not in out
+    for path in (hkv._capi.LIB_PATH, hkv.dist.DIST_LIB_PATH):
+        out = subprocess.run(["ldd", path], capture_output=True, text=True).stdout
+        assert "oracle" not in out and "torch" not in out and "libc10" not in out, path
 
 
 def test_geometry_validation_needs_no_device(hkv):
@@ -181,14 +199,12 @@ def _plan_prefill(hkv, g, seq_new, past, sms=148):
     return [v.value for v in vals]   # tiles in flight, items, splits, min span
 
 
-def test_prefill_plan_never_leaves_a_key_split_empty(hkv, monkeypatch):
+def test_prefill_plan_never_leaves_a_key_split_empty(hkv):
     """Host plan of the tensor-core prefill launch (no device needed): kernel choice, work items and
     key-range splits. With a sliding window the key span differs from item to item by a tile
     depending on how the window falls on the 128-row tile grid, so the split count must be bounded
     by the SHORTEST span over all items — a plan with an empty split makes the kernel wait for a
     tile that is never loaded."""
-    monkeypatch.delenv("HKV_PREFILL_SPLITS", raising=False)
-    monkeypatch.delenv("HKV_PREFILL_KERNEL", raising=False)
     # the headline shape: long pasts get split (148 SMs, 228 pair items x 4 kv heads... ), short ones do not
     g = hkv.Geometry(num_heads=28, num_kv_heads=4, head_dim=128, slots=131072, max_seq_new=2048)
     tif, items, splits, span = _plan_prefill(hkv, g, 2048, 129024)
@@ -204,12 +220,11 @@ def test_prefill_plan_never_leaves_a_key_split_empty(hkv, monkeypatch):
     g96 = hkv.Geometry(num_heads=32, num_kv_heads=32, head_dim=96, slots=4096, max_seq_new=256)
     assert _plan_prefill(hkv, g96, 256, 100) == [0, 256 * 32, 1, 0]
     # window 119 over 36-query items: spans of 2 and 3 tiles alternate; forcing 3 or 4 splits must clamp to 2
-    gw = hkv.Geometry(num_heads=7, num_kv_heads=1, head_dim=128, slots=1231, window_size=119, max_seq_new=345)
     for forced in (1, 2, 3, 4):
-        monkeypatch.setenv("HKV_PREFILL_SPLITS", str(forced))
+        gw = hkv.Geometry(num_heads=7, num_kv_heads=1, head_dim=128, slots=1231, window_size=119, max_seq_new=345,
+                          tune_prefill_splits=forced)
         tif, items, splits, span = _plan_prefill(hkv, gw, 345, 734)
         assert span == 2 and splits == min(forced, 2), (forced, splits, span)
-    monkeypatch.delenv("HKV_PREFILL_SPLITS")
     # and whatever the cost model picks on its own, over many shapes
     import numpy as np
     rng = np.random.default_rng(5)

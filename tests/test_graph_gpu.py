@@ -66,15 +66,13 @@ def test_capture_once_replay_many(hkv, cuda, oracle, shape):
     ctx.close()
 
 
-@pytest.mark.parametrize("splits", ["auto", "3"])
-def test_prefill_chunk_captured_and_replayed(hkv, cuda, oracle, monkeypatch, splits):
+@pytest.mark.parametrize("splits", [0, 3], ids=["auto", "3"])
+def test_prefill_chunk_captured_and_replayed(hkv, cuda, oracle, splits):
     """A prefill chunk (append of its rows + the tensor-core attention, incl. the reset of the
     kernel's work counter and the merge of key splits) is captured once and replayed with new
     contents at the same addresses: every replay must match the oracle. The chunk geometry
     (seq_new, past_len) is frozen in the graph, as an engine replaying a fixed-shape chunk would."""
     torch = cuda
-    if splits != "auto":
-        monkeypatch.setenv("HKV_PREFILL_SPLITS", splits)
     H, KVH, HD, slots, past, S_new = 28, 4, 128, 1024, 600, 150
     rng = np.random.default_rng(7)
     scale = 1.0 / math.sqrt(HD)
@@ -85,7 +83,7 @@ def test_prefill_chunk_captured_and_replayed(hkv, cuda, oracle, monkeypatch, spl
     dvn = torch.zeros(1, S_new, KVH, HD, dtype=torch.float16, device="cuda")
     out = torch.zeros(S_new, H, HD, dtype=torch.float16, device="cuda")
     ctx = hkv.Context(hkv.Geometry(batch=1, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots,
-                                   max_seq_new=S_new))
+                                   max_seq_new=S_new, tune_prefill_splits=splits))
     graph = torch.cuda.CUDAGraph()
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())

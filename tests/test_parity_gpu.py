@@ -353,3 +353,114 @@ def test_runtime_argument_errors(hkv, cuda):
     assert e.value.status == 1
     assert ctx.device_status() == 0  # nothing ran, nothing faulted
     ctx.close()
+
+
+# ---------------------------------------------------------------------------
+# position conventions of the boundary
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("kernel", [GENERIC, TMA], ids=["generic", "tma"])
+def test_host_length_calls_back_to_back_without_sync(hkv, cuda, oracle, kernel):
+    """Successive host-length calls (launch_attention_cached_fp16's contract: seq_len by value) with
+    DIFFERENT lengths and no synchronisation between them: each must attend its own length. The
+    length travels as a kernel argument, so nothing the second call does can reach the first."""
+    torch = cuda
+    B, H, KVH, HD, slots = 2, 28, 4, 128, 1024
+    lens = [1000, 37, 512, 1, 801, 64]
+    q, _, _, kc, vc = make_case(321, B, H, KVH, HD, slots, fill="garbage")
+    scale = 1.0 / math.sqrt(HD)
+    ctx = hkv.Context(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots,
+                                   kernel_select=kernel))
+    dq, dk, dv = to_dev(torch, q), to_dev(torch, kc), to_dev(torch, vc)
+    outs = [torch.full((B, H, HD), float("nan"), dtype=torch.float16, device="cuda") for _ in lens]
+    torch.cuda.synchronize()
+    for n, out in zip(lens, outs):          # enqueued back to back on one stream
+        ctx.decode_attention_len(dq, dk, dv, out, n, scale)
+    assert ctx.device_status() == 0
+    for n, out in zip(lens, outs):
+        ref = oracle.decode(q, kc, vc, np.full(B, n, np.int32), scale, threads=8)
+        assert_close(oracle, out.cpu().numpy(), ref, f"host length {n}")
+    ctx.close()
+
+
+@pytest.mark.parametrize("kernel", [GENERIC, TMA], ids=["generic", "tma"])
+def test_scalar_position_is_shared_by_the_whole_batch(hkv, cuda, oracle, kernel):
+    """The reference's kernels read ONE device int32 for every sequence of the batch
+    (kernels/attention.cu:351, :1129). FLAG_SCALAR_POSITION keeps that convention: a 4-byte
+    position buffer serves batch 3 in the append, the attention and the fused op."""
+    torch = cuda
+    B, H, KVH, HD, slots, pos = 3, 8, 2, 64, 256, 130
+    q, nk, nv, kc, vc = make_case(77, B, H, KVH, HD, slots, np.full(B, pos, np.int32))
+    scale = 1.0 / math.sqrt(HD)
+    ref_k, ref_v = kc.copy(), vc.copy()
+    oracle.append(nk, nv, ref_k, ref_v, np.full(B, pos, np.int32))
+    ref = oracle.decode(q, ref_k, ref_v, np.full(B, pos + 1, np.int32), scale)
+    d_pos = to_dev(torch, np.array([pos], np.int32))            # ONE int32 on the device
+    d_tot = to_dev(torch, np.array([pos + 1], np.int32))
+    ctx = hkv.Context(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots,
+                                   kernel_select=kernel, flags=hkv.FLAG_SCALAR_POSITION))
+    # separate ops
+    dk, dv = to_dev(torch, kc), to_dev(torch, vc)
+    out = torch.full((B, H, HD), float("nan"), dtype=torch.float16, device="cuda")
+    ctx.append(to_dev(torch, nk), to_dev(torch, nv), dk, dv, d_pos, 1)
+    ctx.decode_attention(to_dev(torch, q), dk, dv, out, d_tot, scale)
+    assert ctx.device_status() == 0
+    assert np.array_equal(dk.cpu().numpy().view(np.uint16), ref_k.view(np.uint16))
+    assert np.array_equal(dv.cpu().numpy().view(np.uint16), ref_v.view(np.uint16))
+    assert_close(oracle, out.cpu().numpy(), ref, "scalar position, separate ops")
+    # fused op
+    dk, dv = to_dev(torch, kc), to_dev(torch, vc)
+    out = torch.full((B, H, HD), float("nan"), dtype=torch.float16, device="cuda")
+    ctx.append_decode_attention(to_dev(torch, q), to_dev(torch, nk), to_dev(torch, nv), dk, dv, out, d_pos, scale)
+    assert ctx.device_status() == 0
+    assert np.array_equal(dk.cpu().numpy().view(np.uint16), ref_k.view(np.uint16))
+    assert_close(oracle, out.cpu().numpy(), ref, "scalar position, fused op")
+    ctx.close()
+    # the reference-named launchers use this convention too
+    dk, dv = to_dev(torch, kc), to_dev(torch, vc)
+    out = torch.full((B, H, HD), float("nan"), dtype=torch.float16, device="cuda")
+    hkv.launch_kv_cache_update_dp(to_dev(torch, nk), to_dev(torch, nv), dk, dv, B, 1, KVH, HD, slots, d_pos)
+    hkv.launch_attention_cached_fp16_dp(to_dev(torch, q), dk, dv, out, B, d_tot, H, KVH, HD, slots, scale, 0)
+    torch.cuda.synchronize()
+    assert np.array_equal(dk.cpu().numpy().view(np.uint16), ref_k.view(np.uint16))
+    assert_close(oracle, out.cpu().numpy(), ref, "scalar position, reference-named launchers")
+
+
+def test_append_only_context_allocates_no_attention_workspace(hkv, cuda, oracle):
+    """An append-only context (what the KV_CACHE_UPDATE and QK_NORM_ROPE ops create) appends like any
+    other but refuses attention with HKV_ERR_WORKSPACE instead of touching a workspace it never made."""
+    torch = cuda
+    B, KVH, HD, slots = 2, 4, 128, 4096
+    geo = hkv.Geometry(batch=B, num_heads=KVH, num_kv_heads=KVH, head_dim=HD, slots=slots, max_seq_new=512,
+                       flags=hkv.FLAG_APPEND_ONLY)
+    free0, _ = torch.cuda.mem_get_info()
+    ctx = hkv.Context(geo)
+    free1, _ = torch.cuda.mem_get_info()
+    assert free0 - free1 <= (2 << 20), "an append-only context must not allocate attention workspaces"
+    rng = np.random.default_rng(5)
+    nk, nv = normal_f16(rng, B, 1, KVH, HD), normal_f16(rng, B, 1, KVH, HD)
+    kc, vc = normal_f16(rng, B, slots, KVH, HD), normal_f16(rng, B, slots, KVH, HD)
+    pos = np.array([17, 4095], np.int32)
+    ref_k, ref_v = kc.copy(), vc.copy()
+    oracle.append(nk, nv, ref_k, ref_v, pos)
+    dk, dv = to_dev(torch, kc), to_dev(torch, vc)
+    ctx.append(to_dev(torch, nk), to_dev(torch, nv), dk, dv, to_dev(torch, pos), 1)
+    torch.cuda.synchronize()
+    assert np.array_equal(dk.cpu().numpy().view(np.uint16), ref_k.view(np.uint16))
+    assert np.array_equal(dv.cpu().numpy().view(np.uint16), ref_v.view(np.uint16))
+    out = torch.zeros(B, KVH, HD, dtype=torch.float16, device="cuda")
+    with pytest.raises(hkv.HkvError) as e:
+        ctx.decode_attention(out, dk, dv, out, to_dev(torch, pos), 1.0)
+    assert e.value.status == 6   # HKV_ERR_WORKSPACE
+    ctx.close()
+
+
+def test_prefill_refuses_a_batched_context(hkv, cuda):
+    """The prefill op has no batch dimension (kernels/attention.cu:709): a context of batch > 1 is
+    refused instead of silently processing sequence 0 only."""
+    torch = cuda
+    ctx = hkv.Context(hkv.Geometry(batch=2, num_heads=4, num_kv_heads=4, head_dim=64, slots=128))
+    t = torch.zeros(2 * 128 * 4 * 64, dtype=torch.float16, device="cuda")
+    with pytest.raises(hkv.HkvError) as e:
+        ctx.prefill_attention(t, t, t, t, 4, 0, 1.0)
+    assert e.value.status == 2   # HKV_ERR_GEOMETRY
+    ctx.close()

@@ -82,13 +82,11 @@ VARIANT_CASES = [CASES[0], CASES[2], CASES[4]]
 @pytest.mark.parametrize("splits", [1, 2, 3, 4])
 @pytest.mark.parametrize("tiles_in_flight", [1, 2], ids=["one_tile_kernel", "two_tile_kernel"])
 @pytest.mark.parametrize("case", VARIANT_CASES, ids=lambda c: c[0])
-def test_prefill_kernel_variants_and_key_splits(hkv, cuda, oracle, monkeypatch, case, tiles_in_flight, splits):
+def test_prefill_kernel_variants_and_key_splits(hkv, cuda, oracle, case, tiles_in_flight, splits):
     """Both tensor-core kernels and every key-split count (normally chosen by the cost model; forced
-    here through the library's A/B switches) give the oracle's result."""
+    here through the tune_* fields of the geometry) give the oracle's result."""
     torch = cuda
     name, H, KVH, HD, slots, past, S_new, window = case
-    monkeypatch.setenv("HKV_PREFILL_KERNEL", str(tiles_in_flight))
-    monkeypatch.setenv("HKV_PREFILL_SPLITS", str(splits))
     rng = np.random.default_rng(4242 + splits)
     k = normal_f16(rng, 1, slots, KVH, HD)
     v = normal_f16(rng, 1, slots, KVH, HD)
@@ -98,7 +96,8 @@ def test_prefill_kernel_variants_and_key_splits(hkv, cuda, oracle, monkeypatch, 
     scale = 1.0 / math.sqrt(HD)
     ref = oracle.prefill(q, k[0], v[0], past, scale, window=window, threads=8)
     ctx = hkv.Context(hkv.Geometry(batch=1, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots,
-                                   window_size=window, max_seq_new=S_new))
+                                   window_size=window, max_seq_new=S_new, tune_prefill_kernel=tiles_in_flight,
+                                   tune_prefill_splits=splits))
     out = torch.full((S_new, H, HD), float("nan"), dtype=torch.float16, device="cuda")
     for _ in range(3):   # repeated launches reuse the split workspace
         ctx.prefill_attention(to_dev(torch, q), to_dev(torch, k), to_dev(torch, v), out, S_new, past, scale)
@@ -108,13 +107,12 @@ def test_prefill_kernel_variants_and_key_splits(hkv, cuda, oracle, monkeypatch, 
 
 
 @pytest.mark.parametrize("tiles_in_flight", [1, 2], ids=["one_tile_kernel", "two_tile_kernel"])
-def test_prefill_row_maxima_that_keep_growing(hkv, cuda, oracle, monkeypatch, tiles_in_flight):
+def test_prefill_row_maxima_that_keep_growing(hkv, cuda, oracle, tiles_in_flight):
     """Keys whose magnitude grows with the position make every tile's row maximum outgrow the
     running reference by far more than 2^8: the in-place rescale of O in tensor memory runs on
     (almost) every tile, and scores span hundreds of units."""
     torch = cuda
     H, KVH, HD, slots, past, S_new = 14, 2, 128, 2048, 1500, 120
-    monkeypatch.setenv("HKV_PREFILL_KERNEL", str(tiles_in_flight))
     rng = np.random.default_rng(77)
     k = normal_f16(rng, 1, slots, KVH, HD).astype(np.float32)
     k *= (0.25 + np.arange(slots, dtype=np.float32) / 256.0)[None, :, None, None]   # up to 8x at the end
@@ -123,7 +121,8 @@ def test_prefill_row_maxima_that_keep_growing(hkv, cuda, oracle, monkeypatch, ti
     q = normal_f16(rng, S_new, H, HD)
     scale = 1.0   # scores ~ N(0, HD) * growth: far apart
     ref = oracle.prefill(q, k[0], v[0], past, scale, threads=8)
-    ctx = hkv.Context(hkv.Geometry(batch=1, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots, max_seq_new=S_new))
+    ctx = hkv.Context(hkv.Geometry(batch=1, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots, max_seq_new=S_new,
+                                   tune_prefill_kernel=tiles_in_flight))
     out = torch.full((S_new, H, HD), float("nan"), dtype=torch.float16, device="cuda")
     ctx.prefill_attention(to_dev(torch, q), to_dev(torch, k), to_dev(torch, v), out, S_new, past, scale)
     assert ctx.device_status() == 0
@@ -133,7 +132,7 @@ def test_prefill_row_maxima_that_keep_growing(hkv, cuda, oracle, monkeypatch, ti
     ctx.close()
 
 
-def test_prefill_seeded_random_shapes(hkv, cuda, oracle, monkeypatch):
+def test_prefill_seeded_random_shapes(hkv, cuda, oracle):
     """Thirty seeded random geometries (group size, head_dim 64/128, chunk and past lengths that are
     not multiples of any tile, windows, forced key splits, both tensor-core kernels): every one must
     match the oracle. Catches protocol slips that only show for particular tile counts per item."""
@@ -148,8 +147,8 @@ def test_prefill_seeded_random_shapes(hkv, cuda, oracle, monkeypatch):
         past = int(rng.integers(0, 1500))
         slots = int(past + S_new + rng.integers(0, 200))
         window = int(rng.choice([0, 0, int(rng.integers(1, 700))]))
-        monkeypatch.setenv("HKV_PREFILL_KERNEL", str(int(rng.choice([1, 2]))))
-        monkeypatch.setenv("HKV_PREFILL_SPLITS", str(int(rng.choice([1, 1, 2, 3, 4]))))
+        kernel_variant = int(rng.choice([1, 2]))
+        forced_splits = int(rng.choice([1, 1, 2, 3, 4]))
         k = normal_f16(rng, 1, slots, KVH, HD)
         v = normal_f16(rng, 1, slots, KVH, HD)
         k[0, past + S_new:] = np.float16(np.nan)
@@ -158,7 +157,8 @@ def test_prefill_seeded_random_shapes(hkv, cuda, oracle, monkeypatch):
         scale = float(rng.choice([1.0 / math.sqrt(HD), 0.5]))
         ref = oracle.prefill(q, k[0], v[0], past, scale, window=window, threads=8)
         ctx = hkv.Context(hkv.Geometry(batch=1, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots,
-                                       window_size=window, max_seq_new=S_new))
+                                       window_size=window, max_seq_new=S_new, tune_prefill_kernel=kernel_variant,
+                                       tune_prefill_splits=forced_splits))
         out = torch.full((S_new, H, HD), float("nan"), dtype=torch.float16, device="cuda")
         ctx.prefill_attention(to_dev(torch, q), to_dev(torch, k), to_dev(torch, v), out, S_new, past, scale)
         assert ctx.device_status() == 0, f"case {i}"

@@ -97,14 +97,23 @@ def _nccl_rank(rank, world, port, result_dir):
         ref = oracle.decode(q, full_k, full_v, totals, scale, threads=4)
         shards, slots, lk, lv = build_shards(hkv, world, BLK, kc, vc, totals, pos)
         dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
-        dec = hkv.dist.SeqSplitDecoder(hkv, hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD,
-                                                         slots=slots), shards[rank])
+        stream = torch.cuda.Stream()
+        dec = hkv.dist.SeqSplitDecoder(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots),
+                                       shards[rank], layers=1, scale=scale, stream=stream)
         out = torch.zeros(B, H, HD, dtype=torch.float16, device="cuda")
-        dk, dv = dev(lk[rank]), dev(lv[rank])
-        for _ in range(2):  # twice: the second call re-appends the same row and must agree
-            dec.step(dev(q), dev(nk), dev(nv), dk, dv, out, dev(totals), scale)
+        dk, dv, dq, dnk, dnv, dtot = dev(lk[rank]), dev(lv[rank]), dev(q), dev(nk), dev(nv), dev(totals)
         torch.cuda.synchronize()
-        assert dec.ctx.device_status() == 0
+        dec.bind(dq, dnk, dnv, out, dk, dv, dk.numel(), dtot)
+        replays = 0
+        for _ in range(4):  # un-captured, captured, replayed twice: every call re-appends the same row and must agree
+            replays += dec.step()
+            dec.wait(30000)
+            ok, err = oracle.within_tolerance(out.cpu().numpy(), ref)
+            assert ok, f"rank {rank}: {err}"
+        assert replays == 2
+        d_ms, g_ms, m_ms = dec.step_profiled()
+        assert d_ms > 0 and g_ms > 0 and m_ms > 0
+        assert dec.device_status() == 0
         ok, err = oracle.within_tolerance(out.cpu().numpy(), ref)
         assert ok, f"rank {rank}: {err}"
         open(os.path.join(result_dir, f"ok{rank}"), "w").write("ok")
