@@ -5,6 +5,7 @@
   hkv_host_tests     C++ host adapter tests (registry shim + KV cache objects)
   hkv_watch_tests    CPU-only C++ tests of the host-side failure detection (no CUDA)
   hkv_seqsplit_tests C++ test of the sequence-split decoder (one process per GPU)
+  hkv_gemma4_tests   C++ tests of the heterogeneous/shared cache owner and the per-layer decode loop
   oracle/_build, oracle/_ref   the test-only checkers (see oracle/Makefile)
 
 Run as a script (`python hector-engine_b200/build.py`) or through __graft_entry__.build().
@@ -25,6 +26,7 @@ DIST_LIB = os.path.join(PKG_DIR, "libhkv_dist.so")
 HOST_TESTS = os.path.join(REPO, "tests", "cpp", "hkv_host_tests")
 WATCH_TESTS = os.path.join(REPO, "tests", "cpp", "hkv_watch_tests")
 SEQSPLIT_TESTS = os.path.join(REPO, "tests", "cpp", "hkv_seqsplit_tests")
+GEMMA4_TESTS = os.path.join(REPO, "tests", "cpp", "hkv_gemma4_tests")
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
@@ -133,6 +135,23 @@ def build_seqsplit_tests(force: bool = False) -> str | None:
     return SEQSPLIT_TESTS
 
 
+def build_gemma4_tests(force: bool = False) -> str | None:
+    """C++ tests of Gemma4KVCache and the per-layer BatchedDecodeLoop (oracle linked as the checker)."""
+    main = os.path.join(REPO, "tests", "cpp", "hkv_gemma4_tests.cpp")
+    oracle_dir = os.path.join(REPO, "oracle", "_build")
+    if not os.path.exists(main):
+        return None
+    srcs = _sources(HOST) + [main]
+    if not force and _newer(GEMMA4_TESTS, srcs + [LIB]):
+        return GEMMA4_TESTS
+    cmd = [_nvcc(), *ARCH, "-O2", "-std=c++17", "-o", GEMMA4_TESTS, main,
+           "-I", os.path.join(REPO, "include"), "-I", HOST, "-L", PKG_DIR, "-lhkv", "-L", oracle_dir, "-lhkv_oracle",
+           "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../hector-engine_b200",
+           "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../oracle/_build"]
+    subprocess.run(cmd, check=True)
+    return GEMMA4_TESTS
+
+
 def build_oracle() -> None:
     subprocess.run(["make", "-s", "-C", os.path.join(REPO, "oracle"), "all", f"REF={reference_dir()}"], check=True)
 
@@ -149,6 +168,7 @@ def build_all(force: bool = False) -> None:
     build_host_tests(force=force)
     build_watch_tests(force=force)
     build_seqsplit_tests(force=force)
+    build_gemma4_tests(force=force)
     build_dropin()
 
 

@@ -15,9 +15,12 @@
 // Three pieces, usable separately:
 //   SessionBoard  — slot table + pinned, double-buffered staging of the int32[batch] position arrays;
 //   GraphReplay   — capture-once replay of an enqueue callback with the engine's fallback rules;
-//   BatchedDecodeLoop — owns the K/V planes, an hkv_ctx and both of the above; step() enqueues
-//                   fused append + attention for every layer (with a caller hook between layers
-//                   for the model's other ops) and replays it.
+//   BatchedDecodeLoop — an hkv_ctx per distinct layer geometry and both of the above; step()
+//                   enqueues fused append + attention for every layer (with a caller hook between
+//                   layers for the model's other ops) and replays it. Layers may all be alike (the
+//                   loop then owns the planes) or differ per layer — head_dim, sliding window over a
+//                   linear or ring plane, scale, shared layers that attend an owner's plane without
+//                   appending — as in the reference's Gemma-4 graph.
 #pragma once
 
 #include <cuda_fp16.h>
@@ -26,11 +29,14 @@
 #include <cmath>
 #include <cstdint>
 #include <functional>
+#include <map>
 #include <stdexcept>
 #include <string>
+#include <tuple>
 #include <vector>
 
 #include "hkv.h"
+#include "hkv_gemma4_kv_cache.hpp"
 #include "hkv_kv_cache.hpp"
 
 namespace hkv {
@@ -212,39 +218,94 @@ struct DecodeLoopConfig {
     float scale = 0.0f;     // 0 = 1/sqrt(head_dim), the reference's default (src/command.cpp:160)
 };
 
+// One layer of a model whose layers differ (reference src/graph_builder.cpp:692-778, the Gemma-4
+// emission): its own head_dim, its own window (`window = is_global ? 0 : sliding_window`, :699), its
+// own softmax scale (Gemma-4 passes 1.0, :767/:777), its own plane — which a shared layer borrows
+// from an earlier owner and must not append to (:746).
+struct DecodeLayer {
+    uint32_t head_dim = 0;
+    uint32_t rows = 0;          // rows per sequence of the plane (max_seq_len, or the ring size)
+    int32_t window = 0;         // 0 = attend everything
+    int32_t layout = HKV_LAYOUT_LINEAR;
+    bool append = true;         // false: shared layer, attends an owner's plane, writes nothing
+    float scale = 0.0f;         // 0 = 1/sqrt(head_dim)
+    half* k_plane = nullptr;    // [batch][rows][kv_heads][head_dim], owned by the caller's cache
+    half* v_plane = nullptr;
+};
+
+// The per-layer plan of a Gemma4KVCache: owners append, shared layers only attend; local layers
+// take their sliding window (over a ring plane when the cache was allocated with one).
+inline std::vector<DecodeLayer> decode_layers_of(Gemma4KVCache& cache, float scale) {
+    std::vector<DecodeLayer> out(cache.num_layers());
+    for (uint32_t l = 0; l < cache.num_layers(); ++l) {
+        DecodeLayer& d = out[l];
+        d.head_dim = cache.head_dim(l);
+        d.rows = cache.rows(l);
+        d.window = cache.is_global(l) ? 0 : (int32_t)cache.sliding_window(l);
+        d.layout = cache.is_ring(l) ? HKV_LAYOUT_RING : HKV_LAYOUT_LINEAR;
+        d.append = !cache.is_shared(l);
+        d.scale = scale;
+        d.k_plane = cache.k_cache(l);
+        d.v_plane = cache.v_cache(l);
+    }
+    return out;
+}
+
 class BatchedDecodeLoop {
 public:
     // Called before each layer's attention is enqueued: the place for the model's other ops of
     // that layer (they land in the same captured graph). May be empty.
     using LayerHook = std::function<void(uint32_t layer, cudaStream_t stream)>;
 
+    // Every layer alike; the loop owns the planes.
     BatchedDecodeLoop(const DecodeLoopConfig& cfg, cudaStream_t stream)
         : cfg_(cfg), stream_(stream), board_(cfg.batch, cfg.max_seq_len) {
         KVCacheConfig kc;
         kc.num_layers = cfg.layers; kc.num_kv_heads = cfg.kv_heads; kc.head_dim = cfg.head_dim;
         kc.max_batch_size = cfg.batch; kc.max_seq_len = cfg.max_seq_len;
         if (!cache_.allocate(kc)) throw std::runtime_error("BatchedDecodeLoop: cache allocation failed");
-        hkv_geometry g{};
-        g.batch = (int32_t)cfg.batch; g.num_heads = (int32_t)cfg.heads; g.num_kv_heads = (int32_t)cfg.kv_heads;
-        g.head_dim = (int32_t)cfg.head_dim; g.slots = (int32_t)cfg.max_seq_len; g.window_size = cfg.window;
-        g.layout = HKV_LAYOUT_LINEAR;
-        const int st = hkv_ctx_create(&ctx_, &g);   // allocates: before any capture
-        if (st != HKV_OK) throw std::runtime_error(std::string("BatchedDecodeLoop: hkv_ctx_create: ") + hkv_status_string(st));
-        if (cfg_.scale == 0.0f) cfg_.scale = 1.0f / std::sqrt((float)cfg.head_dim);
+        std::vector<DecodeLayer> layers(cfg.layers);
+        for (uint32_t l = 0; l < cfg.layers; ++l) {
+            layers[l].head_dim = cfg.head_dim; layers[l].rows = cfg.max_seq_len; layers[l].window = cfg.window;
+            layers[l].scale = cfg.scale; layers[l].k_plane = cache_.k_cache(l); layers[l].v_plane = cache_.v_cache(l);
+        }
+        set_layers(std::move(layers));
     }
-    ~BatchedDecodeLoop() { graph_.invalidate(); if (ctx_) hkv_ctx_destroy(ctx_); }
+    // Layers that differ (head_dim, window, ring or linear plane, scale, shared or owner); the planes
+    // belong to the caller's cache object (e.g. Gemma4KVCache + decode_layers_of) and must outlive
+    // the loop. `max_seq_len` bounds the positions a session can reach.
+    BatchedDecodeLoop(uint32_t batch, uint32_t heads, uint32_t kv_heads, uint32_t max_seq_len,
+                      std::vector<DecodeLayer> layers, cudaStream_t stream)
+        : stream_(stream), board_(batch, max_seq_len) {
+        cfg_.layers = (uint32_t)layers.size(); cfg_.batch = batch; cfg_.heads = heads; cfg_.kv_heads = kv_heads;
+        cfg_.max_seq_len = max_seq_len;
+        set_layers(std::move(layers));
+    }
+    ~BatchedDecodeLoop() {
+        graph_.invalidate();
+        for (auto& kv : ctxs_) hkv_ctx_destroy(kv.second);
+    }
     BatchedDecodeLoop(const BatchedDecodeLoop&) = delete;
     BatchedDecodeLoop& operator=(const BatchedDecodeLoop&) = delete;
 
     SessionBoard& board() { return board_; }
     KVCache& cache() { return cache_; }
     GraphReplay& graph() { return graph_; }
-    hkv_ctx* context() { return ctx_; }
+    hkv_ctx* context(uint32_t layer = 0) { return layer < layer_ctx_.size() ? layer_ctx_[layer] : nullptr; }
+    size_t contexts() const { return ctxs_.size(); }
     const DecodeLoopConfig& config() const { return cfg_; }
+    const std::vector<DecodeLayer>& layers() const { return layers_; }
+    // Element offsets of layer l inside the bound activation buffers (layers may differ in head_dim).
+    size_t q_offset(uint32_t layer) const { return q_off_[layer]; }
+    size_t kv_offset(uint32_t layer) const { return kv_off_[layer]; }
+    size_t q_elems() const { return q_off_.back(); }
+    size_t kv_elems() const { return kv_off_.back(); }
 
     // Binds the activation buffers the graph reads and writes; they must keep their addresses for
-    // as long as the graph lives (rebinding drops the graph). Layouts, per layer l:
-    //   q[l] [batch][heads][head_dim], k_new[l]/v_new[l] [batch][kv_heads][head_dim], out[l] like q.
+    // as long as the graph lives (rebinding drops the graph). Layer l uses
+    //   q + q_offset(l) [batch][heads][head_dim(l)], out likewise,
+    //   k_new / v_new + kv_offset(l) [batch][kv_heads][head_dim(l)] (never read for a shared layer).
+    // With every layer alike these are the plain strides l*batch*heads*head_dim and l*batch*kv_heads*head_dim.
     void bind(const half* q, const half* k_new, const half* v_new, half* out, LayerHook hook = nullptr) {
         q_ = q; k_new_ = k_new; v_new_ = v_new; out_ = out; hook_ = std::move(hook);
         graph_.invalidate();
@@ -261,29 +322,69 @@ public:
         return replayed;
     }
     uint64_t steps() const { return tokens_; }
-    // Device-side status word of the context (a bounded wait that ran out, etc.); synchronises.
-    int device_status() { int32_t w = 0; hkv_ctx_device_status(ctx_, stream_, &w); return w; }
+    // Device-side status words of all contexts OR-ed (a bounded wait that ran out, etc.); synchronises.
+    int device_status() {
+        int32_t all = 0;
+        for (auto& kv : ctxs_) { int32_t w = 0; hkv_ctx_device_status(kv.second, stream_, &w); all |= w; }
+        return all;
+    }
 
 private:
+    using CtxKey = std::tuple<uint32_t, uint32_t, int32_t, int32_t>;   // head_dim, rows, window, layout
+    void set_layers(std::vector<DecodeLayer> layers) {
+        if (layers.empty()) throw std::runtime_error("BatchedDecodeLoop: no layers");
+        layers_ = std::move(layers);
+        q_off_.assign(1, 0);
+        kv_off_.assign(1, 0);
+        for (DecodeLayer& d : layers_) {
+            if (!d.head_dim || !d.rows || !d.k_plane || !d.v_plane) throw std::runtime_error("BatchedDecodeLoop: incomplete layer");
+            if (d.scale == 0.0f) d.scale = 1.0f / std::sqrt((float)d.head_dim);
+            const CtxKey key{d.head_dim, d.rows, d.window, d.layout};
+            auto it = ctxs_.find(key);
+            if (it == ctxs_.end()) {   // one context per distinct layer geometry; allocates: before any capture
+                hkv_geometry g{};
+                g.batch = (int32_t)cfg_.batch; g.num_heads = (int32_t)cfg_.heads; g.num_kv_heads = (int32_t)cfg_.kv_heads;
+                g.head_dim = (int32_t)d.head_dim; g.slots = (int32_t)d.rows; g.window_size = d.window; g.layout = d.layout;
+                hkv_ctx* c = nullptr;
+                const int st = hkv_ctx_create(&c, &g);
+                if (st != HKV_OK) {
+                    std::string msg = std::string("BatchedDecodeLoop: hkv_ctx_create: ") + hkv_status_string(st);
+                    if (c) { msg += std::string(" (") + hkv_ctx_last_error(c) + ")"; hkv_ctx_destroy(c); }
+                    throw std::runtime_error(msg);
+                }
+                it = ctxs_.emplace(key, c).first;
+            }
+            layer_ctx_.push_back(it->second);
+            q_off_.push_back(q_off_.back() + (size_t)cfg_.batch * cfg_.heads * d.head_dim);
+            kv_off_.push_back(kv_off_.back() + (size_t)cfg_.batch * cfg_.kv_heads * d.head_dim);
+        }
+    }
     void enqueue_layers(cudaStream_t s) {
-        const size_t qn = (size_t)cfg_.batch * cfg_.heads * cfg_.head_dim;
-        const size_t kn = (size_t)cfg_.batch * cfg_.kv_heads * cfg_.head_dim;
-        for (uint32_t l = 0; l < cfg_.layers; ++l) {
+        for (uint32_t l = 0; l < (uint32_t)layers_.size(); ++l) {
             if (hook_) hook_(l, s);
-            const int st = hkv_append_decode_attention(ctx_, q_ + l * qn, k_new_ + l * kn, v_new_ + l * kn,
-                                                       cache_.k_cache(l), cache_.v_cache(l), out_ + l * qn,
-                                                       board_.d_cache_pos(), cfg_.scale, s);
+            const DecodeLayer& d = layers_[l];
+            hkv_ctx* c = layer_ctx_[l];
+            // owner: fused append + attention at the device position; shared layer: attention only,
+            // over the plane its owner has already appended this token's row to
+            const int st = d.append
+                               ? hkv_append_decode_attention(c, q_ + q_off_[l], k_new_ + kv_off_[l], v_new_ + kv_off_[l], d.k_plane,
+                                                             d.v_plane, out_ + q_off_[l], board_.d_cache_pos(), d.scale, s)
+                               : hkv_decode_attention(c, q_ + q_off_[l], d.k_plane, d.v_plane, out_ + q_off_[l],
+                                                      board_.d_total_seq(), d.scale, s);
             if (st != HKV_OK)
                 throw std::runtime_error(std::string("BatchedDecodeLoop: layer ") + std::to_string(l) + ": " +
-                                         hkv_ctx_last_error(ctx_));
+                                         hkv_ctx_last_error(c));
         }
     }
     DecodeLoopConfig cfg_;
     cudaStream_t stream_;
     SessionBoard board_;
-    KVCache cache_;
+    KVCache cache_;                       // used by the uniform constructor only
     GraphReplay graph_;
-    hkv_ctx* ctx_ = nullptr;
+    std::vector<DecodeLayer> layers_;
+    std::map<CtxKey, hkv_ctx*> ctxs_;
+    std::vector<hkv_ctx*> layer_ctx_;
+    std::vector<size_t> q_off_, kv_off_;
     const half* q_ = nullptr;
     const half* k_new_ = nullptr;
     const half* v_new_ = nullptr;

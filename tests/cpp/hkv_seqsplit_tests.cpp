@@ -168,7 +168,7 @@ int run_rank(int rank, int world, const std::string& idfile, bool leave_at_end) 
             }
             for (int b = 0; b < B; ++b) ++totals[b];
         }
-        REQUIRE(replays == STEPS - 2, "first step un-captured, second captures, the rest replay");
+        REQUIRE(replays == STEPS - 1, "the first step runs un-captured; the second captures the graph and launches it; the rest replay");
         REQUIRE(dec.device_status() == 0, "device status word clean");
         // planes: this rank holds exactly its share of the logical planes, appended rows included
         CUDA_OK(cudaMemcpy(sk.data(), dk, sk.size() * 2, cudaMemcpyDeviceToHost));

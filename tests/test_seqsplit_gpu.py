@@ -105,12 +105,12 @@ def _nccl_rank(rank, world, port, result_dir):
         torch.cuda.synchronize()
         dec.bind(dq, dnk, dnv, out, dk, dv, dk.numel(), dtot)
         replays = 0
-        for _ in range(4):  # un-captured, captured, replayed twice: every call re-appends the same row and must agree
+        for _ in range(4):  # un-captured, captured + launched, replayed twice: every call re-appends the same row and must agree
             replays += dec.step()
             dec.wait(30000)
             ok, err = oracle.within_tolerance(out.cpu().numpy(), ref)
             assert ok, f"rank {rank}: {err}"
-        assert replays == 2
+        assert replays == 3
         d_ms, g_ms, m_ms = dec.step_profiled()
         assert d_ms > 0 and g_ms > 0 and m_ms > 0
         assert dec.device_status() == 0
@@ -132,3 +132,25 @@ def test_sequence_split_nccl_ranks(cuda, tmp_path):
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     mp.spawn(_nccl_rank, args=(world, 29700 + os.getpid() % 200, str(tmp_path)), nprocs=world, join=True)
     assert len(os.listdir(tmp_path)) == world
+
+
+def test_context_refuses_a_call_made_on_another_device(hkv, cuda):
+    """A context's workspace, status word, tensor maps and shared-memory opt-ins live on the device it
+    was created on: a launch entry point called with another device current is refused on the host
+    (HKV_ERR_INVALID_ARG, 'context belongs to device N') instead of launching there."""
+    torch = cuda
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs >= 2 GPUs")
+    ctx = hkv.Context(hkv.Geometry(batch=1, num_heads=4, num_kv_heads=4, head_dim=64, slots=128))
+    t = torch.zeros(128 * 4 * 64, dtype=torch.float16, device="cuda:0")
+    pos = torch.zeros(1, dtype=torch.int32, device="cuda:0")
+    try:
+        torch.cuda.set_device(1)
+        with pytest.raises(hkv.HkvError) as e:
+            ctx.append(t, t, t, t, pos, 1, stream=0)
+        assert e.value.status == 1 and "belongs to device 0" in str(e.value)
+    finally:
+        torch.cuda.set_device(0)
+    ctx.append(t, t, t, t, pos, 1)       # and it still works where it belongs
+    torch.cuda.synchronize()
+    ctx.close()
