@@ -212,16 +212,14 @@ int encode_f16_sw128(hkv_ctx* c, const void* base, int rank, const cuuint64_t* d
 }
 
 constexpr int kPrefillMaxSplits = 4;
+// Below this many 64-row K/V tiles per SM and launch the decode kernel runs as two CTAs per SM.
+constexpr long long kTwoCtaTilesPerSm = 0;
 
-// Key tiles an item of `q_item` queries starting at query q0 spans (the kernels' tile_span).
+// Key tiles an item of `q_item` queries (item index qt) spans — the kernels' own arithmetic.
 int prefill_span_tiles(const PrefillTcArgs& t, int q_item, int qt) {
-    const int q0 = qt * q_item;
-    const int lo = t.window > 0 ? (t.past_len + q0 + 1 - t.window > 0 ? t.past_len + q0 + 1 - t.window : 0) : 0;
-    const int q_last = q0 + q_item < t.S_new ? q0 + q_item : t.S_new;
-    int hi = t.past_len + q_last - 1;
-    if (hi > t.slots - 1) hi = t.slots - 1;
-    const int ntot = hi / kPfKeys - lo / kPfKeys + 1;
-    return ntot < 1 ? 1 : ntot;
+    int kt0, ntot;
+    prefill_item_tiles(t, q_item, prefill_tc_keys(t.HD), qt, kt0, ntot);
+    return ntot;
 }
 
 // Key-range split count of the tensor-core prefill kernels. A kernel deals its work items
@@ -282,29 +280,40 @@ int prefill_splits(const PrefillTcArgs& t, int HD, int q_item, double tile_us, i
 void plan_prefill_tc(const hkv_geometry& g, int seq_new, int past_len, int sm_count, bool have_ws,
                      PrefillTcArgs& t, int& pair, int& min_span, std::vector<double>& scratch) {
     const int G = g.num_heads / g.num_kv_heads, HD = g.head_dim;
+    t.HD = HD;
+    t.ring = g.layout == HKV_LAYOUT_RING ? 1 : 0;
     t.S_new = seq_new;
     t.past_len = past_len;
     t.H = g.num_heads;
     t.KVH = g.num_kv_heads;
     t.G = G;
     t.QT = kPfRows / G;
-    // two query tiles per work item (hkv_prefill_tc2_kernel) unless the whole chunk fits one tile
+    // two query tiles per work item (hkv_prefill_tc2_kernel) unless the whole chunk fits one tile;
+    // head_dim 256 always takes the one-tile kernel (its output alone fills half of tensor memory)
     pair = seq_new > t.QT ? 1 : 0;
     if (g.tune_prefill_kernel) pair = g.tune_prefill_kernel == 1 ? 0 : 1;
+    if (HD == 256) pair = 0;
     const int q_item = pair ? 2 * t.QT : t.QT;
     t.n_qtiles = (seq_new + q_item - 1) / q_item;
     t.slots = g.slots;
     t.window = g.window_size;
-    const double tile_us = pair ? 0.85 + 0.85 * HD / 128.0 : 0.60 + 0.95 * HD / 128.0;   // per key tile of an item
+    const int HDS = prefill_tc_staged_hd(HD);
+    double tile_us = pair ? 0.85 + 0.85 * HDS / 128.0 : 0.60 + 0.95 * HDS / 128.0;   // per 128-row key tile of an item
+    if (prefill_tc_keys(HD) == 64) tile_us *= 0.55;                                   // half-height tiles
     t.splits = prefill_splits(t, HD, q_item, tile_us, sm_count, have_ws, g.tune_prefill_splits, scratch);
     min_span = 1 << 30;
     for (int qt = 0; qt < t.n_qtiles; ++qt) min_span = std::min(min_span, prefill_span_tiles(t, q_item, qt));
 }
 
+// Geometries the tensor-core prefill kernels take: head_dim 64, 96, 128, 256; any group up to 128;
+// linear planes, and ring planes whose row count is a whole number of key tiles.
 bool prefill_tc_ok(const hkv_geometry& g) {
     const int G = g.num_heads / g.num_kv_heads;
-    return (g.head_dim == 64 || g.head_dim == 128) && G <= 128 && g.layout == HKV_LAYOUT_LINEAR &&
-           g.shard_count <= 1 && g.kernel_select != HKV_KERNEL_GENERIC;
+    const bool hd_ok = g.head_dim == 64 || g.head_dim == 96 || g.head_dim == 128 || g.head_dim == 256;
+    if (!hd_ok || G > 128 || g.shard_count > 1 || g.kernel_select == HKV_KERNEL_GENERIC) return false;
+    if (g.layout == HKV_LAYOUT_RING && g.slots % prefill_tc_keys(g.head_dim) != 0) return false;
+    const long long bs = g.batch_stride_elems ? g.batch_stride_elems : (long long)g.slots * g.num_kv_heads * g.head_dim;
+    return bs % 8 == 0;
 }
 
 int encode_map(hkv_ctx* c, const void* base, CUtensorMap* out) {
@@ -438,11 +447,12 @@ int launch_decode(hkv_ctx* c, const void* q, const void* k_new, const void* v_ne
         if (stt) return stt;
         if (fused) { a.k_new = (const __half*)k_new; a.v_new = (const __half*)v_new; }
         const int nt = (c->G + 7) / 8;
-        TmaKernel kern = pick_tma(g.head_dim, nt, c->tma_groups);
+        const int groups = c->tma_groups == 2 ? 2 : 1;
+        TmaKernel kern = pick_tma(g.head_dim, nt, groups);
         long long items = (long long)g.batch * c->max_chunks * g.num_kv_heads;
-        int grid = c->sm_count;
+        int grid = c->tma_groups == 1 ? 2 * c->sm_count : c->sm_count;   // persistent: one or two CTAs per SM
         if (items < grid) grid = (int)items;
-        const int threads = (c->tma_groups * 4 + 1) * 32;
+        const int threads = (groups * 4 + 1) * 32;
         kern<<<grid, threads, c->plan.bytes, st>>>(maps->k, maps->v, a, c->plan.stages);
     } else {
         if (fused) {
@@ -605,10 +615,24 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
     c->kernel = (geometry->kernel_select != HKV_KERNEL_GENERIC && tma_ok) ? HKV_KERNEL_TMA
                                                                            : HKV_KERNEL_GENERIC;
     if (c->kernel == HKV_KERNEL_TMA) {
-        c->tma_groups = geometry->tune_tma_groups == 1 ? 1 : 2;
-        c->plan = tma_plan(geometry->head_dim, c->G, c->tma_groups * 4, geometry->batch, c->smem_optin);
+        // Two shapes of the same kernel (hkv_decode_tma.cuh): one CTA per SM with two consumer groups,
+        // or two CTAs per SM with one group and half the ring each. The second overlaps the fixed
+        // cost per launch and wins while a launch is short: chosen by the K/V tiles an SM streams
+        // at full context.
+        int sm_total = 0;
+        cudaDeviceGetAttribute(&sm_total, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
+        const size_t half_budget = sm_total > 4096 ? (size_t)sm_total / 2 - 2048 : 0;   // two CTAs + the runtime's reserve
+        int rows = geometry->slots;
+        if (geometry->window_size > 0 && geometry->window_size < rows) rows = geometry->window_size + kTileRows;
+        const long long tiles_per_sm = (long long)geometry->batch * geometry->num_kv_heads * ((rows + kTileRows - 1) / kTileRows) / sm;
+        c->tma_groups = geometry->tune_tma_groups ? geometry->tune_tma_groups : (tiles_per_sm < kTwoCtaTilesPerSm ? 1 : 2);
+        if (c->tma_groups == 1) {
+            c->plan = tma_plan(geometry->head_dim, c->G, 4, geometry->batch, half_budget);
+            if (c->plan.stages < 2) c->tma_groups = 2;   // tiles too large for half an SM's shared memory
+        }
+        if (c->tma_groups == 2) c->plan = tma_plan(geometry->head_dim, c->G, 8, geometry->batch, c->smem_optin);
         if (c->plan.stages < 2 && c->tma_groups == 2) {
-            c->tma_groups = 1;
+            c->tma_groups = 0;    // one CTA per SM, one consumer group, the whole shared memory
             c->plan = tma_plan(geometry->head_dim, c->G, 4, geometry->batch, c->smem_optin);
         }
         if (c->plan.stages < 2) {
@@ -617,7 +641,7 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
             c->kernel = HKV_KERNEL_GENERIC;
         } else {
             if (!encode_tiled_fn()) return fail(c, HKV_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
-            TmaKernel kern = pick_tma(geometry->head_dim, (c->G + 7) / 8, c->tma_groups);
+            TmaKernel kern = pick_tma(geometry->head_dim, (c->G + 7) / 8, c->tma_groups == 2 ? 2 : 1);
             // the attribute belongs to the kernel, not to this context: keep it at the device
             // maximum so that contexts with different plans never lower it for each other
             e = cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -627,16 +651,17 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
     }
 
     if (prefill_tc_ok(*geometry)) {
-        const void* pk = geometry->head_dim == 64 ? (const void*)hkv_prefill_tc_kernel<64>
-                                                  : (const void*)hkv_prefill_tc_kernel<128>;
-        e = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)prefill_tc_smem_bytes(geometry->head_dim));
+        const int hds = prefill_tc_staged_hd(geometry->head_dim);
+        const void* pk = hds == 64 ? (const void*)hkv_prefill_tc_kernel<64, 128>
+                       : hds == 128 ? (const void*)hkv_prefill_tc_kernel<128, 128>
+                                    : (const void*)hkv_prefill_tc_kernel<256, 64>;
+        e = cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_tc_smem_bytes(hds));
         if (e != cudaSuccess) return fail_cuda(c, e, "cudaFuncSetAttribute(prefill shared memory)");
-        const void* pk2 = geometry->head_dim == 64 ? (const void*)hkv_prefill_tc2_kernel<64>
-                                                   : (const void*)hkv_prefill_tc2_kernel<128>;
-        e = cudaFuncSetAttribute(pk2, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)prefill_tc2_smem_bytes(geometry->head_dim));
-        if (e != cudaSuccess) return fail_cuda(c, e, "cudaFuncSetAttribute(prefill shared memory)");
+        if (hds != 256) {
+            const void* pk2 = hds == 64 ? (const void*)hkv_prefill_tc2_kernel<64> : (const void*)hkv_prefill_tc2_kernel<128>;
+            e = cudaFuncSetAttribute(pk2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_tc2_smem_bytes(hds));
+            if (e != cudaSuccess) return fail_cuda(c, e, "cudaFuncSetAttribute(prefill shared memory)");
+        }
     }
     if (prefill_tc_ok(*geometry)) {
         e = cudaMalloc(&c->prefill_counter, sizeof(int));
@@ -803,13 +828,22 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
         return fail(c, HKV_ERR_ALIGNMENT, "prefill: fp16 pointer not 2-byte aligned");
     if (c->g.batch != 1) return fail(c, HKV_ERR_GEOMETRY, "prefill: the op is batch 1 (kernels/attention.cu:709)");
     if (!c->workspace) return fail(c, HKV_ERR_WORKSPACE, "prefill: the context was created append-only");
-    if (c->g.layout != HKV_LAYOUT_LINEAR || c->g.shard_count > 1)
-        return fail(c, HKV_ERR_GEOMETRY, "prefill: linear unsharded cache only");
+    if (c->g.shard_count > 1) return fail(c, HKV_ERR_GEOMETRY, "prefill: the cache must not be sequence-sharded");
+    if (c->g.layout == HKV_LAYOUT_RING) {
+        // The ring already holds the chunk. Every position a query attends must still be there: either
+        // nothing has been overwritten yet, or the oldest one needed (past_len + 1 - window) lies within
+        // `slots` of the newest one written (past_len + seq_new - 1).
+        const long long end = (long long)past_len + seq_new;
+        const bool fits = end <= c->g.slots ||
+                          (c->g.window_size > 0 && (long long)seq_new + c->g.window_size - 1 <= c->g.slots);
+        if (!fits)
+            return fail(c, HKV_ERR_GEOMETRY, "prefill: chunk + window do not fit the ring (seq_new + window_size - 1 > slots)");
+    }
     if (seq_new == 0) return HKV_OK;
     // (the tensor-core kernel takes row maxima before scaling, which needs a positive scale)
     if (prefill_tc_ok(c->g) && scale > 0.0f && aligned(q, 16) && aligned(k_cache, 16) && aligned(v_cache, 16) && aligned(out, 16)) {
         const hkv_geometry& g = c->g;
-        const int HD = g.head_dim, G = c->G;
+        const int HD = g.head_dim, G = c->G, HDS = prefill_tc_staged_hd(HD), KEYS = prefill_tc_keys(HD);
         PrefillTcArgs t;
         t.out = (__half*)out;
         t.status = c->d_status;
@@ -819,6 +853,8 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
         if (t.splits > min_span) return fail(c, HKV_ERR_INVALID_ARG, "prefill: internal plan error (a key split would be empty)");
         t.scale_log2 = scale * 1.4426950408889634f;
         t.part = c->prefill_ws;
+        // Boxes are 64 halfs wide; a head_dim of 96 takes two, the second reaching past the tensor's
+        // extent, where the copy engine fills zeros.
         CUtensorMap mq, mk, mv;
         {
             cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)g.num_heads, (cuuint64_t)seq_new};
@@ -831,7 +867,7 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
             cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)g.num_kv_heads, (cuuint64_t)g.slots, 1};
             cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)g.num_kv_heads * HD * 2,
                                      (cuuint64_t)g.slots * g.num_kv_heads * HD * 2};
-            cuuint32_t box[4] = {64u, 1u, (cuuint32_t)kPfKeys, 1u};
+            cuuint32_t box[4] = {64u, 1u, (cuuint32_t)KEYS, 1u};
             int st = encode_f16_sw128(c, k_cache, 4, dims, strides, box, &mk);
             if (st) return st;
             st = encode_f16_sw128(c, v_cache, 4, dims, strides, box, &mv);
@@ -840,27 +876,24 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
         const long long items = (long long)t.n_qtiles * g.num_kv_heads * t.splits;
         const int grid = items < c->sm_count ? (int)items : c->sm_count;
         t.item_counter = c->prefill_counter;
+        cudaStream_t st = (cudaStream_t)stream;
         if (pair) {
-            const cudaError_t me = cudaMemsetAsync(c->prefill_counter, 0, sizeof(int), (cudaStream_t)stream);
+            const cudaError_t me = cudaMemsetAsync(c->prefill_counter, 0, sizeof(int), st);
             if (me != cudaSuccess) return fail_cuda(c, me, "cudaMemsetAsync(prefill work counter)");
-            const size_t smem = prefill_tc2_smem_bytes(HD);
-            if (HD == 64) hkv_prefill_tc2_kernel<64><<<grid, kPf2Threads, smem, (cudaStream_t)stream>>>(mq, mk, mv, t);
-            else hkv_prefill_tc2_kernel<128><<<grid, kPf2Threads, smem, (cudaStream_t)stream>>>(mq, mk, mv, t);
+            const size_t smem = prefill_tc2_smem_bytes(HDS);
+            if (HDS == 64) hkv_prefill_tc2_kernel<64><<<grid, kPf2Threads, smem, st>>>(mq, mk, mv, t);
+            else hkv_prefill_tc2_kernel<128><<<grid, kPf2Threads, smem, st>>>(mq, mk, mv, t);
         } else {
-            const size_t smem = prefill_tc_smem_bytes(HD);
-            if (HD == 64) hkv_prefill_tc_kernel<64><<<grid, kPfThreads, smem, (cudaStream_t)stream>>>(mq, mk, mv, t);
-            else hkv_prefill_tc_kernel<128><<<grid, kPfThreads, smem, (cudaStream_t)stream>>>(mq, mk, mv, t);
+            const size_t smem = prefill_tc_smem_bytes(HDS);
+            if (HDS == 64) hkv_prefill_tc_kernel<64, 128><<<grid, kPfThreads, smem, st>>>(mq, mk, mv, t);
+            else if (HDS == 128) hkv_prefill_tc_kernel<128, 128><<<grid, kPfThreads, smem, st>>>(mq, mk, mv, t);
+            else hkv_prefill_tc_kernel<256, 64><<<grid, kPfThreads, smem, st>>>(mq, mk, mv, t);
         }
         if (t.splits > 1) {
             // merge the key-range partials of every (query, head)
             const long long rows = (long long)seq_new * g.num_heads;
             const unsigned cgrid = (unsigned)((rows + 7) / 8);
-            if (HD == 64)
-                hkv_prefill_combine_kernel<64><<<cgrid, 256, 0, (cudaStream_t)stream>>>(c->prefill_ws, (__half*)out, rows,
-                                                                                       g.num_heads, t.splits);
-            else
-                hkv_prefill_combine_kernel<128><<<cgrid, 256, 0, (cudaStream_t)stream>>>(c->prefill_ws, (__half*)out, rows,
-                                                                                        g.num_heads, t.splits);
+            hkv_prefill_combine_kernel<<<cgrid, 256, 0, st>>>(c->prefill_ws, (__half*)out, rows, g.num_heads, HD, t.splits);
         }
         const cudaError_t e = cudaPeekAtLastError();
         return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "prefill launch");
@@ -877,6 +910,7 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
     a.HD = c->g.head_dim;
     a.slots = c->g.slots;
     a.window = c->g.window_size;
+    a.ring = c->g.layout == HKV_LAYOUT_RING ? 1 : 0;
     a.scale_log2 = scale * 1.4426950408889634f;
     dim3 grid((unsigned)seq_new, (unsigned)c->g.num_heads);
     hkv_prefill_generic_kernel<<<grid, kGenWarps * 32, 0, (cudaStream_t)stream>>>(a);
@@ -985,11 +1019,19 @@ int hkv_qk_norm_rope_kv(hkv_ctx* c, void* q, void* k, const void* v, const void*
     a.eps = eps;
     a.theta = theta;
     a.scaling = scaling_factor <= 0.0f ? 1.0f : scaling_factor;
-    const long long units = (long long)g.batch * seq_new * (g.num_heads + 2 * g.num_kv_heads);
-    long long blocks = (units + kRopeWarps - 1) / kRopeWarps;
-    const long long cap = (long long)c->sm_count * 16;
-    if (blocks > cap) blocks = cap;
-    hkv_qk_norm_rope_kernel<<<(unsigned)blocks, kRopeWarps * 32, 0, (cudaStream_t)stream>>>(a);
+    const long long tokens = (long long)g.batch * seq_new;
+    if (a.rot / 2 > 256) return fail(c, HKV_ERR_GEOMETRY, "qk_norm_rope: rotary_dim above 512");
+    // 8-byte accesses when every row starts on an 8-byte boundary
+    const bool vec = g.head_dim % 4 == 0 && c->batch_stride % 4 == 0 && aligned(q, 8) && aligned(k, 8) &&
+                     (!v || aligned(v, 8)) && (!k_cache || (aligned(k_cache, 8) && aligned(v_cache, 8)));
+    const int per_tok = g.num_heads + 2 * g.num_kv_heads;
+    // one CTA row per token on grid.y: at most 65535 tokens per launch, the rest in further launches
+    for (long long t0 = 0; t0 < tokens; t0 += 65535) {
+        const long long n = tokens - t0 < 65535 ? tokens - t0 : 65535;
+        a.tok0 = t0;
+        dim3 grid((unsigned)((per_tok + kRopeWarps - 1) / kRopeWarps), (unsigned)n);
+        hkv_qk_norm_rope_kernel<<<grid, kRopeWarps * 32, 0, (cudaStream_t)stream>>>(a, vec ? 1 : 0);
+    }
     const cudaError_t e = cudaPeekAtLastError();
     return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "qk_norm_rope launch");
 }
@@ -1060,7 +1102,7 @@ int32_t hkv_preferred_prefill_chunk(const hkv_geometry* g, int32_t sm_count, int
     if (validate_geometry(g, &why) || sm_count <= 0 || target <= 0) return -1;
     if (!prefill_tc_ok(*g)) return target;
     const int G = g->num_heads / g->num_kv_heads;
-    const int q_pair = 2 * (kPfRows / G);
+    const int q_pair = (g->head_dim == 256 ? 1 : 2) * (kPfRows / G);   // queries per work item
     int a = sm_count, b = g->num_kv_heads;
     while (b) { const int r = a % b; a = b; b = r; }   // a = gcd
     const long long unit = (long long)(sm_count / a) * q_pair;   // queries per whole round of items

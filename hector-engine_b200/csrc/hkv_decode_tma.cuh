@@ -64,8 +64,13 @@ inline TmaSmemPlan tma_plan(int HD, int G, int ncw, int B, size_t budget) {
     return TmaSmemPlan{s, fixed + (size_t)s * stage};
 }
 
+// NGROUPS = 2: one CTA per SM, two consumer groups sharing one deep ring (long launches).
+// NGROUPS = 1: TWO CTAs per SM, each with one consumer group and a ring of half the depth: while one
+// CTA merges an item or waits for its first tiles, the other keeps the SM's memory pipe busy — the
+// fixed cost per launch (ramp and tail) that dominates short launches is overlapped instead of paid
+// twice. The host picks by the amount of work per SM.
 template <int HD, int NT, int NGROUPS>
-__global__ void __launch_bounds__((NGROUPS * 4 + 1) * 32, 1)
+__global__ void __launch_bounds__((NGROUPS * 4 + 1) * 32, NGROUPS == 1 ? 2 : 1)
 hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const DecodeArgs a,
                       const int stages) {
@@ -101,13 +106,23 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
         tma_prefetch_desc(&tm_k);
         tma_prefetch_desc(&tm_v);
     }
-    for (int b = tid; b < a.B; b += blockDim.x)
-        prefix[b + 1] = num_chunks(a.map, attended_len(a, b), a.chunk_tiles);
-    __syncthreads();
-    if (tid == 0) {
-        int run = 0;
-        prefix[0] = 0;
-        for (int b = 0; b < a.B; ++b) { run += prefix[b + 1]; prefix[b + 1] = run; }
+    // prefix[b] = work chunks of the sequences before b. Warp 0 scans the batch 32 sequences at a
+    // time with shuffles (a serial scan by one thread costs a microsecond at batch 64, in front of
+    // the first load of every launch).
+    if (warp == 0) {
+        int carry = 0;
+        for (int b0 = 0; b0 < a.B; b0 += 32) {
+            const int b = b0 + lane;
+            int v = b < a.B ? num_chunks(a.map, attended_len(a, b), a.chunk_tiles) : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int u = __shfl_up_sync(0xffffffffu, v, o);
+                if (lane >= o) v += u;
+            }
+            if (b < a.B) prefix[b + 1] = carry + v;
+            carry += __shfl_sync(0xffffffffu, v, 31);
+        }
+        if (lane == 0) prefix[0] = 0;
     }
     __syncthreads();
     const int n_items = prefix[a.B] * a.KVH;

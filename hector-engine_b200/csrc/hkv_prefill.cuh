@@ -16,6 +16,7 @@ struct PrefillArgs {
     const __half* v_cache;
     __half* out;            // [S_new, H, HD]
     int S_new, past_len, H, KVH, HD, slots, window;
+    int ring;               // 1: position p lives in row p % slots
     float scale_log2;
 };
 
@@ -27,7 +28,7 @@ __global__ void __launch_bounds__(kGenWarps * 32) hkv_prefill_generic_kernel(con
     const int G = a.H / a.KVH, kvh = h / G;
     int total = a.past_len + qi + 1;
     const int first = a.window > 0 ? (total - a.window > 0 ? total - a.window : 0) : 0;
-    if (total > a.slots) total = a.slots;
+    if (!a.ring && total > a.slots) total = a.slots;   // a linear plane drops rows past its end
 
     float qr[kGenMaxPerLane], acc[kGenMaxPerLane];
     const __half* qp = a.q + ((long long)qi * a.H + h) * a.HD;
@@ -40,8 +41,9 @@ __global__ void __launch_bounds__(kGenWarps * 32) hkv_prefill_generic_kernel(con
     float m = kNegBig, l = 0.0f;
     const int row_elems = a.KVH * a.HD;
     for (int s = first + warp; s < total; s += kGenWarps) {
-        const __half* kr = a.k_cache + (long long)s * row_elems + kvh * a.HD;
-        const __half* vr = a.v_cache + (long long)s * row_elems + kvh * a.HD;
+        const int row = a.ring ? s % a.slots : s;
+        const __half* kr = a.k_cache + (long long)row * row_elems + kvh * a.HD;
+        const __half* vr = a.v_cache + (long long)row * row_elems + kvh * a.HD;
         float dot = 0.0f;
 #pragma unroll
         for (int i = 0; i < kGenMaxPerLane; ++i) {

@@ -11,8 +11,8 @@
 //     into the M dimension: row r of the 128-row tile is (query r / G, head r % G), QT = 128 / G
 //     queries per tile (18 for a group of 7: 126 of 128 rows used). One bulk-tensor load with
 //     box {64 halfs, G heads, QT queries} brings the tile in as 128-byte-swizzled K-major rows.
-//   * Warp 8 (one lane) is the TMA producer: Q tile per item; K tiles of 128 cache rows through
-//     a 2-stage ring and V tiles through a 3-stage ring (full/empty mbarriers each).
+//   * Warp 8 (one lane) is the TMA producer: Q tile per item; K tiles of 128 (64) cache rows through
+//     a 2-stage ring and V tiles through a 3 (2)-stage ring (full/empty mbarriers each).
 //   * Warp 9 (one lane) issues the MMAs:  S = Q·K^T  (M128 x N128 x K=HD, both operands K-major
 //     from shared memory) into one of two S buffers in tensor memory, and
 //     PV = P·V  (A = P from tensor memory as packed fp16, B = V straight from its row-major
@@ -26,6 +26,9 @@
 //     outgrows its reference by more than 2^8, so the softmax of tile t+1 overlaps P·V of tile t.
 //   * All waits are bounded mbarrier waits; a wait that runs out sets the status word, the
 //     roles leave their loops, outstanding copies are drained and tensor memory is freed.
+//   * head_dim 64, 96, 128 and 256 (96 staged as 128 with zero-filled columns; 256 with 64-row K/V
+//     tiles); linear planes and ring planes (position p in row p % slots) alike: tiles are counted in
+//     logical positions and only the row coordinate of a tile's loads wraps.
 #pragma once
 
 #include <cuda.h>
@@ -38,6 +41,8 @@ struct PrefillTcArgs {
     __half* out;      // [S_new, H, HD]
     int32_t* status;
     int S_new, past_len, H, KVH, G, QT, n_qtiles, slots, window;
+    int HD;           // the tensors' real head_dim (96 is staged as 128 with zero-filled columns)
+    int ring;         // 1: ring plane, position p lives in row p % slots (slots % tile rows == 0)
     float scale_log2;
     // Key-range split: every (query tile, kv head) is cut into `splits` consecutive key ranges
     // so that the work items fill the last wave of SMs; with splits > 1 each range writes an
@@ -52,11 +57,49 @@ constexpr int kPfRows = 128;   // M of the MMA = rows of a query tile
 constexpr int kPfKeys = 128;   // cache rows per K/V tile = N of the score MMA
 constexpr int kPfThreads = 320;  // 8 softmax warps + TMA producer + MMA issuer
 
-constexpr int kPfKStages = 2;  // K tiles in flight (freed right after the score MMA)
-constexpr int kPfVStages = 3;  // V tiles in flight (freed after the output MMA)
+// K tiles in flight (freed right after the score MMA) and V tiles in flight (freed after the output
+// MMA) of the one-tile kernel; head_dim 256 has room for two of each only.
+__host__ __device__ constexpr int prefill_tc_k_stages(int) { return 2; }
+__host__ __device__ constexpr int prefill_tc_v_stages(int HD) { return HD == 256 ? 2 : 3; }
+// Staged head dimension and cache rows per K/V tile for a real head_dim.
+__host__ __device__ constexpr int prefill_tc_staged_hd(int head_dim) { return head_dim == 96 ? 128 : head_dim; }
+__host__ __device__ constexpr int prefill_tc_keys(int head_dim) { return head_dim == 256 ? 64 : 128; }
 
-__host__ __device__ constexpr size_t prefill_tc_smem_bytes(int HD) {
-    return 1024 + (size_t)(1 + kPfKStages + kPfVStages) * kPfRows * HD * 2 + 40 * 8 + 6 * kPfRows * 4;
+__host__ __device__ constexpr size_t prefill_tc_smem_bytes(int HD /*staged*/) {
+    return 1024 + (size_t)kPfRows * HD * 2 +
+           (size_t)(prefill_tc_k_stages(HD) + prefill_tc_v_stages(HD)) * prefill_tc_keys(HD) * HD * 2 + 40 * 8 + 6 * kPfRows * 4;
+}
+
+// ---- geometry of a work item, shared by the kernels and the host planner ----------------------
+// Tiles count `keys` LOGICAL positions; in a linear plane a position is its row, in a ring plane
+// position p lives in row p % slots (a tile never straddles the wrap: slots % keys == 0).
+__host__ __device__ inline int prefill_tile_row(const PrefillTcArgs& a, int pos0) { return a.ring ? pos0 % a.slots : pos0; }
+// Positions [0, kv_valid) hold data; beyond them a plane may hold stale bits.
+__host__ __device__ inline int prefill_kv_valid(const PrefillTcArgs& a) {
+    const int end = a.past_len + a.S_new;
+    return (a.ring || end < a.slots) ? end : a.slots;
+}
+// Last key a query at position qpos may attend (a linear plane drops rows past its end).
+__host__ __device__ inline int prefill_last_key(const PrefillTcArgs& a, int qpos) {
+    return (a.ring || qpos < a.slots) ? qpos : a.slots - 1;
+}
+// Key tiles an item of `q_item` queries (item index qt) spans, before any key split.
+__host__ __device__ inline void prefill_item_tiles(const PrefillTcArgs& a, int q_item, int keys, int qt, int& kt0, int& ntot) {
+    const int q0 = qt * q_item;
+    const int first_min = a.window > 0 ? (a.past_len + q0 + 1 - a.window > 0 ? a.past_len + q0 + 1 - a.window : 0) : 0;
+    const int q_last = q0 + q_item < a.S_new ? q0 + q_item : a.S_new;
+    const int last_max = prefill_last_key(a, a.past_len + q_last - 1);
+    kt0 = first_min / keys;
+    ntot = last_max / keys - kt0 + 1;
+    if (ntot < 1) ntot = 1;
+}
+// This split's share of the span (the host guarantees splits <= shortest span).
+__host__ __device__ inline void prefill_tile_span(const PrefillTcArgs& a, int q_item, int keys, int qt, int sp, int& kt_lo, int& nt) {
+    int kt0, ntot;
+    prefill_item_tiles(a, q_item, keys, qt, kt0, ntot);
+    const int base = ntot / a.splits, rem = ntot % a.splits;
+    kt_lo = kt0 + sp * base + (sp < rem ? sp : rem);
+    nt = base + (sp < rem ? 1 : 0);
 }
 
 // ---- tcgen05 wrappers -------------------------------------------------------------
@@ -176,25 +219,36 @@ __device__ __noinline__ void tmem_scale_columns(uint32_t addr, int n32, float al
     tc_wait_st();
 }
 
-template <int HD>
+// HD is the head dimension the tiles are staged with — 64, 128 or 256; head_dim 96 runs as
+// HD = 128 with the columns 96..127 of Q, K and V zero-filled by the bulk-tensor loads (they lie
+// outside the tensors), which changes neither Q·K^T nor the first 96 columns of P·V. KEYS is the
+// number of cache rows per K/V tile: 128, or 64 for head_dim 256, where shared memory (a 64 KB
+// query tile) and tensor memory (256 output columns) leave room for half-height tiles only.
+template <int HD, int KEYS>
 __global__ void __launch_bounds__(kPfThreads, 1)
 hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const PrefillTcArgs a) {
-    static_assert(HD == 64 || HD == 128, "head_dim 64 or 128");
+    static_assert(HD == 64 || HD == 128 || HD == 256, "staged head_dim 64, 128 or 256");
+    static_assert(KEYS == 64 || KEYS == 128, "64 or 128 cache rows per tile");
+    static_assert(3 * KEYS + HD <= 512, "tensor-memory columns");
     constexpr int NCH = HD / 64;                       // 64-half column blocks
-    constexpr int CHUNK_BYTES = kPfRows * 128;         // one column block of a 128-row tile
-    constexpr int TILE_BYTES = kPfRows * HD * 2;
+    constexpr int Q_CHUNK = kPfRows * 128;             // one column block of the 128-row query tile
+    constexpr int KV_CHUNK = KEYS * 128;               // one column block of a K/V tile
+    constexpr int Q_TILE = kPfRows * HD * 2;
+    constexpr int KV_TILE = KEYS * HD * 2;
+    constexpr int KST = prefill_tc_k_stages(HD), VST = prefill_tc_v_stages(HD);
+    constexpr int KH = KEYS / 2;                       // score columns per softmax thread
     constexpr uint32_t TMEM_COLS = 512;
-    constexpr uint32_t COL_S0 = 0, COL_S1 = 128, COL_PV = 256, COL_P0 = 384, COL_P1 = 448;
-    constexpr uint32_t IDESC_QK = (1u << 4) | ((uint32_t)(kPfKeys >> 3) << 17) | ((uint32_t)(kPfRows >> 4) << 24);
+    constexpr uint32_t COL_S0 = 0, COL_S1 = KEYS, COL_PV = 2 * KEYS, COL_P0 = 2 * KEYS + HD, COL_P1 = COL_P0 + KEYS / 2;
+    constexpr uint32_t IDESC_QK = (1u << 4) | ((uint32_t)(KEYS >> 3) << 17) | ((uint32_t)(kPfRows >> 4) << 24);
     constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(kPfRows >> 4) << 24);
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* q_gen = smem;                                   // Q tile
-    uint8_t* k_gen = smem + TILE_BYTES;                      // kPfKStages K tiles
-    uint8_t* v_gen = k_gen + kPfKStages * TILE_BYTES;        // kPfVStages V tiles
-    uint64_t* bars = reinterpret_cast<uint64_t*>(v_gen + kPfVStages * TILE_BYTES);
+    uint8_t* k_gen = smem + Q_TILE;                          // KST K tiles
+    uint8_t* v_gen = k_gen + KST * KV_TILE;                  // VST V tiles
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_gen + VST * KV_TILE);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
     float* xch = reinterpret_cast<float*>(bars + 40);   // [2 buffers][2 halves][128] maxima + [2][128] sums
     const uint32_t q_smem = smem_u32(q_gen), k_smem = smem_u32(k_gen), v_smem = smem_u32(v_gen);
@@ -214,8 +268,8 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         mbar_init(B_QFULL, 1); mbar_init(B_QEMPTY, 1);
-        for (int s = 0; s < kPfKStages; ++s) { mbar_init(B_KFULL + 8 * s, 1); mbar_init(B_KEMPTY + 8 * s, 1); }
-        for (int s = 0; s < kPfVStages; ++s) { mbar_init(B_VFULL + 8 * s, 1); mbar_init(B_VEMPTY + 8 * s, 1); }
+        for (int s = 0; s < KST; ++s) { mbar_init(B_KFULL + 8 * s, 1); mbar_init(B_KEMPTY + 8 * s, 1); }
+        for (int s = 0; s < VST; ++s) { mbar_init(B_VFULL + 8 * s, 1); mbar_init(B_VEMPTY + 8 * s, 1); }
         for (int s = 0; s < 2; ++s) { mbar_init(B_SFULL + 8 * s, 1); mbar_init(B_SFREE + 8 * s, 256); }
         mbar_init(B_PFULL, 256); mbar_init(B_PVFULL, 1); mbar_init(B_DONE, 1); mbar_init(B_XCH, 256);
         mbar_init(B_OFULL, 1);
@@ -229,29 +283,16 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const uint32_t tmem = *tmem_slot;
 
     const int n_items = a.n_qtiles * a.KVH * a.splits;
-    const int kv_valid = (a.past_len + a.S_new < a.slots) ? a.past_len + a.S_new : a.slots;
+    const int kv_valid = prefill_kv_valid(a);
 
-    // Key-tile range of a query tile (identical in every role).
-    auto tile_span = [&](int qt, int sp, int& kt_lo, int& nt) {
-        const int q0 = qt * a.QT;
-        const int first_min = a.window > 0 ? (a.past_len + q0 + 1 - a.window > 0 ? a.past_len + q0 + 1 - a.window : 0) : 0;
-        int q_last = q0 + a.QT < a.S_new ? q0 + a.QT : a.S_new;
-        int last_max = a.past_len + q_last - 1;
-        if (last_max > a.slots - 1) last_max = a.slots - 1;
-        const int kt0 = first_min / kPfKeys;
-        int ntot = last_max / kPfKeys - kt0 + 1;
-        if (ntot < 1) ntot = 1;
-        // this split's share of the span (the host guarantees splits <= shortest span)
-        const int base = ntot / a.splits, rem = ntot % a.splits;
-        kt_lo = kt0 + sp * base + (sp < rem ? sp : rem);
-        nt = base + (sp < rem ? 1 : 0);
-    };
+    // Key-tile range of a query tile (identical in every role); tiles count KEYS logical positions.
+    auto tile_span = [&](int qt, int sp, int& kt_lo, int& nt) { prefill_tile_span(a, a.QT, KEYS, qt, sp, kt_lo, nt); };
 
     if (warp == 8) {
         // ------------------------------ TMA producer ------------------------------
         // K and V travel through separate rings: a K tile is free again as soon as its score MMA
-        // has run (long before P·V of the same tile), and V has one more stage than K, so the
-        // loads of tile t+2 never wait for the output MMA of tile t.
+        // has run (long before P·V of the same tile), and V has one more stage than K where shared
+        // memory allows, so the loads of tile t+2 never wait for the output MMA of tile t.
         if (lane == 0) {
             uint32_t gt = 0, it = 0, q_it = 0;
             bool ok = true, q_pending = false;
@@ -264,41 +305,39 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 mbar_expect_tx(B_QFULL, (uint32_t)(NCH * a.QT * a.G * 128));
 #pragma unroll
                 for (int c = 0; c < NCH; ++c)
-                    tma_load_3d(q_smem + c * CHUNK_BYTES, &tm_q, B_QFULL, c * 64, kvh * a.G, qt * a.QT);
+                    tma_load_3d(q_smem + c * Q_CHUNK, &tm_q, B_QFULL, c * 64, kvh * a.G, qt * a.QT);
                 q_pending = true;
                 q_it = it;
                 for (int t = 0; t < nt; ++t, ++gt) {
-                    const int row = (kt_lo + t) * kPfKeys;
-                    const uint32_t ks = gt % kPfKStages, ku = gt / kPfKStages;
+                    const int row = prefill_tile_row(a, (kt_lo + t) * KEYS);
+                    const uint32_t ks = gt % KST, ku = gt / KST;
                     if (!mbar_wait(B_KEMPTY + 8 * ks, (ku & 1) ^ 1, a.status)) { ok = false; break; }
-                    mbar_expect_tx(B_KFULL + 8 * ks, TILE_BYTES);
+                    mbar_expect_tx(B_KFULL + 8 * ks, KV_TILE);
 #pragma unroll
                     for (int c = 0; c < NCH; ++c)
-                        tma_load_4d(k_smem + ks * TILE_BYTES + c * CHUNK_BYTES, &tm_k, B_KFULL + 8 * ks, c * 64, kvh,
-                                    row, 0);
-                    const uint32_t vs = gt % kPfVStages, vu = gt / kPfVStages;
+                        tma_load_4d(k_smem + ks * KV_TILE + c * KV_CHUNK, &tm_k, B_KFULL + 8 * ks, c * 64, kvh, row, 0);
+                    const uint32_t vs = gt % VST, vu = gt / VST;
                     if (!mbar_wait(B_VEMPTY + 8 * vs, (vu & 1) ^ 1, a.status)) {
                         // the K copy above is in flight: wait for it before giving up
                         mbar_wait(B_KFULL + 8 * ks, ku & 1, a.status);
                         ok = false;
                         break;
                     }
-                    mbar_expect_tx(B_VFULL + 8 * vs, TILE_BYTES);
+                    mbar_expect_tx(B_VFULL + 8 * vs, KV_TILE);
 #pragma unroll
                     for (int c = 0; c < NCH; ++c)
-                        tma_load_4d(v_smem + vs * TILE_BYTES + c * CHUNK_BYTES, &tm_v, B_VFULL + 8 * vs, c * 64, kvh,
-                                    row, 0);
+                        tma_load_4d(v_smem + vs * KV_TILE + c * KV_CHUNK, &tm_v, B_VFULL + 8 * vs, c * 64, kvh, row, 0);
                 }
             }
             // drain this thread's outstanding copies before the CTA retires (tiles 0..gt-1 were issued)
             if (q_pending) mbar_wait(B_QFULL, q_it & 1, a.status);
-            for (uint32_t i = 1; i <= (uint32_t)kPfKStages && i <= gt; ++i) {
+            for (uint32_t i = 1; i <= (uint32_t)KST && i <= gt; ++i) {
                 const uint32_t g = gt - i;
-                mbar_wait(B_KFULL + 8 * (g % kPfKStages), (g / kPfKStages) & 1, a.status);
+                mbar_wait(B_KFULL + 8 * (g % KST), (g / KST) & 1, a.status);
             }
-            for (uint32_t i = 1; i <= (uint32_t)kPfVStages && i <= gt; ++i) {
+            for (uint32_t i = 1; i <= (uint32_t)VST && i <= gt; ++i) {
                 const uint32_t g = gt - i;
-                mbar_wait(B_VFULL + 8 * (g % kPfVStages), (g / kPfVStages) & 1, a.status);
+                mbar_wait(B_VFULL + 8 * (g % VST), (g / VST) & 1, a.status);
             }
         }
     } else if (warp == 9) {
@@ -308,18 +347,20 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         if (lane == 0) {
             uint32_t gt = 0, it = 0;
             bool ok = true;
+            const int ksteps = (a.HD + 15) / 16;   // k-steps holding real dimensions (the zero-filled ones are skipped)
             auto issue_qk = [&](uint32_t g) -> bool {
-                const uint32_t ks = g % kPfKStages, sb = g & 1;
-                if (!mbar_wait(B_KFULL + 8 * ks, (g / kPfKStages) & 1, a.status) ||
+                const uint32_t ks = g % KST, sb = g & 1;
+                if (!mbar_wait(B_KFULL + 8 * ks, (g / KST) & 1, a.status) ||
                     !mbar_wait(B_SFREE + 8 * sb, ((g >> 1) & 1) ^ 1, a.status))
                     return false;
                 tc_fence_after();
-                const uint32_t kbase = k_smem + ks * TILE_BYTES;
+                const uint32_t kbase = k_smem + ks * KV_TILE;
                 const uint32_t d = tmem + (sb ? COL_S1 : COL_S0);
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
-                    const uint32_t off = (kk / 4) * CHUNK_BYTES + (kk % 4) * 32;
-                    tc_mma_ss(d, umma_desc_sw128(q_smem + off, 16), umma_desc_sw128(kbase + off, 16), IDESC_QK, kk > 0);
+                    if (kk < ksteps)
+                        tc_mma_ss(d, umma_desc_sw128(q_smem + (kk / 4) * Q_CHUNK + (kk % 4) * 32, 16),
+                                  umma_desc_sw128(kbase + (kk / 4) * KV_CHUNK + (kk % 4) * 32, 16), IDESC_QK, kk > 0);
                 }
                 tc_commit(B_SFULL + 8 * sb);
                 tc_commit(B_KEMPTY + 8 * ks);   // the K tile is free once these MMAs have run
@@ -337,19 +378,19 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     } else {
                         tc_commit(B_QEMPTY);  // last score MMA of the item issued: Q tile may be replaced
                     }
-                    const uint32_t vs = gt % kPfVStages;
+                    const uint32_t vs = gt % VST;
                     if (!mbar_wait(B_PFULL, gt & 1, a.status) ||
-                        !mbar_wait(B_VFULL + 8 * vs, (gt / kPfVStages) & 1, a.status)) {
+                        !mbar_wait(B_VFULL + 8 * vs, (gt / VST) & 1, a.status)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
                     // O accumulates in tensor memory over the whole item (the first tile overwrites)
-                    const uint32_t vbase = v_smem + vs * TILE_BYTES;
+                    const uint32_t vbase = v_smem + vs * KV_TILE;
                     const uint32_t pbase = tmem + ((gt & 1) ? COL_P1 : COL_P0);
 #pragma unroll
-                    for (int kk = 0; kk < kPfKeys / 16; ++kk)
-                        tc_mma_ts(tmem + COL_PV, pbase + kk * 8, umma_desc_sw128(vbase + kk * 2048, CHUNK_BYTES),
+                    for (int kk = 0; kk < KEYS / 16; ++kk)
+                        tc_mma_ts(tmem + COL_PV, pbase + kk * 8, umma_desc_sw128(vbase + kk * 2048, KV_CHUNK),
                                   IDESC_PV, (t > 0 || kk > 0) ? 1u : 0u);
                     tc_commit(B_PVFULL);
                     if (t + 1 == nt) tc_commit(B_OFULL);   // the item's output is complete
@@ -362,9 +403,9 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         }
     } else {
         // ------------------------------ softmax / output rows ------------------------------
-        // Two threads per row: warps 0-3 take columns [0, 64) of the score tile and the first
-        // half of the output dimensions, warps 4-7 the other halves. Tensor-memory lanes are
-        // reached through the warp's quadrant (warp % 4).
+        // Two threads per row: warps 0-3 take the first half of the score tile's columns and of the
+        // output dimensions, warps 4-7 the other halves. Tensor-memory lanes are reached through
+        // the warp's quadrant (warp % 4).
         const int quad = warp & 3, half = warp >> 2;
         const int r = quad * 32 + lane;            // row of the tile = lane of tensor memory
         const uint32_t lane_sel = (uint32_t)(quad * 32) << 16;
@@ -381,7 +422,7 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             const bool row_valid = ql < a.QT && qi < a.S_new;
             const int qpos = a.past_len + qi;
             const int first_row = a.window > 0 ? (qpos + 1 - a.window > 0 ? qpos + 1 - a.window : 0) : 0;
-            const int qlim = qpos < a.slots ? qpos : a.slots - 1;  // never attend rows past the plane
+            const int qlim = prefill_last_key(a, qpos);  // never attend rows past a linear plane
             // m_ref: the reference maximum the probabilities and O are scaled by. It only moves
             // when a tile's maximum exceeds it by more than 2^8 (then O is rescaled in tensor
             // memory); otherwise P simply carries the factor, which fp16 holds comfortably.
@@ -389,27 +430,27 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
             for (int t = 0; t < nt; ++t, ++gt) {
                 const uint32_t sb = gt & 1;
-                const uint32_t s_addr = tmem + lane_sel + (sb ? COL_S1 : COL_S0) + half * 64;
-                const int kstart = (kt_lo + t) * kPfKeys + half * 64;   // key of this thread's column 0
+                const uint32_t s_addr = tmem + lane_sel + (sb ? COL_S1 : COL_S0) + half * KH;
+                const int kstart = (kt_lo + t) * KEYS + half * KH;   // key of this thread's column 0
                 ok = __all_sync(0xffffffffu, ok && mbar_wait(B_SFULL + 8 * sb, (gt >> 1) & 1, a.status));
                 if (!ok) continue;
                 tc_fence_after();
-                uint32_t sv[64];
-                tmem_ld32(*reinterpret_cast<uint32_t (*)[32]>(&sv[0]), s_addr);
-                tmem_ld32(*reinterpret_cast<uint32_t (*)[32]>(&sv[32]), s_addr + 32);
+                uint32_t sv[KH];
+#pragma unroll
+                for (int c = 0; c < KH / 32; ++c) tmem_ld32(*reinterpret_cast<uint32_t (*)[32]>(&sv[c * 32]), s_addr + c * 32);
                 tc_wait_ld();
-                // columns [lo, hi] of this thread's 64 are attended (causal + window)
+                // columns [lo, hi] of this thread's KH are attended (causal + window)
                 const int lo = first_row - kstart, hi = qlim - kstart;
-                const bool all_in = __all_sync(0xffffffffu, lo <= 0 && hi >= 63);
+                const bool all_in = __all_sync(0xffffffffu, lo <= 0 && hi >= KH - 1);
                 // the maximum is taken on the raw scores (the scale is positive) and scaled once
                 float mx = -INFINITY;
                 if (all_in) {
 #pragma unroll
-                    for (int j = 0; j < 64; j += 2)
+                    for (int j = 0; j < KH; j += 2)
                         mx = fmax3(mx, __uint_as_float(sv[j]), __uint_as_float(sv[j + 1]));
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 64; ++j) {
+                    for (int j = 0; j < KH; ++j) {
                         const float s = (j >= lo && j <= hi) ? __uint_as_float(sv[j]) : -INFINITY;
                         sv[j] = __float_as_uint(s);
                         mx = fmaxf(mx, s);
@@ -442,9 +483,9 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 // p = 2^(s*scale - m_ref): one packed FMA, two ex2, one packed add, one pack per pair
                 float lsum0 = 0.0f, lsum1 = 0.0f;
                 const float neg_m = -m_ref;
-                uint32_t pk[32];
+                uint32_t pk[KH / 2];
 #pragma unroll
-                for (int j = 0; j < 64; j += 2) {
+                for (int j = 0; j < KH; j += 2) {
                     float x0, x1;
                     ffma2_bcast(x0, x1, __uint_as_float(sv[j]), __uint_as_float(sv[j + 1]), a.scale_log2, neg_m);
                     const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
@@ -453,24 +494,25 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 }
                 const float lsum = lsum0 + lsum1;
                 {
-                    const uint32_t pcol = (sb ? COL_P1 : COL_P0) + half * 32;
-                    tmem_st16(tmem + lane_sel + pcol, *reinterpret_cast<uint32_t (*)[16]>(&pk[0]));
-                    tmem_st16(tmem + lane_sel + pcol + 16, *reinterpret_cast<uint32_t (*)[16]>(&pk[16]));
+                    const uint32_t pcol = (sb ? COL_P1 : COL_P0) + half * (KH / 2);
+#pragma unroll
+                    for (int c = 0; c < KH / 32; ++c)
+                        tmem_st16(tmem + lane_sel + pcol + c * 16, *reinterpret_cast<uint32_t (*)[16]>(&pk[c * 16]));
                 }
                 tc_wait_st();
                 l_run += lsum;
                 // cache rows of this tile past the last written position may hold stale bits:
                 // zero them in the staged V tile so that 0 * garbage cannot produce NaN
-                const int tile0 = (kt_lo + t) * kPfKeys;
-                if (tile0 + kPfKeys > kv_valid) {
-                    const uint32_t vs = gt % kPfVStages;
-                    ok = __all_sync(0xffffffffu, mbar_wait(B_VFULL + 8 * vs, (gt / kPfVStages) & 1, a.status));
+                const int tile0 = (kt_lo + t) * KEYS;
+                if (tile0 + KEYS > kv_valid) {
+                    const uint32_t vs = gt % VST;
+                    ok = __all_sync(0xffffffffu, mbar_wait(B_VFULL + 8 * vs, (gt / VST) & 1, a.status));
                     if (!ok) continue;
-                    uint8_t* vt = v_gen + (size_t)vs * TILE_BYTES;
+                    uint8_t* vt = v_gen + (size_t)vs * KV_TILE;
                     const int first_bad = kv_valid > tile0 ? kv_valid - tile0 : 0;
-                    for (int idx = first_bad * 8 * NCH + tid; idx < kPfKeys * 8 * NCH; idx += 256) {
+                    for (int idx = first_bad * 8 * NCH + tid; idx < KEYS * 8 * NCH; idx += 256) {
                         const int row = idx / (8 * NCH), u = idx % (8 * NCH);
-                        *reinterpret_cast<uint4*>(vt + (u / 8) * CHUNK_BYTES + row * 128 + (u % 8) * 16) =
+                        *reinterpret_cast<uint4*>(vt + (u / 8) * KV_CHUNK + row * 128 + (u % 8) * 16) =
                             make_uint4(0, 0, 0, 0);
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -478,25 +520,6 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 tc_fence_before();
                 mbar_arrive(B_SFREE + 8 * sb);
                 mbar_arrive(B_PFULL);
-            }
-            // Wait for the item's last P·V, then read this thread's half of O. This is a barrier of
-            // its own with one phase per item: the per-tile barrier may still be two phases behind
-            // here (nothing orders P·V of tile nt-2 before this point), where a parity wait passes
-            // a phase early.
-            float o[HH];
-            ok = __all_sync(0xffffffffu, ok && mbar_wait(B_OFULL, si & 1, a.status));
-            ++si;
-            if (ok) {
-                tc_fence_after();
-#pragma unroll
-                for (int c = 0; c < HH / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32(v, tmem + lane_sel + COL_PV + half * HH + c * 32);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) o[c * 32 + j] = __uint_as_float(v[j]);
-                }
-                tc_fence_before();
             }
             // total row sum = both halves' partial sums (same reference maximum)
             float l_tot = l_run;
@@ -507,29 +530,49 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 ++xn;
                 l_tot += xch[4 * kPfRows + (half ^ 1) * kPfRows + r];
             }
-            if (ok && row_valid && a.splits > 1) {
-                float* prow = a.part + (((long long)qi * a.splits + sp) * a.H + (long long)kvh * a.G + g) * (HD + 2);
+            // Wait for the item's last P·V, then write this thread's half of the row out, 32 columns
+            // at a time. This is a barrier of its own with one phase per item: the per-tile barrier
+            // may still be two phases behind here (nothing orders P·V of tile nt-2 before this
+            // point), where a parity wait passes a phase early.
+            ok = __all_sync(0xffffffffu, ok && mbar_wait(B_OFULL, si & 1, a.status));
+            ++si;
+            if (!ok) continue;
+            tc_fence_after();
+            const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
+            float* prow = nullptr;
+            __half* op = nullptr;
+            if (row_valid) {
+                if (a.splits > 1) prow = a.part + (((long long)qi * a.splits + sp) * a.H + (long long)kvh * a.G + g) * (a.HD + 2);
+                else op = a.out + ((long long)qi * a.H + (long long)kvh * a.G + g) * a.HD;
+            }
 #pragma unroll
-                for (int d = 0; d < HH; d += 4)
-                    *reinterpret_cast<float2*>(prow + half * HH + d) = make_float2(o[d], o[d + 1]),
-                    *reinterpret_cast<float2*>(prow + half * HH + d + 2) = make_float2(o[d + 2], o[d + 3]);
-                if (half == 0) {
-                    prow[HD] = m_ref;
-                    prow[HD + 1] = l_tot;
-                }
-            } else if (ok && row_valid) {
-                const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
-                __half* op = a.out + ((long long)qi * a.H + (long long)kvh * a.G + g) * HD + half * HH;
+            for (int c = 0; c < HH / 32; ++c) {
+                const int d0 = half * HH + c * 32;     // first output dimension of this piece
+                uint32_t v[32];
+                tmem_ld32(v, tmem + lane_sel + COL_PV + d0);
+                tc_wait_ld();
+                if (d0 >= a.HD) continue;              // zero-filled padding columns (head_dim 96)
+                if (prow) {
 #pragma unroll
-                for (int d = 0; d < HH; d += 8) {
-                    uint4 w;
-                    w.x = pack_half2(o[d] * inv, o[d + 1] * inv);
-                    w.y = pack_half2(o[d + 2] * inv, o[d + 3] * inv);
-                    w.z = pack_half2(o[d + 4] * inv, o[d + 5] * inv);
-                    w.w = pack_half2(o[d + 6] * inv, o[d + 7] * inv);
-                    *reinterpret_cast<uint4*>(op + d) = w;
+                    for (int j = 0; j < 32; j += 2)
+                        *reinterpret_cast<float2*>(prow + d0 + j) = make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                } else if (op) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint4 w;
+                        w.x = pack_half2(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv);
+                        w.y = pack_half2(__uint_as_float(v[j + 2]) * inv, __uint_as_float(v[j + 3]) * inv);
+                        w.z = pack_half2(__uint_as_float(v[j + 4]) * inv, __uint_as_float(v[j + 5]) * inv);
+                        w.w = pack_half2(__uint_as_float(v[j + 6]) * inv, __uint_as_float(v[j + 7]) * inv);
+                        *reinterpret_cast<uint4*>(op + d0 + j) = w;
+                    }
                 }
             }
+            if (prow && half == 0) {
+                prow[a.HD] = m_ref;
+                prow[a.HD + 1] = l_tot;
+            }
+            tc_fence_before();
         }
     }
     tc_fence_before();
@@ -541,11 +584,9 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 // Merge of the key-range partials written by the kernel above: one warp per (query, head) row,
 // each lane HD/32 output dimensions. The partial rows are [o(HD), m (log2 domain), l] in fp32.
 // ---------------------------------------------------------------------------
-template <int HD>
 __global__ void __launch_bounds__(256) hkv_prefill_combine_kernel(const float* __restrict__ part,
                                                                   __half* __restrict__ out, long long rows,
-                                                                  int H, int splits) {
-    constexpr int EPL = HD / 32;   // 2 or 4 floats per lane; rows are 8-byte aligned
+                                                                  int H, int HD, int splits) {
     const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (row >= rows) return;
     const int lane = threadIdx.x & 31;
@@ -555,29 +596,29 @@ __global__ void __launch_bounds__(256) hkv_prefill_combine_kernel(const float* _
     const float* base = part + (qi * splits * H + head) * (HD + 2);
     float M = kNegBig;
     for (int sp = 0; sp < splits; ++sp) M = fmaxf(M, __ldg(base + sp * stride + HD));
-    float L = 0.0f, acc[EPL];
+    // lane l takes the dimension pairs 2l, 2l + 64, ... (head_dim is even; rows are 8-byte aligned)
+    float L = 0.0f, acc[8];
 #pragma unroll
-    for (int j = 0; j < EPL; ++j) acc[j] = 0.0f;
+    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
     for (int sp = 0; sp < splits; ++sp) {
         const float* r = base + sp * stride;
         const float w = exp2f(__ldg(r + HD) - M);
         L = fmaf(__ldg(r + HD + 1), w, L);
 #pragma unroll
-        for (int j = 0; j < EPL; j += 2) {
-            const float2 v = __ldg(reinterpret_cast<const float2*>(r + lane * EPL + j));
-            acc[j] = fmaf(v.x, w, acc[j]);
-            acc[j + 1] = fmaf(v.y, w, acc[j + 1]);
+        for (int j = 0; j < 4; ++j) {
+            const int d = lane * 2 + 64 * j;
+            if (d < HD) {
+                const float2 v = __ldg(reinterpret_cast<const float2*>(r + d));
+                acc[2 * j] = fmaf(v.x, w, acc[2 * j]);
+                acc[2 * j + 1] = fmaf(v.y, w, acc[2 * j + 1]);
+            }
         }
     }
     const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-    __half* op = out + row * HD + lane * EPL;
-    if constexpr (EPL == 4) {
-        uint2 w;
-        w.x = pack_half2(acc[0] * inv, acc[1] * inv);
-        w.y = pack_half2(acc[2] * inv, acc[3] * inv);
-        *reinterpret_cast<uint2*>(op) = w;
-    } else {
-        *reinterpret_cast<uint32_t*>(op) = pack_half2(acc[0] * inv, acc[1] * inv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int d = lane * 2 + 64 * j;
+        if (d < HD) *reinterpret_cast<uint32_t*>(out + row * HD + d) = pack_half2(acc[2 * j] * inv, acc[2 * j + 1] * inv);
     }
 }
 

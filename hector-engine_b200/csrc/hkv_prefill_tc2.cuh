@@ -1,7 +1,8 @@
 // hkv_prefill_tc2.cuh — the tensor-core prefill kernel with TWO query tiles in flight per CTA.
 //
 // Same contract as hkv_prefill_tc_kernel (reference kernels/attention.cu:664-788: query i attends
-// cache rows [first_i, past_len + i]), different shape of the pipeline:
+// cache rows [first_i, past_len + i]; head_dim 64, 96 — staged as 128 — and 128; linear and ring
+// planes), different shape of the pipeline:
 //   * Work item = (pair of query tiles A and B = 2 x QT consecutive queries, KV head, key split).
 //     Both tiles are contracted against the SAME staged K and V tiles, so shared-memory and L2
 //     traffic per flop halve.
@@ -171,22 +172,10 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     // a.QT = queries per 128-row tile; a.n_qtiles counts PAIRS of tiles here
     const int QT2 = 2 * a.QT;
     const int n_items = a.n_qtiles * a.KVH * a.splits;
-    const int kv_valid = (a.past_len + a.S_new < a.slots) ? a.past_len + a.S_new : a.slots;
+    const int kv_valid = prefill_kv_valid(a);
 
-    // Key-tile range of a tile pair and split (identical in every role).
-    auto tile_span = [&](int qt, int sp, int& kt_lo, int& nt) {
-        const int q0 = qt * QT2;
-        const int first_min = a.window > 0 ? (a.past_len + q0 + 1 - a.window > 0 ? a.past_len + q0 + 1 - a.window : 0) : 0;
-        int q_last = q0 + QT2 < a.S_new ? q0 + QT2 : a.S_new;
-        int last_max = a.past_len + q_last - 1;
-        if (last_max > a.slots - 1) last_max = a.slots - 1;
-        const int kt0 = first_min / kPfKeys;
-        int ntot = last_max / kPfKeys - kt0 + 1;
-        if (ntot < 1) ntot = 1;
-        const int base = ntot / a.splits, rem = ntot % a.splits;   // the host guarantees splits <= shortest span
-        kt_lo = kt0 + sp * base + (sp < rem ? sp : rem);
-        nt = base + (sp < rem ? 1 : 0);
-    };
+    // Key-tile range of a tile pair and split (identical in every role); tiles count logical positions.
+    auto tile_span = [&](int qt, int sp, int& kt_lo, int& nt) { prefill_tile_span(a, QT2, kPfKeys, qt, sp, kt_lo, nt); };
     auto decode_item = [&](int item, int& qt, int& kvh, int& sp) {
         sp = item % a.splits;
         const int rest = item / a.splits;
@@ -229,7 +218,7 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 q_pending = true;
                 q_it = it;
                 for (int t = 0; t < nt; ++t, ++gt) {
-                    const int row = (kt_lo + t) * kPfKeys;
+                    const int row = prefill_tile_row(a, (kt_lo + t) * kPfKeys);
                     const uint32_t ks = gt % kPf2KStages, ku = gt / kPf2KStages;
                     if (!mbar_wait(B_KEMPTY + 8 * ks, (ku & 1) ^ 1, a.status)) { ok = false; break; }
                     mbar_expect_tx(B_KFULL + 8 * ks, TILE_BYTES);
@@ -271,6 +260,7 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             const uint64_t vdesc0 = umma_desc_sw128(v_smem, CHUNK_BYTES);
             const uint32_t desc_hi = (uint32_t)(qdesc0 >> 32);
             const uint32_t q_lo = (uint32_t)qdesc0, k_lo = (uint32_t)kdesc0, v_lo = (uint32_t)vdesc0;
+            const int ksteps = (a.HD + 15) / 16;   // k-steps holding real dimensions (zero-filled ones are skipped)
             // S_grp = Q_grp · K(g)^T   (the K tile must have been waited for)
             auto issue_qk = [&](uint32_t g, int grp) {
                 const uint32_t kd = k_lo + (((g % kPf2KStages) * TILE_BYTES) >> 4);
@@ -280,7 +270,7 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 for (int kk = 0; kk < HD / 16; ++kk) {
                     const uint32_t off = (uint32_t)(((kk / 4) * CHUNK_BYTES + (kk % 4) * 32) >> 4);
                     if (kk == 0) tc_mma_ss_i<false>(d, qd + off, kd + off, desc_hi, IDESC_QK);
-                    else tc_mma_ss_i<true>(d, qd + off, kd + off, desc_hi, IDESC_QK);
+                    else if (kk < ksteps) tc_mma_ss_i<true>(d, qd + off, kd + off, desc_hi, IDESC_QK);
                 }
                 tc_commit(B_SFULL + 8 * grp);
             };
@@ -364,7 +354,7 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             const bool row_valid = ql < a.QT && qi < a.S_new;
             const int qpos = a.past_len + qi;
             const int first_row = a.window > 0 ? (qpos + 1 - a.window > 0 ? qpos + 1 - a.window : 0) : 0;
-            const int qlim = qpos < a.slots ? qpos : a.slots - 1;  // never attend rows past the plane
+            const int qlim = prefill_last_key(a, qpos);  // never attend rows past a linear plane
             // m_ref: the reference maximum P and O are scaled by; it moves (and O is rescaled) only
             // when a tile's maximum exceeds it by more than 2^8 — fp16 holds P up to that factor.
             float m_ref = kNegBig, l_run = 0.0f;
@@ -475,14 +465,15 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             float* prow = nullptr;
             __half* op = nullptr;
             if (row_valid) {
-                if (a.splits > 1) prow = a.part + (((long long)qi * a.splits + sp) * a.H + (long long)kvh * a.G + g) * (HD + 2);
-                else op = a.out + ((long long)qi * a.H + (long long)kvh * a.G + g) * HD;
+                if (a.splits > 1) prow = a.part + (((long long)qi * a.splits + sp) * a.H + (long long)kvh * a.G + g) * (a.HD + 2);
+                else op = a.out + ((long long)qi * a.H + (long long)kvh * a.G + g) * a.HD;
             }
 #pragma unroll
             for (int c = 0; c < HD / 32; ++c) {
                 uint32_t v[32];
                 tmem_ld32(v, o_addr + c * 32);
                 tc_wait_ld_dep(v);
+                if (c * 32 >= a.HD) continue;          // zero-filled padding columns (head_dim 96)
                 if (prow) {
 #pragma unroll
                     for (int j = 0; j < 32; j += 2)
@@ -500,8 +491,8 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 }
             }
             if (prow) {
-                prow[HD] = m_ref;
-                prow[HD + 1] = l_run;
+                prow[a.HD] = m_ref;
+                prow[a.HD + 1] = l_run;
             }
             tc_fence_before();
         }

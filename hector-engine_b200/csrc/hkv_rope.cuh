@@ -8,7 +8,7 @@
 //   dims >= rot pass through normalised
 // but batched over sequences with one device position per sequence, row lookup through
 // the same position->row map as the append (linear drop / ring / shard owner), one warp per
-// (sequence, token, head), no block-wide barrier.
+// (sequence, token, head), the rotation table computed once per token and CTA, 8-byte accesses.
 #pragma once
 
 #include "hkv_common.cuh"
@@ -28,72 +28,108 @@ struct RopeArgs {
     int host_pos;
     SeqMap map;
     int B, S, H, KVH, HD, rot;
+    long long tok0;         // first token (b*S + s) of this launch
     long long batch_stride;
     float eps, theta, scaling;
 };
 
-constexpr int kRopeWarps = 4;
+constexpr int kRopeWarps = 8;
 
-// Unit of work u = ((b*S + s) * (H + 2*KVH) + j): j < H query head, j < H+KVH key head,
-// else value head (copy only, when a cache is given).
-__global__ void __launch_bounds__(kRopeWarps * 32) hkv_qk_norm_rope_kernel(const RopeArgs a) {
+// One CTA serves kRopeWarps units of ONE token: a unit is a query head, a key head or a value head
+// (j < H query head j, j < H + KVH key head, else value head — a plain copy, only when a cache is
+// given). Grid = (ceil((H + 2*KVH) / kRopeWarps), B*S).
+//   * The rotation angles depend on (position, pair index) only, so the CTA computes the cos/sin
+//     table of its token once (rot/2 entries, accurate powf + sincosf: positions reach 10^5 rad)
+//     and every head of the CTA reuses it — the reference recomputes it per head and per pair.
+//   * Rows move in 8-byte pieces (4 halfs per lane: a 128-wide head is one piece per lane) when the
+//     pointers and head_dim allow it, else element by element. A warp stages its head as fp32 in
+//     shared memory, so any rotary_dim <= head_dim <= 512 takes the same code.
+__global__ void __launch_bounds__(kRopeWarps * 32) hkv_qk_norm_rope_kernel(const RopeArgs a, const int vec) {
     __shared__ float s_x[kRopeWarps][512];
+    __shared__ float s_cos[256], s_sin[256];
+    __shared__ float s_w[2][512];          // q and k norm weights as fp32
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int per_tok = a.H + 2 * a.KVH;
-    const long long units = (long long)a.B * a.S * per_tok;
-    for (long long u = (long long)blockIdx.x * kRopeWarps + warp; u < units;
-         u += (long long)gridDim.x * kRopeWarps) {
-        const int j = (int)(u % per_tok);
-        const long long tok = u / per_tok;
-        const int s = (int)(tok % a.S), b = (int)(tok / a.S);
-        const int pos = (a.d_pos ? a.d_pos[b * a.pos_stride] : a.host_pos) + s;
-        const bool is_q = j < a.H, is_k = !is_q && j < a.H + a.KVH;
-        const int kvh = is_q ? 0 : (is_k ? j - a.H : j - a.H - a.KVH);
-        int slot = -1;
-        if (!is_q && a.k_cache) {
-            slot = slot_of_pos(a.map, pos);
-            if (slot < 0) continue;  // dropped past the plane / owned by another rank
+    const long long tok = a.tok0 + blockIdx.y;
+    const int s = (int)(tok % a.S), b = (int)(tok / a.S);
+    const int pos = (a.d_pos ? a.d_pos[b * a.pos_stride] : a.host_pos) + s;
+    const int half_rot = a.rot / 2;
+    const float fp = (float)pos / a.scaling;
+    for (int i = threadIdx.x; i < half_rot; i += blockDim.x) {
+        const float freq = 1.0f / powf(a.theta, (float)(2 * i) / (float)a.rot);
+        float sn, c;
+        sincosf(fp * freq, &sn, &c);
+        s_cos[i] = c;
+        s_sin[i] = sn;
+    }
+    for (int i = threadIdx.x; i < a.HD; i += blockDim.x) {
+        s_w[0][i] = __half2float(a.q_w[i]);
+        s_w[1][i] = __half2float(a.k_w[i]);
+    }
+    __syncthreads();
+
+    const int j = blockIdx.x * kRopeWarps + warp;
+    if (j >= per_tok) return;
+    const bool is_q = j < a.H, is_k = !is_q && j < a.H + a.KVH;
+    const int kvh = is_q ? 0 : (is_k ? j - a.H : j - a.H - a.KVH);
+    int slot = -1;
+    if (!is_q && a.k_cache) {
+        slot = slot_of_pos(a.map, pos);
+        if (slot < 0) return;  // dropped past the plane / owned by another rank
+    }
+    const long long cache_off = (long long)b * a.batch_stride + ((long long)slot * a.KVH + kvh) * a.HD;
+    if (!is_q && !is_k) {  // value head: plain copy into the cache
+        if (!a.k_cache || !a.v) return;
+        const __half* src = a.v + ((tok * a.KVH) + kvh) * a.HD;
+        __half* dst = a.v_cache + cache_off;
+        if (vec) {
+            for (int i = lane; i < a.HD / 4; i += 32) reinterpret_cast<uint2*>(dst)[i] = reinterpret_cast<const uint2*>(src)[i];
+        } else {
+            for (int i = lane; i < a.HD; i += 32) dst[i] = src[i];
         }
-        const long long cache_off =
-            (long long)b * a.batch_stride + ((long long)slot * a.KVH + kvh) * a.HD;
-        if (!is_q && !is_k) {  // value head: plain copy into the cache
-            if (!a.k_cache || !a.v) continue;
-            const __half* src = a.v + ((tok * a.KVH) + kvh) * a.HD;
-            for (int i = lane; i < a.HD; i += 32) a.v_cache[cache_off + i] = src[i];
-            continue;
+        return;
+    }
+    const __half* src = is_q ? a.q + (tok * a.H + j) * a.HD : a.k + (tok * a.KVH + kvh) * a.HD;
+    __half* dst = is_q ? a.q + (tok * a.H + j) * a.HD
+                       : (a.k_cache ? a.k_cache + cache_off : a.k + (tok * a.KVH + kvh) * a.HD);
+    const float* w = s_w[is_q ? 0 : 1];
+    float* x = s_x[warp];
+    float ssq = 0.0f;
+    if (vec) {
+        for (int i = lane; i < a.HD / 4; i += 32) {
+            const uint2 raw = reinterpret_cast<const uint2*>(src)[i];
+            const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+            const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+            x[4 * i] = lo.x; x[4 * i + 1] = lo.y; x[4 * i + 2] = hi.x; x[4 * i + 3] = hi.y;
+            ssq = fmaf(lo.x, lo.x, fmaf(lo.y, lo.y, fmaf(hi.x, hi.x, fmaf(hi.y, hi.y, ssq))));
         }
-        const __half* src = is_q ? a.q + (tok * a.H + j) * a.HD : a.k + (tok * a.KVH + kvh) * a.HD;
-        __half* dst = is_q ? a.q + (tok * a.H + j) * a.HD
-                           : (a.k_cache ? a.k_cache + cache_off : a.k + (tok * a.KVH + kvh) * a.HD);
-        const __half* w = is_q ? a.q_w : a.k_w;
-        float* x = s_x[warp];
-        float ssq = 0.0f;
+    } else {
         for (int i = lane; i < a.HD; i += 32) {
             const float t = __half2float(src[i]);
             x[i] = t;
             ssq = fmaf(t, t, ssq);
         }
+    }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
-        const float inv = 1.0f / sqrtf(ssq / (float)a.HD + a.eps);
-        __syncwarp();
-        for (int i = lane; i < a.HD; i += 32) x[i] = x[i] * inv * __half2float(w[i]);
-        __syncwarp();
-        const int half_rot = a.rot / 2;
-        const float fp = (float)pos / a.scaling;
-        for (int i = lane; i < a.HD; i += 32) {
-            if (i < half_rot) {
-                const float freq = 1.0f / powf(a.theta, (float)(2 * i) / (float)a.rot);
-                float sn, c;
-                sincosf(fp * freq, &sn, &c);
-                const float x0 = x[i], x1 = x[i + half_rot];
-                dst[i] = __float2half_rn(x0 * c - x1 * sn);
-                dst[i + half_rot] = __float2half_rn(x0 * sn + x1 * c);
-            } else if (i >= a.rot) {
-                dst[i] = __float2half_rn(x[i]);
-            }
+    for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+    const float inv = 1.0f / sqrtf(ssq / (float)a.HD + a.eps);
+    __syncwarp();
+    // normalised value of element e, and its rotated image
+    auto norm = [&](int e) { return x[e] * inv * w[e]; };
+    auto rotated = [&](int e) {
+        if (e < half_rot) return norm(e) * s_cos[e] - norm(e + half_rot) * s_sin[e];
+        if (e < a.rot) return norm(e - half_rot) * s_sin[e - half_rot] + norm(e) * s_cos[e - half_rot];
+        return norm(e);
+    };
+    if (vec) {
+        for (int i = lane; i < a.HD / 4; i += 32) {
+            uint2 o;
+            o.x = pack_half2(rotated(4 * i), rotated(4 * i + 1));
+            o.y = pack_half2(rotated(4 * i + 2), rotated(4 * i + 3));
+            reinterpret_cast<uint2*>(dst)[i] = o;
         }
-        __syncwarp();
+    } else {
+        for (int i = lane; i < a.HD; i += 32) dst[i] = __float2half_rn(rotated(i));
     }
 }
 

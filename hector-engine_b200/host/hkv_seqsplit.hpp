@@ -180,12 +180,7 @@ public:
                 return ncclCommGetAsyncError(comm_, &async) != ncclSuccess || (async != ncclSuccess && async != ncclInProgress);
             },
             timeout);
-        if (r != WatchResult::Done && comm_ && !aborted_) {
-            ncclCommAbort(comm_);
-            comm_ = nullptr;
-            aborted_ = true;
-            graph_.invalidate();
-        }
+        if (r != WatchResult::Done && comm_ && !aborted_) abandon();
         cudaGetLastError();
         return r;
     }
@@ -193,10 +188,12 @@ public:
     // for the ranks it leaves behind. Call with nothing of this rank in flight. The object then
     // only serves destruction.
     void abandon() {
+        // The captured graph goes first: a graph that holds this communicator's collectives keeps the
+        // communicator referenced, and NCCL's abort (like its destroy) waits for those references.
+        graph_.invalidate();
         if (comm_) ncclCommAbort(comm_);
         comm_ = nullptr;
         aborted_ = true;
-        graph_.invalidate();
     }
     bool aborted() const { return aborted_; }
     int device_status() { int32_t w = 0; hkv_ctx_device_status(ctx_, stream_, &w); return w; }

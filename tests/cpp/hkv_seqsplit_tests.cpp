@@ -74,7 +74,16 @@ bool close_enough(const std::vector<uint16_t>& got, const std::vector<uint16_t>&
     return ok;
 }
 
+// Progress lines of a rank (unbuffered, so they survive a rank that is stopped at its time limit).
+#define STAGE(...)                                       \
+    do {                                                 \
+        std::printf("[rank %d] ", rank);                 \
+        std::printf(__VA_ARGS__);                        \
+        std::printf("\n");                               \
+    } while (0)
+
 int run_rank(int rank, int world, const std::string& idfile, bool leave_at_end) {
+    setvbuf(stdout, nullptr, _IONBF, 0);
     CUDA_OK(cudaSetDevice(world > 1 ? rank : 0));
     ncclUniqueId id;
     std::memset(&id, 0, sizeof id);
@@ -99,6 +108,7 @@ int run_rank(int rank, int world, const std::string& idfile, bool leave_at_end) 
             roster.reset(new hkv::NodeRoster(rname, world, rank));
         }
     }
+    if (world > 1) STAGE("communicator id exchanged");
     cudaStream_t stream;
     CUDA_OK(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
 
@@ -136,6 +146,7 @@ int run_rank(int rank, int world, const std::string& idfile, bool leave_at_end) 
         cfg.layers = L; cfg.batch = B; cfg.heads = H; cfg.kv_heads = KVH; cfg.head_dim = HD;
         cfg.local_slots = (uint32_t)local_slots; cfg.shard_block = BLK; cfg.rank = rank; cfg.world = world;
         hkv::SeqSplitDecoder dec(cfg, world > 1 ? &id : nullptr, stream);
+        if (world > 1) STAGE("decoder and communicator ready");
         dec.bind(dq, dkn, dvn, dout, dk, dv, lplane, dtot);
         if (roster) dec.attach_roster(roster.get(), 20000ms);
 
@@ -152,6 +163,7 @@ int run_rank(int rank, int world, const std::string& idfile, bool leave_at_end) 
             CUDA_OK(cudaMemcpyAsync(dtot, totals, sizeof totals, cudaMemcpyHostToDevice, stream));
             replays += dec.step() ? 1 : 0;
             const hkv::WatchResult w = dec.wait(30000ms);
+            if (world > 1) STAGE("step %d %s (%s)", s, hkv::watch_result_name(w), dec.graph().valid() ? "graph" : "direct");
             REQUIRE(w == hkv::WatchResult::Done, "the step completes within its deadline");
             if (w != hkv::WatchResult::Done) throw std::runtime_error("step did not complete");
             CUDA_OK(cudaMemcpy(got.data(), dout, got.size() * 2, cudaMemcpyDeviceToHost));
@@ -263,7 +275,7 @@ int main(int argc, char** argv) {
         kids.push_back(pid);
     }
     int bad = 0;
-    const auto deadline = std::chrono::steady_clock::now() + 240s;
+    const auto deadline = std::chrono::steady_clock::now() + 150s;
     std::vector<bool> done(kids.size(), false);
     size_t left = kids.size();
     while (left && std::chrono::steady_clock::now() < deadline) {

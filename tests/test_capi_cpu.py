@@ -216,9 +216,19 @@ def test_prefill_plan_never_leaves_a_key_split_empty(hkv):
     # without a workspace for partials there is no split
     g0 = hkv.Geometry(num_heads=28, num_kv_heads=4, head_dim=128, slots=131072, max_seq_new=0)
     assert _plan_prefill(hkv, g0, 2048, 129024)[2] == 1
+    # head_dim 96 is staged as 128 and takes the same kernels; head_dim 256 only the one-tile kernel,
+    # with 64-row key tiles
+    g96 = hkv.Geometry(num_heads=32, num_kv_heads=32, head_dim=96, slots=4096, max_seq_new=0)
+    assert _plan_prefill(hkv, g96, 256, 100) == [2, 1 * 32, 1, 3]
+    g256 = hkv.Geometry(num_heads=16, num_kv_heads=8, head_dim=256, slots=4096, max_seq_new=0)
+    tif, items, splits, span = _plan_prefill(hkv, g256, 2048, 1024)
+    assert (tif, items, splits) == (1, 32 * 8, 1) and span == (1024 + 64) // 64 - 0
     # geometries the tensor-core kernels do not take: SIMT, one CTA per (query, head)
-    g96 = hkv.Geometry(num_heads=32, num_kv_heads=32, head_dim=96, slots=4096, max_seq_new=256)
-    assert _plan_prefill(hkv, g96, 256, 100) == [0, 256 * 32, 1, 0]
+    g80 = hkv.Geometry(num_heads=32, num_kv_heads=32, head_dim=80, slots=4096, max_seq_new=256)
+    assert _plan_prefill(hkv, g80, 256, 100) == [0, 256 * 32, 1, 0]
+    # a ring plane whose rows are not a whole number of key tiles also falls to the SIMT kernel
+    gring = hkv.Geometry(num_heads=8, num_kv_heads=8, head_dim=128, slots=200, window_size=50, layout=1)
+    assert _plan_prefill(hkv, gring, 64, 1000)[0] == 0
     # window 119 over 36-query items: spans of 2 and 3 tiles alternate; forcing 3 or 4 splits must clamp to 2
     for forced in (1, 2, 3, 4):
         gw = hkv.Geometry(num_heads=7, num_kv_heads=1, head_dim=128, slots=1231, window_size=119, max_seq_new=345,
@@ -232,7 +242,7 @@ def test_prefill_plan_never_leaves_a_key_split_empty(hkv):
         G = int(rng.choice([1, 2, 4, 7, 8])); KVH = int(rng.choice([1, 2, 4, 8]))
         S = int(rng.integers(1, 4000)); past = int(rng.integers(0, 200000))
         win = int(rng.choice([0, int(rng.integers(1, 5000))]))
-        gg = hkv.Geometry(num_heads=G * KVH, num_kv_heads=KVH, head_dim=int(rng.choice([64, 128])),
+        gg = hkv.Geometry(num_heads=G * KVH, num_kv_heads=KVH, head_dim=int(rng.choice([64, 96, 128, 256])),
                           slots=past + S + int(rng.integers(0, 300)), window_size=win, max_seq_new=S)
         tif, items, splits, span = _plan_prefill(hkv, gg, S, past, sms=int(rng.choice([132, 148])))
         assert 1 <= splits <= min(span, 4) and tif in (1, 2) and items >= 1
@@ -250,6 +260,9 @@ def test_preferred_prefill_chunk_makes_items_a_multiple_of_the_sms(hkv):
         assert tif == 2 and (items // splits) % 148 == 0
     mha = hkv.Geometry(num_heads=8, num_kv_heads=8, head_dim=64, slots=4096, max_seq_new=4096)
     assert lib.hkv_preferred_prefill_chunk(C.byref(mha.to_c()), 148, 10000) == 9472   # 37 pairs x 256
-    simt = hkv.Geometry(num_heads=32, num_kv_heads=32, head_dim=96, slots=4096)
+    simt = hkv.Geometry(num_heads=32, num_kv_heads=32, head_dim=80, slots=4096)
     assert lib.hkv_preferred_prefill_chunk(C.byref(simt.to_c()), 148, 777) == 777
+    # head_dim 256: one query tile per item (64 queries at group 2), 148 items x ... / gcd(148, 8) = 37 tiles a round
+    g256 = hkv.Geometry(num_heads=16, num_kv_heads=8, head_dim=256, slots=4096)
+    assert lib.hkv_preferred_prefill_chunk(C.byref(g256.to_c()), 148, 3000) == 37 * 64
     assert lib.hkv_preferred_prefill_chunk(C.byref(gc), 0, 2048) < 0

@@ -464,3 +464,58 @@ def test_prefill_refuses_a_batched_context(hkv, cuda):
         ctx.prefill_attention(t, t, t, t, 4, 0, 1.0)
     assert e.value.status == 2   # HKV_ERR_GEOMETRY
     ctx.close()
+
+
+@pytest.mark.parametrize("groups", [1, 2], ids=["two_ctas_per_sm", "one_cta_per_sm"])
+@pytest.mark.parametrize("shape", [
+    # B, H, KVH, HD, slots, window, layout
+    (5, 28, 4, 128, 4096, 0, 0),     # config 2 shape, ragged lengths
+    (3, 14, 2, 64, 2048, 0, 0),      # config 1 shape
+    (4, 32, 32, 96, 1024, 0, 0),     # config 3 shape (MHA, head_dim 96)
+    (3, 16, 8, 256, 1024, 1024, 1),  # config 4 local layer: ring (256-wide tiles need the whole SM: falls back)
+    (70, 8, 2, 128, 640, 200, 0),    # more sequences than a warp scans at once, sliding window
+], ids=lambda s: "B%d_H%d_KVH%d_HD%d_%d_w%d_l%d" % s)
+def test_both_shapes_of_the_tma_decode_kernel(hkv, cuda, oracle, shape, groups):
+    """The TMA decode kernel runs either as one CTA per SM with two consumer groups or as two CTAs per
+    SM with one group each (chosen by the work per SM; forced here through tune_tma_groups). Both give
+    the oracle's result for the fused append + attention, with ragged and empty sequences."""
+    torch = cuda
+    B, H, KVH, HD, slots, window, layout = shape
+    rng = np.random.default_rng(B * 131 + HD + groups)
+    hi = 3 * slots if layout == 1 else slots
+    pos = rng.integers(0, hi, size=B).astype(np.int32)
+    pos[0] = hi - 1
+    if B > 2:
+        pos[1], pos[2] = 0, -1            # first token of a sequence; a free batch slot
+    q, nk, nv, _, _ = make_case(int(rng.integers(1 << 30)), B, H, KVH, HD, 1)
+    lin = int(pos.max()) + 1               # linear reference planes hold every position
+    kc, vc = normal_f16(rng, B, lin, KVH, HD), normal_f16(rng, B, lin, KVH, HD)
+    ref_k, ref_v = kc.copy(), vc.copy()
+    live = pos >= 0
+    for b in np.nonzero(live)[0]:          # the reference's append: the new row at its position
+        ref_k[b, pos[b]], ref_v[b, pos[b]] = nk[b, 0], nv[b, 0]
+    scale = 1.0 / math.sqrt(HD)
+    ref = oracle.decode(q, ref_k, ref_v, np.maximum(pos + 1, 0), scale, window=window, threads=8)
+    # device planes: the rows below each position (ring: the last `slots` of them), garbage elsewhere
+    dk_h = np.full((B, slots, KVH, HD), np.nan, np.float16)
+    dv_h = np.full((B, slots, KVH, HD), np.inf, np.float16)
+    for b in range(B):
+        for p in range(max(0, int(pos[b]) - slots) if layout == 1 else 0, max(int(pos[b]), 0)):
+            r = p % slots if layout == 1 else p
+            dk_h[b, r], dv_h[b, r] = kc[b, p], vc[b, p]
+    ctx = hkv.Context(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots, window_size=window,
+                                   layout=layout, kernel_select=TMA, tune_tma_groups=groups))
+    dk, dv = to_dev(torch, dk_h), to_dev(torch, dv_h)
+    out = torch.full((B, H, HD), float("nan"), dtype=torch.float16, device="cuda")
+    for _ in range(2):      # the second call re-appends the same rows: same result
+        ctx.append_decode_attention(to_dev(torch, q), to_dev(torch, nk), to_dev(torch, nv), dk, dv, out,
+                                    to_dev(torch, pos), scale)
+    assert ctx.device_status() == 0
+    got = out.cpu().numpy()
+    assert_close(oracle, got, ref, f"fused decode, groups={groups}")
+    assert not got[~live].any(), "a free slot gives a zero row"
+    for b in np.nonzero(live)[0]:
+        r = int(pos[b]) % slots if layout == 1 else int(pos[b])
+        assert np.array_equal(dk[b, r].cpu().numpy().view(np.uint16), nk[b, 0].view(np.uint16))
+        assert np.array_equal(dv[b, r].cpu().numpy().view(np.uint16), nv[b, 0].view(np.uint16))
+    ctx.close()

@@ -1,6 +1,6 @@
 """GPU parity of prefill-over-cache attention (hkv_prefill_attention) against the oracle:
-the tcgen05 tensor-core kernel (head_dim 64 / 128) and the any-geometry SIMT kernel, on the
-same seeded inputs. Tolerance: |x - ref| <= 2e-3 + 1e-2*|ref| per fp16 element."""
+the tcgen05 tensor-core kernels (head_dim 64 / 96 / 128 / 256, linear and ring planes) and the
+any-geometry SIMT kernel, on the same seeded inputs. Tolerance: |x - ref| <= 2e-3 + 1e-2*|ref| per fp16 element."""
 import math
 
 import numpy as np
@@ -20,6 +20,11 @@ CASES = [
     ("group16_window_small", 32, 2, 64, 512, 40, 90, 17),
     ("single_query", 28, 4, 128, 256, 130, 1, 0),
     ("fills_plane_exactly", 28, 4, 128, 384, 256, 128, 0),
+    ("phi3_mha_hd96", 8, 8, 96, 1024, 450, 170, 0),
+    ("hd96_group4_window", 16, 4, 96, 768, 300, 100, 130),
+    ("gemma_hd256_group2", 16, 8, 256, 1024, 500, 150, 0),
+    ("gemma_hd256_window_from_empty", 8, 4, 256, 512, 0, 333, 100),
+    ("hd256_single_query", 4, 2, 256, 256, 200, 1, 0),
 ]
 
 
@@ -76,7 +81,7 @@ def test_chunked_prefill_then_decode_agree(hkv, cuda, oracle):
     ctx.close()
 
 
-VARIANT_CASES = [CASES[0], CASES[2], CASES[4]]
+VARIANT_CASES = [CASES[0], CASES[2], CASES[4], CASES[8], CASES[10]]
 
 
 @pytest.mark.parametrize("splits", [1, 2, 3, 4])
@@ -133,13 +138,13 @@ def test_prefill_row_maxima_that_keep_growing(hkv, cuda, oracle, tiles_in_flight
 
 
 def test_prefill_seeded_random_shapes(hkv, cuda, oracle):
-    """Thirty seeded random geometries (group size, head_dim 64/128, chunk and past lengths that are
+    """Thirty seeded random geometries (group size, head_dim 64/96/128/256, chunk and past lengths that are
     not multiples of any tile, windows, forced key splits, both tensor-core kernels): every one must
     match the oracle. Catches protocol slips that only show for particular tile counts per item."""
     torch = cuda
     rng = np.random.default_rng(20241125)
     for i in range(30):
-        HD = int(rng.choice([64, 128]))
+        HD = int(rng.choice([64, 128, 96, 256]))
         KVH = int(rng.choice([1, 2, 4]))
         G = int(rng.choice([1, 2, 4, 7, 8]))
         H = KVH * G
@@ -167,3 +172,64 @@ def test_prefill_seeded_random_shapes(hkv, cuda, oracle):
         assert_close(oracle, got, ref, f"case {i}: H={H} KVH={KVH} HD={HD} S_new={S_new} past={past} "
                                         f"slots={slots} window={window}")
         ctx.close()
+
+
+RING_CASES = [
+    # name, H, KVH, HD, ring rows, window, past_len, S_new
+    ("ring_not_wrapped_yet", 16, 8, 256, 512, 128, 100, 200),
+    ("ring_wrapped_hd256", 16, 8, 256, 512, 128, 1900, 300),          # 300 + 128 - 1 <= 512
+    ("ring_wrapped_hd128_group7", 28, 4, 128, 1024, 256, 5000, 700),
+    ("ring_wrapped_hd96", 8, 8, 96, 256, 100, 777, 150),
+    ("ring_exact_fit", 8, 2, 64, 256, 129, 1000, 128),               # 128 + 129 - 1 == 256
+]
+
+
+@pytest.mark.parametrize("kernel", [0, 1], ids=["tensor_core", "simt"])
+@pytest.mark.parametrize("case", RING_CASES, ids=lambda c: c[0])
+def test_prefill_over_a_ring_plane_equals_linear_plane_with_window(hkv, cuda, oracle, case, kernel):
+    """A sliding-window layer kept in a ring plane (position p in row p % rows; not in the reference,
+    which keeps a linear plane and masks): a prefill chunk appended into the ring and attended there
+    equals the oracle on the linear plane with the same window, as long as chunk + window - 1 fits the
+    ring. The chunk's rows are appended by the library itself (hkv_append_at wraps)."""
+    torch = cuda
+    name, H, KVH, HD, rows, window, past, S_new = case
+    rng = np.random.default_rng(len(name) * 31 + HD)
+    total = past + S_new
+    lin_k = normal_f16(rng, 1, total, KVH, HD)
+    lin_v = normal_f16(rng, 1, total, KVH, HD)
+    q = normal_f16(rng, S_new, H, HD)
+    scale = 1.0 / math.sqrt(HD)
+    ref = oracle.prefill(q, lin_k[0], lin_v[0], past, scale, window=window, threads=8)
+    # the ring before the chunk: the last `rows` positions below past_len, everything else poison
+    ring_k = np.full((1, rows, KVH, HD), np.nan, np.float16)
+    ring_v = np.full((1, rows, KVH, HD), np.inf, np.float16)
+    for p in range(max(0, past - rows), past):
+        ring_k[0, p % rows], ring_v[0, p % rows] = lin_k[0, p], lin_v[0, p]
+    ctx = hkv.Context(hkv.Geometry(batch=1, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=rows,
+                                   window_size=window, layout=hkv.LAYOUT_RING, kernel_select=kernel, max_seq_new=S_new))
+    dk, dv = to_dev(torch, ring_k), to_dev(torch, ring_v)
+    ctx.append_at(to_dev(torch, lin_k[:, past:]), to_dev(torch, lin_v[:, past:]), dk, dv, past, S_new)
+    out = torch.full((S_new, H, HD), float("nan"), dtype=torch.float16, device="cuda")
+    ctx.prefill_attention(to_dev(torch, q), dk, dv, out, S_new, past, scale)
+    assert ctx.device_status() == 0
+    got = out.cpu().numpy()
+    assert not np.isnan(got.astype(np.float32)).any()
+    assert_close(oracle, got, ref, name)
+    assert ctx.plan_prefill(S_new, past)[0] == (0 if kernel == 1 else (1 if HD == 256 or S_new <= 128 // (H // KVH) else 2))
+    ctx.close()
+
+
+def test_prefill_refuses_a_chunk_that_overwrites_what_it_attends(hkv, cuda):
+    """Ring of 256 rows, window 200, chunk of 100 at position 1000: the first query needs position 801,
+    which the chunk's last row (1099 -> row 1099 % 256) has overwritten (100 + 200 - 1 > 256)."""
+    torch = cuda
+    ctx = hkv.Context(hkv.Geometry(batch=1, num_heads=4, num_kv_heads=4, head_dim=64, slots=256, window_size=200,
+                                   layout=hkv.LAYOUT_RING))
+    t = torch.zeros(256 * 4 * 64, dtype=torch.float16, device="cuda")
+    with pytest.raises(hkv.HkvError) as e:
+        ctx.prefill_attention(t, t, t, t, 100, 1000, 1.0)
+    assert e.value.status == 2 and "do not fit the ring" in str(e.value)
+    ctx.prefill_attention(t, t, t, t, 57, 1000, 1.0)    # 57 + 200 - 1 == 256 fits
+    ctx.prefill_attention(t, t, t, t, 100, 100, 1.0)    # nothing overwritten yet
+    torch.cuda.synchronize()
+    ctx.close()
