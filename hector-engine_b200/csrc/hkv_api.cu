@@ -54,6 +54,7 @@ struct hkv_ctx {
     int pos_stride = 1;             // 0 with HKV_FLAG_SCALAR_POSITION
     float* prefill_ws = nullptr;    // [max_seq_new][kPrefillMaxSplits][H][HD+2] key-split partials of the prefill kernel
     int* prefill_counter = nullptr; // work counter of the two-tile prefill kernel (zeroed on the stream before each launch)
+    int* prefill_row_parts = nullptr; // [max_seq_new][KVH]: partial rows per (query, kv head) under the equal-span schedule
     // host-buffer entry point staging
     __half *st_q = nullptr, *st_k = nullptr, *st_v = nullptr, *st_out = nullptr;
     std::map<std::pair<const void*, const void*>, TmapPair> tmaps;   // keyed on the (k, v) plane pair
@@ -213,7 +214,7 @@ int encode_f16_sw128(hkv_ctx* c, const void* base, int rank, const cuuint64_t* d
 
 constexpr int kPrefillMaxSplits = 4;
 // Below this many 64-row K/V tiles per SM and launch the decode kernel runs as two CTAs per SM.
-constexpr long long kTwoCtaTilesPerSm = 0;
+constexpr long long kTwoCtaTilesPerSm = 64;   // measured: +8...+29 % below, -2 % above
 
 // Key tiles an item of `q_item` queries (item index qt) spans — the kernels' own arithmetic.
 int prefill_span_tiles(const PrefillTcArgs& t, int q_item, int qt) {
@@ -277,8 +278,11 @@ int prefill_splits(const PrefillTcArgs& t, int HD, int q_item, double tile_us, i
 // Host-side plan of one tensor-core prefill launch: which kernel, how the chunk is cut into
 // work items, how many key splits. Fills the shape fields of `t` (not the pointers). Pure
 // arithmetic: no device is touched.
+// Also decides the schedule of the two-tile kernel: equal spans (t.streamk, with `grid` CTAs) whenever
+// partial rows can be kept and no split count is forced; otherwise whole items or uniform key splits.
 void plan_prefill_tc(const hkv_geometry& g, int seq_new, int past_len, int sm_count, bool have_ws,
-                     PrefillTcArgs& t, int& pair, int& min_span, std::vector<double>& scratch) {
+                     PrefillTcArgs& t, int& pair, int& min_span, int& grid, int& max_parts,
+                     std::vector<double>& scratch) {
     const int G = g.num_heads / g.num_kv_heads, HD = g.head_dim;
     t.HD = HD;
     t.ring = g.layout == HKV_LAYOUT_RING ? 1 : 0;
@@ -300,9 +304,47 @@ void plan_prefill_tc(const hkv_geometry& g, int seq_new, int past_len, int sm_co
     const int HDS = prefill_tc_staged_hd(HD);
     double tile_us = pair ? 0.85 + 0.85 * HDS / 128.0 : 0.60 + 0.95 * HDS / 128.0;   // per 128-row key tile of an item
     if (prefill_tc_keys(HD) == 64) tile_us *= 0.55;                                   // half-height tiles
-    t.splits = prefill_splits(t, HD, q_item, tile_us, sm_count, have_ws, g.tune_prefill_splits, scratch);
     min_span = 1 << 30;
-    for (int qt = 0; qt < t.n_qtiles; ++qt) min_span = std::min(min_span, prefill_span_tiles(t, q_item, qt));
+    int max_span = 0;
+    long long total_tiles = 0;
+    for (int qt = 0; qt < t.n_qtiles; ++qt) {
+        const int n = prefill_span_tiles(t, q_item, qt);
+        min_span = std::min(min_span, n);
+        max_span = std::max(max_span, n);
+        total_tiles += n;
+    }
+    total_tiles *= t.KVH;
+    t.streamk = 0;
+    t.part_stride = 1;
+    t.row_parts = nullptr;
+    if (pair && have_ws && g.tune_prefill_splits == 0 && t.n_qtiles <= kPf2MaxPairs) {
+        // Equal spans: every CTA takes total_tiles / grid consecutive key tiles. An item of n tiles
+        // then falls into at most ceil(n / span) + 1 spans; the workspace holds kPrefillMaxSplits
+        // partial rows per query, so the grid shrinks until the longest item is cut into that many at most.
+        long long gsz = std::min<long long>(sm_count, total_tiles);
+        while (gsz > 1 && (max_span * gsz + total_tiles - 1) / total_tiles + 1 > kPrefillMaxSplits) --gsz;
+        // Exact count for that grid (the bound above is loose by one): replay the cuts.
+        int worst = 1;
+        long long P = 0;
+        for (int qt = t.n_qtiles - 1; qt >= 0; --qt) {
+            const int n = prefill_span_tiles(t, q_item, qt);
+            for (int kvh = 0; kvh < t.KVH; ++kvh, P += n)
+                worst = std::max(worst, prefill_span_owner(P + n - 1, total_tiles, (int)gsz) - prefill_span_owner(P, total_tiles, (int)gsz) + 1);
+        }
+        if (worst <= kPrefillMaxSplits) {
+            t.streamk = 1;
+            t.splits = 1;
+            t.part_stride = kPrefillMaxSplits;
+            grid = (int)gsz;
+            max_parts = worst;
+            return;
+        }
+    }
+    t.splits = prefill_splits(t, HD, q_item, tile_us, sm_count, have_ws, g.tune_prefill_splits, scratch);
+    t.part_stride = t.splits;
+    const long long items = (long long)t.n_qtiles * t.KVH * t.splits;
+    grid = items < sm_count ? (int)items : sm_count;
+    max_parts = t.splits;
 }
 
 // Geometries the tensor-core prefill kernels take: head_dim 64, 96, 128, 256; any group up to 128;
@@ -672,6 +714,8 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
                           (geometry->head_dim + 2) * sizeof(float);
         e = cudaMalloc(&c->prefill_ws, nb);
         if (e != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(prefill workspace)");
+        e = cudaMalloc(&c->prefill_row_parts, sizeof(int) * (size_t)geometry->max_seq_new * geometry->num_kv_heads);
+        if (e != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(prefill row counts)");
     }
     c->workspace_bytes = workspace_bytes_for(*geometry, c->max_chunks);
     e = cudaMalloc(&c->workspace, c->workspace_bytes);
@@ -686,6 +730,7 @@ int hkv_ctx_destroy(hkv_ctx* c) {
     if (c->d_status) cudaFree(c->d_status);
     if (c->prefill_ws) cudaFree(c->prefill_ws);
     if (c->prefill_counter) cudaFree(c->prefill_counter);
+    if (c->prefill_row_parts) cudaFree(c->prefill_row_parts);
     if (c->st_q) cudaFree(c->st_q);
     if (c->st_k) cudaFree(c->st_k);
     if (c->st_v) cudaFree(c->st_v);
@@ -847,10 +892,12 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
         PrefillTcArgs t;
         t.out = (__half*)out;
         t.status = c->d_status;
-        int pair = 0, min_span = 0;
+        int pair = 0, min_span = 0, grid = 0, max_parts = 0;
         plan_prefill_tc(g, seq_new, past_len, c->sm_count, c->prefill_ws != nullptr && seq_new <= g.max_seq_new, t, pair,
-                        min_span, c->plan_scratch);
-        if (t.splits > min_span) return fail(c, HKV_ERR_INVALID_ARG, "prefill: internal plan error (a key split would be empty)");
+                        min_span, grid, max_parts, c->plan_scratch);
+        if (t.splits > min_span || grid < 1 || max_parts > kPrefillMaxSplits)
+            return fail(c, HKV_ERR_INVALID_ARG, "prefill: internal plan error (an empty key split or too many parts)");
+        if (t.streamk) t.row_parts = c->prefill_row_parts;
         t.scale_log2 = scale * 1.4426950408889634f;
         t.part = c->prefill_ws;
         // Boxes are 64 halfs wide; a head_dim of 96 takes two, the second reaching past the tensor's
@@ -873,8 +920,6 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
             st = encode_f16_sw128(c, v_cache, 4, dims, strides, box, &mv);
             if (st) return st;
         }
-        const long long items = (long long)t.n_qtiles * g.num_kv_heads * t.splits;
-        const int grid = items < c->sm_count ? (int)items : c->sm_count;
         t.item_counter = c->prefill_counter;
         cudaStream_t st = (cudaStream_t)stream;
         if (pair) {
@@ -889,11 +934,12 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
             else if (HDS == 128) hkv_prefill_tc_kernel<128, 128><<<grid, kPfThreads, smem, st>>>(mq, mk, mv, t);
             else hkv_prefill_tc_kernel<256, 64><<<grid, kPfThreads, smem, st>>>(mq, mk, mv, t);
         }
-        if (t.splits > 1) {
-            // merge the key-range partials of every (query, head)
+        if (t.splits > 1 || (t.streamk && max_parts > 1)) {
+            // merge the key-range partials of every (query, head) that has more than one
             const long long rows = (long long)seq_new * g.num_heads;
             const unsigned cgrid = (unsigned)((rows + 7) / 8);
-            hkv_prefill_combine_kernel<<<cgrid, 256, 0, st>>>(c->prefill_ws, (__half*)out, rows, g.num_heads, HD, t.splits);
+            hkv_prefill_combine_kernel<<<cgrid, 256, 0, st>>>(c->prefill_ws, (__half*)out, rows, g.num_heads, HD, t.splits,
+                                                             t.part_stride, t.row_parts, G);
         }
         const cudaError_t e = cudaPeekAtLastError();
         return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "prefill launch");
@@ -1087,12 +1133,12 @@ int hkv_plan_prefill(const hkv_geometry* g, int32_t seq_new, int32_t past_len, i
         return HKV_OK;
     }
     PrefillTcArgs t{};
-    int pair = 0, min_span = 0;
+    int pair = 0, min_span = 0, grid = 0, max_parts = 0;
     std::vector<double> scratch;
-    plan_prefill_tc(*g, seq_new, past_len, sm_count, g->max_seq_new >= seq_new, t, pair, min_span, scratch);
+    plan_prefill_tc(*g, seq_new, past_len, sm_count, g->max_seq_new >= seq_new, t, pair, min_span, grid, max_parts, scratch);
     if (tiles_in_flight) *tiles_in_flight = pair ? 2 : 1;
-    if (items) *items = t.n_qtiles * t.KVH * t.splits;
-    if (splits) *splits = t.splits;
+    if (items) *items = t.streamk ? grid : t.n_qtiles * t.KVH * t.splits;
+    if (splits) *splits = t.streamk ? 0 : t.splits;
     if (min_span_tiles) *min_span_tiles = min_span;
     return HKV_OK;
 }

@@ -51,6 +51,12 @@ struct PrefillTcArgs {
     int splits;
     float* part;
     int* item_counter;   // two-tile kernel: zeroed before the launch; items beyond the first of each CTA come from it
+    // Equal-span schedule of the two-tile kernel: items are cut where the spans fall, so the number of
+    // partial rows differs from row to row; each (query, kv head) records its count in row_parts and
+    // partial p of query q sits at part[(q * part_stride + p) ...].
+    int streamk;
+    int part_stride;
+    int* row_parts;      // [S_new][KVH] or null
 };
 
 constexpr int kPfRows = 128;   // M of the MMA = rows of a query tile
@@ -584,16 +590,23 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 // Merge of the key-range partials written by the kernel above: one warp per (query, head) row,
 // each lane HD/32 output dimensions. The partial rows are [o(HD), m (log2 domain), l] in fp32.
 // ---------------------------------------------------------------------------
+// With `row_parts` the count of partials is read per (query, kv head) — rows with a single part were
+// written in final form by the attention kernel and are left alone.
 __global__ void __launch_bounds__(256) hkv_prefill_combine_kernel(const float* __restrict__ part,
                                                                   __half* __restrict__ out, long long rows,
-                                                                  int H, int HD, int splits) {
+                                                                  int H, int HD, int splits, int part_stride,
+                                                                  const int* __restrict__ row_parts, int G) {
     const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (row >= rows) return;
     const int lane = threadIdx.x & 31;
     const long long qi = row / H;
     const int head = (int)(row % H);
+    if (row_parts) {
+        splits = row_parts[qi * (H / G) + head / G];
+        if (splits <= 1) return;
+    }
     const long long stride = (long long)H * (HD + 2);
-    const float* base = part + (qi * splits * H + head) * (HD + 2);
+    const float* base = part + (qi * part_stride * H + head) * (HD + 2);
     float M = kNegBig;
     for (int sp = 0; sp < splits; ++sp) M = fmaxf(M, __ldg(base + sp * stride + HD));
     // lane l takes the dimension pairs 2l, 2l + 64, ... (head_dim is even; rows are 8-byte aligned)

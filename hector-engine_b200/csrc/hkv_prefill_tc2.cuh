@@ -43,8 +43,16 @@ constexpr int kPf2Threads = 384;
 constexpr int kPf2EmuOf8 = HKV_PF2_EMU;   // pairs of every 8 whose exp2 runs on the FMA pipe
 
 
+constexpr int kPf2MaxPairs = 1024;   // tile pairs of a chunk the equal-span schedule can tabulate (36 864 queries at group 7)
+
 __host__ __device__ constexpr size_t prefill_tc2_smem_bytes(int HD) {
-    return 1024 + (size_t)(2 + kPf2KStages + kPf2VStages) * kPfRows * HD * 2 + 32 * 8 + 64;
+    return 1024 + (size_t)(2 + kPf2KStages + kPf2VStages) * kPfRows * HD * 2 + 32 * 8 + 16 + 4 * 8 * 4 + (kPf2MaxPairs + 1) * 4 + 16;
+}
+
+// CTA that owns work unit x when W units are cut into `grid` equal contiguous spans with
+// boundaries floor(W * c / grid): the largest c whose boundary is <= x.
+__host__ __device__ inline int prefill_span_owner(long long x, long long W, int grid) {
+    return (int)(((x + 1) * grid + W - 1) / W - 1);
 }
 
 // tcgen05.wait::ld that also names the registers of the load it completes, so that no use of
@@ -145,12 +153,18 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const uint32_t B_PFULL = bar0 + 96;     // [group]
     const uint32_t B_OFULL = bar0 + 112;    // [group] last P·V of an item has completed
     const uint32_t B_DONE = bar0 + 128;
-    // Work queue: the producer takes items off a global counter (whichever CTA is free takes the
-    // next, longest first: greedy balance instead of a fixed deal) and hands each index to the
-    // other roles through four shared-memory slots.
-    const uint32_t B_QF = bar0 + 144;       // [4] slot holds an item index (or -1 = no more work)
+    // Work queue: the producer decides what the CTA works on and hands each piece of work to the
+    // other roles through four shared-memory slots as a descriptor
+    //   {pair of query tiles, kv head, first key tile, key tiles, part index, parts of the item}.
+    // Two schedules: (a) whole items (or equal key-range splits of them) taken off a global counter,
+    // longest first — whichever CTA is free takes the next; (b) equal spans: all key tiles of all items
+    // form one line, cut into gridDim.x equal contiguous spans, so every CTA does the same number of
+    // tile steps whatever the number of items; an item that straddles a cut is finished by two (or
+    // more) CTAs, each writing a partial row that the merge kernel combines.
+    const uint32_t B_QF = bar0 + 144;       // [4] slot holds a descriptor (first word -1 = no more work)
     const uint32_t B_QE = bar0 + 176;       // [4] slot read by the MMA issuer and the 8 softmax warps
-    volatile int* q_items = reinterpret_cast<volatile int*>(tmem_slot + 4);   // [4]
+    volatile int* q_items = reinterpret_cast<volatile int*>(tmem_slot + 4);   // [4][8]
+    int* pre = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 4 + 32));   // [n_qtiles + 1] (equal spans)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
@@ -190,24 +204,41 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     asm volatile("setmaxnreg.dec.sync.aligned.u32 120;");
     if (warp == 8) {
         // ------------------------------ TMA producer ------------------------------
+        const int n_pairs = a.n_qtiles;
+        if (a.streamk) {
+            // pre[j] = key tiles of the pairs before j in processing order (pair n-1-j: longest first)
+            int carry = 0;
+            for (int j0 = 0; j0 < n_pairs; j0 += 32) {
+                const int j = j0 + lane;
+                int kt0, v = 0;
+                if (j < n_pairs) prefill_item_tiles(a, QT2, kPfKeys, n_pairs - 1 - j, kt0, v);
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int u = __shfl_up_sync(0xffffffffu, v, o);
+                    if (lane >= o) v += u;
+                }
+                if (j < n_pairs) pre[j + 1] = carry + v;
+                carry += __shfl_sync(0xffffffffu, v, 31);
+            }
+            if (lane == 0) pre[0] = 0;
+            __syncwarp();
+        }
         if (elect_one()) {
             uint32_t gt = 0, it = 0, q_it = 0, qk = 0;
             bool ok = true, q_pending = false;
-            auto publish = [&](int item) -> bool {
+            auto publish = [&](int qt, int kvh, int kt_lo, int nt, int part, int nparts) -> bool {
                 const uint32_t slot = qk & 3;
                 if (qk >= 4 && !mbar_wait(B_QE + 8 * slot, ((qk >> 2) - 1) & 1, a.status)) return false;
-                q_items[slot] = item;
+                volatile int* d = q_items + slot * 8;
+                d[0] = qt; d[1] = kvh; d[2] = kt_lo; d[3] = nt; d[4] = part; d[5] = nparts;
                 mbar_arrive(B_QF + 8 * slot);
                 ++qk;
                 return true;
             };
-            // first item = this CTA's index, then whatever the shared counter hands out
-            for (int item = blockIdx.x; item < n_items && ok; item = (int)gridDim.x + atomicAdd(a.item_counter, 1), ++it) {
-                if (!publish(item)) { ok = false; break; }
-                int qt, kvh, sp, kt_lo, nt;
-                decode_item(item, qt, kvh, sp);
-                tile_span(qt, sp, kt_lo, nt);
-                if (!mbar_wait(B_QEMPTY, (it & 1) ^ 1, a.status)) { ok = false; break; }
+            // One piece of work: announce it, load its two query tiles, stream its K/V tiles.
+            auto run_piece = [&](int qt, int kvh, int kt_lo, int nt, int part, int nparts) {
+                if (!publish(qt, kvh, kt_lo, nt, part, nparts)) { ok = false; return; }
+                if (!mbar_wait(B_QEMPTY, (it & 1) ^ 1, a.status)) { ok = false; return; }
                 mbar_expect_tx(B_QFULL, (uint32_t)(2 * NCH * a.QT * a.G * 128));
 #pragma unroll
                 for (int t2 = 0; t2 < 2; ++t2)
@@ -220,7 +251,7 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 for (int t = 0; t < nt; ++t, ++gt) {
                     const int row = prefill_tile_row(a, (kt_lo + t) * kPfKeys);
                     const uint32_t ks = gt % kPf2KStages, ku = gt / kPf2KStages;
-                    if (!mbar_wait(B_KEMPTY + 8 * ks, (ku & 1) ^ 1, a.status)) { ok = false; break; }
+                    if (!mbar_wait(B_KEMPTY + 8 * ks, (ku & 1) ^ 1, a.status)) { ok = false; return; }
                     mbar_expect_tx(B_KFULL + 8 * ks, TILE_BYTES);
 #pragma unroll
                     for (int c = 0; c < NCH; ++c)
@@ -230,7 +261,7 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     if (!mbar_wait(B_VEMPTY + 8 * vs, (vu & 1) ^ 1, a.status)) {
                         mbar_wait(B_KFULL + 8 * ks, ku & 1, a.status);   // the K copy above is in flight
                         ok = false;
-                        break;
+                        return;
                     }
                     mbar_expect_tx(B_VFULL + 8 * vs, TILE_BYTES);
 #pragma unroll
@@ -238,8 +269,49 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                         tma_load_4d(v_smem + vs * TILE_BYTES + c * CHUNK_BYTES, &tm_v, B_VFULL + 8 * vs, c * 64, kvh,
                                     row, 0);
                 }
+                ++it;
+            };
+            if (a.streamk) {
+                // this CTA's span [u0, u1) of the line of all key tiles (items in processing order:
+                // pair j, kv head fastest; item (j, kvh) starts at KVH * pre[j] + kvh * T(j))
+                const long long W = (long long)pre[n_pairs] * a.KVH;
+                const long long u0 = W * blockIdx.x / gridDim.x, u1 = W * (blockIdx.x + 1) / gridDim.x;
+                if (u0 < u1) {
+                    int lo = 0, hi = n_pairs - 1;
+                    while (lo < hi) {
+                        const int mid = (lo + hi + 1) >> 1;
+                        if ((long long)a.KVH * pre[mid] <= u0) lo = mid; else hi = mid - 1;
+                    }
+                    int j = lo, T = pre[j + 1] - pre[j];
+                    const long long rem = u0 - (long long)a.KVH * pre[j];
+                    int kvh = (int)(rem / T), off = (int)(rem % T);
+                    for (long long u = u0; u < u1 && ok;) {
+                        const long long left = u1 - u;
+                        const int nt = (long long)(T - off) < left ? T - off : (int)left;
+                        const long long P = (long long)a.KVH * pre[j] + (long long)kvh * T;
+                        const int c_first = prefill_span_owner(P, W, (int)gridDim.x);
+                        const int c_last = prefill_span_owner(P + T - 1, W, (int)gridDim.x);
+                        int kt0, tdummy;
+                        prefill_item_tiles(a, QT2, kPfKeys, n_pairs - 1 - j, kt0, tdummy);
+                        run_piece(n_pairs - 1 - j, kvh, kt0 + off, nt, (int)blockIdx.x - c_first, c_last - c_first + 1);
+                        u += nt;
+                        off = 0;
+                        if (++kvh == a.KVH) {
+                            kvh = 0;
+                            if (++j < n_pairs) T = pre[j + 1] - pre[j];
+                        }
+                    }
+                }
+            } else {
+                // first item = this CTA's index, then whatever the shared counter hands out
+                for (int item = blockIdx.x; item < n_items && ok; item = (int)gridDim.x + atomicAdd(a.item_counter, 1)) {
+                    int qt, kvh, sp, kt_lo, nt;
+                    decode_item(item, qt, kvh, sp);
+                    tile_span(qt, sp, kt_lo, nt);
+                    run_piece(qt, kvh, kt_lo, nt, sp, a.splits);
+                }
             }
-            publish(-1);   // no more work (also after a wait that ran out: the other roles leave at once)
+            publish(-1, 0, 0, 0, 0, 0);   // no more work (also after a wait that ran out: the other roles leave at once)
             // drain this thread's outstanding copies before the CTA retires (tiles 0..gt-1 were issued)
             if (q_pending) mbar_wait(B_QFULL, q_it & 1, a.status);
             for (uint32_t i = 1; i <= (uint32_t)kPf2KStages && i <= gt; ++i) {
@@ -286,12 +358,9 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             };
             for (; ok; ++it) {
                 if (!queue_wait(it)) { ok = false; break; }
-                const int item = q_items[it & 3];
+                const int qt = q_items[(it & 3) * 8], nt = q_items[(it & 3) * 8 + 3];
                 mbar_arrive(B_QE + 8 * (it & 3));
-                if (item < 0) break;
-                int qt, kvh, sp, kt_lo, nt;
-                decode_item(item, qt, kvh, sp);
-                tile_span(qt, sp, kt_lo, nt);
+                if (qt < 0) break;
                 if (!mbar_wait(B_QFULL, it & 1, a.status) ||
                     !mbar_wait(B_KFULL + 8 * (gt % kPf2KStages), (gt / kPf2KStages) & 1, a.status)) { ok = false; break; }
                 tc_fence_after();
@@ -343,13 +412,11 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         for (uint32_t qk = 0; ok; ++qk) {
             ok = __all_sync(0xffffffffu, queue_wait(qk));
             if (!ok) break;
-            const int item = q_items[qk & 3];
+            const volatile int* dsc = q_items + (qk & 3) * 8;
+            const int qt = dsc[0], kvh = dsc[1], kt_lo = dsc[2], nt = dsc[3], part = dsc[4], nparts = dsc[5];
             __syncwarp();
             if (lane == 0) mbar_arrive(B_QE + 8 * (qk & 3));
-            if (item < 0) break;
-            int qt, kvh, sp, kt_lo, nt;
-            decode_item(item, qt, kvh, sp);
-            tile_span(qt, sp, kt_lo, nt);
+            if (qt < 0) break;
             const int qi = qt * QT2 + grp * a.QT + ql;
             const bool row_valid = ql < a.QT && qi < a.S_new;
             const int qpos = a.past_len + qi;
@@ -465,8 +532,10 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             float* prow = nullptr;
             __half* op = nullptr;
             if (row_valid) {
-                if (a.splits > 1) prow = a.part + (((long long)qi * a.splits + sp) * a.H + (long long)kvh * a.G + g) * (a.HD + 2);
+                if (nparts > 1) prow = a.part + (((long long)qi * a.part_stride + part) * a.H + (long long)kvh * a.G + g) * (a.HD + 2);
                 else op = a.out + ((long long)qi * a.H + (long long)kvh * a.G + g) * a.HD;
+                // how many partial rows the merge kernel finds for this (query, kv head)
+                if (a.row_parts && part == 0 && g == 0) a.row_parts[(long long)qi * a.KVH + kvh] = nparts;
             }
 #pragma unroll
             for (int c = 0; c < HD / 32; ++c) {

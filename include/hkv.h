@@ -276,8 +276,12 @@ int hkv_plan_sequence(const hkv_geometry* geometry, int32_t total_seq, int32_t c
 
 /* Plan of one hkv_prefill_attention call on a device with `sm_count` SMs (host arithmetic, no
  * device needed): query tiles in flight per CTA (2 or 1 for the tensor-core kernels, 0 = SIMT
- * kernel), number of work items, key-range splits per item and the shortest key span (in
- * 128-row tiles) of any item. splits <= min_span_tiles always holds: no split is ever empty. */
+ * kernel), number of work items, key-range splits per item and the shortest key span (in key
+ * tiles: 128 rows, 64 for head_dim 256) of any item. splits <= min_span_tiles always holds: no
+ * split is ever empty. *splits == 0 reports the equal-span schedule of the two-tile kernel (taken
+ * whenever the context has a partial-row workspace for the chunk and no split count is forced):
+ * all key tiles of all items form one line that is cut into *items equal spans, one per CTA, and an
+ * item that straddles a cut is finished by the CTAs on either side (at most four per item). */
 int hkv_plan_prefill(const hkv_geometry* geometry, int32_t seq_new, int32_t past_len, int32_t sm_count,
                      int32_t* tiles_in_flight, int32_t* items, int32_t* splits, int32_t* min_span_tiles);
 

@@ -207,10 +207,16 @@ def test_prefill_plan_never_leaves_a_key_split_empty(hkv):
     tile that is never loaded."""
     # the headline shape: long pasts get split (148 SMs, 228 pair items x 4 kv heads... ), short ones do not
     g = hkv.Geometry(num_heads=28, num_kv_heads=4, head_dim=128, slots=131072, max_seq_new=2048)
+    # with a workspace for partial rows the two-tile kernel takes the equal-span schedule: one span per SM
     tif, items, splits, span = _plan_prefill(hkv, g, 2048, 129024)
-    assert tif == 2 and splits > 1 and splits <= span and items == 57 * 4 * splits
+    assert (tif, items, splits) == (2, 148, 0)
     tif, items, splits, span = _plan_prefill(hkv, g, 2048, 0)
-    assert tif == 2 and splits == 1 and span == 1
+    assert (tif, items, splits) == (2, 148, 0) and span == 1
+    # a forced split count keeps the uniform key splits of whole items
+    gf = hkv.Geometry(num_heads=28, num_kv_heads=4, head_dim=128, slots=131072, max_seq_new=2048, tune_prefill_splits=3)
+    assert _plan_prefill(hkv, gf, 2048, 129024)[:3] == [2, 57 * 4 * 3, 3]
+    # four pairs of tiles (2 + 3 + 3 + 3 key tiles) x 4 kv heads: 44 tiles in all, so 44 spans at most
+    assert _plan_prefill(hkv, g, 144, 200)[:3] == [2, 44, 0]
     # a chunk that fits one query tile takes the one-tile kernel
     assert _plan_prefill(hkv, g, 18, 5000)[0] == 1 and _plan_prefill(hkv, g, 19, 5000)[0] == 2
     # without a workspace for partials there is no split
@@ -244,8 +250,10 @@ def test_prefill_plan_never_leaves_a_key_split_empty(hkv):
         win = int(rng.choice([0, int(rng.integers(1, 5000))]))
         gg = hkv.Geometry(num_heads=G * KVH, num_kv_heads=KVH, head_dim=int(rng.choice([64, 96, 128, 256])),
                           slots=past + S + int(rng.integers(0, 300)), window_size=win, max_seq_new=S)
-        tif, items, splits, span = _plan_prefill(hkv, gg, S, past, sms=int(rng.choice([132, 148])))
-        assert 1 <= splits <= min(span, 4) and tif in (1, 2) and items >= 1
+        sms = int(rng.choice([132, 148]))
+        tif, items, splits, span = _plan_prefill(hkv, gg, S, past, sms=sms)
+        assert tif in (1, 2) and items >= 1
+        assert (splits == 0 and tif == 2 and items <= sms) or 1 <= splits <= min(span, 4)
 
 
 def test_preferred_prefill_chunk_makes_items_a_multiple_of_the_sms(hkv):
@@ -255,9 +263,10 @@ def test_preferred_prefill_chunk_makes_items_a_multiple_of_the_sms(hkv):
     assert lib.hkv_preferred_prefill_chunk(C.byref(gc), 148, 2048) == 1332     # 37 pairs x 36 queries
     assert lib.hkv_preferred_prefill_chunk(C.byref(gc), 148, 3000) == 2664
     assert lib.hkv_preferred_prefill_chunk(C.byref(gc), 148, 100) == 1332      # never below one round
+    g1 = hkv.Geometry(num_heads=28, num_kv_heads=4, head_dim=128, slots=131072, max_seq_new=4096, tune_prefill_splits=1)
     for target in (1332, 2664, 3996):
-        tif, items, splits, span = _plan_prefill(hkv, g, target, 30720)
-        assert tif == 2 and (items // splits) % 148 == 0
+        tif, items, splits, span = _plan_prefill(hkv, g1, target, 30720)
+        assert tif == 2 and splits == 1 and items % 148 == 0
     mha = hkv.Geometry(num_heads=8, num_kv_heads=8, head_dim=64, slots=4096, max_seq_new=4096)
     assert lib.hkv_preferred_prefill_chunk(C.byref(mha.to_c()), 148, 10000) == 9472   # 37 pairs x 256
     simt = hkv.Geometry(num_heads=32, num_kv_heads=32, head_dim=80, slots=4096)
