@@ -47,8 +47,12 @@ struct hkv_ctx {
     int kernel = HKV_KERNEL_GENERIC;  // preferred kernel
     int tma_groups = 2;
     TmaSmemPlan plan{0, 0};
-    float* workspace = nullptr;
+    float* workspace = nullptr;     // chunked split-K partials (any-geometry kernel)
     size_t workspace_bytes = 0;
+    float* span_ws = nullptr;       // equal-span partials of the TMA kernel: [2*SMs + batch][H][HD+2]
+    int* span_gpre = nullptr;       // [batch + 1] tile table the TMA kernel leaves for the merge
+    int span_gang = 1;              // CTAs sharing a span (gcd of the kv heads and the grid)
+    int tma_grid = 0;               // persistent grid of the TMA kernel
     int32_t* d_status = nullptr;
     bool ready = false;             // hkv_ctx_create completed
     int pos_stride = 1;             // 0 with HKV_FLAG_SCALAR_POSITION
@@ -229,20 +233,21 @@ int prefill_span_tiles(const PrefillTcArgs& t, int q_item, int qt) {
 // output) and adds what the split costs (fp32 partials written and read back by the merge kernel).
 // Costs are in microseconds, from timings of the kernels on B200.
 int prefill_splits(const PrefillTcArgs& t, int HD, int q_item, double tile_us, int sm_count, bool have_ws,
-                   int tune_splits, std::vector<double>& load) {
-    if (!have_ws) return 1;
+                   int tune_splits, std::vector<double>& load, double* cost_out = nullptr) {
+    if (cost_out) *cost_out = 1.0e30;
+    const int max_s = have_ws ? kPrefillMaxSplits : 1;
     // No split may be empty: the split count is bounded by the SHORTEST span of any item. (With a
     // sliding window the spans differ by one tile from item to item, depending on how the window
     // falls on the tile grid; without one the first item has the shortest.)
     int min_span_tiles = 1 << 30;
     for (int qt = 0; qt < t.n_qtiles; ++qt) min_span_tiles = std::min(min_span_tiles, prefill_span_tiles(t, q_item, qt));
-    if (tune_splits >= 1) return std::min(tune_splits, std::min(kPrefillMaxSplits, min_span_tiles));
+    if (tune_splits >= 1) return std::min(tune_splits, std::min(max_s, min_span_tiles));
     const double item_tiles = q_item > t.QT ? 5.0 : 6.0;
     const double row_bytes = (double)t.S_new * t.H * (HD + 2) * 4.0;
     int best = 1;
     double best_cost = 0.0;
     if (load.size() < (size_t)sm_count) load.resize((size_t)sm_count);   // grows once per context
-    for (int s = 1; s <= kPrefillMaxSplits && s <= min_span_tiles; ++s) {
+    for (int s = 1; s <= max_s && s <= min_span_tiles; ++s) {
         const long long items = (long long)t.n_qtiles * t.KVH * s;
         const int grid = items < sm_count ? (int)items : sm_count;
         // The one-tile kernel deals items round-robin: replay the deal. The two-tile kernel hands
@@ -272,6 +277,7 @@ int prefill_splits(const PrefillTcArgs& t, int HD, int q_item, double tile_us, i
         // efficiently than the model says, and the merge pass is pure overhead)
         if (s == 1 || cost < (greedy ? 0.90 : 0.97) * best_cost) { best = s; best_cost = cost; }
     }
+    if (cost_out) *cost_out = best_cost;
     return best;
 }
 
@@ -315,32 +321,66 @@ void plan_prefill_tc(const hkv_geometry& g, int seq_new, int past_len, int sm_co
     }
     total_tiles *= t.KVH;
     t.streamk = 0;
+    t.sk_whole = 0;
+    t.sk_grid = 0;
     t.part_stride = 1;
     t.row_parts = nullptr;
-    if (pair && have_ws && g.tune_prefill_splits == 0 && t.n_qtiles <= kPf2MaxPairs) {
-        // Equal spans: every CTA takes total_tiles / grid consecutive key tiles. An item of n tiles
-        // then falls into at most ceil(n / span) + 1 spans; the workspace holds kPrefillMaxSplits
-        // partial rows per query, so the grid shrinks until the longest item is cut into that many at most.
-        long long gsz = std::min<long long>(sm_count, total_tiles);
-        while (gsz > 1 && (max_span * gsz + total_tiles - 1) / total_tiles + 1 > kPrefillMaxSplits) --gsz;
-        // Exact count for that grid (the bound above is loose by one): replay the cuts.
-        int worst = 1;
-        long long P = 0;
+    double uniform_cost = 0.0;
+    t.splits = prefill_splits(t, HD, q_item, tile_us, sm_count, have_ws, g.tune_prefill_splits, scratch, &uniform_cost);
+    const long long n_items1 = (long long)t.n_qtiles * t.KVH;
+    // (Measured: with fewer items than SMs uniform key splits do as well; with K/V planes beyond the L2
+    // the spread start offsets of the spans cost the tile reuse that lockstep items get from it.)
+    const double plane_mb = 4.0 * prefill_kv_valid(t) * t.KVH * HD / 1.0e6;
+    if (pair && have_ws && g.tune_prefill_splits == 0 && t.n_qtiles <= kPf2MaxPairs && n_items1 > sm_count &&
+        n_items1 % sm_count != 0 && plane_mb <= 100.0) {
+        // Candidate: whole items for the full rounds of the grid, equal spans for the rest (items are
+        // processed longest first, so the rest are the shortest). The spans shrink to fewer CTAs until
+        // no item is cut into more parts than the workspace holds rows for.
+        const long long whole = (n_items1 / sm_count) * sm_count;
+        const double ov = 5.0;                       // tile steps a piece of work costs besides its key tiles
+        double sum_whole = 0.0;
+        long long tail_tiles = 0, idx = 0;
+        int tail_max = 0;
         for (int qt = t.n_qtiles - 1; qt >= 0; --qt) {
             const int n = prefill_span_tiles(t, q_item, qt);
-            for (int kvh = 0; kvh < t.KVH; ++kvh, P += n)
-                worst = std::max(worst, prefill_span_owner(P + n - 1, total_tiles, (int)gsz) - prefill_span_owner(P, total_tiles, (int)gsz) + 1);
+            for (int kvh = 0; kvh < t.KVH; ++kvh, ++idx) {
+                if (idx < whole) sum_whole += n + ov;
+                else { tail_tiles += n; tail_max = std::max(tail_max, n); }
+            }
         }
-        if (worst <= kPrefillMaxSplits) {
-            t.streamk = 1;
-            t.splits = 1;
-            t.part_stride = kPrefillMaxSplits;
-            grid = (int)gsz;
-            max_parts = worst;
-            return;
+        long long sg = std::min<long long>(sm_count, tail_tiles);
+        int worst = kPrefillMaxSplits + 1;
+        for (; sg >= 1; --sg) {
+            if ((tail_max * sg + tail_tiles - 1) / tail_tiles > kPrefillMaxSplits) continue;   // cheap lower bound first
+            worst = 1;
+            long long P = 0;
+            idx = 0;
+            for (int qt = t.n_qtiles - 1; qt >= 0 && worst <= kPrefillMaxSplits; --qt) {
+                const int n = prefill_span_tiles(t, q_item, qt);
+                for (int kvh = 0; kvh < t.KVH; ++kvh, ++idx) {
+                    if (idx < whole) continue;
+                    worst = std::max(worst, prefill_span_owner(P + n - 1, tail_tiles, (int)sg) - prefill_span_owner(P, tail_tiles, (int)sg) + 1);
+                    P += n;
+                }
+            }
+            if (worst <= kPrefillMaxSplits) break;
+        }
+        if (sg >= 1 && worst <= kPrefillMaxSplits) {
+            const double tail_rows_bytes = (double)(n_items1 - whole) / t.KVH * q_item * t.H * (HD + 2) * 4.0;
+            const double sk_cost = (sum_whole / sm_count + (double)tail_tiles / sg + 2.0 * ov) * tile_us +
+                                   4.0 + 2.0 * 2.0 * tail_rows_bytes / 3.0e6;   // partial rows out and back at ~3 TB/s
+            if (sk_cost < 0.95 * uniform_cost) {
+                t.streamk = 1;
+                t.splits = 1;
+                t.sk_whole = (int)whole;
+                t.sk_grid = (int)sg;
+                t.part_stride = kPrefillMaxSplits;
+                grid = sm_count;
+                max_parts = worst;
+                return;
+            }
         }
     }
-    t.splits = prefill_splits(t, HD, q_item, tile_us, sm_count, have_ws, g.tune_prefill_splits, scratch);
     t.part_stride = t.splits;
     const long long items = (long long)t.n_qtiles * t.KVH * t.splits;
     grid = items < sm_count ? (int)items : sm_count;
@@ -444,7 +484,8 @@ int launch_append(hkv_ctx* c, const void* k_new, const void* v_new, void* k_cach
 // Decode into the workspace; `fused` appends k_new/v_new at position total-1.
 int launch_decode(hkv_ctx* c, const void* q, const void* k_new, const void* v_new, void* k_cache,
                   void* v_cache, const int32_t* d_total, int pos_is_index, int host_len, float scale,
-                  cudaStream_t st) {
+                  cudaStream_t st, bool* used_tma) {
+    *used_tma = false;
     const hkv_geometry& g = c->g;
     if (!q || !k_cache || !v_cache) return fail(c, HKV_ERR_INVALID_ARG, "decode: null tensor");
     if (!aligned(q, 2) || !aligned(k_cache, 2) || !aligned(v_cache, 2))
@@ -462,6 +503,9 @@ int launch_decode(hkv_ctx* c, const void* q, const void* k_new, const void* v_ne
     a.k_cache_w = (__half*)k_cache;
     a.v_cache_w = (__half*)v_cache;
     a.part = c->workspace;
+    a.span_part = nullptr;
+    a.gpre = nullptr;
+    a.span_gang = 1;
     a.total = d_total;
     a.status = c->d_status;
     a.map = c->map;
@@ -491,11 +535,12 @@ int launch_decode(hkv_ctx* c, const void* q, const void* k_new, const void* v_ne
         const int nt = (c->G + 7) / 8;
         const int groups = c->tma_groups == 2 ? 2 : 1;
         TmaKernel kern = pick_tma(g.head_dim, nt, groups);
-        long long items = (long long)g.batch * c->max_chunks * g.num_kv_heads;
-        int grid = c->tma_groups == 1 ? 2 * c->sm_count : c->sm_count;   // persistent: one or two CTAs per SM
-        if (items < grid) grid = (int)items;
+        a.span_part = c->span_ws;
+        a.gpre = c->span_gpre;
+        a.span_gang = c->span_gang;
         const int threads = (groups * 4 + 1) * 32;
-        kern<<<grid, threads, c->plan.bytes, st>>>(maps->k, maps->v, a, c->plan.stages);
+        kern<<<c->tma_grid, threads, c->plan.bytes, st>>>(maps->k, maps->v, a, c->plan.stages);
+        *used_tma = true;
     } else {
         if (fused) {
             // generic path: append first (its own launch), then attend; the new row sits at
@@ -512,8 +557,11 @@ int launch_decode(hkv_ctx* c, const void* q, const void* k_new, const void* v_ne
 
 int launch_combine(hkv_ctx* c, const float* part, long long stride_b, long long stride_c,
                    const int32_t* d_total, int pos_is_index, int host_len, int fixed_count, void* out,
-                   float* out_partial, cudaStream_t st) {
+                   float* out_partial, cudaStream_t st, bool span = false) {
     CombineArgs a;
+    a.gpre = span ? c->span_gpre : nullptr;
+    a.span_spans = span ? c->tma_grid / c->span_gang : 0;
+    a.B = c->g.batch;
     a.part = part;
     a.stride_b = stride_b;
     a.stride_c = stride_c;
@@ -533,7 +581,9 @@ int launch_combine(hkv_ctx* c, const float* part, long long stride_b, long long 
     // kernel): with few (sequence, head) rows and many partials per row the merge is latency-bound
     // and the warp-dealt kernel wins (batch 1-8: +5 %); with many rows the one-thread-per-dimension
     // kernel does (batch 32-64: +2 % of the step).
-    const int most = fixed_count > 0 ? fixed_count : c->max_chunks;
+    // partials a row can have: the chunks of a full plane, or (equal spans) about spans / batch + 1
+    const int most = fixed_count > 0 ? fixed_count
+                     : span ? (c->tma_grid / c->span_gang) / c->g.batch + 1 : c->max_chunks;
     const long long rows = (long long)grid.x * grid.y;
     if (rows <= 2LL * c->sm_count && most > 8) hkv_combine_kernel<<<grid, kCombineThreads, 0, st>>>(a);
     else hkv_combine_few_kernel<<<grid, 128, 0, st>>>(a);
@@ -549,13 +599,14 @@ int decode_full(hkv_ctx* c, const void* q, const void* k_new, const void* v_new,
     const bool timed = c->prof_calls < c->prof_max;
     cudaEvent_t* ev = timed ? &c->prof_events[(size_t)c->prof_calls * 3] : nullptr;
     if (timed) cudaEventRecord(ev[0], st);
-    int stt = launch_decode(c, q, k_new, v_new, k_cache, v_cache, d_total, pos_is_index, host_len, scale, st);
+    bool used_tma = false;
+    int stt = launch_decode(c, q, k_new, v_new, k_cache, v_cache, d_total, pos_is_index, host_len, scale, st, &used_tma);
     if (stt) return stt;
     if (timed) cudaEventRecord(ev[1], st);
     const long long PW = c->g.head_dim + 2;
-    stt = launch_combine(c, c->workspace, (long long)c->max_chunks * c->g.num_heads * PW,
+    stt = launch_combine(c, used_tma ? c->span_ws : c->workspace, (long long)c->max_chunks * c->g.num_heads * PW,
                          (long long)c->g.num_heads * PW, d_total, pos_is_index, host_len, 0, out, out_partial,
-                         st);
+                         st, used_tma);
     if (stt) return stt;
     if (timed) {
         cudaEventRecord(ev[2], st);
@@ -720,6 +771,19 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
     c->workspace_bytes = workspace_bytes_for(*geometry, c->max_chunks);
     e = cudaMalloc(&c->workspace, c->workspace_bytes);
     if (e != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(workspace)");
+    if (c->kernel == HKV_KERNEL_TMA) {
+        // Equal-span schedule: one or two persistent CTAs per SM, in gangs that share a span with one
+        // share of the kv heads each; one partial row set per (span, sequence) piece.
+        c->tma_grid = (c->tma_groups == 1 ? 2 : 1) * sm;
+        int x = c->tma_grid, y = geometry->num_kv_heads;
+        while (y) { const int r = x % y; x = y; y = r; }
+        c->span_gang = x;    // gcd(grid, kv heads)
+        const size_t slots = (size_t)c->tma_grid / c->span_gang + geometry->batch;
+        e = cudaMalloc(&c->span_ws, slots * geometry->num_heads * (geometry->head_dim + 2) * sizeof(float));
+        if (e != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(span workspace)");
+        e = cudaMalloc(&c->span_gpre, sizeof(int) * ((size_t)geometry->batch + 1));
+        if (e != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(tile table)");
+    }
     c->ready = true;
     return HKV_OK;
 }
@@ -727,6 +791,8 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
 int hkv_ctx_destroy(hkv_ctx* c) {
     if (!c) return HKV_OK;
     if (c->workspace) cudaFree(c->workspace);
+    if (c->span_ws) cudaFree(c->span_ws);
+    if (c->span_gpre) cudaFree(c->span_gpre);
     if (c->d_status) cudaFree(c->d_status);
     if (c->prefill_ws) cudaFree(c->prefill_ws);
     if (c->prefill_counter) cudaFree(c->prefill_counter);
@@ -1272,6 +1338,9 @@ extern "C" int hkv_decode_attention_static(const hkv_geometry* geometry, const v
     a.k_cache_w = nullptr;
     a.v_cache_w = nullptr;
     a.part = static_cast<float*>(slot.scratch);
+    a.span_part = nullptr;
+    a.gpre = nullptr;
+    a.span_gang = 1;
     a.total = d_total_seq;
     a.status = nullptr;  // the SIMT kernel has no waits and never touches the status word
     a.map = make_map(g);
@@ -1301,6 +1370,9 @@ extern "C" int hkv_decode_attention_static(const hkv_geometry* geometry, const v
     c.pos_stride = a.pos_stride;
     c.host_len = 0;
     c.fixed_count = 0;
+    c.gpre = nullptr;
+    c.span_spans = 0;
+    c.B = g.batch;
     c.map = a.map;
     c.chunk_tiles = chunk_tiles;
     c.H = g.num_heads;

@@ -157,6 +157,11 @@ struct CombineArgs {
     int pos_stride;                // as DecodeArgs
     int host_len;
     int fixed_count;               // > 0: that many partials per row, whatever the length
+    // Equal-span schedule (span_spans > 0): sequence b's partials sit at slots span + b for the spans
+    // that overlap its tiles, found from the tile table the decode kernel left in gpre.
+    const int* gpre;               // [B+1]
+    int span_spans;                // spans the decode launch was given (grid / gang)
+    int B;
     SeqMap map;
     int chunk_tiles;
     int H, HD;
@@ -174,18 +179,29 @@ constexpr int kCombineThreads = kCombineWarps * 32;
 // through shared memory.
 __global__ void __launch_bounds__(kCombineThreads) hkv_combine_kernel(const CombineArgs a) {
     const int h = blockIdx.x, b = blockIdx.y;
-    const int n = a.fixed_count > 0
-                      ? a.fixed_count
-                      : num_chunks(a.map, length_of(a.total, a.pos_stride, a.pos_is_index, a.host_len, b),
-                                   a.chunk_tiles);
     const int PW = a.HD + 2;
-    const float* base = a.part + b * a.stride_b + (long long)h * PW;
+    int n;
+    const float* base;
+    long long stride_c = a.stride_c;
+    if (a.span_spans > 0) {
+        const int p0 = a.gpre[b], p1 = a.gpre[b + 1], W = a.gpre[a.B];
+        const int spans = span_count(W, a.span_spans);
+        const int first = p1 > p0 ? span_owner(p0, W, spans) : 0;
+        n = p1 > p0 ? span_owner(p1 - 1, W, spans) - first + 1 : 0;
+        stride_c = (long long)a.H * PW;
+        base = a.part + ((long long)(first + b) * a.H + h) * PW;
+    } else {
+        n = a.fixed_count > 0
+                ? a.fixed_count
+                : num_chunks(a.map, length_of(a.total, a.pos_stride, a.pos_is_index, a.host_len, b), a.chunk_tiles);
+        base = a.part + b * a.stride_b + (long long)h * PW;
+    }
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     __shared__ float s_red[kCombineWarps];
     __shared__ float s_acc[kCombineWarps][512];   // head_dim <= 512
     // M = max over partials
     float M = kNegBig;
-    for (int c = tid; c < n; c += kCombineThreads) M = fmaxf(M, base[c * a.stride_c + a.HD]);
+    for (int c = tid; c < n; c += kCombineThreads) M = fmaxf(M, base[c * stride_c + a.HD]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
     if (lane == 0) s_red[warp] = M;
@@ -202,7 +218,7 @@ __global__ void __launch_bounds__(kCombineThreads) hkv_combine_kernel(const Comb
     float L = 0.0f;
 #pragma unroll 4
     for (int c = warp; c < n; c += kCombineWarps) {   // unrolled: four rows' loads in flight per warp
-        const float* row = base + (long long)c * a.stride_c;
+        const float* row = base + (long long)c * stride_c;
         const float w = exp2f(row[a.HD] - M);
         L = fmaf(row[a.HD + 1], w, L);
 #pragma unroll
@@ -241,18 +257,29 @@ __global__ void __launch_bounds__(kCombineThreads) hkv_combine_kernel(const Comb
 // of the kernel above, which only pays when few rows each have many partials (small batches).
 __global__ void __launch_bounds__(128) hkv_combine_few_kernel(const CombineArgs a) {
     const int h = blockIdx.x, b = blockIdx.y;
-    const int n = a.fixed_count > 0
-                      ? a.fixed_count
-                      : num_chunks(a.map, length_of(a.total, a.pos_stride, a.pos_is_index, a.host_len, b),
-                                   a.chunk_tiles);
     const int PW = a.HD + 2;
-    const float* base = a.part + b * a.stride_b + (long long)h * PW;
+    int n;
+    const float* base;
+    long long stride_c = a.stride_c;
+    if (a.span_spans > 0) {
+        const int p0 = a.gpre[b], p1 = a.gpre[b + 1], W = a.gpre[a.B];
+        const int spans = span_count(W, a.span_spans);
+        const int first = p1 > p0 ? span_owner(p0, W, spans) : 0;
+        n = p1 > p0 ? span_owner(p1 - 1, W, spans) - first + 1 : 0;
+        stride_c = (long long)a.H * PW;
+        base = a.part + ((long long)(first + b) * a.H + h) * PW;
+    } else {
+        n = a.fixed_count > 0
+                ? a.fixed_count
+                : num_chunks(a.map, length_of(a.total, a.pos_stride, a.pos_is_index, a.host_len, b), a.chunk_tiles);
+        base = a.part + b * a.stride_b + (long long)h * PW;
+    }
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     __shared__ float s_red[4];
     __shared__ float s_w[128];
     // M = max over partials: the chunks are spread over the threads, so the loads overlap
     float M = kNegBig;
-    for (int c = tid; c < n; c += 128) M = fmaxf(M, base[c * a.stride_c + a.HD]);
+    for (int c = tid; c < n; c += 128) M = fmaxf(M, base[c * stride_c + a.HD]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
     if (lane == 0) s_red[warp] = M;
@@ -264,7 +291,7 @@ __global__ void __launch_bounds__(128) hkv_combine_few_kernel(const CombineArgs 
         const int nb = n - c0 < 128 ? n - c0 : 128;
         __syncthreads();
         if (tid < nb) {
-            const float* row = base + (long long)(c0 + tid) * a.stride_c;
+            const float* row = base + (long long)(c0 + tid) * stride_c;
             const float w = exp2f(row[a.HD] - M);
             s_w[tid] = w;
             L = fmaf(row[a.HD + 1], w, L);
@@ -276,7 +303,7 @@ __global__ void __launch_bounds__(128) hkv_combine_few_kernel(const CombineArgs 
             if (d < a.HD) {
                 float o = acc[i];
 #pragma unroll 8
-                for (int c = 0; c < nb; ++c) o = fmaf(base[(long long)(c0 + c) * a.stride_c + d], s_w[c], o);
+                for (int c = 0; c < nb; ++c) o = fmaf(base[(long long)(c0 + c) * stride_c + d], s_w[c], o);
                 acc[i] = o;
             }
         }

@@ -92,6 +92,15 @@ __host__ __device__ inline int num_chunks(const SeqMap& m, int total, int chunk_
     return (n_tiles + chunk_tiles - 1) / chunk_tiles;
 }
 
+// Equal-span schedule of the TMA decode kernel: the W tiles of a launch form one line that is cut
+// into `spans` equal contiguous pieces with boundaries floor(W * c / spans). Never more spans than
+// tiles, so that no span is empty.
+__host__ __device__ inline int span_count(int W, int spans_wanted) { return W < spans_wanted ? W : spans_wanted; }
+// The span that owns tile x: the largest c whose boundary is <= x.
+__host__ __device__ inline int span_owner(long long x, long long W, int spans) {
+    return (int)(((x + 1) * spans + W - 1) / W - 1);
+}
+
 // Arguments shared by the decode kernels.
 struct DecodeArgs {
     const __half* q;        // [B, H, HD]
@@ -101,7 +110,11 @@ struct DecodeArgs {
     const __half* v_new;
     __half* k_cache_w;      // writable aliases of the planes (fused append)
     __half* v_cache_w;
-    float* part;            // [B, max_chunks, H, HD+2]: o[HD], m (log2 domain), l
+    float* part;            // [B, max_chunks, H, HD+2]: o[HD], m (log2 domain), l (chunked schedule)
+    float* span_part;       // [spans + B, H, HD+2]: the same rows under the equal-span schedule, the
+                            //   piece of sequence b inside span s at slot s + b
+    int* gpre;              // [B+1] tiles before each sequence, written by the kernel for the merge
+    int span_gang;          // CTAs sharing a span, CTA m of the gang taking the kv heads m, m + gang, ...
     const int32_t* total;   // [B] attended length, or cache position when pos_is_index; null -> host_len
     int32_t* status;        // device status word
     SeqMap map;

@@ -7,9 +7,13 @@
 // query head of its group and issues 4-byte loads.
 //
 // Shape of the computation
-//   * Persistent grid (one CTA per SM). Work item = (sequence b, chunk of
-//     `chunk_tiles` 64-row tiles, KV head); items are dealt round-robin to CTAs with the
-//     KV head fastest, so neighbouring CTAs stream neighbouring bytes.
+//   * Persistent grid (one or two CTAs per SM) under an equal-span schedule: the 64-row tiles of all
+//     sequences of the batch form one line (the lengths are read on the device), cut into as many
+//     equal contiguous spans as there are gangs of CTAs. A gang is `span_gang` neighbouring CTAs that
+//     share a span, each taking its own KV heads — so the gang streams neighbouring bytes in step and
+//     every CTA of the launch does the same number of tile steps whatever the batch and the lengths
+//     are: no quantisation over the SMs, no tail, and a sequence is cut only where a span ends (one
+//     partial per (span, sequence) instead of one per fixed-size chunk).
 //   * Warp NCW (last) is the producer: one lane walks the CTA's item list and issues,
 //     per tile, HD/CW box loads for K and for V ([64 rows] x [CW halfs], 128- or 64-byte
 //     swizzle) into a ring of `stages` buffers. It runs ahead across item boundaries,
@@ -22,8 +26,10 @@
 //     Softmax over rows: per-head max via shuffles (xor 4, 8, 16), log2 domain.
 //     Output:  O^T[HD x 8 heads] += V_tile^T · P^T    (A = V^T via ldmatrix.trans,
 //     B = P^T obtained from the score fragment with movmatrix).
-//   * At the end of an item the consumer warps merge their (m, l, O) in shared memory and
-//     write one partial row per head; the combine kernel finishes the softmax.
+//   * At the end of a piece (the part of a sequence inside the span) the consumer warps merge
+//     their (m, l, O) in shared memory and write one partial row per head at slot span + sequence
+//     (distinct for every piece, as both only grow along the line); the combine kernel finds a
+//     sequence's partials from the same arithmetic and finishes the softmax.
 //   * Fused append: the warp that owns the row of the new token patches the staged tile
 //     from k_new/v_new and stores the row into the cache plane; rows that are staged but
 //     not attended (tail of the last tile, outside the window) are masked, and their V
@@ -106,14 +112,15 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
         tma_prefetch_desc(&tm_k);
         tma_prefetch_desc(&tm_v);
     }
-    // prefix[b] = work chunks of the sequences before b. Warp 0 scans the batch 32 sequences at a
-    // time with shuffles (a serial scan by one thread costs a microsecond at batch 64, in front of
-    // the first load of every launch).
+    // prefix[b] = tiles of the sequences before b. Warp 0 scans the batch 32 sequences at a time
+    // with shuffles (a serial scan by one thread costs a microsecond at batch 64, in front of the
+    // first load of every launch).
     if (warp == 0) {
         int carry = 0;
         for (int b0 = 0; b0 < a.B; b0 += 32) {
             const int b = b0 + lane;
-            int v = b < a.B ? num_chunks(a.map, attended_len(a, b), a.chunk_tiles) : 0;
+            int v = 0, tl;
+            if (b < a.B) tile_range(a.map, attended_len(a, b), tl, v);
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const int u = __shfl_up_sync(0xffffffffu, v, o);
@@ -125,41 +132,61 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
         if (lane == 0) prefix[0] = 0;
     }
     __syncthreads();
-    const int n_items = prefix[a.B] * a.KVH;
+    // This CTA's span of the line and its share of the KV heads.
+    const int W = prefix[a.B];
+    if (blockIdx.x == 0)   // the combine kernel finds each sequence's partials from the same table
+        for (int b = tid; b <= a.B; b += blockDim.x) a.gpre[b] = prefix[b];
+    const int GS = a.span_gang;
+    const int NS = span_count(W, (int)gridDim.x / GS);
+    const int span = blockIdx.x / GS, member = blockIdx.x % GS;
+    int u0 = 0, u1 = 0, b_first = 0;
+    if (span < NS) {
+        u0 = (int)((long long)W * span / NS);
+        u1 = (int)((long long)W * (span + 1) / NS);
+        int lo = 0, hi = a.B - 1;          // the sequence that holds tile u0
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (prefix[mid] <= u0) lo = mid; else hi = mid - 1;
+        }
+        b_first = lo;
+    }
 
     if (warp == NCW) {
         // ------------------------------ producer ------------------------------
         if (lane == 0) {
-            int stage = 0, round = 0, issued = 0, b = 0;
+            int stage = 0, round = 0, issued = 0;
             bool ok = true;
-            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-                const int kvh = item % a.KVH, j = item / a.KVH;
-                while (prefix[b + 1] <= j) ++b;
-                const int chunk = j - prefix[b];
-                int tile_lo, n_tiles;
-                tile_range(a.map, attended_len(a, b), tile_lo, n_tiles);
-                const int t0 = tile_lo + chunk * a.chunk_tiles;
-                int nt = tile_lo + n_tiles - t0;
-                if (nt > a.chunk_tiles) nt = a.chunk_tiles;
-                for (int t = 0; t < nt; ++t) {
-                    if (round > 0 &&
-                        !mbar_wait(empty0 + 8 * stage, (uint32_t)(round - 1) & 1u, a.status)) {
-                        ok = false;
-                        break;
+            for (int kvh = member; kvh < a.KVH && ok; kvh += GS) {
+                int b = b_first;
+                for (int u = u0; u < u1 && ok; ++b) {
+                    const int nb = prefix[b + 1] - prefix[b];
+                    if (nb == 0) continue;             // an empty sequence (free batch slot)
+                    const int off = u - prefix[b];
+                    const int nt = nb - off < u1 - u ? nb - off : u1 - u;
+                    int tile_lo, n_tiles;
+                    tile_range(a.map, attended_len(a, b), tile_lo, n_tiles);
+                    const int t0 = tile_lo + off;
+                    u += nt;
+                    for (int t = 0; t < nt; ++t) {
+                        if (round > 0 &&
+                            !mbar_wait(empty0 + 8 * stage, (uint32_t)(round - 1) & 1u, a.status)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t full = full0 + 8 * stage;
+                        const uint32_t dst = smem_base + (uint32_t)stage * STAGE_BYTES;
+                        mbar_expect_tx(full, STAGE_BYTES);
+                        const int row = (t0 + t) * kTileRows;
+#pragma unroll
+                        for (int c = 0; c < NCH; ++c)
+                            tma_load_4d(dst + c * CHUNK_BYTES, &tm_k, full, c * CW, kvh, row, b);
+#pragma unroll
+                        for (int c = 0; c < NCH; ++c)
+                            tma_load_4d(dst + TILE_BYTES + c * CHUNK_BYTES, &tm_v, full, c * CW, kvh,
+                                        row, b);
+                        ++issued;
+                        if (++stage == stages) { stage = 0; ++round; }
                     }
-                    const uint32_t full = full0 + 8 * stage;
-                    const uint32_t dst = smem_base + (uint32_t)stage * STAGE_BYTES;
-                    mbar_expect_tx(full, STAGE_BYTES);
-                    const int row = (t0 + t) * kTileRows;
-#pragma unroll
-                    for (int c = 0; c < NCH; ++c)
-                        tma_load_4d(dst + c * CHUNK_BYTES, &tm_k, full, c * CW, kvh, row, b);
-#pragma unroll
-                    for (int c = 0; c < NCH; ++c)
-                        tma_load_4d(dst + TILE_BYTES + c * CHUNK_BYTES, &tm_v, full, c * CW, kvh,
-                                    row, b);
-                    ++issued;
-                    if (++stage == stages) { stage = 0; ++round; }
                 }
             }
             // Drain: every copy this thread issued has landed before the CTA retires.
@@ -184,20 +211,21 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
     const int k_swz = (CW == 64) ? (k_row & 7) : ((k_row >> 1) & 3);
     const int v_swz = (CW == 64) ? (v_row & 7) : ((v_row >> 1) & 3);
 
-    int stage = 0, round = 0, tile_seq = 0, b = 0;
+    int stage = 0, round = 0, tile_seq = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-        const int kvh = item % a.KVH, j = item / a.KVH;
-        while (prefix[b + 1] <= j) ++b;
-        const int chunk = j - prefix[b];
+    for (int kvh = member; kvh < a.KVH; kvh += GS)
+    for (int b = b_first, u = u0; u < u1; ++b) {
+        const int nb = prefix[b + 1] - prefix[b];
+        if (nb == 0) continue;                 // an empty sequence (free batch slot)
+        const int off = u - prefix[b];
+        const int nt = nb - off < u1 - u ? nb - off : u1 - u;
+        u += nt;
         const int total = attended_len(a, b);
         int tile_lo, n_tiles, row_lo, row_hi;
         tile_range(a.map, total, tile_lo, n_tiles);
         slot_range(a.map, total, row_lo, row_hi);
         const int first = first_pos(a.map, total);
-        const int t0 = tile_lo + chunk * a.chunk_tiles;
-        int nt = tile_lo + n_tiles - t0;
-        if (nt > a.chunk_tiles) nt = a.chunk_tiles;
+        const int t0 = tile_lo + off;
         const bool always_mask = a.map.layout == 1 || (a.map.shard_count > 1 && a.map.window > 0);
         const int new_slot = a.k_new ? slot_of_pos(a.map, total - 1) : -1;
 
@@ -395,8 +423,7 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
             }
         }
         named_bar_sync(1, NCW * 32);
-        float* prow = a.part + (((long long)b * a.max_chunks + chunk) * a.H + (long long)kvh * G) *
-                                   (HD + 2);
+        float* prow = a.span_part + ((long long)(span + b) * a.H + (long long)kvh * G) * (HD + 2);
         for (int idx = tid; idx < G * HD; idx += NCW * 32) {
             const int g = idx / HD, d = idx % HD;
             float M = kNegBig;

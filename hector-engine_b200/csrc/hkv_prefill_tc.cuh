@@ -55,6 +55,8 @@ struct PrefillTcArgs {
     // partial rows differs from row to row; each (query, kv head) records its count in row_parts and
     // partial p of query q sits at part[(q * part_stride + p) ...].
     int streamk;
+    int sk_whole;        // items (longest first) run whole before the equal spans; a multiple of the grid
+    int sk_grid;         // CTAs that share the remaining items' key tiles
     int part_stride;
     int* row_parts;      // [S_new][KVH] or null
 };

@@ -157,10 +157,11 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     // other roles through four shared-memory slots as a descriptor
     //   {pair of query tiles, kv head, first key tile, key tiles, part index, parts of the item}.
     // Two schedules: (a) whole items (or equal key-range splits of them) taken off a global counter,
-    // longest first — whichever CTA is free takes the next; (b) equal spans: all key tiles of all items
-    // form one line, cut into gridDim.x equal contiguous spans, so every CTA does the same number of
-    // tile steps whatever the number of items; an item that straddles a cut is finished by two (or
-    // more) CTAs, each writing a partial row that the merge kernel combines.
+    // longest first — whichever CTA is free takes the next; (b) whole items for as many full rounds of
+    // the grid as there are, then equal spans for the rest: the key tiles of the remaining items form
+    // one line, cut into equal contiguous spans, one per CTA, so the last round costs every CTA the same
+    // number of tile steps instead of leaving most SMs idle; an item that straddles a cut is finished by
+    // two (or more) CTAs, each writing a partial row that the merge kernel combines.
     const uint32_t B_QF = bar0 + 144;       // [4] slot holds a descriptor (first word -1 = no more work)
     const uint32_t B_QE = bar0 + 176;       // [4] slot read by the MMA issuer and the 8 softmax warps
     volatile int* q_items = reinterpret_cast<volatile int*>(tmem_slot + 4);   // [4][8]
@@ -272,33 +273,48 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 ++it;
             };
             if (a.streamk) {
-                // this CTA's span [u0, u1) of the line of all key tiles (items in processing order:
-                // pair j, kv head fastest; item (j, kvh) starts at KVH * pre[j] + kvh * T(j))
-                const long long W = (long long)pre[n_pairs] * a.KVH;
-                const long long u0 = W * blockIdx.x / gridDim.x, u1 = W * (blockIdx.x + 1) / gridDim.x;
-                if (u0 < u1) {
-                    int lo = 0, hi = n_pairs - 1;
-                    while (lo < hi) {
-                        const int mid = (lo + hi + 1) >> 1;
-                        if ((long long)a.KVH * pre[mid] <= u0) lo = mid; else hi = mid - 1;
-                    }
-                    int j = lo, T = pre[j + 1] - pre[j];
-                    const long long rem = u0 - (long long)a.KVH * pre[j];
-                    int kvh = (int)(rem / T), off = (int)(rem % T);
-                    for (long long u = u0; u < u1 && ok;) {
-                        const long long left = u1 - u;
-                        const int nt = (long long)(T - off) < left ? T - off : (int)left;
-                        const long long P = (long long)a.KVH * pre[j] + (long long)kvh * T;
-                        const int c_first = prefill_span_owner(P, W, (int)gridDim.x);
-                        const int c_last = prefill_span_owner(P + T - 1, W, (int)gridDim.x);
-                        int kt0, tdummy;
-                        prefill_item_tiles(a, QT2, kPfKeys, n_pairs - 1 - j, kt0, tdummy);
-                        run_piece(n_pairs - 1 - j, kvh, kt0 + off, nt, (int)blockIdx.x - c_first, c_last - c_first + 1);
-                        u += nt;
-                        off = 0;
-                        if (++kvh == a.KVH) {
-                            kvh = 0;
-                            if (++j < n_pairs) T = pre[j + 1] - pre[j];
+                // Phase 1: the first sk_whole items (the longest, a whole number of rounds of the grid) run
+                // whole, taken off the shared counter: CTAs sweep the keys in rough lockstep, which keeps the
+                // K/V tiles that many items share in L2. Item I = (pair j = I / KVH, kv head I % KVH).
+                for (int item = blockIdx.x; item < a.sk_whole && ok; item = (int)gridDim.x + atomicAdd(a.item_counter, 1)) {
+                    const int j = item / a.KVH;
+                    int kt0, T;
+                    prefill_item_tiles(a, QT2, kPfKeys, n_pairs - 1 - j, kt0, T);
+                    run_piece(n_pairs - 1 - j, item % a.KVH, kt0, T, 0, 1);
+                }
+                // Phase 2: the remaining items (fewer than one round) form one line of key tiles that is cut
+                // into sk_grid equal spans; this CTA takes span [u0, u1). Item (j, kvh) starts at
+                // KVH * pre[j] + kvh * T(j); units are counted from the first item of the tail.
+                const int j0 = a.sk_whole / a.KVH, kvh0 = a.sk_whole % a.KVH;
+                const long long line0 = j0 < n_pairs ? (long long)a.KVH * pre[j0] + (long long)kvh0 * (pre[j0 + 1] - pre[j0]) : 0;
+                const long long W = (long long)pre[n_pairs] * a.KVH - line0;
+                const int sg = a.sk_grid;
+                if (ok && j0 < n_pairs && (int)blockIdx.x < sg && W > 0) {
+                    const long long u0 = line0 + W * blockIdx.x / sg, u1 = line0 + W * (blockIdx.x + 1) / sg;
+                    if (u0 < u1) {
+                        int lo = j0, hi = n_pairs - 1;
+                        while (lo < hi) {
+                            const int mid = (lo + hi + 1) >> 1;
+                            if ((long long)a.KVH * pre[mid] <= u0) lo = mid; else hi = mid - 1;
+                        }
+                        int j = lo, T = pre[j + 1] - pre[j];
+                        const long long rem = u0 - (long long)a.KVH * pre[j];
+                        int kvh = (int)(rem / T), off = (int)(rem % T);
+                        for (long long u = u0; u < u1 && ok;) {
+                            const long long left = u1 - u;
+                            const int nt = (long long)(T - off) < left ? T - off : (int)left;
+                            const long long P = (long long)a.KVH * pre[j] + (long long)kvh * T - line0;
+                            const int c_first = prefill_span_owner(P, W, sg);
+                            const int c_last = prefill_span_owner(P + T - 1, W, sg);
+                            int kt0, tdummy;
+                            prefill_item_tiles(a, QT2, kPfKeys, n_pairs - 1 - j, kt0, tdummy);
+                            run_piece(n_pairs - 1 - j, kvh, kt0 + off, nt, (int)blockIdx.x - c_first, c_last - c_first + 1);
+                            u += nt;
+                            off = 0;
+                            if (++kvh == a.KVH) {
+                                kvh = 0;
+                                if (++j < n_pairs) T = pre[j + 1] - pre[j];
+                            }
                         }
                     }
                 }

@@ -207,16 +207,18 @@ def test_prefill_plan_never_leaves_a_key_split_empty(hkv):
     tile that is never loaded."""
     # the headline shape: long pasts get split (148 SMs, 228 pair items x 4 kv heads... ), short ones do not
     g = hkv.Geometry(num_heads=28, num_kv_heads=4, head_dim=128, slots=131072, max_seq_new=2048)
-    # with a workspace for partial rows the two-tile kernel takes the equal-span schedule: one span per SM
+    # 228 work items on 148 SMs: one full round of whole items, then the 80 shortest items' key tiles
+    # cut into equal spans over all SMs (reported as splits == 0) — when the spans are long enough to pay
+    assert _plan_prefill(hkv, g, 2048, 30720)[:3] == [2, 148, 0]
+    # planes beyond the L2 (264 MB here) keep whole items in lockstep and take uniform key splits instead
     tif, items, splits, span = _plan_prefill(hkv, g, 2048, 129024)
-    assert (tif, items, splits) == (2, 148, 0)
+    assert tif == 2 and splits > 1 and splits <= span and items == 57 * 4 * splits
+    # short key ranges: pieces of a few tiles cost more than the idle SMs of the last round
     tif, items, splits, span = _plan_prefill(hkv, g, 2048, 0)
-    assert (tif, items, splits) == (2, 148, 0) and span == 1
+    assert (tif, items, splits) == (2, 228, 1) and span == 1
     # a forced split count keeps the uniform key splits of whole items
     gf = hkv.Geometry(num_heads=28, num_kv_heads=4, head_dim=128, slots=131072, max_seq_new=2048, tune_prefill_splits=3)
     assert _plan_prefill(hkv, gf, 2048, 129024)[:3] == [2, 57 * 4 * 3, 3]
-    # four pairs of tiles (2 + 3 + 3 + 3 key tiles) x 4 kv heads: 44 tiles in all, so 44 spans at most
-    assert _plan_prefill(hkv, g, 144, 200)[:3] == [2, 44, 0]
     # a chunk that fits one query tile takes the one-tile kernel
     assert _plan_prefill(hkv, g, 18, 5000)[0] == 1 and _plan_prefill(hkv, g, 19, 5000)[0] == 2
     # without a workspace for partials there is no split

@@ -519,3 +519,39 @@ def test_both_shapes_of_the_tma_decode_kernel(hkv, cuda, oracle, shape, groups):
         assert np.array_equal(dk[b, r].cpu().numpy().view(np.uint16), nk[b, 0].view(np.uint16))
         assert np.array_equal(dv[b, r].cpu().numpy().view(np.uint16), nv[b, 0].view(np.uint16))
     ctx.close()
+
+
+@pytest.mark.parametrize("totals", [
+    [1], [64], [65], [0, 1, 0], [1, 64, 65, 0, 128, 129], [4096, 1, 4095, 0, 2049],
+    list(range(0, 70)),                      # 70 sequences of 0..69 rows: fewer tiles than spans
+    [4096] * 3 + [0] * 30 + [17] * 4,        # a few long sequences among many empty ones
+], ids=lambda t: f"{len(t)}seq_max{max(t)}")
+def test_equal_span_schedule_edges(hkv, cuda, oracle, totals):
+    """The TMA decode kernel cuts the line of all 64-row tiles of a launch into equal spans, one per
+    gang of CTAs, with the lengths read on the device: launches with fewer tiles than spans, empty
+    sequences, sequences that end exactly on a tile or span boundary, and one sequence that takes every
+    span must all give the oracle's result (decode and fused append + decode)."""
+    torch = cuda
+    B, H, KVH, HD, slots = len(totals), 28, 4, 128, 4096
+    totals = np.asarray(totals, np.int32)
+    q, nk, nv, kc, vc = make_case(B * 7 + int(totals.sum()), B, H, KVH, HD, slots, fill="garbage")
+    scale = 1.0 / math.sqrt(HD)
+    ref = oracle.decode(q, kc, vc, totals, scale, threads=8)
+    for groups in (1, 2):
+        got, kern = run_decode(hkv, torch, q, kc, vc, totals, scale, H=H, KVH=KVH, HD=HD, kernel=TMA)
+        assert kern == TMA
+        assert_close(oracle, got, ref, f"decode, totals={totals.tolist()[:8]}")
+    # fused: append at position total (sequences with total == slots are full: the reference drops the row)
+    pos = np.minimum(totals, slots - 1).astype(np.int32)
+    ref_k, ref_v = kc.copy(), vc.copy()
+    oracle.append(nk, nv, ref_k, ref_v, pos)
+    ref2 = oracle.decode(q, ref_k, ref_v, pos + 1, scale, threads=8)
+    ctx = hkv.Context(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots, kernel_select=TMA))
+    dk, dv = to_dev(torch, kc), to_dev(torch, vc)
+    out = torch.full((B, H, HD), float("nan"), dtype=torch.float16, device="cuda")
+    ctx.append_decode_attention(to_dev(torch, q), to_dev(torch, nk), to_dev(torch, nv), dk, dv, out, to_dev(torch, pos), scale)
+    assert ctx.device_status() == 0
+    assert_close(oracle, out.cpu().numpy(), ref2, "fused append + decode")
+    assert np.array_equal(dk.cpu().numpy().view(np.uint16), ref_k.view(np.uint16))
+    assert np.array_equal(dv.cpu().numpy().view(np.uint16), ref_v.view(np.uint16))
+    ctx.close()
