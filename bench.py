@@ -552,6 +552,75 @@ def prefill_record(args, torch, hkv, oracle, cfg, name, S, past, steps, warmup, 
     return rec
 
 
+def prefill_sequence_record(args, torch, hkv, oracle, dist, cfg, name, total_tokens, chunk, rank, world):
+    """The long-context config's prefill as stated: every GPU prefills ONE sequence of `total_tokens`
+    tokens (sequences sharded by batch, no collective) in chunks of `chunk` queries through all layers:
+    per chunk and layer, append the chunk's K/V rows, then attention of its queries over the cache so
+    far. One pass is timed (seconds of GPU work); max over ranks."""
+    L, H, KVH, HD = cfg["layers"], cfg["H"], cfg["KVH"], cfg["HD"]
+    dev = "cuda"
+    k = torch.zeros((L, total_tokens, KVH, HD), dtype=torch.float16, device=dev)
+    v = torch.zeros((L, total_tokens, KVH, HD), dtype=torch.float16, device=dev)
+    q = torch.empty((chunk, H, HD), dtype=torch.float16, device=dev)
+    kn = torch.empty((chunk, KVH, HD), dtype=torch.float16, device=dev)
+    vn = torch.empty((chunk, KVH, HD), dtype=torch.float16, device=dev)
+    out = torch.zeros((chunk, H, HD), dtype=torch.float16, device=dev)
+    seeds = [SEED ^ 0xF11 ^ (rank * 0x10001) ^ (i << 20) for i in range(3)]
+    for t, sd in zip((q, kn, vn), seeds):
+        hkv.fill_synthetic(t, sd)
+    ctx = hkv.Context(hkv.Geometry(batch=1, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=total_tokens,
+                                   kernel_select=args.kernel, max_seq_new=chunk))
+    scale = 1.0 / math.sqrt(HD)
+    n_chunks = total_tokens // chunk
+
+    def one_pass(layers):
+        for c in range(n_chunks):
+            for l in layers:
+                ctx.append_at(kn, vn, k[l], v[l], c * chunk, chunk)
+                ctx.prefill_attention(q, k[l], v[l], out, chunk, c * chunk, scale)
+
+    one_pass([0])                      # warm-up on one layer (also fills its plane)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    one_pass(range(L))
+    e1.record()
+    torch.cuda.synchronize()
+    assert ctx.device_status() == 0
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if dist is not None:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    err = None
+    if rank == 0 and not args.no_verify:
+        # the last chunk of the last layer, four queries, against the oracle: every chunk wrote the same
+        # rows, so the plane is the chunk's K/V repeated
+        hkn, hvn = oracle.fill(seeds[1], 0, chunk * KVH * HD).reshape(chunk, KVH, HD), oracle.fill(seeds[2], 0, chunk * KVH * HD).reshape(chunk, KVH, HD)
+        hk, hv = np.tile(hkn, (n_chunks, 1, 1)), np.tile(hvn, (n_chunks, 1, 1))
+        hq = oracle.fill(seeds[0], 0, chunk * H * HD).reshape(chunk, H, HD)
+        past = (n_chunks - 1) * chunk
+        ref = oracle.prefill(hq, hk, hv, past, scale, q_begin=chunk - 4, q_end=chunk, threads=oracle.hardware_threads())
+        ok, err = oracle.within_tolerance(out[chunk - 4:].cpu().numpy(), ref[chunk - 4:])
+        assert ok, f"full-sequence prefill parity failed: {err:.3e}"
+    flops = 4.0 * H * HD * (total_tokens * (total_tokens + 1) / 2.0) * L
+    peak, peak_src = measured_peak("bf16_tflops_sustained", 1400.0)
+    ach = flops / (ms * 1e-3) / 1e12
+    rec = {"workload": f"{name}-shaped prefill of {world} sequence(s) of {total_tokens} tokens, one per GPU, in chunks of "
+                       f"{chunk} queries through {L} layers (append + attention over the cache per chunk and layer)",
+           "n_gpus": world, "value": world * total_tokens / (ms * 1e-3), "unit": "tokens/s", "seconds_per_sequence": ms / 1e3,
+           "roofline": {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                        "peak_source": peak_src + " (a seconds-long run: the sustained figure)",
+                        "algorithmic_flops": flops},
+           "gpu_launches": n_chunks * L * 2, "parity_max_abs_err": err}
+    ctx.close()
+    del k, v
+    gc.collect()
+    torch.cuda.empty_cache()
+    return rec if rank == 0 else None
+
+
 def rope_record(args, torch, hkv, oracle, cfg, name, B, S, slots, steps, warmup):
     """The step in front of the append: per-head RMSNorm of q and k + rotary embedding with K and V
     written straight into the cache (hkv_qk_norm_rope_kv). HBM-bound:
@@ -1225,6 +1294,11 @@ def main():
             if rank == 0:
                 seqsplit.append(rec)
 
+    # ---- the long-context config's prefill: one 131 072-token sequence per GPU, 2 048-query chunks
+    prefill_seq = None
+    if default_workload and not args.no_extras:
+        prefill_seq = prefill_sequence_record(args, torch, hkv, oracle, dist, cfg, args.workload, 131072, 2048, rank, n_gpus)
+
     if rank == 0:
         line = dict(base, config=config, value=tok_s, ms_per_step=ms_per_step,
                     ms_per_step_median=stats["ms_per_step_median"], ms_per_step_min=stats["ms_per_step_min"],
@@ -1237,6 +1311,8 @@ def main():
             line["extras"] = extras
         if seqsplit:
             line["seqsplit"] = seqsplit
+        if prefill_seq is not None:
+            line["prefill_sequences"] = prefill_seq
         print(json.dumps(line))
     return finish()
 

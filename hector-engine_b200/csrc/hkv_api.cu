@@ -181,6 +181,25 @@ size_t workspace_bytes_for(const hkv_geometry& g, int max_chunks) {
     return (size_t)g.batch * max_chunks * g.num_heads * (g.head_dim + 2) * sizeof(float);
 }
 
+// CTAs that share a span of the decode kernel's equal-span schedule. A gang of one CTA per kv head
+// streams all heads of the same cache rows in step (a row holds every kv head side by side, so the
+// gang reads whole rows together — measured: a gang of 4 for 32 kv heads, each CTA walking its span
+// eight times, costs 9 %). CTAs beyond a whole number of gangs idle, so a gang may take two, four or
+// eight heads per CTA when that leaves fewer than 6 % of the grid idle and one head per CTA does not.
+int span_gang_for(int kv_heads, int grid) {
+    int best = 1;
+    double best_util = 0.0;
+    for (int per_cta = 1; per_cta <= 8; per_cta *= 2) {
+        if (kv_heads % per_cta != 0) break;
+        const int gang = kv_heads / per_cta;
+        if (gang > grid) continue;
+        const double util = (double)(grid / gang) * gang / grid;
+        if (util >= 0.94) return gang;
+        if (util > best_util) { best_util = util; best = gang; }
+    }
+    return best;
+}
+
 // ---- TMA kernel table ------------------------------------------------------
 typedef void (*TmaKernel)(const CUtensorMap, const CUtensorMap, const DecodeArgs, const int);
 
@@ -217,8 +236,8 @@ int encode_f16_sw128(hkv_ctx* c, const void* base, int rank, const cuuint64_t* d
 }
 
 constexpr int kPrefillMaxSplits = 4;
-// Below this many 64-row K/V tiles per SM and launch the decode kernel runs as two CTAs per SM.
-constexpr long long kTwoCtaTilesPerSm = 64;   // measured: +8...+29 % below, -2 % above
+// The decode kernel runs as two CTAs per SM unless that would give a sequence more spans than this.
+constexpr int kMaxSpansPerSeqTwoCta = 40;
 
 // Key tiles an item of `q_item` queries (item index qt) spans — the kernels' own arithmetic.
 int prefill_span_tiles(const PrefillTcArgs& t, int q_item, int qt) {
@@ -709,16 +728,15 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
                                                                            : HKV_KERNEL_GENERIC;
     if (c->kernel == HKV_KERNEL_TMA) {
         // Two shapes of the same kernel (hkv_decode_tma.cuh): one CTA per SM with two consumer groups,
-        // or two CTAs per SM with one group and half the ring each. The second overlaps the fixed
-        // cost per launch and wins while a launch is short: chosen by the K/V tiles an SM streams
-        // at full context.
+        // or two CTAs per SM with one group and half the ring each.
         int sm_total = 0;
         cudaDeviceGetAttribute(&sm_total, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
         const size_t half_budget = sm_total > 4096 ? (size_t)sm_total / 2 - 2048 : 0;   // two CTAs + the runtime's reserve
-        int rows = geometry->slots;
-        if (geometry->window_size > 0 && geometry->window_size < rows) rows = geometry->window_size + kTileRows;
-        const long long tiles_per_sm = (long long)geometry->batch * geometry->num_kv_heads * ((rows + kTileRows - 1) / kTileRows) / sm;
-        c->tma_groups = geometry->tune_tma_groups ? geometry->tune_tma_groups : (tiles_per_sm < kTwoCtaTilesPerSm ? 1 : 2);
+        // Two CTAs per SM stream a little faster (7.1 against 6.6 TB/s at batch 64) and hide each other's
+        // merges; they also double the spans, and with them the partials the merge kernel walks per
+        // sequence — which is what a launch of one or two sequences spends its time on.
+        const int spans_two = 2 * sm / span_gang_for(geometry->num_kv_heads, 2 * sm);
+        c->tma_groups = geometry->tune_tma_groups ? geometry->tune_tma_groups : (spans_two / geometry->batch > kMaxSpansPerSeqTwoCta ? 2 : 1);
         if (c->tma_groups == 1) {
             c->plan = tma_plan(geometry->head_dim, c->G, 4, geometry->batch, half_budget);
             if (c->plan.stages < 2) c->tma_groups = 2;   // tiles too large for half an SM's shared memory
@@ -775,9 +793,7 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
         // Equal-span schedule: one or two persistent CTAs per SM, in gangs that share a span with one
         // share of the kv heads each; one partial row set per (span, sequence) piece.
         c->tma_grid = (c->tma_groups == 1 ? 2 : 1) * sm;
-        int x = c->tma_grid, y = geometry->num_kv_heads;
-        while (y) { const int r = x % y; x = y; y = r; }
-        c->span_gang = x;    // gcd(grid, kv heads)
+        c->span_gang = span_gang_for(geometry->num_kv_heads, c->tma_grid);
         const size_t slots = (size_t)c->tma_grid / c->span_gang + geometry->batch;
         e = cudaMalloc(&c->span_ws, slots * geometry->num_heads * (geometry->head_dim + 2) * sizeof(float));
         if (e != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(span workspace)");
@@ -1137,13 +1153,11 @@ int hkv_qk_norm_rope_kv(hkv_ctx* c, void* q, void* k, const void* v, const void*
     const bool vec = g.head_dim % 4 == 0 && c->batch_stride % 4 == 0 && aligned(q, 8) && aligned(k, 8) &&
                      (!v || aligned(v, 8)) && (!k_cache || (aligned(k_cache, 8) && aligned(v_cache, 8)));
     const int per_tok = g.num_heads + 2 * g.num_kv_heads;
-    // one CTA row per token on grid.y: at most 65535 tokens per launch, the rest in further launches
-    for (long long t0 = 0; t0 < tokens; t0 += 65535) {
-        const long long n = tokens - t0 < 65535 ? tokens - t0 : 65535;
-        a.tok0 = t0;
-        dim3 grid((unsigned)((per_tok + kRopeWarps - 1) / kRopeWarps), (unsigned)n);
-        hkv_qk_norm_rope_kernel<<<grid, kRopeWarps * 32, 0, (cudaStream_t)stream>>>(a, vec ? 1 : 0);
-    }
+    // work items of kRopeWarps units of one token; each CTA takes a contiguous range of them
+    const long long items = tokens * ((per_tok + kRopeWarps - 1) / kRopeWarps);
+    const long long cap = (long long)c->sm_count * 8;
+    const unsigned grid = (unsigned)(items < cap ? items : cap);
+    hkv_qk_norm_rope_kernel<<<grid, kRopeWarps * 32, 0, (cudaStream_t)stream>>>(a, vec ? 1 : 0);
     const cudaError_t e = cudaPeekAtLastError();
     return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "qk_norm_rope launch");
 }

@@ -28,47 +28,16 @@ struct RopeArgs {
     int host_pos;
     SeqMap map;
     int B, S, H, KVH, HD, rot;
-    long long tok0;         // first token (b*S + s) of this launch
     long long batch_stride;
     float eps, theta, scaling;
 };
 
 constexpr int kRopeWarps = 8;
 
-// One CTA serves kRopeWarps units of ONE token: a unit is a query head, a key head or a value head
-// (j < H query head j, j < H + KVH key head, else value head — a plain copy, only when a cache is
-// given). Grid = (ceil((H + 2*KVH) / kRopeWarps), B*S).
-//   * The rotation angles depend on (position, pair index) only, so the CTA computes the cos/sin
-//     table of its token once (rot/2 entries, accurate powf + sincosf: positions reach 10^5 rad)
-//     and every head of the CTA reuses it — the reference recomputes it per head and per pair.
-//   * Rows move in 8-byte pieces (4 halfs per lane: a 128-wide head is one piece per lane) when the
-//     pointers and head_dim allow it, else element by element. A warp stages its head as fp32 in
-//     shared memory, so any rotary_dim <= head_dim <= 512 takes the same code.
-__global__ void __launch_bounds__(kRopeWarps * 32) hkv_qk_norm_rope_kernel(const RopeArgs a, const int vec) {
-    __shared__ float s_x[kRopeWarps][512];
-    __shared__ float s_cos[256], s_sin[256];
-    __shared__ float s_w[2][512];          // q and k norm weights as fp32
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int per_tok = a.H + 2 * a.KVH;
-    const long long tok = a.tok0 + blockIdx.y;
-    const int s = (int)(tok % a.S), b = (int)(tok / a.S);
-    const int pos = (a.d_pos ? a.d_pos[b * a.pos_stride] : a.host_pos) + s;
-    const int half_rot = a.rot / 2;
-    const float fp = (float)pos / a.scaling;
-    for (int i = threadIdx.x; i < half_rot; i += blockDim.x) {
-        const float freq = 1.0f / powf(a.theta, (float)(2 * i) / (float)a.rot);
-        float sn, c;
-        sincosf(fp * freq, &sn, &c);
-        s_cos[i] = c;
-        s_sin[i] = sn;
-    }
-    for (int i = threadIdx.x; i < a.HD; i += blockDim.x) {
-        s_w[0][i] = __half2float(a.q_w[i]);
-        s_w[1][i] = __half2float(a.k_w[i]);
-    }
-    __syncthreads();
-
-    const int j = blockIdx.x * kRopeWarps + warp;
+// One unit of one token (see the kernel below); `x` is the calling warp's fp32 staging row.
+__device__ __forceinline__ void rope_unit(const RopeArgs& a, const int vec, const long long tok, const int b, const int pos,
+                                          const int j, const int per_tok, const int half_rot, float* x,
+                                          const float (*s_w)[512], const float* s_cos, const float* s_sin, const int lane) {
     if (j >= per_tok) return;
     const bool is_q = j < a.H, is_k = !is_q && j < a.H + a.KVH;
     const int kvh = is_q ? 0 : (is_k ? j - a.H : j - a.H - a.KVH);
@@ -93,7 +62,6 @@ __global__ void __launch_bounds__(kRopeWarps * 32) hkv_qk_norm_rope_kernel(const
     __half* dst = is_q ? a.q + (tok * a.H + j) * a.HD
                        : (a.k_cache ? a.k_cache + cache_off : a.k + (tok * a.KVH + kvh) * a.HD);
     const float* w = s_w[is_q ? 0 : 1];
-    float* x = s_x[warp];
     float ssq = 0.0f;
     if (vec) {
         for (int i = lane; i < a.HD / 4; i += 32) {
@@ -130,6 +98,52 @@ __global__ void __launch_bounds__(kRopeWarps * 32) hkv_qk_norm_rope_kernel(const
         }
     } else {
         for (int i = lane; i < a.HD; i += 32) dst[i] = __float2half_rn(rotated(i));
+    }
+}
+
+// A work item is kRopeWarps units of ONE token: a unit is a query head, a key head or a value head
+// (j < H query head j, j < H + KVH key head, else value head — a plain copy, only when a cache is
+// given). Items are numbered token-major; every CTA takes a contiguous range of them, so it loads
+// the norm weights once and recomputes the rotation table only when its token changes.
+//   * The rotation angles depend on (position, pair index) only, so a CTA computes the cos/sin
+//     table of a token once (rot/2 entries, accurate powf + sincosf: positions reach 10^5 rad)
+//     and every head of the token reuses it — the reference recomputes it per head and per pair.
+//   * Rows move in 8-byte pieces (4 halfs per lane: a 128-wide head is one piece per lane) when the
+//     pointers and head_dim allow it, else element by element. A warp stages its head as fp32 in
+//     shared memory, so any rotary_dim <= head_dim <= 512 takes the same code.
+__global__ void __launch_bounds__(kRopeWarps * 32) hkv_qk_norm_rope_kernel(const RopeArgs a, const int vec) {
+    __shared__ float s_x[kRopeWarps][512];
+    __shared__ float s_cos[256], s_sin[256];
+    __shared__ float s_w[2][512];          // q and k norm weights as fp32
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int per_tok = a.H + 2 * a.KVH;
+    const int groups = (per_tok + kRopeWarps - 1) / kRopeWarps;       // items per token
+    const long long items = (long long)a.B * a.S * groups;
+    const long long i0 = items * blockIdx.x / gridDim.x, i1 = items * (blockIdx.x + 1) / gridDim.x;
+    const int half_rot = a.rot / 2;
+    for (int i = threadIdx.x; i < a.HD; i += blockDim.x) {
+        s_w[0][i] = __half2float(a.q_w[i]);
+        s_w[1][i] = __half2float(a.k_w[i]);
+    }
+    long long table_tok = -1;
+    for (long long item = i0; item < i1; ++item) {
+    const long long tok = item / groups;
+    const int s = (int)(tok % a.S), b = (int)(tok / a.S);
+    const int pos = (a.d_pos ? a.d_pos[b * a.pos_stride] : a.host_pos) + s;
+    if (tok != table_tok) {                 // block-uniform
+        __syncthreads();                    // the previous token's table is no longer being read
+        const float fp = (float)pos / a.scaling;
+        for (int i = threadIdx.x; i < half_rot; i += blockDim.x) {
+            const float freq = 1.0f / powf(a.theta, (float)(2 * i) / (float)a.rot);
+            float sn, c;
+            sincosf(fp * freq, &sn, &c);
+            s_cos[i] = c;
+            s_sin[i] = sn;
+        }
+        __syncthreads();
+        table_tok = tok;
+    }
+    rope_unit(a, vec, tok, b, pos, (int)(item % groups) * kRopeWarps + warp, per_tok, half_rot, s_x[warp], s_w, s_cos, s_sin, lane);
     }
 }
 
