@@ -20,7 +20,7 @@ Prints ONE JSON line (rank 0).
   roofline     the split-K decode kernel's algorithmic HBM bytes / its CUDA-event duration,
                taken in a separate pass so that no event sits inside the timed region
   cpu_baseline the scalar CPU oracle timed on a bounded sample
-  extras       (1 GPU) compact, parity-checked records of the other BASELINE configs and batch
+  extras       (1 GPU) compact, parity-checked records of the other model shapes and batch
                sizes, of the tensor-core prefill chunk and of the fused norm+RoPE+cache write
   seqsplit     the sequence-split path (one logical cache dealt over the GPUs, NCCL all-gather
                of the partials, hosted in C++): strong scaling of batch 64 / ctx 32768, and on
@@ -51,7 +51,7 @@ SEED = 0x48454B56
 # DRAM bytes (read + write) per algorithmic byte of the TMA decode kernel, from an ncu capture of a
 # batch-8 launch of the default workload; the traffic is the K/V rows themselves, so it scales with
 # the rows a launch reads.
-DRAM_BYTES_PER_ALGORITHMIC_BYTE = 1.0172
+DRAM_BYTES_PER_ALGORITHMIC_BYTE = 1.012
 WORKLOADS = {
     # name: layers, H, KVH, HD, window pattern (None = all global)
     "qwen2-7b": dict(layers=28, H=28, KVH=4, HD=128),

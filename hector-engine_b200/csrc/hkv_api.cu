@@ -123,7 +123,7 @@ int validate_geometry(const hkv_geometry* g, const char** why) {
         return HKV_ERR_INVALID_ARG;
     }
     if ((g->flags & ~(HKV_FLAG_SCALAR_POSITION | HKV_FLAG_APPEND_ONLY)) != 0 || g->tune_prefill_splits < 0 ||
-        g->tune_prefill_kernel < 0 || g->tune_prefill_kernel > 2 || g->tune_tma_groups < 0 || g->tune_tma_groups > 2) {
+        g->tune_prefill_kernel < 0 || g->tune_prefill_kernel > 2 || g->tune_tma_groups < 0 || g->tune_tma_groups > 3) {
         *why = "unknown flag or tuning override";
         return HKV_ERR_INVALID_ARG;
     }
@@ -742,7 +742,7 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
             if (c->plan.stages < 2) c->tma_groups = 2;   // tiles too large for half an SM's shared memory
         }
         if (c->tma_groups == 2) c->plan = tma_plan(geometry->head_dim, c->G, 8, geometry->batch, c->smem_optin);
-        if (c->plan.stages < 2 && c->tma_groups == 2) {
+        if ((c->plan.stages < 2 && c->tma_groups == 2) || c->tma_groups == 3) {
             c->tma_groups = 0;    // one CTA per SM, one consumer group, the whole shared memory
             c->plan = tma_plan(geometry->head_dim, c->G, 4, geometry->batch, c->smem_optin);
         }
@@ -1149,15 +1149,16 @@ int hkv_qk_norm_rope_kv(hkv_ctx* c, void* q, void* k, const void* v, const void*
     a.scaling = scaling_factor <= 0.0f ? 1.0f : scaling_factor;
     const long long tokens = (long long)g.batch * seq_new;
     if (a.rot / 2 > 256) return fail(c, HKV_ERR_GEOMETRY, "qk_norm_rope: rotary_dim above 512");
-    // 8-byte accesses when every row starts on an 8-byte boundary
-    const bool vec = g.head_dim % 4 == 0 && c->batch_stride % 4 == 0 && aligned(q, 8) && aligned(k, 8) &&
+    // register path: 8-byte aligned rows, head_dim and half the rotary span in whole 4-element pieces
+    const bool vec = g.head_dim % 4 == 0 && (a.rot / 2) % 4 == 0 && c->batch_stride % 4 == 0 && aligned(q, 8) && aligned(k, 8) &&
                      (!v || aligned(v, 8)) && (!k_cache || (aligned(k_cache, 8) && aligned(v_cache, 8)));
     const int per_tok = g.num_heads + 2 * g.num_kv_heads;
-    // work items of kRopeWarps units of one token; each CTA takes a contiguous range of them
-    const long long items = tokens * ((per_tok + kRopeWarps - 1) / kRopeWarps);
-    const long long cap = (long long)c->sm_count * 8;
-    const unsigned grid = (unsigned)(items < cap ? items : cap);
-    hkv_qk_norm_rope_kernel<<<grid, kRopeWarps * 32, 0, (cudaStream_t)stream>>>(a, vec ? 1 : 0);
+    const int groups = (per_tok + kRopeWarps - 1) / kRopeWarps;
+    // many tokens: one CTA per token walks all its heads (one rotation table per token); few tokens: one
+    // CTA per group of 8 heads, so that a decode launch still spreads over the SMs
+    const unsigned gx = tokens >= 2LL * c->sm_count ? 1u : (unsigned)groups;
+    const unsigned gy = (unsigned)(tokens < 65535 ? tokens : 65535);
+    hkv_qk_norm_rope_kernel<<<dim3(gx, gy), kRopeWarps * 32, 0, (cudaStream_t)stream>>>(a, vec ? 1 : 0);
     const cudaError_t e = cudaPeekAtLastError();
     return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "qk_norm_rope launch");
 }

@@ -89,7 +89,9 @@ typedef struct hkv_geometry {
     int32_t tune_prefill_splits; /* key-range splits of a prefill work item, 1..4; clamped to
                                     what the plan allows                                 */
     int32_t tune_prefill_kernel; /* 1 = one query tile in flight per CTA, 2 = two        */
-    int32_t tune_tma_groups;     /* consumer groups of the TMA decode kernel, 1 or 2     */
+    int32_t tune_tma_groups;     /* shape of the TMA decode kernel: 1 = two CTAs per SM with one
+                                    consumer group each, 2 = one CTA with two groups, 3 = one CTA
+                                    with one group and the whole shared memory as its ring */
     int32_t reserved[3];
 } hkv_geometry;
 

@@ -261,6 +261,31 @@ static void test_error_behaviour() {
     sh::CommandBuffer upd;
     upd.add_kv_cache_update("k", "v", "q", "nope", 0, 16, 2, 64, 1);
     REQUIRE(throws_with([&] { engine.execute(upd); }, "KV_CACHE_UPDATE: missing tensors"), "missing tensor must throw");
+    // KV_CACHE_UPDATE with a batch and the engine's device position: the reference forwards the batch with
+    // its ONE scalar (kernels/register_kernels.cpp:959-968) and every sequence writes at that position
+    {
+        const int B = 3, S = 16, KVH = 2, HD = 64, pos = 5;
+        engine.alloc_device_cache_pos();
+        T.allocate_and_register("bk_new", {(uint32_t)B, 1, (uint32_t)(KVH * HD)}, sh::DType::FP16);
+        T.allocate_and_register("bv_new", {(uint32_t)B, 1, (uint32_t)(KVH * HD)}, sh::DType::FP16);
+        T.allocate_and_register("bkc", {(uint32_t)B, (uint32_t)S, (uint32_t)KVH, (uint32_t)HD}, sh::DType::FP16);
+        T.allocate_and_register("bvc", {(uint32_t)B, (uint32_t)S, (uint32_t)KVH, (uint32_t)HD}, sh::DType::FP16);
+        std::vector<uint16_t> nk((size_t)B * KVH * HD), nv(nk.size()), hk((size_t)B * S * KVH * HD, 0), hv(hk.size(), 0);
+        hkv_oracle_fill(nk.data(), 11, 0, nk.size());
+        hkv_oracle_fill(nv.data(), 12, 0, nv.size());
+        upload(T.at("bk_new").ptr, nk);
+        upload(T.at("bv_new").ptr, nv);
+        sh::CommandBuffer bupd;
+        bupd.add_kv_cache_update("bkc", "bvc", "bk_new", "bv_new", 0, S, KVH, HD, 1);
+        bupd.commands().back().set("device_pos", uint32_t{1});
+        engine.update_device_cache_pos(pos, 1);
+        engine.execute(bupd);
+        cudaDeviceSynchronize();
+        const int32_t same_pos[3] = {pos, pos, pos};
+        hkv_oracle_append(nk.data(), nv.data(), hk.data(), hv.data(), B, 1, KVH, HD, S, (int64_t)S * KVH * HD, same_pos, 0);
+        REQUIRE(download(T.at("bkc").ptr, hk.size()) == hk && download(T.at("bvc").ptr, hv.size()) == hv,
+                "batched KV_CACHE_UPDATE writes every sequence at the engine's scalar position");
+    }
     // a uint32 parameter stored as int32 is ignored (default used), as in the engine
     sh::Command c;
     c.set("head_dim", int32_t{64});

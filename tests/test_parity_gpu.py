@@ -466,7 +466,7 @@ def test_prefill_refuses_a_batched_context(hkv, cuda):
     ctx.close()
 
 
-@pytest.mark.parametrize("groups", [1, 2], ids=["two_ctas_per_sm", "one_cta_per_sm"])
+@pytest.mark.parametrize("groups", [1, 2, 3], ids=["two_ctas_per_sm", "one_cta_two_groups", "one_cta_one_group"])
 @pytest.mark.parametrize("shape", [
     # B, H, KVH, HD, slots, window, layout
     (5, 28, 4, 128, 4096, 0, 0),     # config 2 shape, ragged lengths
@@ -476,8 +476,8 @@ def test_prefill_refuses_a_batched_context(hkv, cuda):
     (70, 8, 2, 128, 640, 200, 0),    # more sequences than a warp scans at once, sliding window
 ], ids=lambda s: "B%d_H%d_KVH%d_HD%d_%d_w%d_l%d" % s)
 def test_both_shapes_of_the_tma_decode_kernel(hkv, cuda, oracle, shape, groups):
-    """The TMA decode kernel runs either as one CTA per SM with two consumer groups or as two CTAs per
-    SM with one group each (chosen by the work per SM; forced here through tune_tma_groups). Both give
+    """The TMA decode kernel runs as two CTAs per SM with one consumer group each, or as one CTA per SM
+    with two groups or with one (chosen by the host; forced here through tune_tma_groups). All give
     the oracle's result for the fused append + attention, with ragged and empty sequences."""
     torch = cuda
     B, H, KVH, HD, slots, window, layout = shape
