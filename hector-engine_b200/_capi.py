@@ -55,6 +55,7 @@ SIGNATURES = {
     "hkv_append_decode_attention": (C.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I32P, C.c_float, _VP]),
     "hkv_decode_attention_static": (C.c_int, [C.POINTER(HkvGeometry), _VP, _VP, _VP, _VP, _I32P, C.c_float, _VP]),
     "hkv_prefill_attention": (C.c_int, [_VP, _VP, _VP, _VP, _VP, C.c_int32, C.c_int32, C.c_float, _VP]),
+    "hkv_prefill_append_attention": (C.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, C.c_int32, C.c_int32, C.c_float, _VP]),
     "hkv_partial_floats": (C.c_size_t, [C.POINTER(HkvGeometry)]),
     "hkv_decode_partials": (C.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, _F32P, _I32P, C.c_float, _VP]),
     "hkv_combine_partials": (C.c_int, [_VP, _F32P, C.c_int32, _VP, _VP]),

@@ -456,6 +456,75 @@ int get_maps(hkv_ctx* c, const void* k, const void* v, const TmapPair** out) {
     return HKV_OK;
 }
 
+// One launch of a tensor-core prefill kernel (+ its merge) for geometry `g`, which is the context's
+// own or a view of it (the attend-before-append passes). `pass` == nullptr: the plain op.
+struct PrefillPass {
+    int key_limit;    // attend keys below this position only
+    int out_part;     // partial slot (of out_parts) every row writes; the caller merges
+    int out_parts;
+};
+int prefill_tc_launch(hkv_ctx* c, const hkv_geometry& g, const void* q, const void* k_plane, const void* v_plane, void* out,
+                      int seq_new, int past_len, float scale, cudaStream_t st, const PrefillPass* pass) {
+    const int HD = g.head_dim, G = g.num_heads / g.num_kv_heads, HDS = prefill_tc_staged_hd(HD), KEYS = prefill_tc_keys(HD);
+    PrefillTcArgs t;
+    t.out = (__half*)out;
+    t.status = c->d_status;
+    t.key_limit = pass ? pass->key_limit : 0x7fffffff;
+    t.out_part = pass ? pass->out_part : 0;
+    t.out_parts = pass ? pass->out_parts : 0;
+    int pair = 0, min_span = 0, grid = 0, max_parts = 0;
+    plan_prefill_tc(g, seq_new, past_len, c->sm_count, !pass && c->prefill_ws != nullptr && seq_new <= c->g.max_seq_new, t, pair,
+                    min_span, grid, max_parts, c->plan_scratch);
+    if (t.splits > min_span || grid < 1 || max_parts > kPrefillMaxSplits)
+        return fail(c, HKV_ERR_INVALID_ARG, "prefill: internal plan error (an empty key split or too many parts)");
+    if (t.streamk) t.row_parts = c->prefill_row_parts;
+    if (pass) t.part_stride = kPrefillMaxSplits;
+    t.scale_log2 = scale * 1.4426950408889634f;
+    t.part = c->prefill_ws;
+    // Boxes are 64 halfs wide; a head_dim of 96 takes two, the second reaching past the tensor's
+    // extent, where the copy engine fills zeros.
+    CUtensorMap mq, mk, mv;
+    {
+        cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)g.num_heads, (cuuint64_t)seq_new};
+        cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)g.num_heads * HD * 2};
+        cuuint32_t box[3] = {64u, (cuuint32_t)G, (cuuint32_t)t.QT};
+        const int stt = encode_f16_sw128(c, q, 3, dims, strides, box, &mq);
+        if (stt) return stt;
+    }
+    {
+        cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)g.num_kv_heads, (cuuint64_t)g.slots, 1};
+        cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)g.num_kv_heads * HD * 2,
+                                 (cuuint64_t)g.slots * g.num_kv_heads * HD * 2};
+        cuuint32_t box[4] = {64u, 1u, (cuuint32_t)KEYS, 1u};
+        int stt = encode_f16_sw128(c, k_plane, 4, dims, strides, box, &mk);
+        if (stt) return stt;
+        stt = encode_f16_sw128(c, v_plane, 4, dims, strides, box, &mv);
+        if (stt) return stt;
+    }
+    t.item_counter = c->prefill_counter;
+    if (pair) {
+        const cudaError_t me = cudaMemsetAsync(c->prefill_counter, 0, sizeof(int), st);
+        if (me != cudaSuccess) return fail_cuda(c, me, "cudaMemsetAsync(prefill work counter)");
+        const size_t smem = prefill_tc2_smem_bytes(HDS);
+        if (HDS == 64) hkv_prefill_tc2_kernel<64><<<grid, kPf2Threads, smem, st>>>(mq, mk, mv, t);
+        else hkv_prefill_tc2_kernel<128><<<grid, kPf2Threads, smem, st>>>(mq, mk, mv, t);
+    } else {
+        const size_t smem = prefill_tc_smem_bytes(HDS);
+        if (HDS == 64) hkv_prefill_tc_kernel<64, 128><<<grid, kPfThreads, smem, st>>>(mq, mk, mv, t);
+        else if (HDS == 128) hkv_prefill_tc_kernel<128, 128><<<grid, kPfThreads, smem, st>>>(mq, mk, mv, t);
+        else hkv_prefill_tc_kernel<256, 64><<<grid, kPfThreads, smem, st>>>(mq, mk, mv, t);
+    }
+    if (!pass && (t.splits > 1 || (t.streamk && max_parts > 1))) {
+        // merge the key-range partials of every (query, head) that has more than one
+        const long long rows = (long long)seq_new * g.num_heads;
+        const unsigned cgrid = (unsigned)((rows + 7) / 8);
+        hkv_prefill_combine_kernel<<<cgrid, 256, 0, st>>>(c->prefill_ws, (__half*)out, rows, g.num_heads, HD, t.splits,
+                                                         t.part_stride, t.row_parts, G);
+    }
+    const cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "prefill launch");
+}
+
 SeqMap make_map(const hkv_geometry& g) {
     SeqMap m;
     m.slots = g.slots;
@@ -969,62 +1038,7 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
     if (seq_new == 0) return HKV_OK;
     // (the tensor-core kernel takes row maxima before scaling, which needs a positive scale)
     if (prefill_tc_ok(c->g) && scale > 0.0f && aligned(q, 16) && aligned(k_cache, 16) && aligned(v_cache, 16) && aligned(out, 16)) {
-        const hkv_geometry& g = c->g;
-        const int HD = g.head_dim, G = c->G, HDS = prefill_tc_staged_hd(HD), KEYS = prefill_tc_keys(HD);
-        PrefillTcArgs t;
-        t.out = (__half*)out;
-        t.status = c->d_status;
-        int pair = 0, min_span = 0, grid = 0, max_parts = 0;
-        plan_prefill_tc(g, seq_new, past_len, c->sm_count, c->prefill_ws != nullptr && seq_new <= g.max_seq_new, t, pair,
-                        min_span, grid, max_parts, c->plan_scratch);
-        if (t.splits > min_span || grid < 1 || max_parts > kPrefillMaxSplits)
-            return fail(c, HKV_ERR_INVALID_ARG, "prefill: internal plan error (an empty key split or too many parts)");
-        if (t.streamk) t.row_parts = c->prefill_row_parts;
-        t.scale_log2 = scale * 1.4426950408889634f;
-        t.part = c->prefill_ws;
-        // Boxes are 64 halfs wide; a head_dim of 96 takes two, the second reaching past the tensor's
-        // extent, where the copy engine fills zeros.
-        CUtensorMap mq, mk, mv;
-        {
-            cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)g.num_heads, (cuuint64_t)seq_new};
-            cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)g.num_heads * HD * 2};
-            cuuint32_t box[3] = {64u, (cuuint32_t)G, (cuuint32_t)t.QT};
-            const int st = encode_f16_sw128(c, q, 3, dims, strides, box, &mq);
-            if (st) return st;
-        }
-        {
-            cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)g.num_kv_heads, (cuuint64_t)g.slots, 1};
-            cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)g.num_kv_heads * HD * 2,
-                                     (cuuint64_t)g.slots * g.num_kv_heads * HD * 2};
-            cuuint32_t box[4] = {64u, 1u, (cuuint32_t)KEYS, 1u};
-            int st = encode_f16_sw128(c, k_cache, 4, dims, strides, box, &mk);
-            if (st) return st;
-            st = encode_f16_sw128(c, v_cache, 4, dims, strides, box, &mv);
-            if (st) return st;
-        }
-        t.item_counter = c->prefill_counter;
-        cudaStream_t st = (cudaStream_t)stream;
-        if (pair) {
-            const cudaError_t me = cudaMemsetAsync(c->prefill_counter, 0, sizeof(int), st);
-            if (me != cudaSuccess) return fail_cuda(c, me, "cudaMemsetAsync(prefill work counter)");
-            const size_t smem = prefill_tc2_smem_bytes(HDS);
-            if (HDS == 64) hkv_prefill_tc2_kernel<64><<<grid, kPf2Threads, smem, st>>>(mq, mk, mv, t);
-            else hkv_prefill_tc2_kernel<128><<<grid, kPf2Threads, smem, st>>>(mq, mk, mv, t);
-        } else {
-            const size_t smem = prefill_tc_smem_bytes(HDS);
-            if (HDS == 64) hkv_prefill_tc_kernel<64, 128><<<grid, kPfThreads, smem, st>>>(mq, mk, mv, t);
-            else if (HDS == 128) hkv_prefill_tc_kernel<128, 128><<<grid, kPfThreads, smem, st>>>(mq, mk, mv, t);
-            else hkv_prefill_tc_kernel<256, 64><<<grid, kPfThreads, smem, st>>>(mq, mk, mv, t);
-        }
-        if (t.splits > 1 || (t.streamk && max_parts > 1)) {
-            // merge the key-range partials of every (query, head) that has more than one
-            const long long rows = (long long)seq_new * g.num_heads;
-            const unsigned cgrid = (unsigned)((rows + 7) / 8);
-            hkv_prefill_combine_kernel<<<cgrid, 256, 0, st>>>(c->prefill_ws, (__half*)out, rows, g.num_heads, HD, t.splits,
-                                                             t.part_stride, t.row_parts, G);
-        }
-        const cudaError_t e = cudaPeekAtLastError();
-        return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "prefill launch");
+        return prefill_tc_launch(c, c->g, q, k_cache, v_cache, out, seq_new, past_len, scale, (cudaStream_t)stream, nullptr);
     }
     PrefillArgs a;
     a.q = (const __half*)q;
@@ -1042,6 +1056,54 @@ int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const 
     a.scale_log2 = scale * 1.4426950408889634f;
     dim3 grid((unsigned)seq_new, (unsigned)c->g.num_heads);
     hkv_prefill_generic_kernel<<<grid, kGenWarps * 32, 0, (cudaStream_t)stream>>>(a);
+    const cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "prefill launch");
+}
+
+int hkv_prefill_append_attention(hkv_ctx* c, const void* q, const void* k_new, const void* v_new, void* k_cache,
+                                 void* v_cache, void* out, int32_t seq_new, int32_t past_len, float scale, void* stream) {
+    HKV_CHECK_CTX(c);
+    if (!q || !k_new || !v_new || !k_cache || !v_cache || !out) return fail(c, HKV_ERR_INVALID_ARG, "prefill: null tensor");
+    if (seq_new < 0 || past_len < 0) return fail(c, HKV_ERR_INVALID_ARG, "prefill: negative length");
+    if (c->g.batch != 1) return fail(c, HKV_ERR_GEOMETRY, "prefill: the op is batch 1 (kernels/attention.cu:709)");
+    if (seq_new == 0) return HKV_OK;
+    const hkv_geometry& g = c->g;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool ring = g.layout == HKV_LAYOUT_RING;
+    // A plane that holds the chunk next to everything it attends takes the plain order: append, attend.
+    const bool plain = !ring ? true
+                             : ((long long)past_len + seq_new <= g.slots ||
+                                (g.window_size > 0 && (long long)seq_new + g.window_size - 1 <= g.slots));
+    if (plain) {
+        int stt = launch_append(c, k_new, v_new, k_cache, v_cache, nullptr, 0, past_len, seq_new, st);
+        if (stt) return stt;
+        return hkv_prefill_attention(c, q, k_cache, v_cache, out, seq_new, past_len, scale, stream);
+    }
+    // Ring too small for that: attend first. Needs the window inside the ring and a partial-row workspace.
+    if (g.window_size <= 0 || g.window_size > g.slots || seq_new > g.slots)
+        return fail(c, HKV_ERR_GEOMETRY, "prefill: the ring must hold the window (window_size <= slots) and the chunk (seq_new <= slots)");
+    if (!prefill_tc_ok(g) || !c->prefill_ws || seq_new > g.max_seq_new || !(scale > 0.0f) || !aligned(q, 16) || !aligned(k_new, 16) ||
+        !aligned(v_new, 16) || !aligned(k_cache, 16) || !aligned(v_cache, 16) || !aligned(out, 16))
+        return fail(c, HKV_ERR_GEOMETRY, "prefill: attending before the append needs the tensor-core path (head_dim 64/96/128/256, 16-byte aligned tensors, positive scale) and max_seq_new >= seq_new");
+    // pass 1: the rows already in the ring (positions below past_len), partial 0 of 2
+    const PrefillPass cached{past_len, 0, 2};
+    int stt = prefill_tc_launch(c, g, q, k_cache, v_cache, out, seq_new, past_len, scale, st, &cached);
+    if (stt) return stt;
+    // pass 2: the chunk's own rows, as a linear plane of seq_new rows with nothing before it: positions
+    // are relative to past_len, which leaves the causal and window masks unchanged; partial 1 of 2
+    hkv_geometry gc = g;
+    gc.slots = seq_new;
+    gc.layout = HKV_LAYOUT_LINEAR;
+    gc.batch_stride_elems = 0;
+    const PrefillPass chunk{0x7fffffff, 1, 2};
+    stt = prefill_tc_launch(c, gc, q, k_new, v_new, out, seq_new, 0, scale, st, &chunk);
+    if (stt) return stt;
+    const long long rows = (long long)seq_new * g.num_heads;
+    hkv_prefill_combine_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(c->prefill_ws, (__half*)out, rows, g.num_heads, g.head_dim, 2,
+                                                                          kPrefillMaxSplits, nullptr, c->G);
+    // and only now the append (it overwrites rows pass 1 has read)
+    stt = launch_append(c, k_new, v_new, k_cache, v_cache, nullptr, 0, past_len, seq_new, st);
+    if (stt) return stt;
     const cudaError_t e = cudaPeekAtLastError();
     return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "prefill launch");
 }
@@ -1151,7 +1213,8 @@ int hkv_qk_norm_rope_kv(hkv_ctx* c, void* q, void* k, const void* v, const void*
     if (a.rot / 2 > 256) return fail(c, HKV_ERR_GEOMETRY, "qk_norm_rope: rotary_dim above 512");
     // register path: 8-byte aligned rows, head_dim and half the rotary span in whole 4-element pieces
     const bool vec = g.head_dim % 4 == 0 && (a.rot / 2) % 4 == 0 && c->batch_stride % 4 == 0 && aligned(q, 8) && aligned(k, 8) &&
-                     (!v || aligned(v, 8)) && (!k_cache || (aligned(k_cache, 8) && aligned(v_cache, 8)));
+                     aligned(q_norm_w, 8) && aligned(k_norm_w, 8) && (!v || aligned(v, 8)) &&
+                     (!k_cache || (aligned(k_cache, 8) && aligned(v_cache, 8)));
     const int per_tok = g.num_heads + 2 * g.num_kv_heads;
     const int groups = (per_tok + kRopeWarps - 1) / kRopeWarps;
     // many tokens: one CTA per token walks all its heads (one rotation table per token); few tokens: one
@@ -1214,6 +1277,7 @@ int hkv_plan_prefill(const hkv_geometry* g, int32_t seq_new, int32_t past_len, i
         return HKV_OK;
     }
     PrefillTcArgs t{};
+    t.key_limit = 0x7fffffff;
     int pair = 0, min_span = 0, grid = 0, max_parts = 0;
     std::vector<double> scratch;
     plan_prefill_tc(*g, seq_new, past_len, sm_count, g->max_seq_new >= seq_new, t, pair, min_span, grid, max_parts, scratch);

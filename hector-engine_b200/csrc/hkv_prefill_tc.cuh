@@ -54,6 +54,13 @@ struct PrefillTcArgs {
     // Equal-span schedule of the two-tile kernel: items are cut where the spans fall, so the number of
     // partial rows differs from row to row; each (query, kv head) records its count in row_parts and
     // partial p of query q sits at part[(q * part_stride + p) ...].
+    // Attend-before-append (a plane that cannot hold the chunk next to what it attends): the chunk is
+    // attended in two passes — the rows already cached (keys below key_limit = past_len) and the chunk's
+    // own rows (a second launch over k_new/v_new as a plane of their own) — each writing partial
+    // out_part of out_parts for every row, whatever its own splits.
+    int key_limit;       // attend keys below this position only; INT_MAX = no limit
+    int out_part;        // with out_parts > 0: the partial slot every row of this launch writes
+    int out_parts;       // 0 = decided by the schedule
     int streamk;
     int sk_whole;        // items (longest first) run whole before the equal spans; a multiple of the grid
     int sk_grid;         // CTAs that share the remaining items' key tiles
@@ -85,11 +92,14 @@ __host__ __device__ inline int prefill_tile_row(const PrefillTcArgs& a, int pos0
 // Positions [0, kv_valid) hold data; beyond them a plane may hold stale bits.
 __host__ __device__ inline int prefill_kv_valid(const PrefillTcArgs& a) {
     const int end = a.past_len + a.S_new;
-    return (a.ring || end < a.slots) ? end : a.slots;
+    const int v = (a.ring || end < a.slots) ? end : a.slots;
+    return v < a.key_limit ? v : a.key_limit;
 }
-// Last key a query at position qpos may attend (a linear plane drops rows past its end).
+// Last key a query at position qpos may attend (a linear plane drops rows past its end; a pass
+// limited to the rows already cached stops below key_limit).
 __host__ __device__ inline int prefill_last_key(const PrefillTcArgs& a, int qpos) {
-    return (a.ring || qpos < a.slots) ? qpos : a.slots - 1;
+    const int k = (a.ring || qpos < a.slots) ? qpos : a.slots - 1;
+    return k < a.key_limit ? k : a.key_limit - 1;
 }
 // Key tiles an item of `q_item` queries (item index qt) spans, before any key split.
 __host__ __device__ inline void prefill_item_tiles(const PrefillTcArgs& a, int q_item, int keys, int qt, int& kt0, int& ntot) {
@@ -550,7 +560,9 @@ hkv_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             float* prow = nullptr;
             __half* op = nullptr;
             if (row_valid) {
-                if (a.splits > 1) prow = a.part + (((long long)qi * a.splits + sp) * a.H + (long long)kvh * a.G + g) * (a.HD + 2);
+                const int parts = a.out_parts > 0 ? a.out_parts : a.splits;
+                const int part = a.out_parts > 0 ? a.out_part * a.splits + sp : sp;
+                if (parts > 1) prow = a.part + (((long long)qi * a.part_stride + part) * a.H + (long long)kvh * a.G + g) * (a.HD + 2);
                 else op = a.out + ((long long)qi * a.H + (long long)kvh * a.G + g) * a.HD;
             }
 #pragma unroll

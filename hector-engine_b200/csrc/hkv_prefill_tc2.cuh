@@ -324,7 +324,8 @@ hkv_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     int qt, kvh, sp, kt_lo, nt;
                     decode_item(item, qt, kvh, sp);
                     tile_span(qt, sp, kt_lo, nt);
-                    run_piece(qt, kvh, kt_lo, nt, sp, a.splits);
+                    if (a.out_parts > 0) run_piece(qt, kvh, kt_lo, nt, a.out_part * a.splits + sp, a.out_parts * a.splits);
+                    else run_piece(qt, kvh, kt_lo, nt, sp, a.splits);
                 }
             }
             publish(-1, 0, 0, 0, 0, 0);   // no more work (also after a wait that ran out: the other roles leave at once)

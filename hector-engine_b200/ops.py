@@ -174,6 +174,14 @@ class Context:
         self._check(self.lib.hkv_prefill_attention(self._h, _ptr(q), _ptr(k_cache), _ptr(v_cache),
                                                    _ptr(out), seq_new, past_len, scale, _stream(stream)))
 
+    def prefill_append_attention(self, q, k_new, v_new, k_cache, v_cache, out, seq_new, past_len, scale=None, stream=None):
+        """Append a chunk's K/V rows at past_len and attend its queries over the cache — for a ring plane
+        of exactly `window` rows in the order attend, then append (hkv_prefill_append_attention)."""
+        scale = self.geometry.default_scale if scale is None else scale
+        self._check(self.lib.hkv_prefill_append_attention(self._h, _ptr(q), _ptr(k_new), _ptr(v_new), _ptr(k_cache),
+                                                          _ptr(v_cache), _ptr(out), seq_new, past_len, scale,
+                                                          _stream(stream)))
+
     def plan_prefill(self, seq_new: int, past_len: int, sm_count: int | None = None):
         """Host plan of one prefill_attention call -> (query tiles in flight per CTA: 2, 1, or 0 for the
         SIMT kernel; work items; key-range splits; shortest key span in tiles)."""

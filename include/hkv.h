@@ -172,6 +172,19 @@ int hkv_append_decode_attention(hkv_ctx* ctx, const void* q, const void* k_new, 
 int hkv_prefill_attention(hkv_ctx* ctx, const void* q, const void* k_cache, const void* v_cache,
                           void* out, int32_t seq_new, int32_t past_len, float scale, void* stream);
 
+/* Prefill chunk, append included: equals hkv_append_at(k_new, v_new at past_len) followed by
+ * hkv_prefill_attention — the reference's KV_CACHE_UPDATE + ATTENTION_PREFILL_CACHED pair
+ * (src/graph_builder.cpp emits them back to back; kernels/attention.cu:1099-1116, :775-788) — for
+ * every plane, including a ring plane that cannot hold the chunk next to what it attends (a ring
+ * of exactly window_size rows: the reference has no ring). There the chunk is attended BEFORE it
+ * is appended, in two passes over the tensor cores — the rows already cached, and the chunk's own
+ * k_new/v_new — whose partial rows are merged; then the rows are written. Needs window_size <=
+ * slots, seq_new <= slots and, for that order, a context with max_seq_new >= seq_new.
+ * k_new, v_new [seq_new, num_kv_heads, head_dim]; batch 1. */
+int hkv_prefill_append_attention(hkv_ctx* ctx, const void* q, const void* k_new, const void* v_new,
+                                 void* k_cache, void* v_cache, void* out, int32_t seq_new,
+                                 int32_t past_len, float scale, void* stream);
+
 /* Cached decode attention for callers that cannot allocate. It has no counterpart in the
  * reference. Same inputs, outputs and results as hkv_decode_attention, but it needs no
  * context: the split-K partials are kept in a fixed array inside the library image

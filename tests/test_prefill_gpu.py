@@ -233,3 +233,76 @@ def test_prefill_refuses_a_chunk_that_overwrites_what_it_attends(hkv, cuda):
     ctx.prefill_attention(t, t, t, t, 100, 100, 1.0)    # nothing overwritten yet
     torch.cuda.synchronize()
     ctx.close()
+
+
+EXACT_RING_CASES = [
+    # name, H, KVH, HD, ring rows (= window), past_len, S_new
+    ("gemma_local_first_chunk", 16, 8, 256, 1024, 0, 512),
+    ("gemma_local_second_chunk_fills_the_ring", 16, 8, 256, 1024, 512, 512),
+    ("gemma_local_wrapped", 16, 8, 256, 1024, 30720, 512),
+    ("hd128_group7_wrapped_ragged", 28, 4, 128, 256, 1000, 200),
+    ("hd96_wrapped_chunk_as_long_as_the_ring", 8, 8, 96, 256, 777, 256),
+    ("hd64_single_query", 8, 2, 64, 128, 5000, 1),
+]
+
+
+@pytest.mark.parametrize("case", EXACT_RING_CASES, ids=lambda c: c[0])
+def test_prefill_chunk_into_a_ring_of_exactly_window_rows(hkv, cuda, oracle, case):
+    """A sliding-window layer whose ring holds exactly `window` rows cannot take a chunk and then attend it
+    (the chunk would overwrite rows its first queries still need): hkv_prefill_append_attention attends
+    first — the cached rows and the chunk's own K/V in two tensor-core passes, merged — and appends
+    afterwards. Output equals the oracle on a linear plane with the same window; the ring afterwards holds
+    the last `rows` positions bit-exact."""
+    torch = cuda
+    name, H, KVH, HD, rows, past, S_new = case
+    window = rows
+    rng = np.random.default_rng(len(name) * 17 + HD)
+    total = past + S_new
+    lin_k = normal_f16(rng, 1, total, KVH, HD)
+    lin_v = normal_f16(rng, 1, total, KVH, HD)
+    q = normal_f16(rng, S_new, H, HD)
+    scale = 1.0 / math.sqrt(HD)
+    ref = oracle.prefill(q, lin_k[0], lin_v[0], past, scale, window=window, threads=8)
+    ring_k = np.full((1, rows, KVH, HD), np.nan, np.float16)     # rows never written: poison
+    ring_v = np.full((1, rows, KVH, HD), np.inf, np.float16)
+    for p in range(max(0, past - rows), past):
+        ring_k[0, p % rows], ring_v[0, p % rows] = lin_k[0, p], lin_v[0, p]
+    ctx = hkv.Context(hkv.Geometry(batch=1, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=rows,
+                                   window_size=window, layout=hkv.LAYOUT_RING, max_seq_new=512))
+    dk, dv = to_dev(torch, ring_k), to_dev(torch, ring_v)
+    out = torch.full((S_new, H, HD), float("nan"), dtype=torch.float16, device="cuda")
+    ctx.prefill_append_attention(to_dev(torch, q), to_dev(torch, lin_k[0, past:]), to_dev(torch, lin_v[0, past:]),
+                                 dk, dv, out, S_new, past, scale)
+    assert ctx.device_status() == 0
+    got = out.cpu().numpy()
+    assert not np.isnan(got.astype(np.float32)).any()
+    assert_close(oracle, got, ref, name)
+    want_k, want_v = ring_k.copy(), ring_v.copy()
+    for p in range(past, total):
+        want_k[0, p % rows], want_v[0, p % rows] = lin_k[0, p], lin_v[0, p]
+    assert np.array_equal(dk.cpu().numpy().view(np.uint16), want_k.view(np.uint16))
+    assert np.array_equal(dv.cpu().numpy().view(np.uint16), want_v.view(np.uint16))
+    ctx.close()
+
+
+def test_prefill_append_attention_on_a_linear_plane_is_append_then_attend(hkv, cuda, oracle):
+    """Where the plane holds the chunk next to what it attends the combined entry point is the
+    reference's own pair of ops: KV_CACHE_UPDATE, then ATTENTION_PREFILL_CACHED."""
+    torch = cuda
+    H, KVH, HD, slots, past, S_new = 28, 4, 128, 1024, 300, 140
+    rng = np.random.default_rng(5)
+    kc, vc = normal_f16(rng, 1, slots, KVH, HD), normal_f16(rng, 1, slots, KVH, HD)
+    nk, nv = normal_f16(rng, 1, S_new, KVH, HD), normal_f16(rng, 1, S_new, KVH, HD)
+    q = normal_f16(rng, S_new, H, HD)
+    scale = 1.0 / math.sqrt(HD)
+    ref_k, ref_v = kc.copy(), vc.copy()
+    oracle.append(nk, nv, ref_k, ref_v, np.array([past], np.int32))
+    ref = oracle.prefill(q, ref_k[0], ref_v[0], past, scale, threads=8)
+    ctx = hkv.Context(hkv.Geometry(batch=1, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots, max_seq_new=512))
+    dk, dv = to_dev(torch, kc), to_dev(torch, vc)
+    out = torch.zeros(S_new, H, HD, dtype=torch.float16, device="cuda")
+    ctx.prefill_append_attention(to_dev(torch, q), to_dev(torch, nk), to_dev(torch, nv), dk, dv, out, S_new, past, scale)
+    assert ctx.device_status() == 0
+    assert np.array_equal(dk.cpu().numpy().view(np.uint16), ref_k.view(np.uint16))
+    assert_close(oracle, out.cpu().numpy(), ref, "append then attend")
+    ctx.close()
