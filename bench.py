@@ -88,6 +88,8 @@ def parse_args():
                          "sequence-split legs). seqsplit: only the sequence-split leg; --ctx is then the LOGICAL "
                          "context, split over the GPUs. prefill / rope: one kernel's own figure")
     ap.add_argument("--shard-block", type=int, default=1024)
+    ap.add_argument("--exchange", default="auto", choices=["auto", "nccl", "peer"],
+                    help="sequence split: how partials travel between the ranks")
     ap.add_argument("--linear-window", action="store_true",
                     help="window layers keep a linear plane + mask (the reference's layout) instead of a ring")
     return ap.parse_args()
@@ -692,9 +694,10 @@ def rope_record(args, torch, hkv, oracle, cfg, name, B, S, slots, steps, warmup)
 # ---------------------------------------------------------------------------
 def seqsplit_leg(args, torch, hkv, oracle, dist, cfg, logical_ctx, B, rank, world, gpu_id, steps, warmup, label):
     """One logical cache of `logical_ctx` rows per sequence, dealt block-cyclically over the ranks.
-    Per layer: local split-K decode with the append fused in -> NCCL all-gather of one partial per
-    (sequence, head) -> merge; all layers captured once as a CUDA graph by the C++ decoder and replayed.
-    Output replicated on all ranks. Returns the record (rank 0) or None."""
+    Per layer: local split-K decode with the append fused in -> one partial per (sequence, head) to every
+    rank (stored into the ranks' mailboxes over NVLink by the kernel that merges the local partials; or an
+    NCCL all-gather, timed beside it) -> merge; all layers captured once as a CUDA graph by the C++ decoder
+    and replayed. Output replicated on all ranks. Returns the record (rank 0) or None."""
     L, H, KVH, HD = cfg["layers"], cfg["H"], cfg["KVH"], cfg["HD"]
     shard = hkv.dist.SeqShard(rank, world, args.shard_block)
     ctx_local = shard.slots_for(logical_ctx)
@@ -721,17 +724,22 @@ def seqsplit_leg(args, torch, hkv, oracle, dist, cfg, logical_ctx, B, rank, worl
     torch.cuda.synchronize()
     # NCCL announces its version on stdout when a communicator is first created (with NCCL_DEBUG set):
     # stdout carries the one JSON line, so the descriptor points at stderr while the decoder is built
-    sys.stdout.flush()
-    saved_stdout = os.dup(1)
-    os.dup2(2, 1)
-    try:
-        dec = hkv.dist.SeqSplitDecoder(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=ctx_local,
-                                                    kernel_select=args.kernel, chunk_tiles=args.chunk_tiles),
-                                       shard, layers=L, scale=scale, stream=stream)
-    finally:
-        os.dup2(saved_stdout, 1)
-        os.close(saved_stdout)
-    dec.bind(q, kn, vn, out, k, v, B * ctx_local * row, d_tot)
+    def make_decoder(exchange):
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            d = hkv.dist.SeqSplitDecoder(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=ctx_local,
+                                                      kernel_select=args.kernel, chunk_tiles=args.chunk_tiles),
+                                         shard, layers=L, scale=scale, stream=stream, exchange=exchange)
+        finally:
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
+        d.bind(q, kn, vn, out, k, v, B * ctx_local * row, d_tot)
+        return d
+
+    dec = make_decoder(args.exchange)
+    exchange = dec.exchange if world > 1 else "none"
 
     def barrier():
         torch.cuda.synchronize()
@@ -815,6 +823,37 @@ def seqsplit_leg(args, torch, hkv, oracle, dist, cfg, logical_ctx, B, rank, worl
     barrier()
     assert dec.device_status() == 0
     dms, gms, cms = (float(np.median([p[i] for p in prof])) / L for i in range(3))
+    # the same step with the other exchange (the collective), timed the same way, for comparison
+    other = None
+    if world > 1 and exchange == "peer":
+        dec.close()
+        dec = make_decoder("nccl")
+        with torch.cuda.stream(stream):
+            d_tot.copy_(h_tot, non_blocking=True)
+        for _ in range(max(warmup, 2)):
+            step()
+        with torch.cuda.stream(stream):
+            d_tot.copy_(h_tot, non_blocking=True)
+        barrier()
+        ev2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        ev2[0].record(stream)
+        for i in range(steps):
+            step()
+        ev2[1].record(stream)
+        dec.wait(120000)
+        barrier()
+        ms2 = torch.tensor([ev2[0].elapsed_time(ev2[1])], device=dev)
+        dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
+        prof2 = []
+        for _ in range(3):
+            with torch.cuda.stream(stream):
+                prof2.append(dec.step_profiled())
+        barrier()
+        other = {"exchange": "nccl all-gather", "ms_per_step": float(ms2.item()) / steps,
+                 "value": B / (float(ms2.item()) / steps / 1e3),
+                 "decode_ms_per_layer": float(np.median([p[0] for p in prof2])) / L,
+                 "allgather_ms_per_layer": float(np.median([p[1] for p in prof2])) / L,
+                 "combine_ms_per_layer": float(np.median([p[2] for p in prof2])) / L}
     Ls = np.stack([np.minimum(pos0 + 1 + s, logical_ctx) for s in range(steps)]).astype(np.int64)
     # algorithmic bytes over ALL ranks: the K/V rows of every sequence once, + the new row once, + q/out per rank
     alg = float((4 * Ls * KVH * HD).sum(axis=1).mean() + B * 8 * KVH * HD + world * B * 4 * H * HD) * L
@@ -824,9 +863,13 @@ def seqsplit_leg(args, torch, hkv, oracle, dist, cfg, logical_ctx, B, rank, worl
         rec = {"label": label, "workload": f"qwen2-7b-shaped long-context decode: {L} layers, logical ctx {logical_ctx} "
                                            f"dealt block-cyclically ({args.shard_block}) over {world} GPU(s) = {ctx_local} rows "
                                            f"per GPU, batch {B}",
-               "parallelism": f"sequence-split x{world}" + (f", NCCL all-gather of {B * H * (HD + 2) * 4} B per rank per layer"
-                                                            if world > 1 else " (no collective)"),
-               "host": "C++ (libhkv_dist): all layers captured once as a CUDA graph, NCCL on the compute stream",
+               "parallelism": f"sequence-split x{world}" + (
+                   " (no exchange)" if world == 1 else
+                   f", {B * H * (HD + 2) * 4} B per rank per layer stored into every rank's mailbox over NVLink by the kernel "
+                   "that merges the local partials; bounded flag wait in the final merge; no collective launch"
+                   if exchange == "peer" else f", NCCL all-gather of {B * H * (HD + 2) * 4} B per rank per layer"),
+               "exchange": exchange,
+               "host": "C++ (libhkv_dist): all layers captured once as a CUDA graph on the compute stream",
                "n_gpus": world, "batch": B, "ctx": logical_ctx, "rows_per_gpu": ctx_local, "scaling": "strong",
                "value": B / (ms_per_step / 1e3), "unit": "tokens/s", "ms_per_step": ms_per_step,
                "ms_per_step_median_rank0": st["ms_per_step_median"], "ms_per_step_min_rank0": st["ms_per_step_min"],
@@ -834,6 +877,9 @@ def seqsplit_leg(args, torch, hkv, oracle, dist, cfg, logical_ctx, B, rank, worl
                "hbm_gbs_per_gpu": alg / world / (ms_per_step * 1e-3) / 1e9,
                "hbm_frac_of_8TBs_per_gpu": alg / world / (ms_per_step * 1e-3) / 1e9 / 8000.0,
                "decode_ms_per_layer": dms, "allgather_ms_per_layer": gms, "combine_ms_per_layer": cms,
+               "phases": ("decode = split-K kernel + local merge that pushes; combine = flag wait + final merge"
+                          if exchange == "peer" else "decode = split-K kernel + local merge; all-gather; combine = final merge"),
+               "with_nccl_allgather": other,
                "parity_max_abs_err": err, "clocks": clocks, "gpu_launches": steps * L * 3}
     dec.close()
     del k, v, q, kn, vn, out, dec

@@ -36,6 +36,17 @@ class HkvGeometry(C.Structure):
     ]
 
 
+MAX_PEERS = 8
+
+
+class HkvExchange(C.Structure):
+    """Mirror of `struct hkv_exchange` (include/hkv.h): the mailboxes of a peer exchange."""
+    _fields_ = [
+        ("rank", C.c_int32), ("world", C.c_int32), ("mailbox", C.c_void_p * MAX_PEERS),
+        ("wait_limit_ms", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/hkv.h declares
 _VP, _I32P, _F32P = C.c_void_p, C.c_void_p, C.c_void_p
 SIGNATURES = {
@@ -59,6 +70,9 @@ SIGNATURES = {
     "hkv_partial_floats": (C.c_size_t, [C.POINTER(HkvGeometry)]),
     "hkv_decode_partials": (C.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, _F32P, _I32P, C.c_float, _VP]),
     "hkv_combine_partials": (C.c_int, [_VP, _F32P, C.c_int32, _VP, _VP]),
+    "hkv_exchange_bytes": (C.c_int, [_VP, C.c_int32, C.POINTER(C.c_size_t)]),
+    "hkv_decode_partials_publish": (C.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, C.POINTER(HkvExchange), _I32P, C.c_float, _VP]),
+    "hkv_merge_published": (C.c_int, [_VP, C.POINTER(HkvExchange), _VP, _VP]),
     "hkv_append_decode_attention_host": (C.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I32P, C.c_float, _VP]),
     "hkv_qk_norm_rope_kv": (C.c_int, [_VP] * 8 + [_I32P, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_float, C.c_float, _VP]),
     "hkv_ctx_selftest_bounded_wait": (C.c_int, [_VP, C.c_int32, _VP]),

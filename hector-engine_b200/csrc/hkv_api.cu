@@ -94,6 +94,10 @@ int fail(hkv_ctx* c, int code, const char* msg) {
     if (c) c->err = msg;
     return code;
 }
+int fail(hkv_ctx* c, int code, const std::string& msg) {
+    if (c) c->err = msg;
+    return code;
+}
 int fail_cuda(hkv_ctx* c, cudaError_t e, const char* where) {
     if (c) c->err = std::string(where) + ": " + cudaGetErrorString(e);
     return HKV_ERR_CUDA;
@@ -643,10 +647,42 @@ int launch_decode(hkv_ctx* c, const void* q, const void* k_new, const void* v_ne
     return HKV_OK;
 }
 
+constexpr size_t kMailboxHeaderBytes = 512;   // 64 flag words + 64 state words
+
+int check_exchange(hkv_ctx* c, const hkv_exchange* x, const char* who) {
+    if (!x) return fail(c, HKV_ERR_INVALID_ARG, std::string(who) + ": null exchange");
+    if (x->world < 1 || x->world > HKV_MAX_PEERS || x->rank < 0 || x->rank >= x->world)
+        return fail(c, HKV_ERR_INVALID_ARG, std::string(who) + ": rank/world out of range (at most " +
+                                                std::to_string(HKV_MAX_PEERS) + " ranks)");
+    const int shards = c->g.shard_count > 1 ? c->g.shard_count : 1;
+    if (x->world != shards || (shards > 1 && x->rank != c->g.shard_rank))
+        return fail(c, HKV_ERR_GEOMETRY, std::string(who) + ": exchange rank/world differ from the context's shard_rank/shard_count");
+    for (int r = 0; r < x->world; ++r) {
+        if (!x->mailbox[r]) return fail(c, HKV_ERR_INVALID_ARG, std::string(who) + ": null mailbox");
+        if (!aligned(x->mailbox[r], 256)) return fail(c, HKV_ERR_ALIGNMENT, std::string(who) + ": mailbox not 256-byte aligned");
+    }
+    if (x->wait_limit_ms < 0 || x->wait_limit_ms > 10000)
+        return fail(c, HKV_ERR_INVALID_ARG, std::string(who) + ": wait_limit_ms outside 0..10000");
+    return HKV_OK;
+}
+
 int launch_combine(hkv_ctx* c, const float* part, long long stride_b, long long stride_c,
                    const int32_t* d_total, int pos_is_index, int host_len, int fixed_count, void* out,
-                   float* out_partial, cudaStream_t st, bool span = false) {
+                   float* out_partial, cudaStream_t st, bool span = false, const hkv_exchange* x = nullptr) {
     CombineArgs a;
+    a.pub_n = 0;
+    a.pub_state = nullptr;
+    a.pub_part = nullptr;
+    a.pub_parity_stride = 0;
+    if (x) {
+        // mailbox: 64 flag words, 64 state words, then [2][batch*heads*(head_dim+2)] floats
+        uint8_t* mine = (uint8_t*)x->mailbox[x->rank];
+        a.pub_n = x->world;
+        a.pub_part = (float*)(mine + kMailboxHeaderBytes);
+        a.pub_parity_stride = (long long)c->g.batch * c->g.num_heads * (c->g.head_dim + 2);
+        for (int r = 0; r < x->world; ++r) a.pub_flag[r] = (uint32_t*)x->mailbox[r] + x->rank;
+        a.pub_state = (uint32_t*)(mine + kMailboxHeaderBytes / 2);
+    }
     a.gpre = span ? c->span_gpre : nullptr;
     a.span_spans = span ? c->tma_grid / c->span_gang : 0;
     a.B = c->g.batch;
@@ -680,9 +716,9 @@ int launch_combine(hkv_ctx* c, const float* part, long long stride_b, long long 
 
 int decode_full(hkv_ctx* c, const void* q, const void* k_new, const void* v_new, void* k_cache,
                 void* v_cache, void* out, float* out_partial, const int32_t* d_total,
-                int pos_is_index, int host_len, float scale, cudaStream_t st) {
+                int pos_is_index, int host_len, float scale, cudaStream_t st, const hkv_exchange* x = nullptr) {
     if (!c->workspace) return fail(c, HKV_ERR_WORKSPACE, "decode: the context was created append-only");
-    if (!out && !out_partial) return fail(c, HKV_ERR_INVALID_ARG, "decode: null output");
+    if (!out && !out_partial && !x) return fail(c, HKV_ERR_INVALID_ARG, "decode: null output");
     if (out && !aligned(out, 2)) return fail(c, HKV_ERR_ALIGNMENT, "decode: out not 2-byte aligned");
     const bool timed = c->prof_calls < c->prof_max;
     cudaEvent_t* ev = timed ? &c->prof_events[(size_t)c->prof_calls * 3] : nullptr;
@@ -694,7 +730,7 @@ int decode_full(hkv_ctx* c, const void* q, const void* k_new, const void* v_new,
     const long long PW = c->g.head_dim + 2;
     stt = launch_combine(c, used_tma ? c->span_ws : c->workspace, (long long)c->max_chunks * c->g.num_heads * PW,
                          (long long)c->g.num_heads * PW, d_total, pos_is_index, host_len, 0, out, out_partial,
-                         st, used_tma);
+                         st, used_tma, x);
     if (stt) return stt;
     if (timed) {
         cudaEventRecord(ev[2], st);
@@ -1015,6 +1051,51 @@ int hkv_combine_partials(hkv_ctx* c, const float* partials, int32_t num_parts, v
     return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "combine launch");
 }
 
+int hkv_exchange_bytes(const hkv_ctx* c, int32_t world, size_t* bytes_out) {
+    if (!c || !bytes_out || world < 1 || world > HKV_MAX_PEERS) return HKV_ERR_INVALID_ARG;
+    *bytes_out = kMailboxHeaderBytes + 2ull * c->g.batch * c->g.num_heads * (size_t)(c->g.head_dim + 2) * sizeof(float);
+    return HKV_OK;
+}
+
+int hkv_decode_partials_publish(hkv_ctx* c, const void* q, const void* k_new, const void* v_new,
+                             void* k_cache, void* v_cache, const hkv_exchange* exchange,
+                             const int32_t* d_total_seq, float scale, void* stream) {
+    HKV_CHECK_CTX(c);
+    const int stx = check_exchange(c, exchange, "decode_partials_publish");
+    if (stx) return stx;
+    if (!d_total_seq) return fail(c, HKV_ERR_INVALID_ARG, "decode_partials_publish: null length array");
+    if (k_new && !v_new) return fail(c, HKV_ERR_INVALID_ARG, "decode_partials_publish: k_new without v_new");
+    if (k_new && (!aligned(k_new, 2) || !aligned(v_new, 2)))
+        return fail(c, HKV_ERR_ALIGNMENT, "decode_partials_publish: fp16 pointer not 2-byte aligned");
+    return decode_full(c, q, k_new, v_new, k_cache, v_cache, nullptr, nullptr, d_total_seq, 0, 0, scale,
+                       (cudaStream_t)stream, exchange);
+}
+
+int hkv_merge_published(hkv_ctx* c, const hkv_exchange* exchange, void* out, void* stream) {
+    HKV_CHECK_CTX(c);
+    const int stx = check_exchange(c, exchange, "merge_published");
+    if (stx) return stx;
+    if (!out) return fail(c, HKV_ERR_INVALID_ARG, "merge_published: null output");
+    if (!aligned(out, 2)) return fail(c, HKV_ERR_ALIGNMENT, "merge_published: out not 2-byte aligned");
+    if (c->g.head_dim > 512) return fail(c, HKV_ERR_GEOMETRY, "merge_published: head_dim above 512");
+    MergePublishedArgs a;
+    uint8_t* box = (uint8_t*)exchange->mailbox[exchange->rank];
+    for (int r = 0; r < exchange->world; ++r)
+        a.part[r] = (const float*)((const uint8_t*)exchange->mailbox[r] + kMailboxHeaderBytes);
+    a.flags = (const uint32_t*)box;
+    a.state = (const uint32_t*)(box + kMailboxHeaderBytes / 2);
+    a.world = exchange->world;
+    a.rows = c->g.batch * c->g.num_heads;
+    a.HD = c->g.head_dim;
+    a.out = (__half*)out;
+    a.status = c->d_status;
+    a.limit_ns = (unsigned long long)(exchange->wait_limit_ms > 0 ? exchange->wait_limit_ms : 2000) * 1000000ull;
+    const unsigned blocks = (unsigned)((a.rows + kMergeWarps - 1) / kMergeWarps);
+    hkv_merge_published_kernel<<<blocks, kMergeWarps * 32, 0, (cudaStream_t)stream>>>(a);
+    const cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "merge_published launch");
+}
+
 int hkv_prefill_attention(hkv_ctx* c, const void* q, const void* k_cache, const void* v_cache,
                           void* out, int32_t seq_new, int32_t past_len, float scale, void* stream) {
     HKV_CHECK_CTX(c);
@@ -1211,17 +1292,31 @@ int hkv_qk_norm_rope_kv(hkv_ctx* c, void* q, void* k, const void* v, const void*
     a.scaling = scaling_factor <= 0.0f ? 1.0f : scaling_factor;
     const long long tokens = (long long)g.batch * seq_new;
     if (a.rot / 2 > 256) return fail(c, HKV_ERR_GEOMETRY, "qk_norm_rope: rotary_dim above 512");
-    // register path: 8-byte aligned rows, head_dim and half the rotary span in whole 4-element pieces
-    const bool vec = g.head_dim % 4 == 0 && (a.rot / 2) % 4 == 0 && c->batch_stride % 4 == 0 && aligned(q, 8) && aligned(k, 8) &&
-                     aligned(q_norm_w, 8) && aligned(k_norm_w, 8) && (!v || aligned(v, 8)) &&
-                     (!k_cache || (aligned(k_cache, 8) && aligned(v_cache, 8)));
-    const int per_tok = g.num_heads + 2 * g.num_kv_heads;
-    const int groups = (per_tok + kRopeWarps - 1) / kRopeWarps;
-    // many tokens: one CTA per token walks all its heads (one rotation table per token); few tokens: one
-    // CTA per group of 8 heads, so that a decode launch still spreads over the SMs
-    const unsigned gx = tokens >= 2LL * c->sm_count ? 1u : (unsigned)groups;
-    const unsigned gy = (unsigned)(tokens < 65535 ? tokens : 65535);
-    hkv_qk_norm_rope_kernel<<<dim3(gx, gy), kRopeWarps * 32, 0, (cudaStream_t)stream>>>(a, vec ? 1 : 0);
+    // register path: 16-byte aligned rows, head_dim and half the rotary span in whole 8-element pieces
+    const bool fast = g.head_dim % 8 == 0 && g.head_dim <= 256 && (a.rot / 2) % 8 == 0 && c->batch_stride % 8 == 0 &&
+                      aligned(q, 16) && aligned(k, 16) && (!v || aligned(v, 16)) &&
+                      (!k_cache || (aligned(k_cache, 16) && aligned(v_cache, 16)));
+    const bool copy_v = k_cache && v;
+    const int per_tok = g.num_heads + g.num_kv_heads + ((fast ? copy_v : true) ? g.num_kv_heads : 0);
+    int heads_per_warp = 1;
+    if (fast) {
+        int lanes = 1;
+        while (lanes < g.head_dim / 8) lanes <<= 1;
+        heads_per_warp = 32 / lanes;
+    }
+    const int warp_units = (per_tok + heads_per_warp - 1) / heads_per_warp;
+    // many tokens: a CTA owns a contiguous range of tokens (equal ranges, at most four resident CTAs per
+    // SM: one wave); few tokens: one range per token and as many CTAs per token as its units fill, so
+    // that a decode launch still spreads over the SMs
+    unsigned gx = 1, gy;
+    if (tokens >= 2LL * c->sm_count) {
+        const long long per = (tokens + 4LL * c->sm_count - 1) / (4LL * c->sm_count);
+        gy = (unsigned)((tokens + per - 1) / per);
+    } else {
+        gx = (unsigned)((warp_units + kRopeWarps - 1) / kRopeWarps);
+        gy = (unsigned)tokens;
+    }
+    hkv_qk_norm_rope_kernel<<<dim3(gx, gy), kRopeWarps * 32, 0, (cudaStream_t)stream>>>(a, fast ? 1 : 0);
     const cudaError_t e = cudaPeekAtLastError();
     return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "qk_norm_rope launch");
 }

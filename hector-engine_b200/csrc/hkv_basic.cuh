@@ -167,10 +167,46 @@ struct CombineArgs {
     int H, HD;
     __half* out;         // [B, H, HD] or null
     float* out_partial;  // [B, H, HD+2] or null
+    // Peer exchange (pub_n > 0): the merged partial goes to this rank's own mailbox (local memory, the
+    // parity of the current epoch); the last CTA to finish publishes the new epoch in every rank's
+    // mailbox (one 4-byte store per rank over NVLink). The peers then READ the partial from here.
+    int pub_n;
+    float* pub_part;                 // parity 0 of the partial area of this rank's mailbox
+    long long pub_parity_stride;     // floats between the two parities
+    uint32_t* pub_flag[kMaxPeers];   // this rank's flag word in mailbox r
+    uint32_t* pub_state;             // this rank's own {epoch, CTAs finished}
 };
 
 constexpr int kCombineWarps = 8;
 constexpr int kCombineThreads = kCombineWarps * 32;
+
+// Epoch of the exchange a merging launch belongs to (all CTAs read it before the last one advances it).
+__device__ __forceinline__ uint32_t pub_epoch(const CombineArgs& a) {
+    return a.pub_n ? *reinterpret_cast<volatile uint32_t*>(a.pub_state) : 0u;
+}
+__device__ __forceinline__ void store_partial(const CombineArgs& a, const uint32_t epoch, const long long idx, const float v) {
+    if (a.out_partial) a.out_partial[idx] = v;
+    if (a.pub_n) a.pub_part[(long long)(epoch & 1u) * a.pub_parity_stride + idx] = v;
+}
+// After a CTA's last store: the classic last-block pattern (stores, device-scope fence, counter). The
+// CTA that finds itself last has, through the counter, observed every other CTA's stores; its
+// system-scope fence orders all of them before the flag stores that release the epoch to the peers.
+// Never waits.
+__device__ __forceinline__ void pub_publish(const CombineArgs& a, const uint32_t epoch) {
+    if (!a.pub_n) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t ctas = gridDim.x * gridDim.y;
+        if (atomicAdd(a.pub_state + 1, 1u) == ctas - 1) {
+            a.pub_state[1] = 0;
+            *reinterpret_cast<volatile uint32_t*>(a.pub_state) = epoch + 1;
+            __threadfence_system();
+            for (int r = 0; r < a.pub_n; ++r)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.pub_flag[r]), "r"(epoch + 1) : "memory");
+        }
+    }
+}
 
 // One CTA per (head, sequence). The partials are dealt to the warps (warp w takes c = w, w+8, ...);
 // a warp reads one partial row at a time, lane l the output dimensions l, l+32, ... — coalesced
@@ -197,6 +233,7 @@ __global__ void __launch_bounds__(kCombineThreads) hkv_combine_kernel(const Comb
         base = a.part + b * a.stride_b + (long long)h * PW;
     }
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t epoch = pub_epoch(a);
     __shared__ float s_red[kCombineWarps];
     __shared__ float s_acc[kCombineWarps][512];   // head_dim <= 512
     // M = max over partials
@@ -243,13 +280,13 @@ __global__ void __launch_bounds__(kCombineThreads) hkv_combine_kernel(const Comb
 #pragma unroll
         for (int w = 0; w < kCombineWarps; ++w) o += s_acc[w][d];
         if (a.out) a.out[((long long)b * a.H + h) * a.HD + d] = __float2half_rn(o * inv);
-        if (a.out_partial) a.out_partial[((long long)b * a.H + h) * PW + d] = o;
+        store_partial(a, epoch, ((long long)b * a.H + h) * PW + d, o);
     }
-    if (a.out_partial && tid == 0) {
-        float* row = a.out_partial + ((long long)b * a.H + h) * PW;
-        row[a.HD] = M;
-        row[a.HD + 1] = L;
+    if (tid == 0) {
+        store_partial(a, epoch, ((long long)b * a.H + h) * PW + a.HD, M);
+        store_partial(a, epoch, ((long long)b * a.H + h) * PW + a.HD + 1, L);
     }
+    pub_publish(a, epoch);
 }
 
 // The merge for many (sequence, head) rows: one thread per output dimension walks the row's
@@ -275,6 +312,7 @@ __global__ void __launch_bounds__(128) hkv_combine_few_kernel(const CombineArgs 
         base = a.part + b * a.stride_b + (long long)h * PW;
     }
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t epoch = pub_epoch(a);
     __shared__ float s_red[4];
     __shared__ float s_w[128];
     // M = max over partials: the chunks are spread over the threads, so the loads overlap
@@ -320,13 +358,103 @@ __global__ void __launch_bounds__(128) hkv_combine_few_kernel(const CombineArgs 
         const int d = tid + 128 * i;
         if (d < a.HD) {
             if (a.out) a.out[((long long)b * a.H + h) * a.HD + d] = __float2half_rn(acc[i] * inv);
-            if (a.out_partial) a.out_partial[((long long)b * a.H + h) * PW + d] = acc[i];
+            store_partial(a, epoch, ((long long)b * a.H + h) * PW + d, acc[i]);
         }
     }
-    if (a.out_partial && threadIdx.x == 0) {
-        float* row = a.out_partial + ((long long)b * a.H + h) * PW;
-        row[a.HD] = M;
-        row[a.HD + 1] = L;
+    if (threadIdx.x == 0) {
+        store_partial(a, epoch, ((long long)b * a.H + h) * PW + a.HD, M);
+        store_partial(a, epoch, ((long long)b * a.H + h) * PW + a.HD + 1, L);
+    }
+    pub_publish(a, epoch);
+}
+
+// ---------------------------------------------------------------------------
+// Merge of published partials: the receiving half of the peer exchange. Every CTA first waits — with
+// a bound — until the flag of every rank in THIS rank's mailbox has reached the epoch of the
+// publishing launch that precedes this one on the stream; then one warp per (sequence, head) row
+// reads that epoch's partial of every rank — its own from local memory, the others' through their
+// peer-mapped mailboxes over NVLink (plain system-scope loads, nothing cached) — and merges them.
+// When the wait runs out the rows are left untouched, the status word gets kStatusWaitRanOut and the
+// kernel returns normally; launches that find the bit already set return at once.
+// ---------------------------------------------------------------------------
+struct MergePublishedArgs {
+    const float* part[kMaxPeers];   // parity 0 of rank r's partial area, as mapped here: [2][rows][HD+2]
+    const uint32_t* flags;          // [world] in this rank's mailbox, written by the peers
+    const uint32_t* state;          // this rank's epoch counter
+    int world, rows, HD;
+    __half* out;                    // [rows][HD]
+    int32_t* status;
+    unsigned long long limit_ns;
+};
+
+constexpr int kMergeWarps = 4;
+
+__device__ __forceinline__ float ld_sys(const float* p) {
+    float v;
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(kMergeWarps * 32) hkv_merge_published_kernel(const MergePublishedArgs a) {
+    __shared__ int s_ok;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t expect = *reinterpret_cast<const volatile uint32_t*>(a.state);
+    // a wait that already ran out (an earlier layer of this step) is not repeated: a lost peer costs
+    // one limit per step, not one per layer
+    if (tid == 0) s_ok = (*reinterpret_cast<volatile int32_t*>(a.status) & kStatusWaitRanOut) ? 0 : 1;
+    __syncthreads();
+    if (s_ok && tid < a.world) {
+        unsigned long long t0, t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        for (;;) {
+            uint32_t seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.flags + tid) : "memory");
+            if ((int32_t)(seen - expect) >= 0) break;
+            __nanosleep(100);
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (t1 - t0 > a.limit_ns) {
+                atomicOr(a.status, kStatusWaitRanOut);
+                s_ok = 0;
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const int row = blockIdx.x * kMergeWarps + warp;
+    if (row >= a.rows) return;
+    const int PW = a.HD + 2;
+    const long long at = (long long)((expect - 1u) & 1u) * a.rows * PW + (long long)row * PW;
+    // the two scalars of every rank first (lanes 0..world-1 fetch them in parallel), then the rows
+    float m_r = kNegBig, l_r = 0.0f;
+    if (lane < a.world) {
+        m_r = ld_sys(a.part[lane] + at + a.HD);
+        l_r = ld_sys(a.part[lane] + at + a.HD + 1);
+    }
+    float M = m_r;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    const float w_r = lane < a.world ? exp2f(m_r - M) : 0.0f;
+    float L = l_r * w_r;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    float acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
+    for (int r = 0; r < a.world; ++r) {
+        const float* p = a.part[r] + at;
+        const float w = __shfl_sync(0xffffffffu, w_r, r);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int d = lane + 32 * i;
+            if (d < a.HD) acc[i] = fmaf(ld_sys(p + d), w, acc[i]);
+        }
+    }
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int d = lane + 32 * i;
+        if (d < a.HD) a.out[(long long)row * a.HD + d] = __float2half_rn(acc[i] * inv);
     }
 }
 

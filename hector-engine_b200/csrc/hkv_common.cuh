@@ -14,6 +14,7 @@ constexpr int kTileRows = 64;          // rows per split-K tile (unit of chunk_t
 constexpr float kNegBig = -1.0e30f;    // "minus infinity" that survives subtraction
 constexpr int kStatusWaitRanOut = 1;   // device status bits
 constexpr int kStatusBoundCheck = 2;
+constexpr int kMaxPeers = 8;           // ranks of one node in a peer exchange (HKV_MAX_PEERS)
 
 // How logical positions of one sequence map to rows of its cache plane.
 struct SeqMap {

@@ -45,6 +45,11 @@ int hkvd_unique_id(void* out) {
 
 int hkvd_create(hkvd_decoder** out, const hkv_geometry* g, int32_t layers, const void* unique_id, float scale,
                 void* stream) {
+    return hkvd_create_with(out, g, layers, unique_id, scale, stream, HKVD_EXCHANGE_AUTO, 0);
+}
+
+int hkvd_create_with(hkvd_decoder** out, const hkv_geometry* g, int32_t layers, const void* unique_id, float scale,
+                     void* stream, int32_t exchange, int32_t peer_wait_ms) {
     if (!out) return HKV_ERR_INVALID_ARG;
     *out = nullptr;
     hkvd_decoder* d = new (std::nothrow) hkvd_decoder();
@@ -61,6 +66,10 @@ int hkvd_create(hkvd_decoder** out, const hkv_geometry* g, int32_t layers, const
     c.shard_block = g->shard_block > 0 ? (uint32_t)g->shard_block : 1024u;
     c.scale = scale; c.chunk_tiles = g->chunk_tiles; c.kernel_select = g->kernel_select;
     if (c.world > 1 && !unique_id) return fail(d, HKV_ERR_INVALID_ARG, "hkvd_create: shard_count > 1 needs a unique id");
+    if (exchange < HKVD_EXCHANGE_AUTO || exchange > HKVD_EXCHANGE_PEER_STORES || peer_wait_ms < 0 || peer_wait_ms > 10000)
+        return fail(d, HKV_ERR_INVALID_ARG, "hkvd_create: unknown exchange or wait limit outside 0..10000 ms");
+    c.exchange = (hkv::Exchange)exchange;
+    if (peer_wait_ms > 0) c.peer_wait_ms = peer_wait_ms;
     try {
         ncclUniqueId id;
         if (unique_id) std::memcpy(&id, unique_id, sizeof id);
@@ -68,6 +77,12 @@ int hkvd_create(hkvd_decoder** out, const hkv_geometry* g, int32_t layers, const
     } catch (const std::exception& e) {
         return fail(d, HKVD_ERR_HOST, e.what());
     }
+    return 0;
+}
+
+int hkvd_exchange(const hkvd_decoder* d, int32_t* exchange_out) {
+    if (!d || !d->dec || !exchange_out) return HKV_ERR_INVALID_ARG;
+    *exchange_out = (int32_t)d->dec->exchange();
     return 0;
 }
 

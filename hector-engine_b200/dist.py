@@ -98,6 +98,8 @@ def load_dist() -> C.CDLL:
     sigs = {
         "hkvd_unique_id": (C.c_int, [vp]),
         "hkvd_create": (C.c_int, [C.POINTER(vp), C.POINTER(_capi.HkvGeometry), i32, vp, C.c_float, vp]),
+        "hkvd_create_with": (C.c_int, [C.POINTER(vp), C.POINTER(_capi.HkvGeometry), i32, vp, C.c_float, vp, i32, i32]),
+        "hkvd_exchange": (C.c_int, [vp, i32p]),
         "hkvd_destroy": (C.c_int, [vp]),
         "hkvd_last_error": (C.c_char_p, [vp]),
         "hkvd_bind": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, C.c_uint64, vp]),
@@ -128,9 +130,12 @@ def _ptr(x) -> int:
 
 class SeqSplitDecoder:
     """Binding of the C++ sequence-split decoder (host/hkv_seqsplit.hpp behind include/hkv_dist.h):
-    per layer  local split-K partials -> NCCL all-gather -> merge, all layers captured once into a
-    CUDA graph and replayed. The communicator is the C++ object's own; torch.distributed is used
-    only to hand rank 0's communicator id to the other ranks.
+    per layer  local split-K partials -> NCCL all-gather -> merge  (or, `exchange="peer"`, partials
+    stored straight into every rank's mailbox over NVLink and merged after a bounded flag wait: no
+    collective launch), all layers captured once into a CUDA graph and replayed. The communicator is
+    the C++ object's own; torch.distributed is used only to hand rank 0's communicator id to the
+    other ranks. `exchange`: "auto" (peer stores when every rank can map every mailbox, else NCCL),
+    "nccl", "peer"; `.exchange` says what is in use.
 
         dec = SeqSplitDecoder(geometry, shard, layers, stream=s)
         dec.bind(q, k_new, v_new, out, k_planes, v_planes, layer_stride_elems, d_total_seq)
@@ -138,7 +143,10 @@ class SeqSplitDecoder:
         dec.wait(5000)        # host-side wait with a deadline; raises on a stuck or failed peer
     """
 
-    def __init__(self, geometry, shard: SeqShard, layers: int, scale: float = 0.0, stream=None, group=None):
+    EXCHANGES = {"auto": 0, "nccl": 1, "peer": 2}
+
+    def __init__(self, geometry, shard: SeqShard, layers: int, scale: float = 0.0, stream=None, group=None,
+                 exchange: str = "auto", peer_wait_ms: int = 0):
         import torch
         self.lib = load_dist()
         self.shard = shard
@@ -159,7 +167,8 @@ class SeqSplitDecoder:
             uid = C.create_string_buffer(box[0], UNIQUE_ID_BYTES)
         self.stream = stream if stream is not None else torch.cuda.current_stream()
         handle = C.c_void_p()
-        st = self.lib.hkvd_create(C.byref(handle), C.byref(self._g), layers, uid, scale, self.stream.cuda_stream)
+        st = self.lib.hkvd_create_with(C.byref(handle), C.byref(self._g), layers, uid, scale, self.stream.cuda_stream,
+                                       self.EXCHANGES[exchange], peer_wait_ms)
         self._h = handle
         if st:
             msg = self.lib.hkvd_last_error(handle).decode() if handle else "allocation failed"
@@ -169,6 +178,12 @@ class SeqSplitDecoder:
     def _check(self, st: int):
         if st:
             raise SeqSplitError(st, self.lib.hkvd_last_error(self._h).decode())
+
+    @property
+    def exchange(self) -> str:
+        mode = C.c_int32(0)
+        self._check(self.lib.hkvd_exchange(self._h, C.byref(mode)))
+        return {1: "nccl", 2: "peer"}[mode.value]
 
     def bind(self, q, k_new, v_new, out, k_planes, v_planes, layer_stride_elems: int, d_total_seq):
         self._check(self.lib.hkvd_bind(self._h, _ptr(q), _ptr(k_new), _ptr(v_new), _ptr(out), _ptr(k_planes),

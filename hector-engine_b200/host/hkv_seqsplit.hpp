@@ -8,15 +8,28 @@
 //                             token's position stages and stores its K/V row inside the same kernel
 //     ncclAllGather           batch*heads*(head_dim+2)*4 bytes per rank, NVLink/NVSwitch
 //     hkv_combine_partials    merges the `world` partials, fp16 output replicated on every rank
-// The whole multi-layer step is captured ONCE into a CUDA graph (NCCL collectives are capturable)
-// and replayed while only the device-side length array changes, under the same capture rules as
-// the engine's own graph (reference src/engine.cpp:206-231: work only on the capture stream, no
-// allocation, no synchronisation, no host reads). Partials arrive in local memory through NCCL
-// before any kernel reads them: no kernel here loads from a peer or waits on one.
+// or, when every rank can map every other rank's memory (Exchange::PeerStores, the default then),
+// without any collective launch:
+//     hkv_decode_partials_publish  the same decode; the kernel that merges this rank's split-K partials
+//                                  leaves the result in this rank's mailbox and publishes an epoch
+//                                  flag in every rank's mailbox (4-byte stores over NVLink)
+//     hkv_merge_published          waits — bounded — for all flags in its OWN mailbox, then reads every
+//                                  rank's partial from that rank's mailbox (plain peer loads) while it
+//                                  merges, writes fp16
+// Mailboxes are cudaMalloc'd per rank and mapped by the others through CUDA IPC handles, handed
+// round once at construction with an NCCL all-gather. The only cross-GPU wait is the merge kernel's
+// bounded poll of flag words in local memory.
+// The whole multi-layer step is captured ONCE into a CUDA graph (NCCL collectives and the mailbox
+// kernels are capturable: the epoch lives in device memory) and replayed while only the device-side
+// length array changes, under the same capture rules as the engine's own graph (reference
+// src/engine.cpp:206-231: work only on the capture stream, no allocation, no synchronisation, no
+// host reads).
 //
-// Failure handling is host-side only (hkv_step_watch.hpp): wait() polls the stream and
+// Failure handling is host-side (hkv_step_watch.hpp): wait() polls the stream and
 // ncclCommGetAsyncError against a deadline and aborts the communicator when a peer is stuck or
-// gone; an optional NodeRoster lets a rank that left between steps be noticed before the launch.
+// gone; in mailbox mode a peer that stops pushing makes the merge kernel's wait run out (status
+// word, the kernel returns), which wait() reports as TimedOut; an optional NodeRoster lets a rank
+// that left between steps be noticed before the launch.
 //
 // The reference engine has no multi-GPU path (its README lists it as absent); this is new work
 // behind the same C ABI (include/hkv.h).
@@ -27,8 +40,10 @@
 #include <nccl.h>
 
 #include <chrono>
+#include <algorithm>
 #include <cmath>
 #include <cstdint>
+#include <cstring>
 #include <stdexcept>
 #include <string>
 #include <vector>
@@ -39,6 +54,12 @@
 
 namespace hkv {
 
+enum class Exchange : int32_t {
+    Auto = 0,        // PeerStores when every rank managed to map every mailbox, else Nccl
+    Nccl = 1,        // ncclAllGather between the two kernels
+    PeerStores = 2,  // mailboxes (peer-mapped memory); construction fails when a mapping is refused
+};
+
 struct SeqSplitConfig {
     uint32_t layers = 0, batch = 1, heads = 0, kv_heads = 0, head_dim = 0;
     uint32_t local_slots = 0;    // rows per sequence held by THIS rank
@@ -46,6 +67,8 @@ struct SeqSplitConfig {
     int rank = 0, world = 1;
     float scale = 0.0f;          // 0 = 1/sqrt(head_dim) (reference default, src/command.cpp:160)
     int32_t chunk_tiles = 0, kernel_select = 0;
+    Exchange exchange = Exchange::Auto;
+    int32_t peer_wait_ms = 2000;  // bound of the merge kernel's wait for the peers' flags
 };
 
 struct SeqSplitTimes {
@@ -81,10 +104,37 @@ public:
             if (!id) throw std::runtime_error("SeqSplitDecoder: world > 1 needs a communicator id");
             const ncclResult_t r = ncclCommInitRank(&comm_, cfg.world, *id, cfg.rank);
             if (r != ncclSuccess) throw std::runtime_error(std::string("SeqSplitDecoder: ncclCommInitRank: ") + ncclGetErrorString(r));
+            if (cfg.exchange != Exchange::Nccl) {
+                if (cfg.world > HKV_MAX_PEERS) {
+                    if (cfg.exchange == Exchange::PeerStores)
+                        throw std::runtime_error("SeqSplitDecoder: mailboxes serve at most " + std::to_string(HKV_MAX_PEERS) + " ranks");
+                } else {
+                    std::string why;
+                    peer_ = map_mailboxes(&why);
+                    if (!peer_ && cfg.exchange == Exchange::PeerStores)
+                        throw std::runtime_error("SeqSplitDecoder: mailboxes could not be mapped on every rank: " + why);
+                }
+            }
         }
     }
     ~SeqSplitDecoder() {
         graph_.invalidate();
+        cudaStreamSynchronize(stream_);
+        // A peer may still be reading this rank's last partial (its merge of the last step): the ranks
+        // meet once more before any mailbox is freed — unless the communicator is gone, in which case
+        // the peers have stopped launching (a departure is announced between steps).
+        if (peer_ && comm_ && !aborted_ && meet_ != nullptr &&
+            ncclAllReduce(meet_, meet_, 1, ncclInt, ncclSum, comm_, stream_) == ncclSuccess) {
+            // with a deadline: a rank that is torn down alone (an error path) must not wait for ever
+            const WatchResult met = watch_step([this] { return cudaStreamQuery(stream_) == cudaSuccess; },
+                                               [] { return false; }, std::chrono::milliseconds(5000));
+            if (met != WatchResult::Done) {
+                ncclCommAbort(comm_);
+                comm_ = nullptr;
+            }
+        }
+        unmap_mailboxes();
+        if (meet_) cudaFree(meet_);
         for (cudaEvent_t e : events_) cudaEventDestroy(e);
         if (comm_) ncclCommDestroy(comm_);
         if (part_) cudaFree(part_);
@@ -99,6 +149,8 @@ public:
     GraphReplay& graph() { return graph_; }
     uint64_t steps() const { return steps_; }
     size_t partial_bytes() const { return part_floats_ * sizeof(float); }
+    // What moves the partials between the ranks (decided at construction, the same on every rank).
+    Exchange exchange() const { return peer_ ? Exchange::PeerStores : Exchange::Nccl; }
 
     // Buffers the step reads and writes; they keep their addresses for as long as the graph lives
     // (rebinding drops it). Per layer l:
@@ -182,6 +234,11 @@ public:
             timeout);
         if (r != WatchResult::Done && comm_ && !aborted_) abandon();
         cudaGetLastError();
+        if (r == WatchResult::Done && peer_ && (device_status() & 1)) {
+            // a merge kernel gave up waiting for a peer's flag: the step's output is not valid
+            if (!aborted_) abandon();
+            return WatchResult::TimedOut;
+        }
         return r;
     }
     // Tears the communicator down without the peers (ncclCommAbort): for a rank that leaves, and
@@ -221,9 +278,93 @@ private:
             throw std::runtime_error(std::string("SeqSplitDecoder: ") + what + " (layer " + std::to_string(layer) + "): " +
                                      hkv_ctx_last_error(ctx_));
     }
+    // Allocates and zeroes this rank's mailbox, hands its IPC handle round (one NCCL all-gather, which
+    // also orders every rank's zeroing before anybody's first push) and maps the others'. Returns
+    // whether EVERY rank succeeded (agreed by an all-reduce), so that all ranks pick the same exchange.
+    bool map_mailboxes(std::string* why) {
+        const int world = cfg_.world, rank = cfg_.rank;
+        bool ok = true;
+        size_t bytes = 0;
+        if (hkv_exchange_bytes(ctx_, world, &bytes) != HKV_OK) { ok = false; *why = "hkv_exchange_bytes"; }
+        cudaIpcMemHandle_t mine{};
+        if (cudaMalloc(&meet_, sizeof(int)) != cudaSuccess || cudaMemset(meet_, 0, sizeof(int)) != cudaSuccess) {
+            ok = false;
+            *why = "cudaMalloc(meeting word)";
+        }
+        if (ok && (cudaMalloc(&mailbox_, bytes) != cudaSuccess || cudaMemset(mailbox_, 0, bytes) != cudaSuccess ||
+                   cudaDeviceSynchronize() != cudaSuccess || cudaIpcGetMemHandle(&mine, mailbox_) != cudaSuccess)) {
+            ok = false;
+            *why = std::string("mailbox allocation / cudaIpcGetMemHandle: ") + cudaGetErrorString(cudaGetLastError());
+        }
+        // handles (and a success flag per rank) travel in one device buffer
+        constexpr size_t kSlot = sizeof(cudaIpcMemHandle_t) + 8;
+        std::vector<unsigned char> host(kSlot * world, 0);
+        unsigned char* d_all = nullptr;
+        cuda_check(cudaMalloc(&d_all, kSlot * world), "cudaMalloc(handles)");
+        std::memcpy(host.data() + kSlot * rank, &mine, sizeof mine);
+        host[kSlot * rank + sizeof mine] = ok ? 1 : 0;
+        cuda_check(cudaMemcpy(d_all + kSlot * rank, host.data() + kSlot * rank, kSlot, cudaMemcpyHostToDevice), "cudaMemcpy(handle)");
+        ncclResult_t r = ncclAllGather(d_all + kSlot * rank, d_all, kSlot, ncclChar, comm_, stream_);
+        if (r != ncclSuccess) { cudaFree(d_all); throw std::runtime_error(std::string("SeqSplitDecoder: ncclAllGather(handles): ") + ncclGetErrorString(r)); }
+        cuda_check(cudaStreamSynchronize(stream_), "cudaStreamSynchronize(handles)");
+        cuda_check(cudaMemcpy(host.data(), d_all, kSlot * world, cudaMemcpyDeviceToHost), "cudaMemcpy(handles)");
+        for (int p = 0; p < world; ++p) ok = ok && host[kSlot * p + sizeof mine] == 1;
+        x_ = hkv_exchange{};
+        x_.rank = rank; x_.world = world; x_.wait_limit_ms = cfg_.peer_wait_ms;
+        if (ok) {
+            for (int p = 0; p < world && ok; ++p) {
+                if (p == rank) { x_.mailbox[p] = mailbox_; continue; }
+                cudaIpcMemHandle_t h;
+                std::memcpy(&h, host.data() + kSlot * p, sizeof h);
+                void* mapped = nullptr;
+                const cudaError_t e = cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess);
+                if (e != cudaSuccess) {
+                    ok = false;
+                    *why = "cudaIpcOpenMemHandle(rank " + std::to_string(p) + "): " + cudaGetErrorString(e);
+                    cudaGetLastError();
+                } else {
+                    x_.mailbox[p] = mapped;
+                }
+            }
+        }
+        // agree: one byte per rank again
+        std::fill(host.begin(), host.end(), 0);
+        host[kSlot * rank] = ok ? 1 : 0;
+        cuda_check(cudaMemcpy(d_all + kSlot * rank, host.data() + kSlot * rank, kSlot, cudaMemcpyHostToDevice), "cudaMemcpy(agree)");
+        r = ncclAllGather(d_all + kSlot * rank, d_all, kSlot, ncclChar, comm_, stream_);
+        if (r != ncclSuccess) { cudaFree(d_all); throw std::runtime_error(std::string("SeqSplitDecoder: ncclAllGather(agree): ") + ncclGetErrorString(r)); }
+        cuda_check(cudaStreamSynchronize(stream_), "cudaStreamSynchronize(agree)");
+        cuda_check(cudaMemcpy(host.data(), d_all, kSlot * world, cudaMemcpyDeviceToHost), "cudaMemcpy(agree)");
+        cudaFree(d_all);
+        bool all = true;
+        for (int p = 0; p < world; ++p)
+            if (host[kSlot * p] != 1) { all = false; if (why->empty()) *why = "rank " + std::to_string(p) + " could not map a mailbox"; }
+        if (!all) unmap_mailboxes();
+        return all;
+    }
+    void unmap_mailboxes() {
+        for (int p = 0; p < HKV_MAX_PEERS; ++p) {
+            if (p != cfg_.rank && x_.mailbox[p]) cudaIpcCloseMemHandle(x_.mailbox[p]);
+            x_.mailbox[p] = nullptr;
+        }
+        if (mailbox_) cudaFree(mailbox_);
+        mailbox_ = nullptr;
+        peer_ = false;
+    }
     void enqueue_layers(cudaStream_t s, cudaEvent_t* ev) {
         const size_t qn = (size_t)cfg_.batch * cfg_.heads * cfg_.head_dim;
         const size_t kn = (size_t)cfg_.batch * cfg_.kv_heads * cfg_.head_dim;
+        for (uint32_t l = 0; l < cfg_.layers && peer_; ++l) {
+            if (ev) cudaEventRecord(ev[l * 4], s);
+            hkv_check(hkv_decode_partials_publish(ctx_, q_ + l * qn, k_new_ ? k_new_ + l * kn : nullptr,
+                                               v_new_ ? v_new_ + l * kn : nullptr, k_ + l * layer_stride_,
+                                               v_ + l * layer_stride_, &x_, d_total_, cfg_.scale, s),
+                      "hkv_decode_partials_publish", l);
+            if (ev) { cudaEventRecord(ev[l * 4 + 1], s); cudaEventRecord(ev[l * 4 + 2], s); }
+            hkv_check(hkv_merge_published(ctx_, &x_, out_ + l * qn, s), "hkv_merge_published", l);
+            if (ev) cudaEventRecord(ev[l * 4 + 3], s);
+        }
+        if (peer_) return;
         for (uint32_t l = 0; l < cfg_.layers; ++l) {
             if (ev) cudaEventRecord(ev[l * 4], s);
             hkv_check(hkv_decode_partials(ctx_, q_ + l * qn, k_new_ ? k_new_ + l * kn : nullptr,
@@ -251,6 +392,10 @@ private:
     bool warmed_ = false;   // a collective has run outside capture
     float* part_ = nullptr;       // [batch][heads][head_dim + 2]
     float* gathered_ = nullptr;   // [world][batch][heads][head_dim + 2]
+    bool peer_ = false;           // partials travel through mailboxes, not a collective
+    void* mailbox_ = nullptr;     // this rank's mailbox (hkv_exchange_bytes)
+    int* meet_ = nullptr;         // one word for the all-reduce the ranks meet on before mailboxes are freed
+    hkv_exchange x_{};            // every rank's mailbox as mapped here
     size_t part_floats_ = 0;
     GraphReplay graph_;
     std::vector<cudaEvent_t> events_;

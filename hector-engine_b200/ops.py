@@ -212,6 +212,32 @@ class Context:
         self._check(self.lib.hkv_combine_partials(self._h, _ptr(partials), num_parts, _ptr(out),
                                                   _stream(stream)))
 
+    # -- peer exchange (peer-mapped mailboxes instead of a collective) ----------------
+    def exchange_bytes(self, world: int) -> int:
+        n = C.c_size_t(0)
+        self._check(self.lib.hkv_exchange_bytes(self._h, world, C.byref(n)))
+        return int(n.value)
+
+    @staticmethod
+    def make_exchange(rank: int, mailboxes, wait_limit_ms: int = 0):
+        """`mailboxes[r]`: rank r's mailbox as this process addresses it (a zeroed uint8 tensor of
+        exchange_bytes(world) bytes, or a raw pointer for a peer's mapped allocation)."""
+        x = _capi.HkvExchange()
+        x.rank, x.world, x.wait_limit_ms = rank, len(mailboxes), wait_limit_ms
+        for r, m in enumerate(mailboxes):
+            x.mailbox[r] = m if isinstance(m, int) else _ptr(m)
+        return x
+
+    def decode_partials_publish(self, q, k_new, v_new, k_cache, v_cache, exchange, d_total_seq, scale=None,
+                             stream=None):
+        scale = self.geometry.default_scale if scale is None else scale
+        self._check(self.lib.hkv_decode_partials_publish(
+            self._h, _ptr(q), _ptr(k_new), _ptr(v_new), _ptr(k_cache), _ptr(v_cache), C.byref(exchange),
+            _ptr(d_total_seq), scale, _stream(stream)))
+
+    def merge_published(self, exchange, out, stream=None):
+        self._check(self.lib.hkv_merge_published(self._h, C.byref(exchange), _ptr(out), _stream(stream)))
+
 
 STATIC_SCRATCH_BYTES = 8 << 20
 

@@ -226,6 +226,41 @@ int hkv_decode_partials(hkv_ctx* ctx, const void* q, const void* k_new, const vo
 int hkv_combine_partials(hkv_ctx* ctx, const float* partials, int32_t num_parts, void* out,
                          void* stream);
 
+/* The same exchange WITHOUT a collective launch: the kernel that merges this rank's split-K
+ * partials leaves the merged partial in this rank's own mailbox and publishes an epoch flag in
+ * every rank's mailbox (one 4-byte store per rank over NVLink); the merge kernel waits — with a
+ * bound — for the flags of all ranks in its OWN mailbox and then reads every rank's partial straight
+ * from that rank's mailbox (plain peer loads over NVLink, no multicast) while it merges. No
+ * counterpart in the reference (single-GPU).
+ *
+ * A mailbox is one device allocation of hkv_exchange_bytes() bytes per rank, zeroed once before
+ * the first step, that every rank of the node has mapped (cudaIpcOpenMemHandle or any other peer
+ * mapping): mailbox[r] is rank r's mailbox as THIS process addresses it, mailbox[rank] the local
+ * one. Layout: 64 flag words (flag s = last epoch rank s has published), 64 state words of the owner
+ * (its epoch counter and a CTA counter), then [2][batch*num_heads*(head_dim+2)] floats — the owner's
+ * partial of two consecutive epochs, because a rank may run one exchange ahead of a peer that is still
+ * merging the previous one. Every rank must make the same sequence of publish/merge calls.
+ *
+ * hkv_decode_partials_publish: hkv_decode_partials with the mailbox as destination; never waits.
+ * hkv_merge_published: waits at most wait_limit_ms (0 = 2000) for every rank's flag, then writes
+ *   fp16 `out` [batch, num_heads, head_dim]. When the wait runs out the rows are left untouched,
+ *   bit 1 of the device status word is set (hkv_ctx_device_status) and the kernel returns normally;
+ *   later merges return at once until the status word has been read.
+ * Both only enqueue and are capturable; the epoch lives in the mailbox, so a captured pair can be
+ * replayed. */
+#define HKV_MAX_PEERS 8
+typedef struct hkv_exchange {
+    int32_t rank, world;             /* 0 <= rank < world <= HKV_MAX_PEERS                    */
+    void* mailbox[HKV_MAX_PEERS];    /* 256-byte aligned; entries >= world are ignored          */
+    int32_t wait_limit_ms;           /* bound of the merge kernel's wait; 0 = 2000, at most 10000 */
+    int32_t reserved;
+} hkv_exchange;
+int hkv_exchange_bytes(const hkv_ctx* ctx, int32_t world, size_t* bytes_out);
+int hkv_decode_partials_publish(hkv_ctx* ctx, const void* q, const void* k_new, const void* v_new,
+                             void* k_cache, void* v_cache, const hkv_exchange* exchange,
+                             const int32_t* d_total_seq, float scale, void* stream);
+int hkv_merge_published(hkv_ctx* ctx, const hkv_exchange* exchange, void* out, void* stream);
+
 /* ---- host-buffer convenience (end-to-end timing, tests) --------------------------- */
 
 /* Fused op with HOST q / k_new / v_new / out (pinned memory recommended): copies the

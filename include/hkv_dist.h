@@ -5,7 +5,8 @@
  * (its README lists multi-GPU as absent); they sit behind the same boundary as include/hkv.h so
  * that an engine process per GPU can drive long-context decode.
  *
- * Per layer the step is  hkv_decode_partials -> ncclAllGather -> hkv_combine_partials  on the
+ * Per layer the step is  hkv_decode_partials -> ncclAllGather -> hkv_combine_partials  (or, without a
+ * collective launch, hkv_decode_partials_publish -> hkv_merge_published through peer-mapped mailboxes) on the
  * caller's stream; hkvd_step captures all layers once into a CUDA graph and replays it while only
  * the device-side length array changes. Every function returns 0 on success, an hkv_status
  * (include/hkv.h) or HKVD_* below otherwise; hkvd_last_error gives the text. Nothing here waits
@@ -41,6 +42,21 @@ int hkvd_unique_id(void* out);
  * when shard_count <= 1. Allocates and initialises NCCL: not capturable; collective over all ranks. */
 int hkvd_create(hkvd_decoder** out, const hkv_geometry* geometry, int32_t layers, const void* unique_id,
                 float scale, void* stream);
+/* The same with the exchange chosen by the caller. HKVD_EXCHANGE_NCCL: ncclAllGather between the two
+ * kernels of a layer. HKVD_EXCHANGE_PEER_STORES: no collective launch — each rank's partial-merging
+ * kernel publishes an epoch flag in every rank's mailbox over NVLink and the final merge reads the
+ * ranks' partials through the peer-mapped mailboxes (hkv_decode_partials_publish / hkv_merge_published,
+ * include/hkv.h); needs every rank to map every other rank's mailbox through CUDA IPC (one process per
+ * GPU on one node, at most HKV_MAX_PEERS ranks) and fails otherwise. HKVD_EXCHANGE_AUTO (what hkvd_create
+ * uses): peer stores when every rank could map, else NCCL; all ranks always agree. peer_wait_ms bounds
+ * the merge kernel's wait for the peers' flags (0 = 2000); when it runs out hkvd_wait returns
+ * HKVD_ERR_TIMEOUT. hkvd_exchange reports what the decoder uses. */
+#define HKVD_EXCHANGE_AUTO 0
+#define HKVD_EXCHANGE_NCCL 1
+#define HKVD_EXCHANGE_PEER_STORES 2
+int hkvd_create_with(hkvd_decoder** out, const hkv_geometry* geometry, int32_t layers, const void* unique_id,
+                     float scale, void* stream, int32_t exchange, int32_t peer_wait_ms);
+int hkvd_exchange(const hkvd_decoder* d, int32_t* exchange_out);
 int hkvd_destroy(hkvd_decoder* d);
 const char* hkvd_last_error(const hkvd_decoder* d);
 

@@ -82,7 +82,7 @@ bool close_enough(const std::vector<uint16_t>& got, const std::vector<uint16_t>&
         std::printf("\n");                               \
     } while (0)
 
-int run_rank(int rank, int world, const std::string& idfile, bool leave_at_end) {
+int run_rank(int rank, int world, const std::string& idfile, bool leave_at_end, const std::string& exchange) {
     setvbuf(stdout, nullptr, _IONBF, 0);
     CUDA_OK(cudaSetDevice(world > 1 ? rank : 0));
     ncclUniqueId id;
@@ -145,8 +145,12 @@ int run_rank(int rank, int world, const std::string& idfile, bool leave_at_end) 
         hkv::SeqSplitConfig cfg;
         cfg.layers = L; cfg.batch = B; cfg.heads = H; cfg.kv_heads = KVH; cfg.head_dim = HD;
         cfg.local_slots = (uint32_t)local_slots; cfg.shard_block = BLK; cfg.rank = rank; cfg.world = world;
+        cfg.exchange = exchange == "peer" ? hkv::Exchange::PeerStores : exchange == "nccl" ? hkv::Exchange::Nccl : hkv::Exchange::Auto;
+        cfg.peer_wait_ms = 5000;
         hkv::SeqSplitDecoder dec(cfg, world > 1 ? &id : nullptr, stream);
-        if (world > 1) STAGE("decoder and communicator ready");
+        if (world > 1) STAGE("decoder and communicator ready (%s)", dec.exchange() == hkv::Exchange::PeerStores ? "mailboxes" : "all-gather");
+        if (world > 1 && exchange == "peer") REQUIRE(dec.exchange() == hkv::Exchange::PeerStores, "mailboxes mapped on every rank");
+        if (world == 1 || exchange == "nccl") REQUIRE(dec.exchange() == hkv::Exchange::Nccl, "no mailboxes unless asked for");
         dec.bind(dq, dkn, dvn, dout, dk, dv, lplane, dtot);
         if (roster) dec.attach_roster(roster.get(), 20000ms);
 
@@ -198,7 +202,8 @@ int run_rank(int rank, int world, const std::string& idfile, bool leave_at_end) 
                     }
                 }
         REQUIRE(planes_ok, "owner planes bit-exact (appended rows stored by their owner only)");
-        std::printf("rank %d/%d: %d steps, %llu replays, graph of %zu nodes, max abs err %.3e\n", rank, world, STEPS,
+        std::printf("rank %d/%d (%s): %d steps, %llu replays, graph of %zu nodes, max abs err %.3e\n", rank, world,
+                    dec.exchange() == hkv::Exchange::PeerStores ? "mailboxes" : "all-gather", STEPS,
                     (unsigned long long)replays, dec.graph().node_count(), worst);
 
         if (leave_at_end && world > 1) {
@@ -239,60 +244,67 @@ int main(int argc, char** argv) {
     int rank = -1, world = 0;
     std::string idfile;
     bool leave = false;
+    std::string exchange = "auto";
     for (int i = 1; i < argc; ++i) {
         const std::string a = argv[i];
         if (a == "--list") { std::printf("seqsplit_decoder\n"); return 0; }
         if (a == "--rank" && i + 1 < argc) rank = std::atoi(argv[++i]);
         else if (a == "--world" && i + 1 < argc) world = std::atoi(argv[++i]);
         else if (a == "--idfile" && i + 1 < argc) idfile = argv[++i];
+        else if (a == "--exchange" && i + 1 < argc) exchange = argv[++i];
         else if (a == "--leave") leave = true;
     }
-    if (rank >= 0) return run_rank(rank, world, idfile, leave);
+    if (rank >= 0) return run_rank(rank, world, idfile, leave, exchange);
 
     int ndev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) { std::printf("FAIL: no CUDA device\n"); return 1; }
     if (world <= 0) world = ndev < 4 ? ndev : 4;
     if (world > ndev) { std::printf("FAIL: %d ranks asked, %d GPUs present\n", world, ndev); return 1; }
     if (world == 1) {
-        const int rc = run_rank(0, 1, "", false);
+        const int rc = run_rank(0, 1, "", false, "auto");
         if (!rc) std::printf("ALL PASSED (world 1)\n");
         return rc;
     }
-    // one child per GPU; each is this binary with --rank
-    char tmpl[] = "/tmp/hkv-seqsplit-id-XXXXXX";
-    const int fd = mkstemp(tmpl);
-    if (fd >= 0) { close(fd); unlink(tmpl); }
-    idfile = tmpl;
+    // one child per GPU, each this binary with --rank; the whole sequence once per exchange
     setenv("NCCL_NVLS_ENABLE", "0", 0);   // a rank leaves at the end of this test: keep multicast objects out of it
-    std::vector<pid_t> kids;
-    for (int r = 0; r < world; ++r) {
-        const pid_t pid = fork();
-        if (pid == 0) {
-            const std::string rs = std::to_string(r), ws = std::to_string(world);
-            execl(argv[0], argv[0], "--rank", rs.c_str(), "--world", ws.c_str(), "--idfile", idfile.c_str(), "--leave", (char*)nullptr);
-            _exit(127);
-        }
-        kids.push_back(pid);
-    }
     int bad = 0;
-    const auto deadline = std::chrono::steady_clock::now() + 150s;
-    std::vector<bool> done(kids.size(), false);
-    size_t left = kids.size();
-    while (left && std::chrono::steady_clock::now() < deadline) {
-        for (size_t i = 0; i < kids.size(); ++i) {
-            if (done[i]) continue;
-            int status = 0;
-            if (waitpid(kids[i], &status, WNOHANG) == kids[i]) {
-                done[i] = true;
-                --left;
-                if (!WIFEXITED(status) || WEXITSTATUS(status) != 0) ++bad;
+    for (const char* mode : {"nccl", "peer"}) {
+        char tmpl[] = "/tmp/hkv-seqsplit-id-XXXXXX";
+        const int fd = mkstemp(tmpl);
+        if (fd >= 0) { close(fd); unlink(tmpl); }
+        idfile = tmpl;
+        std::printf("== exchange: %s\n", mode);
+        std::vector<pid_t> kids;
+        for (int r = 0; r < world; ++r) {
+            const pid_t pid = fork();
+            if (pid == 0) {
+                const std::string rs = std::to_string(r), ws = std::to_string(world);
+                execl(argv[0], argv[0], "--rank", rs.c_str(), "--world", ws.c_str(), "--idfile", idfile.c_str(), "--exchange", mode,
+                      "--leave", (char*)nullptr);
+                _exit(127);
             }
+            kids.push_back(pid);
         }
-        std::this_thread::sleep_for(50ms);
+        const auto deadline = std::chrono::steady_clock::now() + 150s;
+        std::vector<bool> done(kids.size(), false);
+        size_t left = kids.size();
+        while (left && std::chrono::steady_clock::now() < deadline) {
+            for (size_t i = 0; i < kids.size(); ++i) {
+                if (done[i]) continue;
+                int status = 0;
+                if (waitpid(kids[i], &status, WNOHANG) == kids[i]) {
+                    done[i] = true;
+                    --left;
+                    if (!WIFEXITED(status) || WEXITSTATUS(status) != 0) ++bad;
+                }
+            }
+            std::this_thread::sleep_for(50ms);
+        }
+        for (size_t i = 0; i < kids.size(); ++i)
+            if (!done[i]) { kill(kids[i], SIGKILL); waitpid(kids[i], nullptr, 0); ++bad; std::printf("FAIL: rank %zu exceeded the time limit\n", i); }
+        unlink(idfile.c_str());
+        if (bad) break;
     }
-    for (size_t i = 0; i < kids.size(); ++i)
-        if (!done[i]) { kill(kids[i], SIGKILL); waitpid(kids[i], nullptr, 0); ++bad; std::printf("FAIL: rank %zu exceeded the time limit\n", i); }
-    unlink(idfile.c_str());
     if (!bad) std::printf("ALL PASSED (world %d)\n", world);
     return bad ? 1 : 0;
 }

@@ -34,7 +34,7 @@ def test_dist_library_exports_every_declared_symbol(hkv):
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     names = sorted(set(re.findall(r"\b(hkvd_[a-z0-9_]+)\s*\(", text)))
     lib = hkv.dist.load_dist()
-    assert len(names) == 11
+    assert len(names) == 13
     for name in names:
         assert hasattr(lib, name), f"{name} declared in include/hkv_dist.h but not exported"
     assert set(names) == set(lib._hkvd_symbols)

@@ -118,3 +118,48 @@ def test_rope_kv_reproduces_reference_kernel(hkv, cuda, oracle, case):
     assert_close(oracle, dq.cpu().numpy(), GOLD[name + "/q"].view(np.float16), name + " q vs reference")
     assert_close(oracle, dkc.cpu().numpy(), GOLD[name + "/k_cache"].view(np.float16), name + " k_cache vs reference")
     ctx.close()
+
+
+ROPE_SHAPES = [
+    # name, B, S, H, KVH, HD, rotary_dim, slots, layout
+    ("phi3_chunk_ranges_of_tokens", 1, 700, 6, 2, 96, 96, 1024, 0),       # 12 pieces on 16 lanes; CTAs own token ranges
+    ("gemma_hd256_ring", 2, 200, 4, 2, 256, 256, 256, 1),                 # one head per warp; chunk wraps the ring
+    ("hd64_four_heads_per_warp", 3, 130, 14, 2, 64, 64, 256, 0),           # the last sequences run off the plane
+    ("hd128_partial_rotary_odd_units", 2, 2, 9, 3, 128, 64, 512, 0),      # 15 units: a half-empty warp slot
+    ("element_path_hd72_rot36", 1, 5, 3, 1, 72, 36, 256, 0),              # rotary_dim/2 not in 8-element pieces
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", ROPE_SHAPES, ids=lambda c: c[0])
+def test_rope_kv_shapes(hkv, cuda, oracle, case):
+    torch = cuda
+    name, B, S, H, KVH, HD, rot, slots, layout = case
+    rng = np.random.default_rng(zlib.crc32(name.encode()))
+    q, k, v = normal_f16(rng, B, S, H, HD), normal_f16(rng, B, S, KVH, HD), normal_f16(rng, B, S, KVH, HD)
+    qw = (1 + 0.1 * rng.standard_normal(HD, dtype=np.float32)).astype(np.float16)
+    kw = (1 + 0.1 * rng.standard_normal(HD, dtype=np.float32)).astype(np.float16)
+    kc, vc = normal_f16(rng, B, slots, KVH, HD), normal_f16(rng, B, slots, KVH, HD)
+    pos = (np.arange(B, dtype=np.int32) * 37 + 211).astype(np.int32)
+    rq, rk, rkc, rvc = q.copy(), k.copy(), kc.copy(), vc.copy()
+    oracle.qk_norm_rope(rq, rk, v, qw, kw, pos, k_cache=rkc, v_cache=rvc, layout=layout, rotary_dim=rot, theta=1e4)
+    ctx = hkv.Context(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots, layout=layout,
+                                   window_size=slots if layout else 0, flags=hkv.FLAG_APPEND_ONLY))
+    dq, dk, dkc, dvc = to_dev(torch, q), to_dev(torch, k), to_dev(torch, kc), to_dev(torch, vc)
+    ctx.qk_norm_rope_kv(dq, dk, to_dev(torch, v), to_dev(torch, qw), to_dev(torch, kw), dkc, dvc, to_dev(torch, pos),
+                        seq_new=S, rotary_dim=rot, theta=1e4)
+    torch.cuda.synchronize()
+    assert np.array_equal(dvc.cpu().numpy().view(np.uint16), rvc.view(np.uint16)), "V rows must be bit-exact"
+    assert np.array_equal(dk.cpu().numpy().view(np.uint16), k.view(np.uint16)), "k must stay untouched"
+    assert_close(oracle, dq.cpu().numpy(), rq, name + " q")
+    assert_close(oracle, dkc.cpu().numpy(), rkc, name + " k_cache")
+    # the in-place form on the same shapes
+    rq2, rk2 = q.copy(), k.copy()
+    oracle.qk_norm_rope(rq2, rk2, None, qw, kw, pos, rotary_dim=rot, theta=1e4)
+    dq2, dk2 = to_dev(torch, q), to_dev(torch, k)
+    ctx.qk_norm_rope_kv(dq2, dk2, None, to_dev(torch, qw), to_dev(torch, kw), None, None, to_dev(torch, pos),
+                        seq_new=S, rotary_dim=rot, theta=1e4)
+    torch.cuda.synchronize()
+    assert_close(oracle, dq2.cpu().numpy(), rq2, name + " q (in place)")
+    assert_close(oracle, dk2.cpu().numpy(), rk2, name + " k (in place)")
+    ctx.close()

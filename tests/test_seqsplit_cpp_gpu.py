@@ -1,8 +1,9 @@
 """Runs the C++ test of the sequence-split decoder (tests/cpp/hkv_seqsplit_tests.cpp): one process
-per GPU (up to 4), NCCL all-gather on the compute stream, the multi-layer step captured once and
-replayed, outputs against the oracle on the full logical cache, owner planes bit-exact. With two
-or more GPUs the last rank then leaves between steps and the others must refuse the next step on
-the host. With one GPU the same decoder runs as a world of one (no collective)."""
+per GPU (up to 4), the multi-layer step captured once and replayed, outputs against the oracle on
+the full logical cache, owner planes bit-exact — once with the NCCL all-gather on the compute stream
+and once with the mailbox exchange (plain peer stores). With two or more GPUs the last rank then
+leaves between steps and the others must refuse the next step on the host. With one GPU the same
+decoder runs as a world of one (no exchange)."""
 import os
 import subprocess
 

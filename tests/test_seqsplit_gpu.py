@@ -77,6 +77,80 @@ def test_sequence_split_single_gpu_emulation(hkv, cuda, oracle, world, BLK, kern
         c.close()
 
 
+@pytest.mark.parametrize("world,BLK,batch", [(2, 64, 3), (4, 128, 3), (8, 64, 1)])
+def test_peer_exchange_single_gpu_emulation(hkv, cuda, oracle, world, BLK, batch):
+    """The mailbox exchange with every rank on one GPU: per step all ranks' publishing launches are
+    enqueued before the first merge, so each merge finds its flags already published (no kernel
+    waits for a later launch). Three steps exercise both parities of the mailboxes; every rank's
+    merged output must match the oracle on the full logical cache."""
+    torch = cuda
+    B, H, KVH, HD, ctx = batch, 28, 4, 128, 2048
+    totals0 = np.array([2040, 1000, 65][:B], np.int32)
+    q, nk, nv, kc, vc = make_case(world * 17 + BLK, B, H, KVH, HD, ctx, fill="garbage")
+    scale = 1.0 / math.sqrt(HD)
+    shards, slots, lk, lv = build_shards(hkv, world, BLK, kc, vc, totals0 - 1, np.full(B, -1))
+    ctxs, planes, boxes = [], [], []
+    for r in range(world):
+        c = hkv.Context(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots,
+                                     shard_rank=r, shard_count=world, shard_block=BLK))
+        ctxs.append(c)
+        planes.append((to_dev(torch, lk[r]), to_dev(torch, lv[r])))
+        boxes.append(torch.zeros(c.exchange_bytes(world), dtype=torch.uint8, device="cuda"))
+    assert boxes[0].numel() == 512 + 2 * B * H * (HD + 2) * 4
+    xs = [hkv.Context.make_exchange(r, boxes, wait_limit_ms=200) for r in range(world)]
+    full_k, full_v = kc.copy(), vc.copy()
+    dq, dnk, dnv = to_dev(torch, q), to_dev(torch, nk), to_dev(torch, nv)
+    outs = [torch.zeros(B, H, HD, dtype=torch.float16, device="cuda") for _ in range(world)]
+    for step in range(3):
+        totals = totals0 + step
+        oracle.append(nk, nv, full_k, full_v, totals - 1)
+        ref = oracle.decode(q, full_k, full_v, totals, scale, threads=8)
+        dtot = to_dev(torch, totals)
+        for r in range(world):
+            ctxs[r].decode_partials_publish(dq, dnk, dnv, planes[r][0], planes[r][1], xs[r], dtot, scale)
+        for r in range(world):
+            ctxs[r].merge_published(xs[r], outs[r])
+        torch.cuda.synchronize()
+        for r in range(world):
+            assert ctxs[r].device_status() == 0
+            assert_close(oracle, outs[r].cpu().numpy(), ref, f"step {step}, rank {r} of {world}")
+        epochs = [int(b[256:260].view(torch.int32)[0]) for b in boxes]
+        assert epochs == [step + 1] * world
+    for c in ctxs:
+        c.close()
+
+
+def test_peer_exchange_wait_runs_out_as_a_status(hkv, cuda):
+    """A peer that never publishes: the merge kernel's wait gives up after its limit, leaves the output
+    rows alone, reports through the status word and returns; the context keeps working."""
+    torch = cuda
+    B, H, KVH, HD, slots = 2, 8, 2, 64, 128
+    c = hkv.Context(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots,
+                                 shard_rank=0, shard_count=2, shard_block=64))
+    boxes = [torch.zeros(c.exchange_bytes(2), dtype=torch.uint8, device="cuda") for _ in range(2)]
+    x = hkv.Context.make_exchange(0, boxes, wait_limit_ms=50)
+    rng = np.random.default_rng(3)
+    f16 = lambda *s: to_dev(torch, rng.standard_normal(s, dtype=np.float32).astype(np.float16))
+    q, k, v = f16(B, 1, H, HD), f16(B, slots, KVH, HD), f16(B, slots, KVH, HD)
+    tot = to_dev(torch, np.array([100, 7], np.int32))
+    out = torch.full((B, H, HD), 7.0, dtype=torch.float16, device="cuda")
+    c.decode_partials_publish(q, None, None, k, v, x, tot)
+    c.merge_published(x, out)                       # rank 1 never publishes
+    torch.cuda.synchronize()
+    assert c.device_status() == 1                # the wait ran out; reading clears the word
+    assert bool((out == 7.0).all())
+    assert c.device_status() == 0
+    # the mailbox is still consistent: once "rank 1" has published, the same epoch merges
+    boxes[0][4:8].view(torch.int32)[0] = 1       # flag word of rank 1 in rank 0's mailbox
+    c.merge_published(x, out)
+    torch.cuda.synchronize()
+    assert c.device_status() == 0
+    assert not bool((out == 7.0).all())
+    with pytest.raises(hkv.HkvError):
+        c.merge_published(hkv.Context.make_exchange(1, boxes), out)      # not this context's rank
+    c.close()
+
+
 def _nccl_rank(rank, world, port, result_dir):
     sys.path[:0] = [REPO, os.path.join(REPO, "oracle"), HERE]
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -98,26 +172,29 @@ def _nccl_rank(rank, world, port, result_dir):
         shards, slots, lk, lv = build_shards(hkv, world, BLK, kc, vc, totals, pos)
         dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
         stream = torch.cuda.Stream()
-        dec = hkv.dist.SeqSplitDecoder(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots),
-                                       shards[rank], layers=1, scale=scale, stream=stream)
-        out = torch.zeros(B, H, HD, dtype=torch.float16, device="cuda")
-        dk, dv, dq, dnk, dnv, dtot = dev(lk[rank]), dev(lv[rank]), dev(q), dev(nk), dev(nv), dev(totals)
-        torch.cuda.synchronize()
-        dec.bind(dq, dnk, dnv, out, dk, dv, dk.numel(), dtot)
-        replays = 0
-        for _ in range(4):  # un-captured, captured + launched, replayed twice: every call re-appends the same row and must agree
-            replays += dec.step()
-            dec.wait(30000)
+        for exchange in ("nccl", "peer"):   # the collective, then the mailboxes (plain peer stores)
+            dec = hkv.dist.SeqSplitDecoder(hkv.Geometry(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots),
+                                           shards[rank], layers=1, scale=scale, stream=stream, exchange=exchange,
+                                           peer_wait_ms=5000)
+            assert dec.exchange == exchange
+            out = torch.zeros(B, H, HD, dtype=torch.float16, device="cuda")
+            dk, dv, dq, dnk, dnv, dtot = dev(lk[rank]), dev(lv[rank]), dev(q), dev(nk), dev(nv), dev(totals)
+            torch.cuda.synchronize()
+            dec.bind(dq, dnk, dnv, out, dk, dv, dk.numel(), dtot)
+            replays = 0
+            for _ in range(4):  # un-captured, captured + launched, replayed twice: every call re-appends the same row and must agree
+                replays += dec.step()
+                dec.wait(30000)
+                ok, err = oracle.within_tolerance(out.cpu().numpy(), ref)
+                assert ok, f"rank {rank} ({exchange}): {err}"
+            assert replays == 3
+            d_ms, g_ms, m_ms = dec.step_profiled()
+            assert d_ms > 0 and m_ms > 0 and (g_ms > 0 or exchange == "peer")
+            assert dec.device_status() == 0
             ok, err = oracle.within_tolerance(out.cpu().numpy(), ref)
-            assert ok, f"rank {rank}: {err}"
-        assert replays == 3
-        d_ms, g_ms, m_ms = dec.step_profiled()
-        assert d_ms > 0 and g_ms > 0 and m_ms > 0
-        assert dec.device_status() == 0
-        ok, err = oracle.within_tolerance(out.cpu().numpy(), ref)
-        assert ok, f"rank {rank}: {err}"
+            assert ok, f"rank {rank} ({exchange}): {err}"
+            dec.close()
         open(os.path.join(result_dir, f"ok{rank}"), "w").write("ok")
-        dec.close()
     finally:
         dist.destroy_process_group()
 
