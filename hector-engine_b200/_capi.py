@@ -74,6 +74,8 @@ SIGNATURES = {
     "hkv_decode_partials_publish": (C.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, C.POINTER(HkvExchange), _I32P, C.c_float, _VP]),
     "hkv_merge_published": (C.c_int, [_VP, C.POINTER(HkvExchange), _VP, _VP]),
     "hkv_append_decode_attention_host": (C.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I32P, C.c_float, _VP]),
+    "hkv_append_decode_attention_host_pipelined": (C.c_int, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I32P, C.c_float, _VP]),
+    "hkv_host_flush": (C.c_int, [_VP, _VP]),
     "hkv_qk_norm_rope_kv": (C.c_int, [_VP] * 8 + [_I32P, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_float, C.c_float, _VP]),
     "hkv_ctx_selftest_bounded_wait": (C.c_int, [_VP, C.c_int32, _VP]),
     "hkv_ctx_profile_begin": (C.c_int, [_VP, C.c_int32]),

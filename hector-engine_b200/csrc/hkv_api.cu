@@ -61,6 +61,16 @@ struct hkv_ctx {
     int* prefill_row_parts = nullptr; // [max_seq_new][KVH]: partial rows per (query, kv head) under the equal-span schedule
     // host-buffer entry point staging
     __half *st_q = nullptr, *st_k = nullptr, *st_v = nullptr, *st_out = nullptr;
+    // pipelined host op: a ring of staging sets, a stream for each copy direction
+    struct HostSlot {
+        __half *q = nullptr, *k = nullptr, *v = nullptr, *out = nullptr;
+        cudaEvent_t in_done = nullptr, compute_done = nullptr, out_done = nullptr;
+        bool used = false;
+    };
+    static constexpr int kHostSlots = 4;
+    HostSlot host_slots[kHostSlots];
+    cudaStream_t host_in = nullptr, host_out = nullptr;
+    unsigned long long host_calls = 0;
     std::map<std::pair<const void*, const void*>, TmapPair> tmaps;   // keyed on the (k, v) plane pair
     std::string err;
     std::vector<double> plan_scratch;   // per-SM loads of the prefill split cost model
@@ -922,6 +932,19 @@ int hkv_ctx_destroy(hkv_ctx* c) {
     if (c->st_k) cudaFree(c->st_k);
     if (c->st_v) cudaFree(c->st_v);
     if (c->st_out) cudaFree(c->st_out);
+    if (c->host_in) cudaStreamSynchronize(c->host_in);
+    if (c->host_out) cudaStreamSynchronize(c->host_out);
+    for (hkv_ctx::HostSlot& h : c->host_slots) {
+        if (h.q) cudaFree(h.q);
+        if (h.k) cudaFree(h.k);
+        if (h.v) cudaFree(h.v);
+        if (h.out) cudaFree(h.out);
+        if (h.in_done) cudaEventDestroy(h.in_done);
+        if (h.compute_done) cudaEventDestroy(h.compute_done);
+        if (h.out_done) cudaEventDestroy(h.out_done);
+    }
+    if (c->host_in) cudaStreamDestroy(c->host_in);
+    if (c->host_out) cudaStreamDestroy(c->host_out);
     for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
     delete c;
     return HKV_OK;
@@ -1215,6 +1238,66 @@ int hkv_append_decode_attention_host(hkv_ctx* c, const void* h_q, const void* h_
     if (stt) return stt;
     if ((e = cudaMemcpyAsync(h_out, c->st_out, qb, cudaMemcpyDeviceToHost, st)) != cudaSuccess)
         return fail_cuda(c, e, "cudaMemcpyAsync(D2H)");
+    return HKV_OK;
+}
+
+int hkv_append_decode_attention_host_pipelined(hkv_ctx* c, const void* h_q, const void* h_k_new,
+                                               const void* h_v_new, void* k_cache, void* v_cache,
+                                               void* h_out, const int32_t* d_cache_pos, float scale,
+                                               void* stream) {
+    HKV_CHECK_CTX(c);
+    if (!h_q || !h_k_new || !h_v_new || !h_out) return fail(c, HKV_ERR_INVALID_ARG, "host op: null buffer");
+    if (!d_cache_pos) return fail(c, HKV_ERR_INVALID_ARG, "host op: null position array");
+    const size_t qb = (size_t)c->g.batch * c->g.num_heads * c->g.head_dim * 2;
+    const size_t kb = (size_t)c->g.batch * c->g.num_kv_heads * c->g.head_dim * 2;
+    cudaError_t e;
+    if (!c->host_in) {
+        if ((e = cudaStreamCreateWithFlags(&c->host_in, cudaStreamNonBlocking)) != cudaSuccess ||
+            (e = cudaStreamCreateWithFlags(&c->host_out, cudaStreamNonBlocking)) != cudaSuccess)
+            return fail_cuda(c, e, "cudaStreamCreate(host copies)");
+    }
+    hkv_ctx::HostSlot& h = c->host_slots[c->host_calls % hkv_ctx::kHostSlots];
+    if (!h.q) {
+        if ((e = cudaMalloc(&h.q, qb)) != cudaSuccess || (e = cudaMalloc(&h.k, kb)) != cudaSuccess ||
+            (e = cudaMalloc(&h.v, kb)) != cudaSuccess || (e = cudaMalloc(&h.out, qb)) != cudaSuccess)
+            return fail_cuda(c, e, "cudaMalloc(staging)");
+        if ((e = cudaEventCreateWithFlags(&h.in_done, cudaEventDisableTiming)) != cudaSuccess ||
+            (e = cudaEventCreateWithFlags(&h.compute_done, cudaEventDisableTiming)) != cudaSuccess ||
+            (e = cudaEventCreateWithFlags(&h.out_done, cudaEventDisableTiming)) != cudaSuccess)
+            return fail_cuda(c, e, "cudaEventCreate(staging)");
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    if (h.used) {
+        // the set's inputs are free once the launch that read them has run; its output once it has been copied out
+        if ((e = cudaStreamWaitEvent(c->host_in, h.compute_done, 0)) != cudaSuccess ||
+            (e = cudaStreamWaitEvent(st, h.out_done, 0)) != cudaSuccess)
+            return fail_cuda(c, e, "cudaStreamWaitEvent(staging reuse)");
+    }
+    if ((e = cudaMemcpyAsync(h.q, h_q, qb, cudaMemcpyHostToDevice, c->host_in)) != cudaSuccess ||
+        (e = cudaMemcpyAsync(h.k, h_k_new, kb, cudaMemcpyHostToDevice, c->host_in)) != cudaSuccess ||
+        (e = cudaMemcpyAsync(h.v, h_v_new, kb, cudaMemcpyHostToDevice, c->host_in)) != cudaSuccess ||
+        (e = cudaEventRecord(h.in_done, c->host_in)) != cudaSuccess ||
+        (e = cudaStreamWaitEvent(st, h.in_done, 0)) != cudaSuccess)
+        return fail_cuda(c, e, "cudaMemcpyAsync(H2D)");
+    const int stt = decode_full(c, h.q, h.k, h.v, k_cache, v_cache, h.out, nullptr, d_cache_pos, 1, 0, scale, st);
+    if (stt) return stt;
+    if ((e = cudaEventRecord(h.compute_done, st)) != cudaSuccess ||
+        (e = cudaStreamWaitEvent(c->host_out, h.compute_done, 0)) != cudaSuccess ||
+        (e = cudaMemcpyAsync(h_out, h.out, qb, cudaMemcpyDeviceToHost, c->host_out)) != cudaSuccess ||
+        (e = cudaEventRecord(h.out_done, c->host_out)) != cudaSuccess)
+        return fail_cuda(c, e, "cudaMemcpyAsync(D2H)");
+    h.used = true;
+    ++c->host_calls;
+    return HKV_OK;
+}
+
+int hkv_host_flush(hkv_ctx* c, void* stream) {
+    HKV_CHECK_CTX(c);
+    for (hkv_ctx::HostSlot& h : c->host_slots) {
+        if (!h.used) continue;
+        const cudaError_t e = cudaStreamWaitEvent((cudaStream_t)stream, h.out_done, 0);
+        if (e != cudaSuccess) return fail_cuda(c, e, "cudaStreamWaitEvent(flush)");
+    }
     return HKV_OK;
 }
 

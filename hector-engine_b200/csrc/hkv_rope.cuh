@@ -91,21 +91,24 @@ __device__ __forceinline__ void unpack8(const uint4& raw, float (&x)[8]) {
 // The register path (host: rows 16-byte aligned, head_dim a multiple of 8 and at most 256, rotary_dim/2
 // a multiple of 8). A head is held by the smallest power-of-two group of lanes that covers its 16-byte
 // pieces (16 lanes for head_dim 128: a warp works on TWO heads at a time), one piece of 8 elements per
-// lane. What keeps the instruction count per byte low — the first version of this kernel was bound by
-// instruction issue, not by memory:
-//   * the rotation partner of a piece is a whole piece rot/16 lanes away: its RAW 16 bytes come over in
-//     four shuffles and are normalised here with the partner's weights (same head, same 1/rms);
-//   * pieces outside the rotated span use cos = 1, sin = 0, query/key/value lanes differ only in the
-//     weights they read and in the address they store to: no divergent branches in the unit;
-//   * a CTA owns a contiguous range of tokens, computes theta^(-2i/rot) once, and the cos/sin tables of
-//     up to four tokens at a time with all its threads (one sincosf per thread);
-//   * every warp issues the 16-byte loads of U of its units before it touches the first.
+// lane. The kernel moves 256-byte rows and must stay under ~0.15 warp instructions per byte to be
+// bound by memory rather than by instruction issue (its first versions were not), so:
+//   * a CTA owns a contiguous range of tokens, computes theta^(-2i/rot) once and, for up to four
+//     tokens at a time, the cos/sin of each pair with all its threads (one sincosf per thread), then
+//     folds them with the norm weights into two tables per (token, q|k):
+//         A[i] = w[i]·cos_i   B[i] = ∓w[partner(i)]·sin_i     (A = w, B = 0 outside the rotated span)
+//     so that an output element is  rsqrt(mean(x²)+eps) · (x[i]·A[i] + x[partner(i)]·B[i]):
+//     three floating-point instructions, no branch, the same code for every lane;
+//   * the partner of a piece is a whole piece rot/16 lanes away: its RAW 16 bytes come over in four
+//     shuffles; query / key / value lanes differ only in table and store address;
+//   * (token, unit) pairs are walked incrementally — no division in the loop — and every warp issues
+//     the 16-byte loads of U of its units before it touches the first.
 template <int U>
 __device__ __forceinline__ void rope_tokens_fast(const RopeArgs& a, float* s_cos, float* s_sin, float* s_freq,
-                                                 float (*s_w)[512], int* s_row) {
+                                                 float (*s_w)[512], float* s_A, float* s_B, long long* s_off) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int half_rot = a.rot / 2;
-    const int P = a.HD / 8, hp = half_rot / 8, rp = a.rot / 8;
+    const int HD = a.HD, half_rot = a.rot / 2;
+    const int P = HD / 8, hp = half_rot / 8, rp = a.rot / 8;
     int LPH = 1;                                   // lanes per head
     while (LPH < P) LPH <<= 1;
     const int HPW = 32 / LPH;                      // heads per warp
@@ -114,13 +117,13 @@ __device__ __forceinline__ void rope_tokens_fast(const RopeArgs& a, float* s_cos
     const bool rot_lo = p < hp, rot_hi = !rot_lo && p < rp;
     const int pi = rot_lo ? p + hp : (rot_hi ? p - hp : p);     // partner piece
     const int src_lane = lane - p + pi;
-    const int tpiece = rot_lo ? p : p - hp;                     // table piece (when rotated)
-    const float sgn = rot_lo ? -1.0f : 1.0f;
     const bool copy_v = a.k_cache && a.v;
-    const int per_tok = a.H + a.KVH + (copy_v ? a.KVH : 0);
-    const int slots_per_tok = (per_tok + HPW - 1) / HPW;
+    const int HK = a.H + a.KVH;
+    const int per_tok = HK + (copy_v ? a.KVH : 0);
+    const int spt = (per_tok + HPW - 1) / HPW;     // warp-level units ("slots") per token
+    const float inv_hd = 1.0f / (float)HD;
 
-    for (int i = tid; i < a.HD; i += blockDim.x) {
+    for (int i = tid; i < HD; i += blockDim.x) {
         s_w[0][i] = __half2float(a.q_w[i]);
         s_w[1][i] = __half2float(a.k_w[i]);
     }
@@ -130,7 +133,7 @@ __device__ __forceinline__ void rope_tokens_fast(const RopeArgs& a, float* s_cos
     const long long per = (tokens + gridDim.y - 1) / gridDim.y;
     const long long t_begin = blockIdx.y * per;
     const long long t_end = t_begin + per < tokens ? t_begin + per : tokens;
-    int TB = (int)blockDim.x / (half_rot > 0 ? half_rot : 1);   // tokens whose tables fit one pass of the CTA
+    int TB = (int)blockDim.x / (half_rot > 0 ? half_rot : 1);   // tokens whose angles fit one pass of the CTA
     TB = TB < 1 ? 1 : (TB > 4 ? 4 : TB);
     const int stride = gridDim.x * kRopeWarps;
 
@@ -140,40 +143,66 @@ __device__ __forceinline__ void rope_tokens_fast(const RopeArgs& a, float* s_cos
         for (int e = tid; e < nb * half_rot; e += blockDim.x) {
             const int tt = e / half_rot, i = e - tt * half_rot;
             const long long tok = tb + tt;
-            const int s = (int)(tok % a.S), b = (int)(tok / a.S);
-            const int pos = (a.d_pos ? a.d_pos[b * a.pos_stride] : a.host_pos) + s;
+            const int pos = (a.d_pos ? a.d_pos[(int)(tok / a.S) * a.pos_stride] : a.host_pos) + (int)(tok % a.S);
             float sn, c;
             sincosf(((float)pos / a.scaling) * s_freq[i], &sn, &c);
             s_cos[e] = c;
             s_sin[e] = sn;
-            if (i == 0) s_row[tt] = a.k_cache ? slot_of_pos(a.map, pos) : -1;
         }
-        if (half_rot == 0) {
-            for (int tt = tid; tt < nb; tt += blockDim.x) {
-                const long long tok = tb + tt;
-                const int pos = (a.d_pos ? a.d_pos[(int)(tok / a.S) * a.pos_stride] : a.host_pos) + (int)(tok % a.S);
-                s_row[tt] = a.k_cache ? slot_of_pos(a.map, pos) : -1;
+        if (tid < nb) {                     // where the token's K/V rows go: element offset into the planes, or -1
+            const long long tok = tb + tid;
+            const int b = (int)(tok / a.S);
+            const int pos = (a.d_pos ? a.d_pos[b * a.pos_stride] : a.host_pos) + (int)(tok % a.S);
+            const int row = a.k_cache ? slot_of_pos(a.map, pos) : -1;
+            s_off[tid] = row < 0 ? -1 : (long long)b * a.batch_stride + (long long)row * a.KVH * HD;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nb; ++tt) {   // the folded tables of token tt: [q | k][HD]
+            const float* cs = s_cos + tt * half_rot;
+            const float* sn = s_sin + tt * half_rot;
+            for (int r = tid; r < 2 * HD; r += blockDim.x) {
+                const int kind = r >= HD ? 1 : 0, i = r - kind * HD;
+                const float* w = s_w[kind];
+                float A = w[i], B = 0.0f;
+                if (i < half_rot) {
+                    A *= cs[i];
+                    B = -w[i + half_rot] * sn[i];
+                } else if (i < a.rot) {
+                    A *= cs[i - half_rot];
+                    B = w[i - half_rot] * sn[i - half_rot];
+                }
+                s_A[tt * 2 * HD + r] = A;
+                s_B[tt * 2 * HD + r] = B;
             }
         }
         __syncthreads();
-        const int items = nb * slots_per_tok;
-        for (int it0 = blockIdx.x * kRopeWarps + warp; it0 < items; it0 += U * stride) {
+        const __half* q_base = a.q + tb * a.H * HD + 8 * p;
+        const __half* k_base = a.k + tb * a.KVH * HD + 8 * p;
+        const __half* v_base = copy_v ? a.v + tb * a.KVH * HD + 8 * p : nullptr;
+        int it = blockIdx.x * kRopeWarps + warp;
+        int tt = it / spt, slot = it - tt * spt;
+        while (tt < nb) {
             uint4 raw[U];
+            int utt[U], uj[U];
+            const __half* usrc[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const int it = it0 + u * stride;
-                const int tt = it / slots_per_tok, j = (it - tt * slots_per_tok) * HPW + sub;
-                const bool ok = it < items && lane_live && j < per_tok;
-                raw[u] = ok ? __ldg(reinterpret_cast<const uint4*>(rope_unit_src(a, tb + tt, j)) + p)
-                            : make_uint4(0u, 0u, 0u, 0u);
+                utt[u] = tt;
+                uj[u] = slot * HPW + sub;
+                const int j = uj[u];
+                const bool ok = tt < nb && lane_live && j < per_tok;
+                const __half* src = j < a.H ? q_base + (tt * a.H + j) * HD
+                                  : j < HK  ? k_base + (tt * a.KVH + (j - a.H)) * HD
+                                            : v_base + (tt * a.KVH + (j - HK)) * HD;
+                raw[u] = ok ? __ldg(reinterpret_cast<const uint4*>(src)) : make_uint4(0u, 0u, 0u, 0u);
+                usrc[u] = src;
+                slot += stride;
+                while (slot >= spt) { slot -= spt; ++tt; }
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const int it = it0 + u * stride;
-                if (it >= items) break;     // warp-uniform
-                const int tt = it / slots_per_tok, j = (it - tt * slots_per_tok) * HPW + sub;
-                const long long tok = tb + tt;
-                const bool is_q = j < a.H, is_k = !is_q && j < a.H + a.KVH;
+                if (utt[u] >= nb) break;    // warp-uniform
+                const int j = uj[u], t = utt[u];
                 float x[8], px[8];
                 unpack8(raw[u], x);
                 float ssq = 0.0f;
@@ -182,54 +211,42 @@ __device__ __forceinline__ void rope_tokens_fast(const RopeArgs& a, float* s_cos
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1)
                     if (o < LPH) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
-                const float inv = 1.0f / sqrtf(ssq / (float)a.HD + a.eps);
+                const float inv = rsqrtf(fmaf(ssq, inv_hd, a.eps));
                 uint4 praw;
                 praw.x = __shfl_sync(0xffffffffu, raw[u].x, src_lane);
                 praw.y = __shfl_sync(0xffffffffu, raw[u].y, src_lane);
                 praw.z = __shfl_sync(0xffffffffu, raw[u].z, src_lane);
                 praw.w = __shfl_sync(0xffffffffu, raw[u].w, src_lane);
-                unpack8(praw, px);
                 if (!lane_live || j >= per_tok) continue;
-                const float* w = s_w[is_q ? 0 : 1];
-                const bool rotated = rot_lo || rot_hi;
-                const float* tc = s_cos + tt * half_rot + 8 * tpiece;
-                const float* ts = s_sin + tt * half_rot + 8 * tpiece;
-                uint32_t packed[4];
-#pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {      // four elements at a time: fewer live registers
-                    const float4 wn = *reinterpret_cast<const float4*>(w + 8 * p + 4 * hf);
-                    const float4 wp = *reinterpret_cast<const float4*>(w + 8 * pi + 4 * hf);
-                    float4 cc = make_float4(1.f, 1.f, 1.f, 1.f), ss = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (rotated) {
-                        cc = *reinterpret_cast<const float4*>(tc + 4 * hf);
-                        ss = *reinterpret_cast<const float4*>(ts + 4 * hf);
-                    }
-                    const float* xs = x + 4 * hf;
-                    const float* ps = px + 4 * hf;
-                    const float r0 = fmaf(sgn * (ps[0] * (inv * wp.x)), ss.x, (xs[0] * (inv * wn.x)) * cc.x);
-                    const float r1 = fmaf(sgn * (ps[1] * (inv * wp.y)), ss.y, (xs[1] * (inv * wn.y)) * cc.y);
-                    const float r2 = fmaf(sgn * (ps[2] * (inv * wp.z)), ss.z, (xs[2] * (inv * wn.z)) * cc.z);
-                    const float r3 = fmaf(sgn * (ps[3] * (inv * wp.w)), ss.w, (xs[3] * (inv * wn.w)) * cc.w);
-                    packed[2 * hf] = pack_half2(r0, r1);
-                    packed[2 * hf + 1] = pack_half2(r2, r3);
+                const bool is_q = j < a.H;
+                uint4 o;
+                if (j < HK) {
+                    unpack8(praw, px);
+                    const float* tA = s_A + ((t * 2 + (is_q ? 0 : 1)) * HD + 8 * p);
+                    const float* tB = s_B + ((t * 2 + (is_q ? 0 : 1)) * HD + 8 * p);
+                    const float4 a0 = *reinterpret_cast<const float4*>(tA), a1 = *reinterpret_cast<const float4*>(tA + 4);
+                    const float4 b0 = *reinterpret_cast<const float4*>(tB), b1 = *reinterpret_cast<const float4*>(tB + 4);
+                    o.x = pack_half2(inv * fmaf(px[0], b0.x, x[0] * a0.x), inv * fmaf(px[1], b0.y, x[1] * a0.y));
+                    o.y = pack_half2(inv * fmaf(px[2], b0.z, x[2] * a0.z), inv * fmaf(px[3], b0.w, x[3] * a0.w));
+                    o.z = pack_half2(inv * fmaf(px[4], b1.x, x[4] * a1.x), inv * fmaf(px[5], b1.y, x[5] * a1.y));
+                    o.w = pack_half2(inv * fmaf(px[6], b1.z, x[6] * a1.z), inv * fmaf(px[7], b1.w, x[7] * a1.w));
+                } else {
+                    o = raw[u];             // value head: plain copy into the cache
                 }
-                uint4 o = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                 __half* dst;
                 if (is_q) {
-                    dst = a.q + (tok * a.H + j) * a.HD;
+                    dst = const_cast<__half*>(usrc[u]);      // rewritten in place
                 } else {
-                    const int kvh = is_k ? j - a.H : j - a.H - a.KVH;
+                    const int kvh = j < HK ? j - a.H : j - HK;
                     if (a.k_cache) {
-                        const int row = s_row[tt];
-                        if (row < 0) continue;          // dropped past the plane / owned by another rank
-                        const long long off = (tok / a.S) * a.batch_stride + ((long long)row * a.KVH + kvh) * a.HD;
-                        dst = (is_k ? a.k_cache : a.v_cache) + off;
-                        if (!is_k) o = raw[u];          // value head: plain copy into the cache
+                        const long long off = s_off[t];
+                        if (off < 0) continue;          // dropped past the plane / owned by another rank
+                        dst = (j < HK ? a.k_cache : a.v_cache) + off + kvh * HD + 8 * p;
                     } else {
-                        dst = a.k + (tok * a.KVH + kvh) * a.HD;
+                        dst = const_cast<__half*>(usrc[u]);  // no cache: k rewritten in place
                     }
                 }
-                reinterpret_cast<uint4*>(dst)[p] = o;
+                *reinterpret_cast<uint4*>(dst) = o;
             }
         }
     }
@@ -249,13 +266,14 @@ __global__ void __launch_bounds__(kRopeWarps * 32, 4) hkv_qk_norm_rope_kernel(co
     __shared__ __align__(16) float s_cos[256];
     __shared__ __align__(16) float s_sin[256];
     __shared__ __align__(16) float s_w[2][512];          // q and k norm weights as fp32
+    __shared__ __align__(16) float s_buf[kRopeWarps * 512];   // fast: the A and B tables; else: the warps' staging rows
     if (fast) {
         __shared__ float s_freq[256];
-        __shared__ int s_row[4];
-        rope_tokens_fast<3>(a, s_cos, s_sin, s_freq, s_w, s_row);
+        __shared__ long long s_off[4];
+        rope_tokens_fast<3>(a, s_cos, s_sin, s_freq, s_w, s_buf, s_buf + 2048, s_off);
         return;
     }
-    __shared__ float s_x[kRopeWarps][512];
+    float (*s_x)[512] = reinterpret_cast<float (*)[512]>(s_buf);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int per_tok = a.H + 2 * a.KVH;
     const int half_rot = a.rot / 2;

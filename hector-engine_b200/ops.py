@@ -169,6 +169,18 @@ class Context:
             self._h, _ptr(h_q), _ptr(h_k_new), _ptr(h_v_new), _ptr(k_cache), _ptr(v_cache),
             _ptr(h_out), _ptr(d_cache_pos), scale, _stream(stream)))
 
+    def append_decode_attention_host_pipelined(self, h_q, h_k_new, h_v_new, k_cache, v_cache, h_out,
+                                               d_cache_pos, scale=None, stream=None):
+        """As append_decode_attention_host, with the copies on the context's own streams so that they
+        overlap neighbouring calls' kernels; h_out is complete after host_flush() + a sync of `stream`."""
+        scale = self.geometry.default_scale if scale is None else scale
+        self._check(self.lib.hkv_append_decode_attention_host_pipelined(
+            self._h, _ptr(h_q), _ptr(h_k_new), _ptr(h_v_new), _ptr(k_cache), _ptr(v_cache),
+            _ptr(h_out), _ptr(d_cache_pos), scale, _stream(stream)))
+
+    def host_flush(self, stream=None):
+        self._check(self.lib.hkv_host_flush(self._h, _stream(stream)))
+
     def prefill_attention(self, q, k_cache, v_cache, out, seq_new, past_len, scale=None, stream=None):
         scale = self.geometry.default_scale if scale is None else scale
         self._check(self.lib.hkv_prefill_attention(self._h, _ptr(q), _ptr(k_cache), _ptr(v_cache),

@@ -271,6 +271,20 @@ int hkv_append_decode_attention_host(hkv_ctx* ctx, const void* h_q, const void* 
                                      void* h_out, const int32_t* d_cache_pos, float scale,
                                      void* stream);
 
+/* The same with the copies taken off `stream`: inputs go host -> device on a copy stream of the
+ * context, the result device -> host on another, through a ring of four staging sets, so that the
+ * copies of one call overlap the kernels of its neighbours (a decode step is one such call per
+ * layer). Differences from the call above: the host inputs must be final when the call is MADE
+ * (they are not ordered after earlier work on `stream`), and h_out is complete only once `stream`
+ * has passed an hkv_host_flush enqueued after the call. The kernels themselves run on `stream` in
+ * call order, so the cache planes see the same sequence of appends. Not capturable. */
+int hkv_append_decode_attention_host_pipelined(hkv_ctx* ctx, const void* h_q, const void* h_k_new,
+                                               const void* h_v_new, void* k_cache, void* v_cache,
+                                               void* h_out, const int32_t* d_cache_pos, float scale,
+                                               void* stream);
+/* Makes `stream` wait for every output copy the pipelined call above has enqueued so far. */
+int hkv_host_flush(hkv_ctx* ctx, void* stream);
+
 /* ---- the step in front of the append (next row of the path) ------------------------ */
 
 /* Per-head RMSNorm of q and k + rotary embedding; with cache planes given, the rotated K and

@@ -225,6 +225,21 @@ def test_fused_append_decode(hkv, cuda, oracle, shape, kernel):
     torch.cuda.synchronize()
     assert np.array_equal(ho.numpy().view(np.uint16), out.cpu().numpy().view(np.uint16))
     assert np.array_equal(dk2.cpu().numpy().view(np.uint16), ref_k.view(np.uint16))
+    # pipelined form: copies on the context's own streams; ten calls cycle the four staging sets more than
+    # twice, each call with its own host buffers and planes, all outputs complete after one flush
+    n = 10
+    hos = [torch.zeros(B, H, HD, dtype=torch.float16).pin_memory() for _ in range(n)]
+    planes = [(to_dev(torch, kc), to_dev(torch, vc)) for _ in range(n)]
+    dpos = to_dev(torch, pos)
+    torch.cuda.synchronize()
+    for i in range(n):
+        ctx.append_decode_attention_host_pipelined(hq, hk, hv, planes[i][0], planes[i][1], hos[i], dpos, scale)
+    ctx.host_flush()
+    torch.cuda.synchronize()
+    for i in range(n):
+        assert np.array_equal(hos[i].numpy().view(np.uint16), out.cpu().numpy().view(np.uint16)), f"pipelined call {i}"
+        assert np.array_equal(planes[i][0].cpu().numpy().view(np.uint16), ref_k.view(np.uint16))
+    assert ctx.device_status() == 0
     ctx.close()
 
 
