@@ -480,7 +480,7 @@ struct PrefillPass {
 int prefill_tc_launch(hkv_ctx* c, const hkv_geometry& g, const void* q, const void* k_plane, const void* v_plane, void* out,
                       int seq_new, int past_len, float scale, cudaStream_t st, const PrefillPass* pass) {
     const int HD = g.head_dim, G = g.num_heads / g.num_kv_heads, HDS = prefill_tc_staged_hd(HD), KEYS = prefill_tc_keys(HD);
-    PrefillTcArgs t;
+    PrefillTcArgs t{};
     t.out = (__half*)out;
     t.status = c->d_status;
     t.key_limit = pass ? pass->key_limit : 0x7fffffff;
@@ -557,7 +557,7 @@ int launch_append(hkv_ctx* c, const void* k_new, const void* v_new, void* k_cach
     if (!aligned(k_new, 2) || !aligned(v_new, 2) || !aligned(k_cache, 2) || !aligned(v_cache, 2))
         return fail(c, HKV_ERR_ALIGNMENT, "append: fp16 pointer not 2-byte aligned");
     if (seq_new == 0) return HKV_OK;
-    AppendArgs a;
+    AppendArgs a{};
     a.k_new = (const __half*)k_new;
     a.v_new = (const __half*)v_new;
     a.k_cache = (__half*)k_cache;
@@ -596,7 +596,7 @@ int launch_decode(hkv_ctx* c, const void* q, const void* k_new, const void* v_ne
     const bool fused = k_new != nullptr;
     if (fused && !v_new) return fail(c, HKV_ERR_INVALID_ARG, "decode: k_new without v_new");
 
-    DecodeArgs a;
+    DecodeArgs a{};
     a.q = (const __half*)q;
     a.k_cache = (const __half*)k_cache;
     a.v_cache = (const __half*)v_cache;
@@ -679,7 +679,7 @@ int check_exchange(hkv_ctx* c, const hkv_exchange* x, const char* who) {
 int launch_combine(hkv_ctx* c, const float* part, long long stride_b, long long stride_c,
                    const int32_t* d_total, int pos_is_index, int host_len, int fixed_count, void* out,
                    float* out_partial, cudaStream_t st, bool span = false, const hkv_exchange* x = nullptr) {
-    CombineArgs a;
+    CombineArgs a{};
     a.pub_n = 0;
     a.pub_state = nullptr;
     a.pub_part = nullptr;
@@ -1101,7 +1101,7 @@ int hkv_merge_published(hkv_ctx* c, const hkv_exchange* exchange, void* out, voi
     if (!out) return fail(c, HKV_ERR_INVALID_ARG, "merge_published: null output");
     if (!aligned(out, 2)) return fail(c, HKV_ERR_ALIGNMENT, "merge_published: out not 2-byte aligned");
     if (c->g.head_dim > 512) return fail(c, HKV_ERR_GEOMETRY, "merge_published: head_dim above 512");
-    MergePublishedArgs a;
+    MergePublishedArgs a{};
     uint8_t* box = (uint8_t*)exchange->mailbox[exchange->rank];
     for (int r = 0; r < exchange->world; ++r)
         a.part[r] = (const float*)((const uint8_t*)exchange->mailbox[r] + kMailboxHeaderBytes);
@@ -1349,7 +1349,7 @@ int hkv_qk_norm_rope_kv(hkv_ctx* c, void* q, void* k, const void* v, const void*
         return fail(c, HKV_ERR_ALIGNMENT, "qk_norm_rope: fp16 pointer not 2-byte aligned");
     if (seq_new == 0) return HKV_OK;
     const hkv_geometry& g = c->g;
-    RopeArgs a;
+    RopeArgs a{};
     a.q = (__half*)q;
     a.k = (__half*)k;
     a.v = (const __half*)v;
@@ -1586,7 +1586,7 @@ extern "C" int hkv_decode_attention_static(const hkv_geometry* geometry, const v
     // Nothing in the array has to start at zero: the combine kernel reads exactly the partial
     // rows the decode kernel of the same call has written (both derive the count from
     // d_total_seq), so the previous call's contents are never observed.
-    DecodeArgs a;
+    DecodeArgs a{};
     a.q = (const __half*)q;
     a.k_cache = (const __half*)k_cache;
     a.v_cache = (const __half*)v_cache;
@@ -1617,7 +1617,7 @@ extern "C" int hkv_decode_attention_static(const hkv_geometry* geometry, const v
     dim3 grid((unsigned)max_chunks, (unsigned)g.num_heads, (unsigned)g.batch);
     hkv_decode_generic_kernel<<<grid, kGenWarps * 32, 0, st>>>(a);
 
-    CombineArgs c;
+    CombineArgs c{};
     const long long PW = g.head_dim + 2;
     c.part = static_cast<const float*>(slot.scratch);
     c.stride_b = (long long)max_chunks * g.num_heads * PW;

@@ -170,11 +170,11 @@ struct CombineArgs {
     // Peer exchange (pub_n > 0): the merged partial goes to this rank's own mailbox (local memory, the
     // parity of the current epoch); the last CTA to finish publishes the new epoch in every rank's
     // mailbox (one 4-byte store per rank over NVLink). The peers then READ the partial from here.
-    int pub_n;
-    float* pub_part;                 // parity 0 of the partial area of this rank's mailbox
-    long long pub_parity_stride;     // floats between the two parities
-    uint32_t* pub_flag[kMaxPeers];   // this rank's flag word in mailbox r
-    uint32_t* pub_state;             // this rank's own {epoch, CTAs finished}
+    int pub_n = 0;
+    float* pub_part = nullptr;       // parity 0 of the partial area of this rank's mailbox
+    long long pub_parity_stride = 0; // floats between the two parities
+    uint32_t* pub_flag[kMaxPeers] = {};  // this rank's flag word in mailbox r
+    uint32_t* pub_state = nullptr;   // this rank's own {epoch, CTAs finished}
 };
 
 constexpr int kCombineWarps = 8;
