@@ -680,18 +680,13 @@ int launch_combine(hkv_ctx* c, const float* part, long long stride_b, long long 
                    const int32_t* d_total, int pos_is_index, int host_len, int fixed_count, void* out,
                    float* out_partial, cudaStream_t st, bool span = false, const hkv_exchange* x = nullptr) {
     CombineArgs a{};
-    a.pub_n = 0;
-    a.pub_state = nullptr;
-    a.pub_part = nullptr;
-    a.pub_parity_stride = 0;
     if (x) {
         // mailbox: 64 flag words, 64 state words, then [2][batch*heads*(head_dim+2)] floats
         uint8_t* mine = (uint8_t*)x->mailbox[x->rank];
         a.pub_n = x->world;
         a.pub_part = (float*)(mine + kMailboxHeaderBytes);
         a.pub_parity_stride = (long long)c->g.batch * c->g.num_heads * (c->g.head_dim + 2);
-        for (int r = 0; r < x->world; ++r) a.pub_flag[r] = (uint32_t*)x->mailbox[r] + x->rank;
-        a.pub_state = (uint32_t*)(mine + kMailboxHeaderBytes / 2);
+        a.pub_state = (const uint32_t*)(mine + kMailboxHeaderBytes / 2);
     }
     a.gpre = span ? c->span_gpre : nullptr;
     a.span_spans = span ? c->tma_grid / c->span_gang : 0;
@@ -1103,10 +1098,12 @@ int hkv_merge_published(hkv_ctx* c, const hkv_exchange* exchange, void* out, voi
     if (c->g.head_dim > 512) return fail(c, HKV_ERR_GEOMETRY, "merge_published: head_dim above 512");
     MergePublishedArgs a{};
     uint8_t* box = (uint8_t*)exchange->mailbox[exchange->rank];
-    for (int r = 0; r < exchange->world; ++r)
+    for (int r = 0; r < exchange->world; ++r) {
         a.part[r] = (const float*)((const uint8_t*)exchange->mailbox[r] + kMailboxHeaderBytes);
+        a.flag_out[r] = (uint32_t*)exchange->mailbox[r] + exchange->rank;
+    }
     a.flags = (const uint32_t*)box;
-    a.state = (const uint32_t*)(box + kMailboxHeaderBytes / 2);
+    a.state = (uint32_t*)(box + kMailboxHeaderBytes / 2);
     a.world = exchange->world;
     a.rows = c->g.batch * c->g.num_heads;
     a.HD = c->g.head_dim;

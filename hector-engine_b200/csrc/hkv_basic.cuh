@@ -168,45 +168,25 @@ struct CombineArgs {
     __half* out;         // [B, H, HD] or null
     float* out_partial;  // [B, H, HD+2] or null
     // Peer exchange (pub_n > 0): the merged partial goes to this rank's own mailbox (local memory, the
-    // parity of the current epoch); the last CTA to finish publishes the new epoch in every rank's
-    // mailbox (one 4-byte store per rank over NVLink). The peers then READ the partial from here.
+    // parity of the current epoch), where the peers READ it once the merge kernel of this rank has
+    // released the epoch.
     int pub_n = 0;
     float* pub_part = nullptr;       // parity 0 of the partial area of this rank's mailbox
     long long pub_parity_stride = 0; // floats between the two parities
-    uint32_t* pub_flag[kMaxPeers] = {};  // this rank's flag word in mailbox r
-    uint32_t* pub_state = nullptr;   // this rank's own {epoch, CTAs finished}
+    const uint32_t* pub_state = nullptr;   // this rank's epoch counter (advanced by the merge kernel)
 };
 
-constexpr int kCombineWarps = 8;
-constexpr int kCombineThreads = kCombineWarps * 32;
-
-// Epoch of the exchange a merging launch belongs to (all CTAs read it before the last one advances it).
+// Epoch of the exchange a publishing launch belongs to.
 __device__ __forceinline__ uint32_t pub_epoch(const CombineArgs& a) {
-    return a.pub_n ? *reinterpret_cast<volatile uint32_t*>(a.pub_state) : 0u;
+    return a.pub_n ? *reinterpret_cast<const volatile uint32_t*>(a.pub_state) : 0u;
 }
 __device__ __forceinline__ void store_partial(const CombineArgs& a, const uint32_t epoch, const long long idx, const float v) {
     if (a.out_partial) a.out_partial[idx] = v;
     if (a.pub_n) a.pub_part[(long long)(epoch & 1u) * a.pub_parity_stride + idx] = v;
 }
-// After a CTA's last store: the classic last-block pattern (stores, device-scope fence, counter). The
-// CTA that finds itself last has, through the counter, observed every other CTA's stores; its
-// system-scope fence orders all of them before the flag stores that release the epoch to the peers.
-// Never waits.
-__device__ __forceinline__ void pub_publish(const CombineArgs& a, const uint32_t epoch) {
-    if (!a.pub_n) return;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const uint32_t ctas = gridDim.x * gridDim.y;
-        if (atomicAdd(a.pub_state + 1, 1u) == ctas - 1) {
-            a.pub_state[1] = 0;
-            *reinterpret_cast<volatile uint32_t*>(a.pub_state) = epoch + 1;
-            __threadfence_system();
-            for (int r = 0; r < a.pub_n; ++r)
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.pub_flag[r]), "r"(epoch + 1) : "memory");
-        }
-    }
-}
+
+constexpr int kCombineWarps = 8;
+constexpr int kCombineThreads = kCombineWarps * 32;
 
 // One CTA per (head, sequence). The partials are dealt to the warps (warp w takes c = w, w+8, ...);
 // a warp reads one partial row at a time, lane l the output dimensions l, l+32, ... — coalesced
@@ -286,7 +266,6 @@ __global__ void __launch_bounds__(kCombineThreads) hkv_combine_kernel(const Comb
         store_partial(a, epoch, ((long long)b * a.H + h) * PW + a.HD, M);
         store_partial(a, epoch, ((long long)b * a.H + h) * PW + a.HD + 1, L);
     }
-    pub_publish(a, epoch);
 }
 
 // The merge for many (sequence, head) rows: one thread per output dimension walks the row's
@@ -365,22 +344,27 @@ __global__ void __launch_bounds__(128) hkv_combine_few_kernel(const CombineArgs 
         store_partial(a, epoch, ((long long)b * a.H + h) * PW + a.HD, M);
         store_partial(a, epoch, ((long long)b * a.H + h) * PW + a.HD + 1, L);
     }
-    pub_publish(a, epoch);
 }
 
 // ---------------------------------------------------------------------------
-// Merge of published partials: the receiving half of the peer exchange. Every CTA first waits — with
-// a bound — until the flag of every rank in THIS rank's mailbox has reached the epoch of the
-// publishing launch that precedes this one on the stream; then one warp per (sequence, head) row
-// reads that epoch's partial of every rank — its own from local memory, the others' through their
-// peer-mapped mailboxes over NVLink (plain system-scope loads, nothing cached) — and merges them.
+// Merge of published partials: both halves of the peer exchange's handshake.
+//   1. The first CTA to arrive releases this rank's partial of the current epoch: one system-scope
+//      fence, then the new epoch stored into the flag word this rank owns in every rank's mailbox
+//      (4-byte stores over NVLink). The partial was written by the launch before this one on the
+//      stream, so it is complete; nothing of the publishing kernels pays for fences or counters.
+//   2. Every CTA waits — with a bound — until the flag of every rank in THIS rank's mailbox has reached
+//      the epoch, then one warp per (sequence, head) row reads that epoch's partial of every rank — its
+//      own from local memory, the others' through their peer-mapped mailboxes over NVLink (plain
+//      system-scope loads, nothing cached) — and merges them.
+//   3. The last CTA to finish advances the epoch counter for the next exchange.
 // When the wait runs out the rows are left untouched, the status word gets kStatusWaitRanOut and the
-// kernel returns normally; launches that find the bit already set return at once.
+// kernel returns normally (the epoch still advances); launches that find the bit already set do not wait.
 // ---------------------------------------------------------------------------
 struct MergePublishedArgs {
     const float* part[kMaxPeers];   // parity 0 of rank r's partial area, as mapped here: [2][rows][HD+2]
+    uint32_t* flag_out[kMaxPeers];  // this rank's flag word in rank r's mailbox
     const uint32_t* flags;          // [world] in this rank's mailbox, written by the peers
-    const uint32_t* state;          // this rank's epoch counter
+    uint32_t* state;                // this rank's {epoch, CTAs finished, CTAs arrived}
     int world, rows, HD;
     __half* out;                    // [rows][HD]
     int32_t* status;
@@ -398,10 +382,17 @@ __device__ __forceinline__ float ld_sys(const float* p) {
 __global__ void __launch_bounds__(kMergeWarps * 32) hkv_merge_published_kernel(const MergePublishedArgs a) {
     __shared__ int s_ok;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t expect = *reinterpret_cast<const volatile uint32_t*>(a.state);
-    // a wait that already ran out (an earlier layer of this step) is not repeated: a lost peer costs
-    // one limit per step, not one per layer
-    if (tid == 0) s_ok = (*reinterpret_cast<volatile int32_t*>(a.status) & kStatusWaitRanOut) ? 0 : 1;
+    const uint32_t expect = *reinterpret_cast<const volatile uint32_t*>(a.state) + 1u;
+    if (tid == 0) {
+        if (atomicAdd(a.state + 2, 1u) == 0u) {          // first to arrive: release this rank's partial
+            __threadfence_system();
+            for (int r = 0; r < a.world; ++r)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.flag_out[r]), "r"(expect) : "memory");
+        }
+        // a wait that already ran out (an earlier layer of this step) is not repeated: a lost peer costs
+        // one limit per step, not one per layer
+        s_ok = (*reinterpret_cast<volatile int32_t*>(a.status) & kStatusWaitRanOut) ? 0 : 1;
+    }
     __syncthreads();
     if (s_ok && tid < a.world) {
         unsigned long long t0, t1;
@@ -420,41 +411,48 @@ __global__ void __launch_bounds__(kMergeWarps * 32) hkv_merge_published_kernel(c
         }
     }
     __syncthreads();
-    if (!s_ok) return;
     const int row = blockIdx.x * kMergeWarps + warp;
-    if (row >= a.rows) return;
-    const int PW = a.HD + 2;
-    const long long at = (long long)((expect - 1u) & 1u) * a.rows * PW + (long long)row * PW;
-    // the two scalars of every rank first (lanes 0..world-1 fetch them in parallel), then the rows
-    float m_r = kNegBig, l_r = 0.0f;
-    if (lane < a.world) {
-        m_r = ld_sys(a.part[lane] + at + a.HD);
-        l_r = ld_sys(a.part[lane] + at + a.HD + 1);
-    }
-    float M = m_r;
+    if (s_ok && row < a.rows) {
+        const int PW = a.HD + 2;
+        const long long at = (long long)((expect - 1u) & 1u) * a.rows * PW + (long long)row * PW;
+        // the two scalars of every rank first (lanes 0..world-1 fetch them in parallel), then the rows
+        float m_r = kNegBig, l_r = 0.0f;
+        if (lane < a.world) {
+            m_r = ld_sys(a.part[lane] + at + a.HD);
+            l_r = ld_sys(a.part[lane] + at + a.HD + 1);
+        }
+        float M = m_r;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-    const float w_r = lane < a.world ? exp2f(m_r - M) : 0.0f;
-    float L = l_r * w_r;
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        const float w_r = lane < a.world ? exp2f(m_r - M) : 0.0f;
+        float L = l_r * w_r;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
-    float acc[16];
+        for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+        float acc[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
-    for (int r = 0; r < a.world; ++r) {
-        const float* p = a.part[r] + at;
-        const float w = __shfl_sync(0xffffffffu, w_r, r);
+        for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
+        for (int r = 0; r < a.world; ++r) {
+            const float* p = a.part[r] + at;
+            const float w = __shfl_sync(0xffffffffu, w_r, r);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int d = lane + 32 * i;
+                if (d < a.HD) acc[i] = fmaf(ld_sys(p + d), w, acc[i]);
+            }
+        }
+        const float inv = L > 0.0f ? 1.0f / L : 0.0f;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const int d = lane + 32 * i;
-            if (d < a.HD) acc[i] = fmaf(ld_sys(p + d), w, acc[i]);
+            if (d < a.HD) a.out[(long long)row * a.HD + d] = __float2half_rn(acc[i] * inv);
         }
     }
-    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const int d = lane + 32 * i;
-        if (d < a.HD) a.out[(long long)row * a.HD + d] = __float2half_rn(acc[i] * inv);
+    // the last CTA to finish closes the exchange: the next publishing launch reads the new epoch
+    __syncthreads();
+    if (tid == 0 && atomicAdd(a.state + 1, 1u) == gridDim.x - 1) {
+        a.state[1] = 0;
+        a.state[2] = 0;
+        *reinterpret_cast<volatile uint32_t*>(a.state) = expect;
     }
 }
 

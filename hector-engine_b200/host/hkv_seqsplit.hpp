@@ -11,11 +11,11 @@
 // or, when every rank can map every other rank's memory (Exchange::PeerStores, the default then),
 // without any collective launch:
 //     hkv_decode_partials_publish  the same decode; the kernel that merges this rank's split-K partials
-//                                  leaves the result in this rank's mailbox and publishes an epoch
-//                                  flag in every rank's mailbox (4-byte stores over NVLink)
-//     hkv_merge_published          waits — bounded — for all flags in its OWN mailbox, then reads every
-//                                  rank's partial from that rank's mailbox (plain peer loads) while it
-//                                  merges, writes fp16
+//                                  leaves the result in this rank's mailbox
+//     hkv_merge_published          releases it (an epoch flag into every rank's mailbox: 4-byte stores
+//                                  over NVLink), waits — bounded — for all flags in its OWN mailbox, then
+//                                  reads every rank's partial from that rank's mailbox (plain peer
+//                                  loads) while it merges, writes fp16
 // Mailboxes are cudaMalloc'd per rank and mapped by the others through CUDA IPC handles, handed
 // round once at construction with an NCCL all-gather. The only cross-GPU wait is the merge kernel's
 // bounded poll of flag words in local memory.

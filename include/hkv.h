@@ -227,25 +227,26 @@ int hkv_combine_partials(hkv_ctx* ctx, const float* partials, int32_t num_parts,
                          void* stream);
 
 /* The same exchange WITHOUT a collective launch: the kernel that merges this rank's split-K
- * partials leaves the merged partial in this rank's own mailbox and publishes an epoch flag in
- * every rank's mailbox (one 4-byte store per rank over NVLink); the merge kernel waits — with a
- * bound — for the flags of all ranks in its OWN mailbox and then reads every rank's partial straight
- * from that rank's mailbox (plain peer loads over NVLink, no multicast) while it merges. No
- * counterpart in the reference (single-GPU).
+ * partials leaves the merged partial in this rank's own mailbox; the merge kernel first releases
+ * it — an epoch flag stored into every rank's mailbox, one 4-byte store per rank over NVLink —
+ * then waits, with a bound, for the flags of all ranks in its OWN mailbox and reads every rank's
+ * partial straight from that rank's mailbox (plain peer loads over NVLink, no multicast) while it
+ * merges. No counterpart in the reference (single-GPU).
  *
  * A mailbox is one device allocation of hkv_exchange_bytes() bytes per rank, zeroed once before
  * the first step, that every rank of the node has mapped (cudaIpcOpenMemHandle or any other peer
  * mapping): mailbox[r] is rank r's mailbox as THIS process addresses it, mailbox[rank] the local
- * one. Layout: 64 flag words (flag s = last epoch rank s has published), 64 state words of the owner
- * (its epoch counter and a CTA counter), then [2][batch*num_heads*(head_dim+2)] floats — the owner's
- * partial of two consecutive epochs, because a rank may run one exchange ahead of a peer that is still
- * merging the previous one. Every rank must make the same sequence of publish/merge calls.
+ * one. Layout: 64 flag words (flag s = last epoch rank s has released), 64 state words of the owner
+ * (its epoch counter and two CTA counters), then [2][batch*num_heads*(head_dim+2)] floats — the
+ * owner's partial of two consecutive epochs, because a rank may run one exchange ahead of a peer that
+ * is still merging the previous one. Every rank must make the same sequence of calls, each
+ * hkv_decode_partials_publish followed by one hkv_merge_published on the same stream.
  *
  * hkv_decode_partials_publish: hkv_decode_partials with the mailbox as destination; never waits.
- * hkv_merge_published: waits at most wait_limit_ms (0 = 2000) for every rank's flag, then writes
- *   fp16 `out` [batch, num_heads, head_dim]. When the wait runs out the rows are left untouched,
- *   bit 1 of the device status word is set (hkv_ctx_device_status) and the kernel returns normally;
- *   later merges return at once until the status word has been read.
+ * hkv_merge_published: releases, waits at most wait_limit_ms (0 = 2000) for every rank's flag, then
+ *   writes fp16 `out` [batch, num_heads, head_dim], and closes the epoch. When the wait runs out the
+ *   rows are left untouched, bit 1 of the device status word is set (hkv_ctx_device_status) and the
+ *   kernel returns normally; later merges do not wait until the status word has been read.
  * Both only enqueue and are capturable; the epoch lives in the mailbox, so a captured pair can be
  * replayed. */
 #define HKV_MAX_PEERS 8

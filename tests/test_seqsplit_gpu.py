@@ -79,9 +79,11 @@ def test_sequence_split_single_gpu_emulation(hkv, cuda, oracle, world, BLK, kern
 
 @pytest.mark.parametrize("world,BLK,batch", [(2, 64, 3), (4, 128, 3), (8, 64, 1)])
 def test_peer_exchange_single_gpu_emulation(hkv, cuda, oracle, world, BLK, batch):
-    """The mailbox exchange with every rank on one GPU: per step all ranks' publishing launches are
-    enqueued before the first merge, so each merge finds its flags already published (no kernel
-    waits for a later launch). Three steps exercise both parities of the mailboxes; every rank's
+    """The mailbox exchange with every rank on one GPU. A rank's merge kernel releases its own epoch
+    flag and then waits for the others', which on one GPU would be later launches of the same
+    stream — so here the test itself stores the epoch into every flag word between the publishing
+    launches and the merges (what the peers' merge kernels do on their own GPUs; the real handshake
+    runs in the multi-GPU tests). Three steps exercise both parities of the mailboxes; every rank's
     merged output must match the oracle on the full logical cache."""
     torch = cuda
     B, H, KVH, HD, ctx = batch, 28, 4, 128, 2048
@@ -108,6 +110,8 @@ def test_peer_exchange_single_gpu_emulation(hkv, cuda, oracle, world, BLK, batch
         dtot = to_dev(torch, totals)
         for r in range(world):
             ctxs[r].decode_partials_publish(dq, dnk, dnv, planes[r][0], planes[r][1], xs[r], dtot, scale)
+        for b in boxes:
+            b[:4 * world].view(torch.int32).fill_(step + 1)
         for r in range(world):
             ctxs[r].merge_published(xs[r], outs[r])
         torch.cuda.synchronize()
@@ -140,12 +144,15 @@ def test_peer_exchange_wait_runs_out_as_a_status(hkv, cuda):
     assert c.device_status() == 1                # the wait ran out; reading clears the word
     assert bool((out == 7.0).all())
     assert c.device_status() == 0
-    # the mailbox is still consistent: once "rank 1" has published, the same epoch merges
-    boxes[0][4:8].view(torch.int32)[0] = 1       # flag word of rank 1 in rank 0's mailbox
+    # the epoch has advanced all the same; the next exchange works once "rank 1" releases its flag
+    assert int(boxes[0][256:260].view(torch.int32)[0]) == 1
+    c.decode_partials_publish(q, None, None, k, v, x, tot)
+    boxes[0][4:8].view(torch.int32)[0] = 2       # flag word of rank 1 in rank 0's mailbox
     c.merge_published(x, out)
     torch.cuda.synchronize()
     assert c.device_status() == 0
     assert not bool((out == 7.0).all())
+    assert [int(b[0:4].view(torch.int32)[0]) for b in boxes] == [2, 2]   # rank 0 released epoch 2 in both mailboxes
     with pytest.raises(hkv.HkvError):
         c.merge_published(hkv.Context.make_exchange(1, boxes), out)      # not this context's rank
     c.close()
