@@ -226,7 +226,11 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
         slot_range(a.map, total, row_lo, row_hi);
         const int first = first_pos(a.map, total);
         const int t0 = tile_lo + off;
-        const bool always_mask = a.map.layout == 1 || (a.map.shard_count > 1 && a.map.window > 0);
+        // A ring that has wrapped holds an attended position in EVERY row when the window spans the whole
+        // ring (what a sliding-window layer allocates): no row of any tile needs checking. Only a ring
+        // larger than its window keeps stale rows between the window's ends.
+        const bool ring_stale_rows = a.map.layout == 1 && total > a.map.slots && a.map.window > 0 && a.map.window < a.map.slots;
+        const bool always_mask = ring_stale_rows || (a.map.shard_count > 1 && a.map.window > 0);
         const int new_slot = a.k_new ? slot_of_pos(a.map, total - 1) : -1;
 
         // Query fragments: B operand [16 d x 8 heads], head = r4, d pair = c4*2 (+8).
