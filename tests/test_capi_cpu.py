@@ -42,6 +42,14 @@ def test_dist_library_exports_every_declared_symbol(hkv):
     assert lib.hkvd_unique_id(None) == 1          # HKV_ERR_INVALID_ARG, before NCCL is touched
     assert lib.hkvd_step(None, 0, None) == 1 and lib.hkvd_wait(None, 10) == 1
     del buf
+    # argument checks of the creating call come before any device or communicator work
+    g = hkv.Geometry(batch=2, num_heads=8, num_kv_heads=2, head_dim=64, slots=128).to_c()
+    for exchange, wait_ms in ((7, 0), (-1, 0), (2, 20000), (0, -5)):
+        handle = C.c_void_p()
+        assert lib.hkvd_create_with(C.byref(handle), C.byref(g), 2, None, 0.0, None, exchange, wait_ms) == 1
+        assert b"exchange" in lib.hkvd_last_error(handle)
+        assert lib.hkvd_exchange(handle, None) == 1
+        lib.hkvd_destroy(handle)
 
 
 def test_product_library_has_no_oracle_or_torch_dependency(hkv):
