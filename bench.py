@@ -466,10 +466,13 @@ def measured_peak(key, fallback):
     return fallback, "fallback"
 
 
-def prefill_record(args, torch, hkv, oracle, cfg, name, S, past, steps, warmup, gpu_id=None, window=0, ring_slots=0):
+def prefill_record(args, torch, hkv, oracle, cfg, name, S, past, steps, warmup, gpu_id=None, window=0, ring_slots=0,
+                   attend_first=False):
     """Chunked prefill over the cache (batch 1, one layer per call): append the chunk's K/V,
     then attention of its S queries over rows [0, past + S). Tensor-bound:
-    flops = 4*H*HD*sum_q(attended rows of q)."""
+    flops = 4*H*HD*sum_q(attended rows of q). `attend_first`: the one-call form for a ring of exactly
+    `window` rows (hkv_prefill_append_attention: attends the cached rows and the chunk's own rows, then
+    appends)."""
     H, KVH, HD = cfg["H"], cfg["KVH"], cfg["HD"]
     ring = ring_slots > 0
     slots = ring_slots if ring else past + S
@@ -488,15 +491,24 @@ def prefill_record(args, torch, hkv, oracle, cfg, name, S, past, steps, warmup, 
     scale = 1.0 / math.sqrt(HD)
 
     def step():
-        ctx.append_at(kn, vn, k, v, past, S)
-        ctx.prefill_attention(q, k, v, out, S, past, scale)
+        if attend_first:
+            ctx.prefill_append_attention(q, kn, vn, k, v, out, S, past, scale)
+        else:
+            ctx.append_at(kn, vn, k, v, past, S)
+            ctx.prefill_attention(q, k, v, out, S, past, scale)
 
+    before = (k.cpu().numpy(), v.cpu().numpy()) if attend_first and not args.no_verify else None
     step()
     assert ctx.device_status() == 0
     err = None
     if not args.no_verify:  # sampled queries against the oracle (linear planes + window mask semantics)
         hq = q.cpu().numpy()
-        if ring:    # logical view of the ring: position p lives in row p % slots
+        if attend_first:   # the ring as it was BEFORE the call held positions [past - slots, past); then the chunk
+            hk = np.zeros((past + S, KVH, HD), np.float16); hv = np.zeros_like(hk)
+            pos = np.arange(max(0, past - slots), past)
+            hk[pos], hv[pos] = before[0][pos % slots], before[1][pos % slots]
+            hk[past:], hv[past:] = kn.cpu().numpy(), vn.cpu().numpy()
+        elif ring:    # logical view of the ring: position p lives in row p % slots
             first = max(0, past + S - slots)
             pos = np.arange(first, past + S)
             hk = np.zeros((past + S, KVH, HD), np.float16); hv = np.zeros_like(hk)
@@ -522,8 +534,11 @@ def prefill_record(args, torch, hkv, oracle, cfg, name, S, past, steps, warmup, 
     evs = []
     for _ in range(steps):
         a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-        a.record(); ctx.append_at(kn, vn, k, v, past, S)
-        b.record(); ctx.prefill_attention(q, k, v, out, S, past, scale)
+        if attend_first:   # one call: both passes, the merge and the append
+            a.record(); b.record(); ctx.prefill_append_attention(q, kn, vn, k, v, out, S, past, scale)
+        else:
+            a.record(); ctx.append_at(kn, vn, k, v, past, S)
+            b.record(); ctx.prefill_attention(q, k, v, out, S, past, scale)
         c.record(); evs.append((a, b, c))
     torch.cuda.synchronize()
     clocks = None
@@ -540,7 +555,9 @@ def prefill_record(args, torch, hkv, oracle, cfg, name, S, past, steps, warmup, 
     plan = ctx.plan_prefill(S, past)
     rec = {"workload": f"{name}-shaped chunked prefill over the cache: chunk {S} queries, {past} rows already cached, "
                        f"{H}q/{KVH}kv heads, head_dim {HD}" + (f", window {window}" if window else "") +
-                       (f", ring plane of {slots} rows" if ring else "") + ", one layer per step, batch 1",
+                       (f", ring plane of {slots} rows" if ring else "") +
+                       (", attend-then-append in one call (hkv_prefill_append_attention)" if attend_first else "") +
+                       ", one layer per step, batch 1",
            "chunk": S, "past_len": past, "value": S / (tot["ms_per_step_median"] * 1e-3), "unit": "tokens/s", **tot,
            "attention_ms_median": attn["ms_per_step_median"], "attention_ms_min": attn["ms_per_step_min"],
            "roofline": {"bound": "tensor", "kernel": "tcgen05 prefill (hkv_prefill_tc*_kernel)" if plan[0]
@@ -1328,6 +1345,8 @@ def main():
             guarded(prefill_record, args, torch, hkv, oracle, WORKLOADS["gemma-local-global"], "gemma-local-global", 2048, 30720, 10, 3),
             guarded(prefill_record, args, torch, hkv, oracle, WORKLOADS["gemma-local-global"], "gemma-local-global (local layer)",
                            512, 30720, 10, 3, window=1024, ring_slots=2048),
+            guarded(prefill_record, args, torch, hkv, oracle, WORKLOADS["gemma-local-global"], "gemma-local-global (local layer)",
+                           512, 30720, 10, 3, window=1024, ring_slots=1024, attend_first=True),
         ]
         extras["rope"] = [guarded(rope_record, args, torch, hkv, oracle, q7, "qwen2-7b", 64, 1, 4096, 20, 5),
                           guarded(rope_record, args, torch, hkv, oracle, q7, "qwen2-7b", 1, 2048, 4096, 20, 5)]
@@ -1342,15 +1361,26 @@ def main():
         if n_gpus == 8:
             legs.append(("long-context config: batch 64, logical ctx 131072 over 8 GPUs", 131072))
         for label, logical in legs:
-            rec = seqsplit_leg(args, torch, hkv, oracle, dist, cfg, logical, B, rank, n_gpus, gpu_id, args.steps,
-                               max(args.warmup, 3), label)
+            # a leg that fails (on every rank alike: e.g. out of memory) must not take the headline line with it
+            try:
+                rec = seqsplit_leg(args, torch, hkv, oracle, dist, cfg, logical, B, rank, n_gpus, gpu_id, args.steps,
+                                   max(args.warmup, 3), label)
+            except Exception as exc:   # noqa: BLE001 - reported in the record
+                rec = {"label": label, "error": f"{type(exc).__name__}: {exc}"[:400]}
+                gc.collect()
+                torch.cuda.empty_cache()
             if rank == 0:
                 seqsplit.append(rec)
 
     # ---- the long-context config's prefill: one 131 072-token sequence per GPU, 2 048-query chunks
     prefill_seq = None
     if default_workload and not args.no_extras:
-        prefill_seq = prefill_sequence_record(args, torch, hkv, oracle, dist, cfg, args.workload, 131072, 2048, rank, n_gpus)
+        try:
+            prefill_seq = prefill_sequence_record(args, torch, hkv, oracle, dist, cfg, args.workload, 131072, 2048, rank, n_gpus)
+        except Exception as exc:   # noqa: BLE001 - reported in the record
+            prefill_seq = {"error": f"{type(exc).__name__}: {exc}"[:400]}
+            gc.collect()
+            torch.cuda.empty_cache()
 
     if rank == 0:
         line = dict(base, config=config, value=tok_s, ms_per_step=ms_per_step,
