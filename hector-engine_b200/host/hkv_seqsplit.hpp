@@ -81,66 +81,14 @@ public:
     // the launcher's own means); ignored when world == 1. Allocates: construct before any capture.
     SeqSplitDecoder(const SeqSplitConfig& cfg, const ncclUniqueId* id, cudaStream_t stream)
         : cfg_(cfg), stream_(stream) {
-        if (!cfg.layers || !cfg.batch || !cfg.heads || !cfg.kv_heads || !cfg.head_dim || !cfg.local_slots)
-            throw std::runtime_error("SeqSplitDecoder: incomplete configuration");
-        if (cfg.world < 1 || cfg.rank < 0 || cfg.rank >= cfg.world)
-            throw std::runtime_error("SeqSplitDecoder: rank/world out of range");
-        if (cfg_.scale == 0.0f) cfg_.scale = 1.0f / std::sqrt((float)cfg.head_dim);
-        hkv_geometry g{};
-        g.batch = (int32_t)cfg.batch; g.num_heads = (int32_t)cfg.heads; g.num_kv_heads = (int32_t)cfg.kv_heads;
-        g.head_dim = (int32_t)cfg.head_dim; g.slots = (int32_t)cfg.local_slots; g.layout = HKV_LAYOUT_LINEAR;
-        g.shard_rank = cfg.rank; g.shard_count = cfg.world; g.shard_block = (int32_t)cfg.shard_block;
-        g.chunk_tiles = cfg.chunk_tiles; g.kernel_select = cfg.kernel_select;
-        const int st = hkv_ctx_create(&ctx_, &g);
-        if (st != HKV_OK) {
-            std::string msg = std::string("SeqSplitDecoder: hkv_ctx_create: ") + hkv_status_string(st);
-            if (ctx_) { msg += std::string(" (") + hkv_ctx_last_error(ctx_) + ")"; hkv_ctx_destroy(ctx_); ctx_ = nullptr; }
-            throw std::runtime_error(msg);
-        }
-        part_floats_ = (size_t)cfg.batch * cfg.heads * (cfg.head_dim + 2);
-        cuda_check(cudaMalloc(&part_, part_floats_ * sizeof(float)), "cudaMalloc(partial)");
-        cuda_check(cudaMalloc(&gathered_, part_floats_ * sizeof(float) * cfg.world), "cudaMalloc(gathered)");
-        if (cfg.world > 1) {
-            if (!id) throw std::runtime_error("SeqSplitDecoder: world > 1 needs a communicator id");
-            const ncclResult_t r = ncclCommInitRank(&comm_, cfg.world, *id, cfg.rank);
-            if (r != ncclSuccess) throw std::runtime_error(std::string("SeqSplitDecoder: ncclCommInitRank: ") + ncclGetErrorString(r));
-            if (cfg.exchange != Exchange::Nccl) {
-                if (cfg.world > HKV_MAX_PEERS) {
-                    if (cfg.exchange == Exchange::PeerStores)
-                        throw std::runtime_error("SeqSplitDecoder: mailboxes serve at most " + std::to_string(HKV_MAX_PEERS) + " ranks");
-                } else {
-                    std::string why;
-                    peer_ = map_mailboxes(&why);
-                    if (!peer_ && cfg.exchange == Exchange::PeerStores)
-                        throw std::runtime_error("SeqSplitDecoder: mailboxes could not be mapped on every rank: " + why);
-                }
-            }
+        try {
+            construct(id);
+        } catch (...) {
+            release(false);   // a constructor that throws runs no destructor: give back what it took
+            throw;
         }
     }
-    ~SeqSplitDecoder() {
-        graph_.invalidate();
-        cudaStreamSynchronize(stream_);
-        // A peer may still be reading this rank's last partial (its merge of the last step): the ranks
-        // meet once more before any mailbox is freed — unless the communicator is gone, in which case
-        // the peers have stopped launching (a departure is announced between steps).
-        if (peer_ && comm_ && !aborted_ && meet_ != nullptr &&
-            ncclAllReduce(meet_, meet_, 1, ncclInt, ncclSum, comm_, stream_) == ncclSuccess) {
-            // with a deadline: a rank that is torn down alone (an error path) must not wait for ever
-            const WatchResult met = watch_step([this] { return cudaStreamQuery(stream_) == cudaSuccess; },
-                                               [] { return false; }, std::chrono::milliseconds(5000));
-            if (met != WatchResult::Done) {
-                ncclCommAbort(comm_);
-                comm_ = nullptr;
-            }
-        }
-        unmap_mailboxes();
-        if (meet_) cudaFree(meet_);
-        for (cudaEvent_t e : events_) cudaEventDestroy(e);
-        if (comm_) ncclCommDestroy(comm_);
-        if (part_) cudaFree(part_);
-        if (gathered_) cudaFree(gathered_);
-        if (ctx_) hkv_ctx_destroy(ctx_);
-    }
+    ~SeqSplitDecoder() { release(true); }
     SeqSplitDecoder(const SeqSplitDecoder&) = delete;
     SeqSplitDecoder& operator=(const SeqSplitDecoder&) = delete;
 
@@ -256,6 +204,74 @@ public:
     int device_status() { int32_t w = 0; hkv_ctx_device_status(ctx_, stream_, &w); return w; }
 
 private:
+    void construct(const ncclUniqueId* id) {
+        const SeqSplitConfig& cfg = cfg_;
+        if (!cfg.layers || !cfg.batch || !cfg.heads || !cfg.kv_heads || !cfg.head_dim || !cfg.local_slots)
+            throw std::runtime_error("SeqSplitDecoder: incomplete configuration");
+        if (cfg.world < 1 || cfg.rank < 0 || cfg.rank >= cfg.world)
+            throw std::runtime_error("SeqSplitDecoder: rank/world out of range");
+        if (cfg_.scale == 0.0f) cfg_.scale = 1.0f / std::sqrt((float)cfg.head_dim);
+        hkv_geometry g{};
+        g.batch = (int32_t)cfg.batch; g.num_heads = (int32_t)cfg.heads; g.num_kv_heads = (int32_t)cfg.kv_heads;
+        g.head_dim = (int32_t)cfg.head_dim; g.slots = (int32_t)cfg.local_slots; g.layout = HKV_LAYOUT_LINEAR;
+        g.shard_rank = cfg.rank; g.shard_count = cfg.world; g.shard_block = (int32_t)cfg.shard_block;
+        g.chunk_tiles = cfg.chunk_tiles; g.kernel_select = cfg.kernel_select;
+        const int st = hkv_ctx_create(&ctx_, &g);
+        if (st != HKV_OK) {
+            std::string msg = std::string("SeqSplitDecoder: hkv_ctx_create: ") + hkv_status_string(st);
+            if (ctx_) msg += std::string(" (") + hkv_ctx_last_error(ctx_) + ")";
+            throw std::runtime_error(msg);
+        }
+        part_floats_ = (size_t)cfg.batch * cfg.heads * (cfg.head_dim + 2);
+        cuda_check(cudaMalloc(&part_, part_floats_ * sizeof(float)), "cudaMalloc(partial)");
+        cuda_check(cudaMalloc(&gathered_, part_floats_ * sizeof(float) * cfg.world), "cudaMalloc(gathered)");
+        if (cfg.world > 1) {
+            if (!id) throw std::runtime_error("SeqSplitDecoder: world > 1 needs a communicator id");
+            const ncclResult_t r = ncclCommInitRank(&comm_, cfg.world, *id, cfg.rank);
+            if (r != ncclSuccess) throw std::runtime_error(std::string("SeqSplitDecoder: ncclCommInitRank: ") + ncclGetErrorString(r));
+            if (cfg.exchange != Exchange::Nccl) {
+                if (cfg.world > HKV_MAX_PEERS) {
+                    if (cfg.exchange == Exchange::PeerStores)
+                        throw std::runtime_error("SeqSplitDecoder: mailboxes serve at most " + std::to_string(HKV_MAX_PEERS) + " ranks");
+                } else {
+                    std::string why;
+                    peer_ = map_mailboxes(&why);
+                    if (!peer_ && cfg.exchange == Exchange::PeerStores)
+                        throw std::runtime_error("SeqSplitDecoder: mailboxes could not be mapped on every rank: " + why);
+                }
+            }
+        }
+    }
+    // Gives everything back. `meet`: the ranks are torn down together (the destructor of a healthy decoder).
+    void release(bool meet) {
+        graph_.invalidate();
+        cudaStreamSynchronize(stream_);
+        // A peer may still be reading this rank's last partial (its merge of the last step): the ranks
+        // meet once more before any mailbox is freed — unless the communicator is gone, in which case
+        // the peers have stopped launching (a departure is announced between steps).
+        if (meet && peer_ && comm_ && !aborted_ && meet_ != nullptr &&
+            ncclAllReduce(meet_, meet_, 1, ncclInt, ncclSum, comm_, stream_) == ncclSuccess) {
+            // with a deadline: a rank that is torn down alone (an error path) must not wait for ever
+            const WatchResult met = watch_step([this] { return cudaStreamQuery(stream_) == cudaSuccess; },
+                                               [] { return false; }, std::chrono::milliseconds(5000));
+            if (met != WatchResult::Done) {
+                ncclCommAbort(comm_);
+                comm_ = nullptr;
+            }
+        }
+        unmap_mailboxes();
+        if (meet_) cudaFree(meet_);
+        meet_ = nullptr;
+        for (cudaEvent_t e : events_) cudaEventDestroy(e);
+        events_.clear();
+        if (comm_) (meet ? ncclCommDestroy(comm_) : ncclCommAbort(comm_));
+        comm_ = nullptr;
+        if (part_) cudaFree(part_);
+        if (gathered_) cudaFree(gathered_);
+        part_ = gathered_ = nullptr;
+        if (ctx_) hkv_ctx_destroy(ctx_);
+        ctx_ = nullptr;
+    }
     static void cuda_check(cudaError_t e, const char* what) {
         if (e != cudaSuccess) throw std::runtime_error(std::string("SeqSplitDecoder: ") + what + ": " + cudaGetErrorString(e));
     }
