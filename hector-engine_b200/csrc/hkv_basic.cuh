@@ -428,17 +428,29 @@ __global__ void __launch_bounds__(kMergeWarps * 32) hkv_merge_published_kernel(c
         float L = l_r * w_r;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+        // The rows, 128 dimensions at a time: the loads of ALL ranks are issued before the first is used, so the
+        // merge pays about one NVLink round trip per slab instead of one per rank.
         float acc[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
-        for (int r = 0; r < a.world; ++r) {
-            const float* p = a.part[r] + at;
-            const float w = __shfl_sync(0xffffffffu, w_r, r);
+        float wr[kMaxPeers];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const int d = lane + 32 * i;
-                if (d < a.HD) acc[i] = fmaf(ld_sys(p + d), w, acc[i]);
-            }
+        for (int r = 0; r < kMaxPeers; ++r) wr[r] = __shfl_sync(0xffffffffu, w_r, r);
+#pragma unroll
+        for (int slab = 0; slab < 4; ++slab) {
+            if (slab * 128 >= a.HD) break;
+            float v[kMaxPeers][4];
+#pragma unroll
+            for (int r = 0; r < kMaxPeers; ++r)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int d = slab * 128 + lane + 32 * i;
+                    v[r][i] = (r < a.world && d < a.HD) ? ld_sys(a.part[r] + at + d) : 0.0f;
+                }
+#pragma unroll
+            for (int r = 0; r < kMaxPeers; ++r)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[slab * 4 + i] = fmaf(v[r][i], wr[r], acc[slab * 4 + i]);
         }
         const float inv = L > 0.0f ? 1.0f / L : 0.0f;
 #pragma unroll
