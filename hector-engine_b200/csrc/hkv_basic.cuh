@@ -214,34 +214,39 @@ __global__ void __launch_bounds__(kCombineThreads) hkv_combine_kernel(const Comb
     }
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t epoch = pub_epoch(a);
-    __shared__ float s_red[kCombineWarps];
+    __shared__ float s_max[kCombineWarps];
+    __shared__ float s_sum[kCombineWarps];
     __shared__ float s_acc[kCombineWarps][512];   // head_dim <= 512
-    // M = max over partials
-    float M = kNegBig;
-    for (int c = tid; c < n; c += kCombineThreads) M = fmaxf(M, base[c * stride_c + a.HD]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-    if (lane == 0) s_red[warp] = M;
-    __syncthreads();
-    M = s_red[0];
-#pragma unroll
-    for (int w = 1; w < kCombineWarps; ++w) M = fmaxf(M, s_red[w]);
-    __syncthreads();   // s_red is reused below
-    // this warp's share
+    // One pass: a warp folds its rows into a running (maximum, sum, row) — no separate pass for the
+    // maximum, so the launch is one round trip shorter — four rows' loads in flight at a time.
     const int ndim = (a.HD + 31) >> 5;   // dimensions per lane, <= 16
     float acc[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
-    float L = 0.0f;
-#pragma unroll 4
-    for (int c = warp; c < n; c += kCombineWarps) {   // unrolled: four rows' loads in flight per warp
-        const float* row = base + (long long)c * stride_c;
-        const float w = exp2f(row[a.HD] - M);
-        L = fmaf(row[a.HD + 1], w, L);
+    float Mw = kNegBig, Lw = 0.0f;
+    for (int c0 = warp; c0 < n; c0 += 4 * kCombineWarps) {
+        float m[4], l[4], x[4][16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const int d = lane + 32 * i;
-            if (i < ndim && d < a.HD) acc[i] = fmaf(row[d], w, acc[i]);
+        for (int u = 0; u < 4; ++u) {
+            const int c = c0 + u * kCombineWarps;
+            const float* row = base + (long long)(c < n ? c : c0) * stride_c;
+            m[u] = c < n ? row[a.HD] : kNegBig;
+            l[u] = c < n ? row[a.HD + 1] : 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int d = lane + 32 * i;
+                x[u][i] = (i < ndim && d < a.HD && c < n) ? row[d] : 0.0f;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float Mn = fmaxf(Mw, m[u]);
+            const float keep = exp2f(Mw - Mn), w = exp2f(m[u] - Mn);
+            Lw = fmaf(l[u], w, Lw * keep);
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                if (i < ndim) acc[i] = fmaf(x[u][i], w, acc[i] * keep);
+            Mw = Mn;
         }
     }
 #pragma unroll
@@ -249,16 +254,26 @@ __global__ void __launch_bounds__(kCombineThreads) hkv_combine_kernel(const Comb
         const int d = lane + 32 * i;
         if (i < ndim && d < a.HD) s_acc[warp][d] = acc[i];
     }
-    if (lane == 0) s_red[warp] = L;
+    if (lane == 0) {
+        s_max[warp] = Mw;
+        s_sum[warp] = Lw;
+    }
     __syncthreads();
-    L = 0.0f;
+    float M = s_max[0];
 #pragma unroll
-    for (int w = 0; w < kCombineWarps; ++w) L += s_red[w];
+    for (int w = 1; w < kCombineWarps; ++w) M = fmaxf(M, s_max[w]);
+    float wgt[kCombineWarps];
+    float L = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kCombineWarps; ++w) {
+        wgt[w] = exp2f(s_max[w] - M);
+        L = fmaf(s_sum[w], wgt[w], L);
+    }
     const float inv = L > 0.0f ? 1.0f / L : 0.0f;
     for (int d = tid; d < a.HD; d += kCombineThreads) {
         float o = 0.0f;
 #pragma unroll
-        for (int w = 0; w < kCombineWarps; ++w) o += s_acc[w][d];
+        for (int w = 0; w < kCombineWarps; ++w) o = fmaf(s_acc[w][d], wgt[w], o);
         if (a.out) a.out[((long long)b * a.H + h) * a.HD + d] = __float2half_rn(o * inv);
         store_partial(a, epoch, ((long long)b * a.H + h) * PW + d, o);
     }
