@@ -284,8 +284,8 @@ __global__ void __launch_bounds__(kCombineThreads) hkv_combine_kernel(const Comb
 }
 
 // The merge for many (sequence, head) rows: one thread per output dimension walks the row's
-// partials directly; no cross-warp reduction, half the threads and a fraction of the shared memory
-// of the kernel above, which only pays when few rows each have many partials (small batches).
+// partials directly; no cross-warp reduction and half the threads of the kernel above, which only
+// pays when few rows each have many partials (small batches).
 __global__ void __launch_bounds__(128) hkv_combine_few_kernel(const CombineArgs a) {
     const int h = blockIdx.x, b = blockIdx.y;
     const int PW = a.HD + 2;
@@ -305,47 +305,26 @@ __global__ void __launch_bounds__(128) hkv_combine_few_kernel(const CombineArgs 
                 : num_chunks(a.map, length_of(a.total, a.pos_stride, a.pos_is_index, a.host_len, b), a.chunk_tiles);
         base = a.part + b * a.stride_b + (long long)h * PW;
     }
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
     const uint32_t epoch = pub_epoch(a);
-    __shared__ float s_red[4];
-    __shared__ float s_w[128];
-    // M = max over partials: the chunks are spread over the threads, so the loads overlap
+    // Every thread reads the row's n (maximum, sum) pairs itself — the same addresses across the CTA, so
+    // they are broadcast from L1 — and needs no exchange with the others: no shared memory, no barrier.
     float M = kNegBig;
-    for (int c = tid; c < n; c += 128) M = fmaxf(M, base[c * stride_c + a.HD]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-    if (lane == 0) s_red[warp] = M;
-    __syncthreads();
-    M = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
-    float L = 0.0f;        // thread-partial sum of weights * l, reduced at the end
+#pragma unroll 4
+    for (int c = 0; c < n; ++c) M = fmaxf(M, base[(long long)c * stride_c + a.HD]);
+    float L = 0.0f;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // output dims tid, tid+128, ... (head_dim <= 512)
-    for (int c0 = 0; c0 < n; c0 += 128) {
-        const int nb = n - c0 < 128 ? n - c0 : 128;
-        __syncthreads();
-        if (tid < nb) {
-            const float* row = base + (long long)(c0 + tid) * stride_c;
-            const float w = exp2f(row[a.HD] - M);
-            s_w[tid] = w;
-            L = fmaf(row[a.HD + 1], w, L);
-        }
-        __syncthreads();
+#pragma unroll 4
+    for (int c = 0; c < n; ++c) {
+        const float* row = base + (long long)c * stride_c;
+        const float w = exp2f(row[a.HD] - M);
+        L = fmaf(row[a.HD + 1], w, L);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int d = tid + 128 * i;
-            if (d < a.HD) {
-                float o = acc[i];
-#pragma unroll 8
-                for (int c = 0; c < nb; ++c) o = fmaf(base[(long long)(c0 + c) * stride_c + d], s_w[c], o);
-                acc[i] = o;
-            }
+            if (d < a.HD) acc[i] = fmaf(row[d], w, acc[i]);
         }
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
-    __syncthreads();
-    if (lane == 0) s_red[warp] = L;
-    __syncthreads();
-    L = s_red[0] + s_red[1] + s_red[2] + s_red[3];
     const float inv = L > 0.0f ? 1.0f / L : 0.0f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
