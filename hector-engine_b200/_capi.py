@@ -32,7 +32,7 @@ class HkvGeometry(C.Structure):
         ("shard_rank", C.c_int32), ("shard_count", C.c_int32), ("shard_block", C.c_int32),
         ("kernel_select", C.c_int32), ("max_seq_new", C.c_int32), ("flags", C.c_int32),
         ("tune_prefill_splits", C.c_int32), ("tune_prefill_kernel", C.c_int32), ("tune_tma_groups", C.c_int32),
-        ("reserved", C.c_int32 * 3),
+        ("q_seq_stride_elems", C.c_int32), ("new_kv_seq_stride_elems", C.c_int32), ("reserved", C.c_int32 * 1),
     ]
 
 

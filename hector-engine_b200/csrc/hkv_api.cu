@@ -54,6 +54,7 @@ struct hkv_ctx {
     int span_gang = 1;              // CTAs sharing a span (gcd of the kv heads and the grid)
     int tma_grid = 0;               // persistent grid of the TMA kernel
     int32_t* d_status = nullptr;
+    long long q_stride = 0, new_stride = 0;   // elements between sequences' q / k_new rows in decode-side calls
     bool ready = false;             // hkv_ctx_create completed
     int pos_stride = 1;             // 0 with HKV_FLAG_SCALAR_POSITION
     float* prefill_ws = nullptr;    // [max_seq_new][kPrefillMaxSplits][H][HD+2] key-split partials of the prefill kernel
@@ -145,6 +146,12 @@ int validate_geometry(const hkv_geometry* g, const char** why) {
     const long long dense = (long long)g->slots * g->num_kv_heads * g->head_dim;
     if (g->batch_stride_elems != 0 && g->batch_stride_elems < dense) {
         *why = "batch_stride_elems smaller than one sequence's plane";
+        return HKV_ERR_INVALID_ARG;
+    }
+    if ((g->q_seq_stride_elems != 0 && g->q_seq_stride_elems < g->num_heads * g->head_dim) ||
+        (g->new_kv_seq_stride_elems != 0 && g->new_kv_seq_stride_elems < g->num_kv_heads * g->head_dim) ||
+        g->reserved[0] != 0) {
+        *why = "q_seq_stride_elems / new_kv_seq_stride_elems smaller than one sequence's row, or a reserved field set";
         return HKV_ERR_INVALID_ARG;
     }
     if (g->shard_count > 1) {
@@ -551,9 +558,12 @@ SeqMap make_map(const hkv_geometry& g) {
 }
 
 int launch_append(hkv_ctx* c, const void* k_new, const void* v_new, void* k_cache, void* v_cache,
-                  const int32_t* d_pos, int pos_bias, int host_pos, int seq_new, cudaStream_t st) {
+                  const int32_t* d_pos, int pos_bias, int host_pos, int seq_new, cudaStream_t st, bool dense = false) {
     if (!k_new || !v_new || !k_cache || !v_cache) return fail(c, HKV_ERR_INVALID_ARG, "append: null tensor");
     if (seq_new < 0) return fail(c, HKV_ERR_INVALID_ARG, "append: negative seq_new");
+    const long long natural = (long long)c->g.num_kv_heads * c->g.head_dim;
+    if (!dense && seq_new > 1 && c->new_stride != natural)
+        return fail(c, HKV_ERR_GEOMETRY, "append: new_kv_seq_stride_elems describes one new token per sequence; seq_new > 1 takes dense tensors");
     if (!aligned(k_new, 2) || !aligned(v_new, 2) || !aligned(k_cache, 2) || !aligned(v_cache, 2))
         return fail(c, HKV_ERR_ALIGNMENT, "append: fp16 pointer not 2-byte aligned");
     if (seq_new == 0) return HKV_OK;
@@ -571,8 +581,9 @@ int launch_append(hkv_ctx* c, const void* k_new, const void* v_new, void* k_cach
     a.S = seq_new;
     a.row_elems = c->g.num_kv_heads * c->g.head_dim;
     a.batch_stride = c->batch_stride;
+    a.src_stride = (dense || seq_new > 1) ? (long long)seq_new * a.row_elems : c->new_stride;
     const bool vec = aligned(k_new, 16) && aligned(v_new, 16) && aligned(k_cache, 16) &&
-                     aligned(v_cache, 16) && a.row_elems % 8 == 0 && c->batch_stride % 8 == 0;
+                     aligned(v_cache, 16) && a.row_elems % 8 == 0 && c->batch_stride % 8 == 0 && a.src_stride % 8 == 0;
     const long long pieces = 2ll * a.B * a.S * (vec ? a.row_elems / 8 : a.row_elems);
     long long blocks = (pieces + 255) / 256;
     const long long cap = (long long)c->sm_count * 16;
@@ -586,7 +597,7 @@ int launch_append(hkv_ctx* c, const void* k_new, const void* v_new, void* k_cach
 // Decode into the workspace; `fused` appends k_new/v_new at position total-1.
 int launch_decode(hkv_ctx* c, const void* q, const void* k_new, const void* v_new, void* k_cache,
                   void* v_cache, const int32_t* d_total, int pos_is_index, int host_len, float scale,
-                  cudaStream_t st, bool* used_tma) {
+                  cudaStream_t st, bool* used_tma, bool dense = false) {
     *used_tma = false;
     const hkv_geometry& g = c->g;
     if (!q || !k_cache || !v_cache) return fail(c, HKV_ERR_INVALID_ARG, "decode: null tensor");
@@ -622,10 +633,12 @@ int launch_decode(hkv_ctx* c, const void* q, const void* k_new, const void* v_ne
     a.host_len = host_len;
     a.batch_stride = c->batch_stride;
     a.scale_log2 = scale * 1.4426950408889634f;
+    a.q_stride = dense ? (long long)g.num_heads * g.head_dim : c->q_stride;
+    a.new_stride = dense ? (long long)g.num_kv_heads * g.head_dim : c->new_stride;
 
     bool use_tma = c->kernel == HKV_KERNEL_TMA && aligned(q, 16) && aligned(k_cache, 16) &&
-                   aligned(v_cache, 16) &&
-                   (!fused || (aligned(k_new, 16) && aligned(v_new, 16)));
+                   aligned(v_cache, 16) && a.q_stride % 8 == 0 &&
+                   (!fused || (aligned(k_new, 16) && aligned(v_new, 16) && a.new_stride % 8 == 0));
     if (!use_tma && g.kernel_select == HKV_KERNEL_TMA)
         return fail(c, HKV_ERR_ALIGNMENT, "decode: TMA kernel requires 16-byte aligned tensors");
 
@@ -648,7 +661,7 @@ int launch_decode(hkv_ctx* c, const void* q, const void* k_new, const void* v_ne
             // generic path: append first (its own launch), then attend; the new row sits at
             // position total - 1 when the array holds attended lengths
             if (!d_total) return fail(c, HKV_ERR_INVALID_ARG, "fused decode needs device positions");
-            const int stt = launch_append(c, k_new, v_new, k_cache, v_cache, d_total, pos_is_index ? 0 : -1, 0, 1, st);
+            const int stt = launch_append(c, k_new, v_new, k_cache, v_cache, d_total, pos_is_index ? 0 : -1, 0, 1, st, dense);
             if (stt) return stt;
         }
         dim3 grid((unsigned)c->max_chunks, (unsigned)g.num_heads, (unsigned)g.batch);
@@ -721,7 +734,8 @@ int launch_combine(hkv_ctx* c, const float* part, long long stride_b, long long 
 
 int decode_full(hkv_ctx* c, const void* q, const void* k_new, const void* v_new, void* k_cache,
                 void* v_cache, void* out, float* out_partial, const int32_t* d_total,
-                int pos_is_index, int host_len, float scale, cudaStream_t st, const hkv_exchange* x = nullptr) {
+                int pos_is_index, int host_len, float scale, cudaStream_t st, const hkv_exchange* x = nullptr,
+                bool dense = false) {
     if (!c->workspace) return fail(c, HKV_ERR_WORKSPACE, "decode: the context was created append-only");
     if (!out && !out_partial && !x) return fail(c, HKV_ERR_INVALID_ARG, "decode: null output");
     if (out && !aligned(out, 2)) return fail(c, HKV_ERR_ALIGNMENT, "decode: out not 2-byte aligned");
@@ -729,7 +743,7 @@ int decode_full(hkv_ctx* c, const void* q, const void* k_new, const void* v_new,
     cudaEvent_t* ev = timed ? &c->prof_events[(size_t)c->prof_calls * 3] : nullptr;
     if (timed) cudaEventRecord(ev[0], st);
     bool used_tma = false;
-    int stt = launch_decode(c, q, k_new, v_new, k_cache, v_cache, d_total, pos_is_index, host_len, scale, st, &used_tma);
+    int stt = launch_decode(c, q, k_new, v_new, k_cache, v_cache, d_total, pos_is_index, host_len, scale, st, &used_tma, dense);
     if (stt) return stt;
     if (timed) cudaEventRecord(ev[1], st);
     const long long PW = c->g.head_dim + 2;
@@ -820,6 +834,9 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
                           : (long long)geometry->slots * geometry->num_kv_heads * geometry->head_dim;
     c->map = make_map(*geometry);
     c->pos_stride = (geometry->flags & HKV_FLAG_SCALAR_POSITION) ? 0 : 1;
+    c->q_stride = geometry->q_seq_stride_elems ? geometry->q_seq_stride_elems : (long long)geometry->num_heads * geometry->head_dim;
+    c->new_stride = geometry->new_kv_seq_stride_elems ? geometry->new_kv_seq_stride_elems
+                                                      : (long long)geometry->num_kv_heads * geometry->head_dim;
     fill_plan(*geometry, sm, c->chunk_tiles, c->max_chunks);
     e = cudaMalloc(&c->d_status, sizeof(int32_t));
     if (e != cudaSuccess) return fail_cuda(c, e, "cudaMalloc(status)");
@@ -1176,7 +1193,7 @@ int hkv_prefill_append_attention(hkv_ctx* c, const void* q, const void* k_new, c
                              : ((long long)past_len + seq_new <= g.slots ||
                                 (g.window_size > 0 && (long long)seq_new + g.window_size - 1 <= g.slots));
     if (plain) {
-        int stt = launch_append(c, k_new, v_new, k_cache, v_cache, nullptr, 0, past_len, seq_new, st);
+        int stt = launch_append(c, k_new, v_new, k_cache, v_cache, nullptr, 0, past_len, seq_new, st, true);
         if (stt) return stt;
         return hkv_prefill_attention(c, q, k_cache, v_cache, out, seq_new, past_len, scale, stream);
     }
@@ -1203,7 +1220,7 @@ int hkv_prefill_append_attention(hkv_ctx* c, const void* q, const void* k_new, c
     hkv_prefill_combine_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(c->prefill_ws, (__half*)out, rows, g.num_heads, g.head_dim, 2,
                                                                           kPrefillMaxSplits, nullptr, c->G);
     // and only now the append (it overwrites rows pass 1 has read)
-    stt = launch_append(c, k_new, v_new, k_cache, v_cache, nullptr, 0, past_len, seq_new, st);
+    stt = launch_append(c, k_new, v_new, k_cache, v_cache, nullptr, 0, past_len, seq_new, st, true);
     if (stt) return stt;
     const cudaError_t e = cudaPeekAtLastError();
     return e == cudaSuccess ? HKV_OK : fail_cuda(c, e, "prefill launch");
@@ -1231,7 +1248,7 @@ int hkv_append_decode_attention_host(hkv_ctx* c, const void* h_q, const void* h_
         return fail_cuda(c, e, "cudaMemcpyAsync(H2D)");
     if (!d_cache_pos) return fail(c, HKV_ERR_INVALID_ARG, "host op: null position array");
     const int stt = decode_full(c, c->st_q, c->st_k, c->st_v, k_cache, v_cache, c->st_out, nullptr,
-                                d_cache_pos, 1, 0, scale, st);
+                                d_cache_pos, 1, 0, scale, st, nullptr, true);
     if (stt) return stt;
     if ((e = cudaMemcpyAsync(h_out, c->st_out, qb, cudaMemcpyDeviceToHost, st)) != cudaSuccess)
         return fail_cuda(c, e, "cudaMemcpyAsync(D2H)");
@@ -1276,7 +1293,7 @@ int hkv_append_decode_attention_host_pipelined(hkv_ctx* c, const void* h_q, cons
         (e = cudaEventRecord(h.in_done, c->host_in)) != cudaSuccess ||
         (e = cudaStreamWaitEvent(st, h.in_done, 0)) != cudaSuccess)
         return fail_cuda(c, e, "cudaMemcpyAsync(H2D)");
-    const int stt = decode_full(c, h.q, h.k, h.v, k_cache, v_cache, h.out, nullptr, d_cache_pos, 1, 0, scale, st);
+    const int stt = decode_full(c, h.q, h.k, h.v, k_cache, v_cache, h.out, nullptr, d_cache_pos, 1, 0, scale, st, nullptr, true);
     if (stt) return stt;
     if ((e = cudaEventRecord(h.compute_done, st)) != cudaSuccess ||
         (e = cudaStreamWaitEvent(c->host_out, h.compute_done, 0)) != cudaSuccess ||
@@ -1610,6 +1627,8 @@ extern "C" int hkv_decode_attention_static(const hkv_geometry* geometry, const v
     a.batch_stride = g.batch_stride_elems ? g.batch_stride_elems
                                           : (long long)g.slots * g.num_kv_heads * g.head_dim;
     a.scale_log2 = scale * 1.4426950408889634f;
+    a.q_stride = g.q_seq_stride_elems ? g.q_seq_stride_elems : (long long)g.num_heads * g.head_dim;
+    a.new_stride = (long long)g.num_kv_heads * g.head_dim;
     cudaStream_t st = (cudaStream_t)stream;
     dim3 grid((unsigned)max_chunks, (unsigned)g.num_heads, (unsigned)g.batch);
     hkv_decode_generic_kernel<<<grid, kGenWarps * 32, 0, st>>>(a);

@@ -25,6 +25,7 @@ struct AppendArgs {
     SeqMap map;
     int B, S, row_elems;   // row_elems = KVH*HD
     long long batch_stride;
+    long long src_stride;  // elements between sequences in k_new / v_new (S*row_elems when dense)
 };
 
 template <typename VecT>
@@ -43,7 +44,7 @@ __global__ void __launch_bounds__(256) hkv_append_kernel(const AppendArgs a) {
         const int pos = (a.d_pos ? a.d_pos[b * a.pos_stride] + a.pos_bias : a.host_pos) + s;
         const int slot = slot_of_pos(a.map, pos);
         if (slot < 0) continue;
-        const __half* src = (plane ? a.v_new : a.k_new) + ((long long)b * a.S + s) * a.row_elems;
+        const __half* src = (plane ? a.v_new : a.k_new) + (long long)b * a.src_stride + (long long)s * a.row_elems;
         __half* dst = (plane ? a.v_cache : a.k_cache) + (long long)b * a.batch_stride +
                       (long long)slot * a.row_elems;
         reinterpret_cast<VecT*>(dst)[piece] = reinterpret_cast<const VecT*>(src)[piece];
@@ -78,7 +79,7 @@ __global__ void __launch_bounds__(kGenWarps * 32) hkv_decode_generic_kernel(cons
     if (row1 > a.map.slots) row1 = a.map.slots;
 
     float qr[kGenMaxPerLane], acc[kGenMaxPerLane];
-    const __half* qp = a.q + ((long long)b * a.H + h) * a.HD;
+    const __half* qp = a.q + (long long)b * a.q_stride + (long long)h * a.HD;
 #pragma unroll
     for (int i = 0; i < kGenMaxPerLane; ++i) {
         const int d = lane + 32 * i;

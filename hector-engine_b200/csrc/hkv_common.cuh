@@ -127,6 +127,8 @@ struct DecodeArgs {
     int host_len;           // attended length of every sequence when total is null
     long long batch_stride; // elements
     float scale_log2;       // scale * log2(e)
+    long long q_stride;     // elements between sequences' q rows (H*HD when dense)
+    long long new_stride;   // elements between sequences' k_new / v_new rows (KVH*HD when dense)
 };
 
 // Attended length of sequence b from a device position array (one entry per sequence, or one

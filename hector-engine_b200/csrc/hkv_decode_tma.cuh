@@ -238,7 +238,7 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
             const int head = n * 8 + r4;
-            const __half* qp = a.q + ((long long)b * a.H + (long long)kvh * G + head) * HD;
+            const __half* qp = a.q + (long long)b * a.q_stride + ((long long)kvh * G + head) * HD;
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
                 if (head < G) {
@@ -299,7 +299,7 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
                     // fused append: stage the new row and store it into the cache planes
                     const int tr = new_slot - row0;
                     const int swz = (CW == 64) ? (tr & 7) : ((tr >> 1) & 3);
-                    const long long src = ((long long)b * a.KVH + kvh) * HD;
+                    const long long src = (long long)b * a.new_stride + (long long)kvh * HD;
                     const long long dst = (long long)b * a.batch_stride +
                                           ((long long)new_slot * a.KVH + kvh) * HD;
                     for (int u = lane; u < HD / 8; u += 32) {

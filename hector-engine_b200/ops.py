@@ -52,6 +52,8 @@ class Geometry:
     tune_prefill_splits: int = 0   # 0 = the library's own choice (parity tests force each variant)
     tune_prefill_kernel: int = 0
     tune_tma_groups: int = 0
+    q_seq_stride_elems: int = 0       # decode calls: q / k_new / v_new as views into a fused QKV activation
+    new_kv_seq_stride_elems: int = 0
 
     def to_c(self) -> HkvGeometry:
         g = HkvGeometry()
@@ -64,6 +66,7 @@ class Geometry:
         g.kernel_select, g.max_seq_new, g.flags = self.kernel_select, self.max_seq_new, self.flags
         g.tune_prefill_splits, g.tune_prefill_kernel = self.tune_prefill_splits, self.tune_prefill_kernel
         g.tune_tma_groups = self.tune_tma_groups
+        g.q_seq_stride_elems, g.new_kv_seq_stride_elems = self.q_seq_stride_elems, self.new_kv_seq_stride_elems
         return g
 
     @property

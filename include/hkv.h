@@ -92,7 +92,16 @@ typedef struct hkv_geometry {
     int32_t tune_tma_groups;     /* shape of the TMA decode kernel: 1 = two CTAs per SM with one
                                     consumer group each, 2 = one CTA with two groups, 3 = one CTA
                                     with one group and the whole shared memory as its ring */
-    int32_t reserved[3];
+    /* Decode-side calls (one new token per sequence) may read q and k_new / v_new straight out of a
+     * fused QKV activation [batch][num_heads*head_dim | num_kv_heads*head_dim | num_kv_heads*head_dim]
+     * — the zero-copy split the reference does for batch 1 only (kernels/register_kernels.cpp:587-593):
+     * elements between consecutive sequences' q rows, and between their k_new (= v_new) rows.
+     * 0 = dense ([batch, num_heads, head_dim] and [batch, num_kv_heads, head_dim]). The outputs stay
+     * dense. Calls with several new tokens per sequence (hkv_append with seq_new > 1, prefill, rope)
+     * take dense tensors. */
+    int32_t q_seq_stride_elems;
+    int32_t new_kv_seq_stride_elems;
+    int32_t reserved[1];
 } hkv_geometry;
 
 /* hkv_geometry.flags */

@@ -570,3 +570,56 @@ def test_equal_span_schedule_edges(hkv, cuda, oracle, totals):
     assert np.array_equal(dk.cpu().numpy().view(np.uint16), ref_k.view(np.uint16))
     assert np.array_equal(dv.cpu().numpy().view(np.uint16), ref_v.view(np.uint16))
     ctx.close()
+
+
+@pytest.mark.parametrize("kernel", [1, 2], ids=["generic", "tma"])
+def test_decode_reads_q_k_v_out_of_a_fused_qkv_activation(hkv, cuda, oracle, kernel):
+    """The zero-copy QKV split (reference kernels/register_kernels.cpp:587-593, batch 1 only there):
+    q, k_new and v_new are views into one [batch][q | k | v] activation, described to the context by
+    the two sequence strides. Results must equal the dense call bit for bit — outputs and planes."""
+    torch = cuda
+    B, H, KVH, HD, slots = 3, 28, 4, 128, 512
+    pos = np.array([5, 300, 511], np.int32)
+    q, nk, nv, kc, vc = make_case(77, B, H, KVH, HD, slots, fill="garbage")
+    scale = 1.0 / math.sqrt(HD)
+    row = (H + 2 * KVH) * HD
+    fused = torch.zeros(B, row, dtype=torch.float16, device="cuda")
+    fused[:, :H * HD] = to_dev(torch, q).reshape(B, -1)
+    fused[:, H * HD:(H + KVH) * HD] = to_dev(torch, nk).reshape(B, -1)
+    fused[:, (H + KVH) * HD:] = to_dev(torch, nv).reshape(B, -1)
+    qp = fused.data_ptr()
+    kp, vp = qp + H * HD * 2, qp + (H + KVH) * HD * 2
+    geo = dict(batch=B, num_heads=H, num_kv_heads=KVH, head_dim=HD, slots=slots, kernel_select=kernel)
+    dense = hkv.Context(hkv.Geometry(**geo))
+    strided = hkv.Context(hkv.Geometry(**geo, q_seq_stride_elems=row, new_kv_seq_stride_elems=row))
+    dpos = to_dev(torch, pos)
+    outs, planes = [], []
+    for ctx, args in ((dense, (to_dev(torch, q), to_dev(torch, nk), to_dev(torch, nv))), (strided, (qp, kp, vp))):
+        dk, dv = to_dev(torch, kc), to_dev(torch, vc)
+        out = torch.zeros(B, H, HD, dtype=torch.float16, device="cuda")
+        ctx.append_decode_attention(args[0], args[1], args[2], dk, dv, out, dpos, scale)
+        assert ctx.device_status() == 0
+        # the two-call form through the same views
+        dk2, dv2 = to_dev(torch, kc), to_dev(torch, vc)
+        out2 = torch.zeros_like(out)
+        ctx.append(args[1], args[2], dk2, dv2, dpos, seq_new=1)
+        ctx.decode_attention(args[0], dk2, dv2, out2, to_dev(torch, pos + 1), scale)
+        torch.cuda.synchronize()
+        assert np.array_equal(dk2.cpu().numpy().view(np.uint16), dk.cpu().numpy().view(np.uint16))
+        outs.append((out.cpu().numpy(), out2.cpu().numpy()))
+        planes.append((dk.cpu().numpy(), dv.cpu().numpy()))
+    for i in range(2):
+        assert np.array_equal(outs[0][i].view(np.uint16), outs[1][i].view(np.uint16)), "outputs differ from the dense call"
+        assert np.array_equal(planes[0][i].view(np.uint16), planes[1][i].view(np.uint16)), "planes differ from the dense call"
+    ref_k, ref_v = kc.copy(), vc.copy()
+    oracle.append(nk, nv, ref_k, ref_v, pos)
+    assert np.array_equal(planes[1][0].view(np.uint16), ref_k.view(np.uint16))
+    assert_close(oracle, outs[1][0], oracle.decode(q, ref_k, ref_v, pos + 1, scale, threads=8), "fused QKV views")
+    # several new tokens per sequence are not described by the one-token strides
+    with pytest.raises(hkv.HkvError):
+        strided.append(kp, vp, to_dev(torch, kc), to_dev(torch, vc), dpos, seq_new=2)
+    # a stride smaller than a sequence's row is refused when the context is created
+    with pytest.raises(hkv.HkvError):
+        hkv.Context(hkv.Geometry(**geo, q_seq_stride_elems=H * HD - 8))
+    dense.close()
+    strided.close()
