@@ -58,6 +58,8 @@ int hkvd_create_with(hkvd_decoder** out, const hkv_geometry* g, int32_t layers, 
     if (!g || layers <= 0) return fail(d, HKV_ERR_INVALID_ARG, "hkvd_create: null geometry or no layers");
     if (g->layout != HKV_LAYOUT_LINEAR || g->window_size != 0)
         return fail(d, HKV_ERR_GEOMETRY, "hkvd_create: sequence split takes linear planes without a window");
+    if (g->q_seq_stride_elems != 0 || g->new_kv_seq_stride_elems != 0)
+        return fail(d, HKV_ERR_GEOMETRY, "hkvd_create: the sequence-split step binds dense q / k_new / v_new (one block per layer)");
     hkv::SeqSplitConfig c;
     c.layers = (uint32_t)layers; c.batch = (uint32_t)g->batch; c.heads = (uint32_t)g->num_heads;
     c.kv_heads = (uint32_t)g->num_kv_heads; c.head_dim = (uint32_t)g->head_dim; c.local_slots = (uint32_t)g->slots;
