@@ -139,52 +139,16 @@ __device__ __forceinline__ void rope_tokens_fast(const RopeArgs& a, float* s_cos
 
     for (long long tb = t_begin; tb < t_end; tb += TB) {
         const int nb = (int)(t_end - tb < TB ? t_end - tb : TB);
-        __syncthreads();                    // weights and frequencies written; the previous tables no longer read
-        for (int e = tid; e < nb * half_rot; e += blockDim.x) {
-            const int tt = e / half_rot, i = e - tt * half_rot;
-            const long long tok = tb + tt;
-            const int pos = (a.d_pos ? a.d_pos[(int)(tok / a.S) * a.pos_stride] : a.host_pos) + (int)(tok % a.S);
-            float sn, c;
-            sincosf(((float)pos / a.scaling) * s_freq[i], &sn, &c);
-            s_cos[e] = c;
-            s_sin[e] = sn;
-        }
-        if (tid < nb) {                     // where the token's K/V rows go: element offset into the planes, or -1
-            const long long tok = tb + tid;
-            const int b = (int)(tok / a.S);
-            const int pos = (a.d_pos ? a.d_pos[b * a.pos_stride] : a.host_pos) + (int)(tok % a.S);
-            const int row = a.k_cache ? slot_of_pos(a.map, pos) : -1;
-            s_off[tid] = row < 0 ? -1 : (long long)b * a.batch_stride + (long long)row * a.KVH * HD;
-        }
-        __syncthreads();
-        for (int tt = 0; tt < nb; ++tt) {   // the folded tables of token tt: [q | k][HD]
-            const float* cs = s_cos + tt * half_rot;
-            const float* sn = s_sin + tt * half_rot;
-            for (int r = tid; r < 2 * HD; r += blockDim.x) {
-                const int kind = r >= HD ? 1 : 0, i = r - kind * HD;
-                const float* w = s_w[kind];
-                float A = w[i], B = 0.0f;
-                if (i < half_rot) {
-                    A *= cs[i];
-                    B = -w[i + half_rot] * sn[i];
-                } else if (i < a.rot) {
-                    A *= cs[i - half_rot];
-                    B = w[i - half_rot] * sn[i - half_rot];
-                }
-                s_A[tt * 2 * HD + r] = A;
-                s_B[tt * 2 * HD + r] = B;
-            }
-        }
-        __syncthreads();
         const __half* q_base = a.q + tb * a.H * HD + 8 * p;
         const __half* k_base = a.k + tb * a.KVH * HD + 8 * p;
         const __half* v_base = copy_v ? a.v + tb * a.KVH * HD + 8 * p : nullptr;
         int it = blockIdx.x * kRopeWarps + warp;
         int tt = it / spt, slot = it - tt * spt;
-        while (tt < nb) {
-            uint4 raw[U];
-            int utt[U], uj[U];
-            const __half* usrc[U];
+        uint4 raw[U];
+        int utt[U], uj[U];
+        const __half* usrc[U];
+        // Issues the loads of this warp's next U units (they need nothing but the token index).
+        auto load_round = [&]() {
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 utt[u] = tt;
@@ -199,6 +163,54 @@ __device__ __forceinline__ void rope_tokens_fast(const RopeArgs& a, float* s_cos
                 slot += stride;
                 while (slot >= spt) { slot -= spt; ++tt; }
             }
+        };
+        // The first round's rows and this thread's position are requested BEFORE the tables are built:
+        // their latency runs under the trigonometry (a decode-sized launch is nothing but these latencies).
+        load_round();
+        int pos_pre = 0;
+        if (tid < nb * half_rot) {
+            const long long tok = tb + tid / half_rot;
+            pos_pre = (a.d_pos ? a.d_pos[(int)(tok / a.S) * a.pos_stride] : a.host_pos) + (int)(tok % a.S);
+        }
+        __syncthreads();                    // weights and frequencies written; the previous tables no longer read
+        for (int e = tid; e < nb * half_rot; e += blockDim.x) {
+            const int t = e / half_rot, i = e - t * half_rot;
+            const long long tok = tb + t;
+            const int pos = e == tid ? pos_pre
+                                     : (a.d_pos ? a.d_pos[(int)(tok / a.S) * a.pos_stride] : a.host_pos) + (int)(tok % a.S);
+            float sn, c;
+            sincosf(((float)pos / a.scaling) * s_freq[i], &sn, &c);
+            s_cos[e] = c;
+            s_sin[e] = sn;
+        }
+        if (tid < nb) {                     // where the token's K/V rows go: element offset into the planes, or -1
+            const long long tok = tb + tid;
+            const int b = (int)(tok / a.S);
+            const int pos = (a.d_pos ? a.d_pos[b * a.pos_stride] : a.host_pos) + (int)(tok % a.S);
+            const int row = a.k_cache ? slot_of_pos(a.map, pos) : -1;
+            s_off[tid] = row < 0 ? -1 : (long long)b * a.batch_stride + (long long)row * a.KVH * HD;
+        }
+        __syncthreads();
+        for (int t = 0; t < nb; ++t) {      // the folded tables of token t: [q | k][HD]
+            const float* cs = s_cos + t * half_rot;
+            const float* sn = s_sin + t * half_rot;
+            for (int r = tid; r < 2 * HD; r += blockDim.x) {
+                const int kind = r >= HD ? 1 : 0, i = r - kind * HD;
+                const float* w = s_w[kind];
+                float A = w[i], B = 0.0f;
+                if (i < half_rot) {
+                    A *= cs[i];
+                    B = -w[i + half_rot] * sn[i];
+                } else if (i < a.rot) {
+                    A *= cs[i - half_rot];
+                    B = w[i - half_rot] * sn[i - half_rot];
+                }
+                s_A[t * 2 * HD + r] = A;
+                s_B[t * 2 * HD + r] = B;
+            }
+        }
+        __syncthreads();
+        while (utt[0] < nb) {               // warp-uniform
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 if (utt[u] >= nb) break;    // warp-uniform
@@ -248,6 +260,8 @@ __device__ __forceinline__ void rope_tokens_fast(const RopeArgs& a, float* s_cos
                 }
                 *reinterpret_cast<uint4*>(dst) = o;
             }
+            if (tt >= nb) break;            // warp-uniform: nothing left for this warp in the stage
+            load_round();
         }
     }
 }
