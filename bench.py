@@ -87,7 +87,8 @@ def parse_args():
                     help="batch: sequences sharded over GPUs, no collective (default; adds the extras and the "
                          "sequence-split legs). seqsplit: only the sequence-split leg; --ctx is then the LOGICAL "
                          "context, split over the GPUs. prefill / rope: one kernel's own figure")
-    ap.add_argument("--shard-block", type=int, default=1024)
+    ap.add_argument("--shard-block", type=int, default=256,
+                    help="sequence split: positions per dealt block (256 balances the ranks' rows better than 1024: +3 %% at 4 GPUs)")
     ap.add_argument("--exchange", default="auto", choices=["auto", "nccl", "peer"],
                     help="sequence split: how partials travel between the ranks")
     ap.add_argument("--linear-window", action="store_true",
