@@ -91,6 +91,8 @@ def parse_args():
                     help="sequence split: positions per dealt block (256 balances the ranks' rows better than 1024: +3 %% at 4 GPUs)")
     ap.add_argument("--exchange", default="auto", choices=["auto", "nccl", "peer"],
                     help="sequence split: how partials travel between the ranks")
+    ap.add_argument("--ring-extra", type=int, default=0,
+                    help="rows a window layer's ring plane has beyond its window (a plane sized for chunked prefill)")
     ap.add_argument("--linear-window", action="store_true",
                     help="window layers keep a linear plane + mask (the reference's layout) instead of a ring")
     return ap.parse_args()
@@ -232,14 +234,15 @@ def pick_batch(torch, cfg, ctx, requested):
     raise SystemExit("not enough free device memory for batch 1")
 
 
-def layer_specs(cfg, ctx, linear_window=False):
+def layer_specs(cfg, ctx, linear_window=False, ring_extra=0):
     """Per layer: (rows per sequence, window, layout). Window layers use a ring plane of
-    `window` rows unless linear_window asks for the reference's layout (linear plane + mask)."""
+    `window` (+ ring_extra: a plane sized for chunked prefill) rows unless linear_window asks for the
+    reference's layout (linear plane + mask)."""
     specs = []
     for l in range(cfg["layers"]):
         w = cfg.get("window", 0) if cfg.get("local_every") and (l % cfg["local_every"]) != cfg["local_every"] - 1 else 0
         if w and not linear_window:
-            specs.append((w, w, 1))
+            specs.append((w + ring_extra, w, 1))
         else:
             specs.append((ctx, w, 0))
     return specs
@@ -254,11 +257,12 @@ def start_positions(cfg, ctx, B, rank):
 
 
 class Workload:
-    def __init__(self, torch, hkv, cfg, ctx, B, rank, kernel=0, chunk_tiles=0, linear_window=False, tma_groups=0):
+    def __init__(self, torch, hkv, cfg, ctx, B, rank, kernel=0, chunk_tiles=0, linear_window=False, tma_groups=0,
+                 ring_extra=0):
         self.torch, self.hkv, self.cfg, self.ctx_len, self.B, self.rank = torch, hkv, cfg, ctx, B, rank
         L, H, KVH, HD = cfg["layers"], cfg["H"], cfg["KVH"], cfg["HD"]
         self.scale = 1.0 / math.sqrt(HD)
-        self.specs = layer_specs(cfg, ctx, linear_window)
+        self.specs = layer_specs(cfg, ctx, linear_window, ring_extra)
         dev = "cuda"
         self.k = [torch.empty((B, s, KVH, HD), dtype=torch.float16, device=dev) for s, _, _ in self.specs]
         self.v = [torch.empty((B, s, KVH, HD), dtype=torch.float16, device=dev) for s, _, _ in self.specs]
@@ -1225,7 +1229,8 @@ def main():
               "l2": "inputs larger than L2 (K/V read per step >> 126 MB)", "fp16_kv": True,
               "timing": "the whole step captured once as a CUDA graph and replayed (the engine's execution mode); "
                         "CUDA events on the replay stream, max over ranks"}
-    w = Workload(torch, hkv, cfg, ctx, B, rank, args.kernel, args.chunk_tiles, args.linear_window, args.tma_groups)
+    w = Workload(torch, hkv, cfg, ctx, B, rank, args.kernel, args.chunk_tiles, args.linear_window, args.tma_groups,
+                 args.ring_extra)
     L = cfg["layers"]
     verify_err = None
     if not args.no_verify:

@@ -70,6 +70,25 @@ inline TmaSmemPlan tma_plan(int HD, int G, int ncw, int B, size_t budget) {
     return TmaSmemPlan{s, fixed + (size_t)s * stage};
 }
 
+// Tiles of one sequence for this kernel: as tile_range(), except that a wrapped ring LARGER than its window
+// (a plane sized for chunked prefill: window + chunk - 1 rows) contributes only the tiles its window touches — a
+// cyclic run of tiles starting at the window's first row — instead of the whole ring. `wrap_tiles` is the ring's
+// tile count when the run is cyclic (tile index tile_lo + t wraps there), else a number no index reaches.
+__device__ __forceinline__ void tma_tile_range(const SeqMap& m, int total, int& tile_lo, int& n_tiles, int& wrap_tiles) {
+    wrap_tiles = 0x7fffffff;
+    if (m.layout == 1 && m.shard_count <= 1 && total > m.slots && m.window > 0 && m.window < m.slots &&
+        m.slots % kTileRows == 0) {
+        const int ring_tiles = m.slots / kTileRows;
+        const int s_first = (total - m.window) % m.slots;
+        const int n = (s_first % kTileRows + m.window + kTileRows - 1) / kTileRows;
+        tile_lo = s_first / kTileRows;
+        n_tiles = n < ring_tiles ? n : ring_tiles;
+        wrap_tiles = ring_tiles;
+        return;
+    }
+    tile_range(m, total, tile_lo, n_tiles);
+}
+
 // NGROUPS = 2: one CTA per SM, two consumer groups sharing one deep ring (long launches).
 // NGROUPS = 1: TWO CTAs per SM, each with one consumer group and a ring of half the depth: while one
 // CTA merges an item or waits for its first tiles, the other keeps the SM's memory pipe busy — the
@@ -119,8 +138,8 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
         int carry = 0;
         for (int b0 = 0; b0 < a.B; b0 += 32) {
             const int b = b0 + lane;
-            int v = 0, tl;
-            if (b < a.B) tile_range(a.map, attended_len(a, b), tl, v);
+            int v = 0, tl, wt;
+            if (b < a.B) tma_tile_range(a.map, attended_len(a, b), tl, v, wt);
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const int u = __shfl_up_sync(0xffffffffu, v, o);
@@ -163,8 +182,8 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
                     if (nb == 0) continue;             // an empty sequence (free batch slot)
                     const int off = u - prefix[b];
                     const int nt = nb - off < u1 - u ? nb - off : u1 - u;
-                    int tile_lo, n_tiles;
-                    tile_range(a.map, attended_len(a, b), tile_lo, n_tiles);
+                    int tile_lo, n_tiles, wrap_tiles;
+                    tma_tile_range(a.map, attended_len(a, b), tile_lo, n_tiles, wrap_tiles);
                     const int t0 = tile_lo + off;
                     u += nt;
                     for (int t = 0; t < nt; ++t) {
@@ -176,7 +195,7 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
                         const uint32_t full = full0 + 8 * stage;
                         const uint32_t dst = smem_base + (uint32_t)stage * STAGE_BYTES;
                         mbar_expect_tx(full, STAGE_BYTES);
-                        const int row = (t0 + t) * kTileRows;
+                        const int row = ((t0 + t >= wrap_tiles) ? t0 + t - wrap_tiles : t0 + t) * kTileRows;
 #pragma unroll
                         for (int c = 0; c < NCH; ++c)
                             tma_load_4d(dst + c * CHUNK_BYTES, &tm_k, full, c * CW, kvh, row, b);
@@ -221,16 +240,26 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
         const int nt = nb - off < u1 - u ? nb - off : u1 - u;
         u += nt;
         const int total = attended_len(a, b);
-        int tile_lo, n_tiles, row_lo, row_hi;
-        tile_range(a.map, total, tile_lo, n_tiles);
+        int tile_lo, n_tiles, row_lo, row_hi, wrap_tiles;
+        tma_tile_range(a.map, total, tile_lo, n_tiles, wrap_tiles);
         slot_range(a.map, total, row_lo, row_hi);
         const int first = first_pos(a.map, total);
         const int t0 = tile_lo + off;
         // A ring that has wrapped holds an attended position in EVERY row when the window spans the whole
-        // ring (what a sliding-window layer allocates): no row of any tile needs checking. Only a ring
-        // larger than its window keeps stale rows between the window's ends.
-        const bool ring_stale_rows = a.map.layout == 1 && total > a.map.slots && a.map.window > 0 && a.map.window < a.map.slots;
-        const bool always_mask = ring_stale_rows || (a.map.shard_count > 1 && a.map.window > 0);
+        // ring (what a sliding-window layer allocates): no row of any tile needs checking. A ring larger than
+        // its window keeps stale rows outside the window: its tiles are checked, cheaply — positions along a
+        // wrapped ring follow from the row of the newest position (the seam) without a division per row.
+        const bool ring_wrapped = a.map.layout == 1 && total > a.map.slots;
+        const bool ring_stale_rows = ring_wrapped && a.map.window > 0 && a.map.window < a.map.slots;
+        const bool always_mask = a.map.shard_count > 1 && a.map.window > 0;
+        int seam = 0, ring_base = 0;
+        if (ring_wrapped) {
+            seam = (total - 1) % a.map.slots;
+            ring_base = total - 1 - seam;
+        }
+        auto pos_at = [&](int s) {
+            return ring_wrapped ? ring_base + s - (s > seam ? a.map.slots : 0) : pos_of_slot(a.map, s, total);
+        };
         const int new_slot = a.k_new ? slot_of_pos(a.map, total - 1) : -1;
 
         // Query fragments: B operand [16 d x 8 heads], head = r4, d pair = c4*2 (+8).
@@ -273,15 +302,17 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
                 const uint32_t vbase = kbase + TILE_BYTES;
                 uint8_t* kgen = smem + (size_t)stage * STAGE_BYTES;
                 uint8_t* vgen = kgen + TILE_BYTES;
-                const int row0 = (t0 + t) * kTileRows;
-                const bool masked = always_mask || row0 < row_lo || row0 + kTileRows > row_hi;
+                const int row0 = ((t0 + t >= wrap_tiles) ? t0 + t - wrap_tiles : t0 + t) * kTileRows;
+                bool masked = always_mask || row0 < row_lo || row0 + kTileRows > row_hi;
+                if (ring_stale_rows)   // whole tile inside the window: rows run upward from row0's position, no seam inside
+                    masked = (seam >= row0 && seam < row0 + kTileRows - 1) || row0 + kTileRows > a.map.slots || pos_at(row0) < first;
                 bool touched = false;
 
                 if (masked) {
                     // zero the V rows of this warp that are staged but not attended
                     for (int r = 0; r < 16; ++r) {
                         const int s = row0 + wig * 16 + r;
-                        const int p = pos_of_slot(a.map, s, total);
+                        const int p = pos_at(s);
                         const bool valid = s < a.map.slots && p >= first && p < total;
                         if (!valid) {
                             const int tr = wig * 16 + r;
@@ -337,7 +368,7 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
                 bool vA = true, vB = true;
                 if (masked) {
                     const int sA = row0 + wig * 16 + r4, sB = sA + 8;
-                    const int pA = pos_of_slot(a.map, sA, total), pB = pos_of_slot(a.map, sB, total);
+                    const int pA = pos_at(sA), pB = pos_at(sB);
                     vA = sA < a.map.slots && pA >= first && pA < total;
                     vB = sB < a.map.slots && pB >= first && pB < total;
                 }

@@ -194,7 +194,9 @@ def test_ring_cache_equals_linear_window(hkv, cuda, oracle, kernel):
     (4, 28, 4, 128, 1024, 0, 0, [0, 63, 64, 1023]),   # tile edges, first and last row
     (3, 16, 8, 256, 128, 128, 1, [5, 128, 1000]),     # ring
     (2, 32, 32, 96, 300, 0, 0, [17, 299]),
-], ids=["cfg1", "edges", "ring", "hd96"])
+    (3, 16, 8, 256, 320, 128, 1, [5, 319, 1000]),     # ring larger than its window: the window's tiles wrap (3, 4, 0)
+    (2, 28, 4, 128, 448, 256, 1, [447, 5000]),
+], ids=["cfg1", "edges", "ring", "hd96", "ring_gt_window_hd256", "ring_gt_window_hd128"])
 def test_fused_append_decode(hkv, cuda, oracle, shape, kernel):
     torch = cuda
     B, H, KVH, HD, slots, window, layout, pos = shape
