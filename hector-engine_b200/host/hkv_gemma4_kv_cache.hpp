@@ -7,8 +7,11 @@
 //   * planes are zero-filled; tensors are published as `<prefix>.layerN.k` / `.v` with shape
 //     {batch, rows, kv_heads, head_dim(N)}; host position bookkeeping as KVCache.
 // One extension: with `ring_window` > 0 the local (sliding-window) owners get ring planes of
-// `ring_window` rows indexed position mod ring_window instead of max_seq_len rows; attention over
-// them equals the reference's linear plane with window_size = ring_window.
+// `ring_window` rows indexed position mod ring_window instead of max_seq_len rows. The ring must hold
+// the layers' sliding window; attention over it equals the reference's linear plane with the same
+// window. Exactly the window is the smallest plane; window + prefill chunk - 1 rows (a multiple of 64)
+// lets a chunked prefill append before it attends, and costs decode nothing (the decode kernel reads
+// only the tiles the window touches).
 #pragma once
 
 #include <cuda_fp16.h>
