@@ -225,16 +225,24 @@ int span_gang_for(int kv_heads, int grid) {
 typedef void (*TmaKernel)(const CUtensorMap, const CUtensorMap, const DecodeArgs, const int);
 
 template <int HD>
-TmaKernel pick_tma_hd(int nt, int groups) {
+TmaKernel pick_tma_hd(int nt, int groups, bool stale) {
+    if (stale) {
+        if (nt == 1) return groups == 1 ? hkv_decode_tma_kernel<HD, 1, 1, true> : hkv_decode_tma_kernel<HD, 1, 2, true>;
+        return groups == 1 ? hkv_decode_tma_kernel<HD, 2, 1, true> : hkv_decode_tma_kernel<HD, 2, 2, true>;
+    }
     if (nt == 1) return groups == 1 ? hkv_decode_tma_kernel<HD, 1, 1> : hkv_decode_tma_kernel<HD, 1, 2>;
     return groups == 1 ? hkv_decode_tma_kernel<HD, 2, 1> : hkv_decode_tma_kernel<HD, 2, 2>;
 }
-TmaKernel pick_tma(int HD, int nt, int groups) {
+// A ring plane larger than its window, in whole tiles: the kernels that walk only the window's tiles.
+bool tma_stale_ring(const hkv_geometry& g) {
+    return g.layout == HKV_LAYOUT_RING && g.window_size > 0 && g.window_size < g.slots && g.slots % kTileRows == 0;
+}
+TmaKernel pick_tma(int HD, int nt, int groups, bool stale) {
     switch (HD) {
-        case 64: return pick_tma_hd<64>(nt, groups);
-        case 96: return pick_tma_hd<96>(nt, groups);
-        case 128: return pick_tma_hd<128>(nt, groups);
-        case 256: return pick_tma_hd<256>(nt, groups);
+        case 64: return pick_tma_hd<64>(nt, groups, stale);
+        case 96: return pick_tma_hd<96>(nt, groups, stale);
+        case 128: return pick_tma_hd<128>(nt, groups, stale);
+        case 256: return pick_tma_hd<256>(nt, groups, stale);
     }
     return nullptr;
 }
@@ -649,7 +657,7 @@ int launch_decode(hkv_ctx* c, const void* q, const void* k_new, const void* v_ne
         if (fused) { a.k_new = (const __half*)k_new; a.v_new = (const __half*)v_new; }
         const int nt = (c->G + 7) / 8;
         const int groups = c->tma_groups == 2 ? 2 : 1;
-        TmaKernel kern = pick_tma(g.head_dim, nt, groups);
+        TmaKernel kern = pick_tma(g.head_dim, nt, groups, tma_stale_ring(g));
         a.span_part = c->span_ws;
         a.gpre = c->span_gpre;
         a.span_gang = c->span_gang;
@@ -879,7 +887,7 @@ int hkv_ctx_create(hkv_ctx** out, const hkv_geometry* geometry) {
             c->kernel = HKV_KERNEL_GENERIC;
         } else {
             if (!encode_tiled_fn()) return fail(c, HKV_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
-            TmaKernel kern = pick_tma(geometry->head_dim, (c->G + 7) / 8, c->tma_groups == 2 ? 2 : 1);
+            TmaKernel kern = pick_tma(geometry->head_dim, (c->G + 7) / 8, c->tma_groups == 2 ? 2 : 1, tma_stale_ring(*geometry));
             // the attribute belongs to the kernel, not to this context: keep it at the device
             // maximum so that contexts with different plans never lower it for each other
             e = cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -94,7 +94,9 @@ __device__ __forceinline__ void tma_tile_range(const SeqMap& m, int total, int& 
 // CTA merges an item or waits for its first tiles, the other keeps the SM's memory pipe busy — the
 // fixed cost per launch (ramp and tail) that dominates short launches is overlapped instead of paid
 // twice. The host picks by the amount of work per SM.
-template <int HD, int NT, int NGROUPS>
+// STALE: the plane is a ring larger than its window (see tma_tile_range); its bookkeeping is compiled
+// into the kernels that need it only, the others keep their registers.
+template <int HD, int NT, int NGROUPS, bool STALE = false>
 __global__ void __launch_bounds__((NGROUPS * 4 + 1) * 32, NGROUPS == 1 ? 2 : 1)
 hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const DecodeArgs a,
@@ -139,7 +141,10 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
         for (int b0 = 0; b0 < a.B; b0 += 32) {
             const int b = b0 + lane;
             int v = 0, tl, wt;
-            if (b < a.B) tma_tile_range(a.map, attended_len(a, b), tl, v, wt);
+            if (b < a.B) {
+                if (STALE) tma_tile_range(a.map, attended_len(a, b), tl, v, wt);
+                else tile_range(a.map, attended_len(a, b), tl, v);
+            }
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const int u = __shfl_up_sync(0xffffffffu, v, o);
@@ -182,8 +187,9 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
                     if (nb == 0) continue;             // an empty sequence (free batch slot)
                     const int off = u - prefix[b];
                     const int nt = nb - off < u1 - u ? nb - off : u1 - u;
-                    int tile_lo, n_tiles, wrap_tiles;
-                    tma_tile_range(a.map, attended_len(a, b), tile_lo, n_tiles, wrap_tiles);
+                    int tile_lo, n_tiles, wrap_tiles = 0x7fffffff;
+                    if (STALE) tma_tile_range(a.map, attended_len(a, b), tile_lo, n_tiles, wrap_tiles);
+                    else tile_range(a.map, attended_len(a, b), tile_lo, n_tiles);
                     const int t0 = tile_lo + off;
                     u += nt;
                     for (int t = 0; t < nt; ++t) {
@@ -195,7 +201,7 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
                         const uint32_t full = full0 + 8 * stage;
                         const uint32_t dst = smem_base + (uint32_t)stage * STAGE_BYTES;
                         mbar_expect_tx(full, STAGE_BYTES);
-                        const int row = ((t0 + t >= wrap_tiles) ? t0 + t - wrap_tiles : t0 + t) * kTileRows;
+                        const int row = ((STALE && t0 + t >= wrap_tiles) ? t0 + t - wrap_tiles : t0 + t) * kTileRows;
 #pragma unroll
                         for (int c = 0; c < NCH; ++c)
                             tma_load_4d(dst + c * CHUNK_BYTES, &tm_k, full, c * CW, kvh, row, b);
@@ -240,8 +246,9 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
         const int nt = nb - off < u1 - u ? nb - off : u1 - u;
         u += nt;
         const int total = attended_len(a, b);
-        int tile_lo, n_tiles, row_lo, row_hi, wrap_tiles;
-        tma_tile_range(a.map, total, tile_lo, n_tiles, wrap_tiles);
+        int tile_lo, n_tiles, row_lo, row_hi, wrap_tiles = 0x7fffffff;
+        if (STALE) tma_tile_range(a.map, total, tile_lo, n_tiles, wrap_tiles);
+        else tile_range(a.map, total, tile_lo, n_tiles);
         slot_range(a.map, total, row_lo, row_hi);
         const int first = first_pos(a.map, total);
         const int t0 = tile_lo + off;
@@ -249,9 +256,11 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
         // ring (what a sliding-window layer allocates): no row of any tile needs checking. A ring larger than
         // its window keeps stale rows outside the window: its tiles are checked, cheaply — positions along a
         // wrapped ring follow from the row of the newest position (the seam) without a division per row.
-        const bool ring_wrapped = a.map.layout == 1 && total > a.map.slots;
+        const bool ring_wrapped = STALE && a.map.layout == 1 && total > a.map.slots;
         const bool ring_stale_rows = ring_wrapped && a.map.window > 0 && a.map.window < a.map.slots;
-        const bool always_mask = a.map.shard_count > 1 && a.map.window > 0;
+        // (without STALE a wrapped ring larger than its window still decodes correctly: every tile checked row by row)
+        const bool always_mask = (!STALE && a.map.layout == 1 && total > a.map.slots && a.map.window > 0 && a.map.window < a.map.slots) ||
+                                 (a.map.shard_count > 1 && a.map.window > 0);
         int seam = 0, ring_base = 0;
         if (ring_wrapped) {
             seam = (total - 1) % a.map.slots;
@@ -302,7 +311,7 @@ hkv_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k,
                 const uint32_t vbase = kbase + TILE_BYTES;
                 uint8_t* kgen = smem + (size_t)stage * STAGE_BYTES;
                 uint8_t* vgen = kgen + TILE_BYTES;
-                const int row0 = ((t0 + t >= wrap_tiles) ? t0 + t - wrap_tiles : t0 + t) * kTileRows;
+                const int row0 = ((STALE && t0 + t >= wrap_tiles) ? t0 + t - wrap_tiles : t0 + t) * kTileRows;
                 bool masked = always_mask || row0 < row_lo || row0 + kTileRows > row_hi;
                 if (ring_stale_rows)   // whole tile inside the window: rows run upward from row0's position, no seam inside
                     masked = (seam >= row0 && seam < row0 + kTileRows - 1) || row0 + kTileRows > a.map.slots || pos_at(row0) < first;
