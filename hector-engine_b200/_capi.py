@@ -82,6 +82,7 @@ SIGNATURES = {
     "hkv_ctx_profile_end": (C.c_int, [_VP, _VP, C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_int32)]),
     "hkv_slot_of_position": (C.c_int32, [C.POINTER(HkvGeometry), C.c_int32]),
     "hkv_position_of_slot": (C.c_int32, [C.POINTER(HkvGeometry), C.c_int32, C.c_int32]),
+    "hkv_plan_decode_tiles": (C.c_int, [C.POINTER(HkvGeometry), C.c_int32] + [C.POINTER(C.c_int32)] * 3),
     "hkv_plan_sequence": (C.c_int, [C.POINTER(HkvGeometry), C.c_int32, C.c_int32] + [C.POINTER(C.c_int32)] * 4),
     "hkv_plan_prefill": (C.c_int, [C.POINTER(HkvGeometry), C.c_int32, C.c_int32, C.c_int32] + [C.POINTER(C.c_int32)] * 4),
     "hkv_preferred_prefill_chunk": (C.c_int32, [C.POINTER(HkvGeometry), C.c_int32, C.c_int32]),

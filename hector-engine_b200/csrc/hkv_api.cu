@@ -1463,6 +1463,25 @@ int hkv_plan_sequence(const hkv_geometry* g, int32_t total_seq, int32_t chunk_ti
     return HKV_OK;
 }
 
+int hkv_plan_decode_tiles(const hkv_geometry* g, int32_t total_seq, int32_t* tile_lo, int32_t* n_tiles, int32_t* wrap_tiles) {
+    const char* why;
+    const int st = validate_geometry(g, &why);
+    if (st) return st;
+    if (total_seq < 0) return HKV_ERR_INVALID_ARG;
+    const SeqMap m = make_map(*g);
+    int tl = 0, nt = 0, wt = 0;
+    if (tma_stale_ring(*g)) {
+        tma_tile_range(m, total_seq, tl, nt, wt);
+        if (wt == 0x7fffffff) wt = 0;
+    } else {
+        tile_range(m, total_seq, tl, nt);
+    }
+    if (tile_lo) *tile_lo = tl;
+    if (n_tiles) *n_tiles = nt;
+    if (wrap_tiles) *wrap_tiles = wt;
+    return HKV_OK;
+}
+
 int hkv_plan_prefill(const hkv_geometry* g, int32_t seq_new, int32_t past_len, int32_t sm_count,
                      int32_t* tiles_in_flight, int32_t* items, int32_t* splits, int32_t* min_span_tiles) {
     const char* why;

@@ -87,6 +87,25 @@ __host__ __device__ inline void tile_range(const SeqMap& m, int total, int& tile
     tile_lo = lo / kTileRows;
     n_tiles = (hi + kTileRows - 1) / kTileRows - tile_lo;
 }
+// Tiles of one sequence for the TMA decode kernel: as tile_range(), except that a wrapped ring LARGER than its window
+// (a plane sized for chunked prefill: window + chunk - 1 rows) contributes only the tiles its window touches — a
+// cyclic run of tiles starting at the window's first row — instead of the whole ring. `wrap_tiles` is the ring's
+// tile count when the run is cyclic (tile index tile_lo + t wraps there), else a number no index reaches.
+__host__ __device__ inline void tma_tile_range(const SeqMap& m, int total, int& tile_lo, int& n_tiles, int& wrap_tiles) {
+    wrap_tiles = 0x7fffffff;
+    if (m.layout == 1 && m.shard_count <= 1 && total > m.slots && m.window > 0 && m.window < m.slots &&
+        m.slots % kTileRows == 0) {
+        const int ring_tiles = m.slots / kTileRows;
+        const int s_first = (total - m.window) % m.slots;
+        const int n = (s_first % kTileRows + m.window + kTileRows - 1) / kTileRows;
+        tile_lo = s_first / kTileRows;
+        n_tiles = n < ring_tiles ? n : ring_tiles;
+        wrap_tiles = ring_tiles;
+        return;
+    }
+    tile_range(m, total, tile_lo, n_tiles);
+}
+
 __host__ __device__ inline int num_chunks(const SeqMap& m, int total, int chunk_tiles) {
     int tile_lo, n_tiles;
     tile_range(m, total, tile_lo, n_tiles);

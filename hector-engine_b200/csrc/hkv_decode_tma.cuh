@@ -70,25 +70,6 @@ inline TmaSmemPlan tma_plan(int HD, int G, int ncw, int B, size_t budget) {
     return TmaSmemPlan{s, fixed + (size_t)s * stage};
 }
 
-// Tiles of one sequence for this kernel: as tile_range(), except that a wrapped ring LARGER than its window
-// (a plane sized for chunked prefill: window + chunk - 1 rows) contributes only the tiles its window touches — a
-// cyclic run of tiles starting at the window's first row — instead of the whole ring. `wrap_tiles` is the ring's
-// tile count when the run is cyclic (tile index tile_lo + t wraps there), else a number no index reaches.
-__device__ __forceinline__ void tma_tile_range(const SeqMap& m, int total, int& tile_lo, int& n_tiles, int& wrap_tiles) {
-    wrap_tiles = 0x7fffffff;
-    if (m.layout == 1 && m.shard_count <= 1 && total > m.slots && m.window > 0 && m.window < m.slots &&
-        m.slots % kTileRows == 0) {
-        const int ring_tiles = m.slots / kTileRows;
-        const int s_first = (total - m.window) % m.slots;
-        const int n = (s_first % kTileRows + m.window + kTileRows - 1) / kTileRows;
-        tile_lo = s_first / kTileRows;
-        n_tiles = n < ring_tiles ? n : ring_tiles;
-        wrap_tiles = ring_tiles;
-        return;
-    }
-    tile_range(m, total, tile_lo, n_tiles);
-}
-
 // NGROUPS = 2: one CTA per SM, two consumer groups sharing one deep ring (long launches).
 // NGROUPS = 1: TWO CTAs per SM, each with one consumer group and a ring of half the depth: while one
 // CTA merges an item or waits for its first tiles, the other keeps the SM's memory pipe busy — the

@@ -347,6 +347,12 @@ int32_t hkv_position_of_slot(const hkv_geometry* geometry, int32_t slot, int32_t
  * tiles and number of work items (chunks) for `chunk_tiles` tiles per item. */
 int hkv_plan_sequence(const hkv_geometry* geometry, int32_t total_seq, int32_t chunk_tiles,
                       int32_t* first_pos, int32_t* tile_lo, int32_t* n_tiles, int32_t* n_chunks);
+/* The 64-row tiles the TMA decode kernel walks for a sequence of `total_seq` attended positions:
+ * tile indices tile_lo, tile_lo + 1, ... (n_tiles of them), taken modulo *wrap_tiles when that is
+ * non-zero — a wrapped ring plane larger than its window contributes only the cyclic run of tiles
+ * its window touches. Host arithmetic only (tests, schedulers). */
+int hkv_plan_decode_tiles(const hkv_geometry* geometry, int32_t total_seq, int32_t* tile_lo, int32_t* n_tiles,
+                          int32_t* wrap_tiles);
 
 /* Plan of one hkv_prefill_attention call on a device with `sm_count` SMs (host arithmetic, no
  * device needed): query tiles in flight per CTA (2 or 1 for the tensor-core kernels, 0 = SIMT

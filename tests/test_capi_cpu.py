@@ -285,3 +285,31 @@ def test_preferred_prefill_chunk_makes_items_a_multiple_of_the_sms(hkv):
     g256 = hkv.Geometry(num_heads=16, num_kv_heads=8, head_dim=256, slots=4096)
     assert lib.hkv_preferred_prefill_chunk(C.byref(g256.to_c()), 148, 3000) == 37 * 64
     assert lib.hkv_preferred_prefill_chunk(C.byref(gc), 0, 2048) < 0
+
+
+def test_decode_tile_run_of_a_ring_larger_than_its_window_covers_exactly_the_window(hkv):
+    """Index arithmetic of the decode kernel's tile walk (csrc/hkv_common.cuh: tma_tile_range), checked on
+    the host over random rings: the cyclic run of tiles holds every row with an attended position, every
+    tile of the run holds at least one such row (nothing is read for nothing), and it never laps the ring."""
+    lib = hkv._capi.load()
+    rng = np.random.default_rng(11)
+    for _ in range(400):
+        ring_tiles = int(rng.integers(2, 40))
+        slots = ring_tiles * 64
+        window = int(rng.integers(1, slots))
+        total = int(rng.integers(slots + 1, slots * 6))
+        g = hkv.Geometry(batch=1, num_heads=8, num_kv_heads=2, head_dim=64, slots=slots, window_size=window, layout=1).to_c()
+        tl, nt, wt = C.c_int32(), C.c_int32(), C.c_int32()
+        assert lib.hkv_plan_decode_tiles(C.byref(g), total, C.byref(tl), C.byref(nt), C.byref(wt)) == 0
+        assert wt.value == ring_tiles and 1 <= nt.value <= ring_tiles and 0 <= tl.value < ring_tiles
+        run = [(tl.value + t) % ring_tiles for t in range(nt.value)]
+        assert len(set(run)) == len(run), "the run laps the ring"
+        attended_tiles = {(p % slots) // 64 for p in range(total - window, total)}
+        assert attended_tiles == set(run), (slots, window, total, run, sorted(attended_tiles))
+    # planes that are not such rings walk a plain run: no wrap
+    for geo in (dict(slots=1024, window_size=1024, layout=1), dict(slots=4096, window_size=0, layout=0),
+                dict(slots=4096, window_size=512, layout=0), dict(slots=1000, window_size=256, layout=1)):
+        g = hkv.Geometry(batch=1, num_heads=8, num_kv_heads=2, head_dim=64, **geo).to_c()
+        tl, nt, wt = C.c_int32(), C.c_int32(), C.c_int32()
+        assert lib.hkv_plan_decode_tiles(C.byref(g), 5000, C.byref(tl), C.byref(nt), C.byref(wt)) == 0
+        assert wt.value == 0 and (tl.value + nt.value) * 64 <= ((geo["slots"] + 63) // 64) * 64
