@@ -83,6 +83,7 @@ SIGNATURES = {
     "hkv_slot_of_position": (C.c_int32, [C.POINTER(HkvGeometry), C.c_int32]),
     "hkv_position_of_slot": (C.c_int32, [C.POINTER(HkvGeometry), C.c_int32, C.c_int32]),
     "hkv_plan_decode_tiles": (C.c_int, [C.POINTER(HkvGeometry), C.c_int32] + [C.POINTER(C.c_int32)] * 3),
+    "hkv_plan_decode_spans": (C.c_int, [C.POINTER(HkvGeometry), C.c_void_p, C.c_int32] + [C.c_void_p] * 2 + [C.POINTER(C.c_int32)] * 2),
     "hkv_plan_sequence": (C.c_int, [C.POINTER(HkvGeometry), C.c_int32, C.c_int32] + [C.POINTER(C.c_int32)] * 4),
     "hkv_plan_prefill": (C.c_int, [C.POINTER(HkvGeometry), C.c_int32, C.c_int32, C.c_int32] + [C.POINTER(C.c_int32)] * 4),
     "hkv_preferred_prefill_chunk": (C.c_int32, [C.POINTER(HkvGeometry), C.c_int32, C.c_int32]),

@@ -1482,6 +1482,35 @@ int hkv_plan_decode_tiles(const hkv_geometry* g, int32_t total_seq, int32_t* til
     return HKV_OK;
 }
 
+int hkv_plan_decode_spans(const hkv_geometry* g, const int32_t* totals, int32_t spans_wanted, int32_t* first_span,
+                          int32_t* n_parts, int32_t* total_tiles, int32_t* spans_used) {
+    const char* why;
+    const int st = validate_geometry(g, &why);
+    if (st) return st;
+    if (!totals || spans_wanted <= 0) return HKV_ERR_INVALID_ARG;
+    const SeqMap m = make_map(*g);
+    const bool stale = tma_stale_ring(*g);
+    // the same tile table the decode kernel builds in shared memory and leaves for the merge kernel
+    std::vector<int> pre((size_t)g->batch + 1, 0);
+    for (int b = 0; b < g->batch; ++b) {
+        int tl = 0, nt = 0, wt = 0;
+        if (stale) tma_tile_range(m, totals[b], tl, nt, wt);
+        else tile_range(m, totals[b], tl, nt);
+        pre[(size_t)b + 1] = pre[(size_t)b] + nt;
+    }
+    const int W = pre[(size_t)g->batch];
+    const int spans = span_count(W, spans_wanted);
+    for (int b = 0; b < g->batch; ++b) {   // what hkv_combine_*_kernel derives for sequence b
+        const int p0 = pre[(size_t)b], p1 = pre[(size_t)b + 1];
+        const int first = p1 > p0 ? span_owner(p0, W, spans) : 0;
+        if (first_span) first_span[b] = first;
+        if (n_parts) n_parts[b] = p1 > p0 ? span_owner(p1 - 1, W, spans) - first + 1 : 0;
+    }
+    if (total_tiles) *total_tiles = W;
+    if (spans_used) *spans_used = spans;
+    return HKV_OK;
+}
+
 int hkv_plan_prefill(const hkv_geometry* g, int32_t seq_new, int32_t past_len, int32_t sm_count,
                      int32_t* tiles_in_flight, int32_t* items, int32_t* splits, int32_t* min_span_tiles) {
     const char* why;

@@ -353,6 +353,13 @@ int hkv_plan_sequence(const hkv_geometry* geometry, int32_t total_seq, int32_t c
  * its window touches. Host arithmetic only (tests, schedulers). */
 int hkv_plan_decode_tiles(const hkv_geometry* geometry, int32_t total_seq, int32_t* tile_lo, int32_t* n_tiles,
                           int32_t* wrap_tiles);
+/* The equal-span schedule of one decode launch, as the kernels derive it on the device: the tiles of
+ * all sequences (host array totals[batch] of attended lengths) form one line of *total_tiles tiles cut
+ * into *spans_used = min(spans_wanted, tiles) equal spans, span c covering tiles
+ * [floor(T*c/S), floor(T*(c+1)/S)); sequence b's partials come from the spans
+ * first_span[b] .. first_span[b] + n_parts[b] - 1 and sit at partial slot span + b. Host arithmetic only. */
+int hkv_plan_decode_spans(const hkv_geometry* geometry, const int32_t* totals, int32_t spans_wanted,
+                          int32_t* first_span, int32_t* n_parts, int32_t* total_tiles, int32_t* spans_used);
 
 /* Plan of one hkv_prefill_attention call on a device with `sm_count` SMs (host arithmetic, no
  * device needed): query tiles in flight per CTA (2 or 1 for the tensor-core kernels, 0 = SIMT

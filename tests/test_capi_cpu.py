@@ -313,3 +313,38 @@ def test_decode_tile_run_of_a_ring_larger_than_its_window_covers_exactly_the_win
         tl, nt, wt = C.c_int32(), C.c_int32(), C.c_int32()
         assert lib.hkv_plan_decode_tiles(C.byref(g), 5000, C.byref(tl), C.byref(nt), C.byref(wt)) == 0
         assert wt.value == 0 and (tl.value + nt.value) * 64 <= ((geo["slots"] + 63) // 64) * 64
+
+
+def test_equal_span_schedule_agrees_between_the_decode_and_the_merge_side(hkv):
+    """The decode kernel cuts the line of tiles at floor(T*c/S); the merge kernel finds a sequence's
+    partials with the inverse (span_owner). Over random batches: a span overlaps a sequence exactly when
+    the merge side lists it, and the partial slot span + b is used by one piece only."""
+    lib = hkv._capi.load()
+    rng = np.random.default_rng(5)
+    for _ in range(300):
+        B = int(rng.integers(1, 70))
+        slots = int(rng.integers(1, 600)) * 64
+        g = hkv.Geometry(batch=B, num_heads=8, num_kv_heads=2, head_dim=64, slots=slots).to_c()
+        totals = rng.integers(0, slots + 1, size=B).astype(np.int32)
+        totals[rng.random(B) < 0.1] = 0                      # free batch slots
+        want = int(rng.choice([1, 37, 74, 148, 296]))
+        first, parts = np.zeros(B, np.int32), np.zeros(B, np.int32)
+        T, S = C.c_int32(), C.c_int32()
+        assert lib.hkv_plan_decode_spans(C.byref(g), totals.ctypes.data, want, first.ctypes.data, parts.ctypes.data,
+                                         C.byref(T), C.byref(S)) == 0
+        tiles = (totals.astype(np.int64) + 63) // 64
+        pre = np.concatenate([[0], np.cumsum(tiles)])
+        assert T.value == pre[-1] and S.value == min(want, max(T.value, 0))
+        used = set()
+        for c in range(S.value):
+            u0, u1 = T.value * c // S.value, T.value * (c + 1) // S.value
+            assert u1 > u0, "an empty span"
+            for b in range(B):
+                overlaps = tiles[b] > 0 and pre[b] < u1 and pre[b + 1] > u0
+                listed = parts[b] > 0 and first[b] <= c < first[b] + parts[b]
+                assert overlaps == listed, (B, want, c, b)
+                if overlaps:
+                    assert c + b not in used, "two pieces share a partial slot"
+                    used.add(c + b)
+        assert all(parts[b] == 0 for b in range(B) if tiles[b] == 0)
+        assert max(used, default=0) < S.value + B            # the workspace holds spans + batch slots
