@@ -63,6 +63,25 @@ WORKLOADS = {
 }
 
 
+# The one JSON line goes to the process's ORIGINAL standard output; everything else that writes to file
+# descriptor 1 meanwhile (NCCL announces its version there when a communicator is first created) goes to stderr.
+_REAL_STDOUT = None
+
+
+def claim_stdout():
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(obj):
+    sys.stdout.flush()
+    data = (json.dumps(obj) + "\n").encode()
+    os.write(_REAL_STDOUT if _REAL_STDOUT is not None else 1, data)
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -950,7 +969,7 @@ def reference_main(args):
     torch.cuda.set_device(local)
     ref = oracle.load_reference()
     if ref is None:
-        print(json.dumps({"impl": "reference", "unavailable":
+        emit(({"impl": "reference", "unavailable":
                           "oracle/_ref/libhector_ref_attention.so not built (reference checkout absent at build time)"}))
         return 0
     cfg = dict(WORKLOADS[args.workload])
@@ -961,9 +980,10 @@ def reference_main(args):
     gpu_id = gpu_uuid(torch, local)
     stream = torch.cuda.current_stream().cuda_stream
     scale = 1.0 / math.sqrt(HD)
-    base = {"unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "fp16 storage / fp32 accumulate", "data": "synthetic",
-            "impl": "reference"}
+    # n_gpus echoes the launch; the reference has no multi-GPU path, so rank 0 alone runs it on one GPU
+    base = {"unit": "tokens/s", "n_gpus": max(1, args.gpus), "gpus_used": 1, "steps": args.steps, "warmup": args.warmup,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16 storage / fp32 accumulate",
+            "data": "synthetic", "impl": "reference"}
     gen = torch.Generator(device="cuda").manual_seed(SEED)
     normal = lambda *shape: torch.empty(shape, dtype=torch.float16, device="cuda").normal_(generator=gen)
 
@@ -1004,7 +1024,7 @@ def reference_main(args):
         val = S / (ms * 1e-3)
         sample = (f"the reference's attention_prefill_cached kernel rebuilt for sm_100a, run on the GPU: {len(los)} slices "
                   f"of {n} queries of the chunk per step, time scaled to {S} queries (one CTA per (query, head): additive)")
-        print(json.dumps(dict(base, metric="prefill attention tokens/s (one layer)", mode="prefill",
+        emit((dict(base, metric="prefill attention tokens/s (one layer)", mode="prefill",
                               config={"workload": f"{args.workload}-shaped chunked prefill over the cache: chunk {S} queries, "
                                                   f"{past} rows already cached, {H}q/{KVH}kv heads, head_dim {HD}, one layer "
                                                   f"per step, batch 1", "chunk": S, "past_len": past},
@@ -1138,7 +1158,7 @@ def reference_main(args):
                 reference_batch1_graph={"value": 1.0 / (b1["ms_per_step"] / 1e3), "unit": "tokens/s", **b1,
                                         "note": "the engine's own mode: batch 1, all layers captured once as a CUDA graph "
                                                 "and replayed (sequence 0 of the workload)"})
-    print(json.dumps(line))
+    emit((line))
     return 0
 
 
@@ -1193,7 +1213,7 @@ def main():
         if rank == 0:
             rec = prefill_record(args, torch, hkv, oracle, cfg, args.workload, args.chunk, args.past, args.steps, args.warmup,
                                  gpu_id, window=0)
-            print(json.dumps(dict(base, metric="prefill attention tokens/s (one layer)", mode="prefill", n_gpus=1,
+            emit((dict(base, metric="prefill attention tokens/s (one layer)", mode="prefill", n_gpus=1,
                                   config={"workload": rec.pop("workload"), "chunk": rec.pop("chunk"),
                                           "past_len": rec.pop("past_len"), "l2": rec.pop("l2")},
                                   gpu_launches=args.steps * 2, e2e=None, cpu_baseline=None, **rec)))
@@ -1203,7 +1223,7 @@ def main():
             B = args.batch or 1
             rec = rope_record(args, torch, hkv, oracle, cfg, args.workload, B, args.chunk, max(args.chunk + 64, 4096),
                               args.steps, args.warmup)
-            print(json.dumps(dict(base, metric="fused qk-norm + rope + KV write tokens/s (one layer)", mode="rope", n_gpus=1,
+            emit((dict(base, metric="fused qk-norm + rope + KV write tokens/s (one layer)", mode="rope", n_gpus=1,
                                   config={"workload": rec.pop("workload"), "l2": rec.pop("l2")},
                                   gpu_launches=args.steps, e2e=None, cpu_baseline=None, **rec)))
         return finish()
@@ -1212,7 +1232,7 @@ def main():
         rec = seqsplit_leg(args, torch, hkv, oracle, dist, cfg, ctx, B, rank, n_gpus, gpu_id, args.steps, args.warmup,
                            "requested")
         if rank == 0:
-            print(json.dumps(dict(base, mode="seqsplit", scaling="strong",
+            emit((dict(base, mode="seqsplit", scaling="strong",
                                   config={"workload": rec["workload"], "parallelism": rec["parallelism"], "ctx": ctx,
                                           "global_batch": B, "l2": "inputs larger than L2"},
                                   value=rec["value"], ms_per_step=rec["ms_per_step"], clocks=rec["clocks"],
@@ -1423,9 +1443,10 @@ def main():
             line["seqsplit"] = seqsplit
         if prefill_seq is not None:
             line["prefill_sequences"] = prefill_seq
-        print(json.dumps(line))
+        emit((line))
     return finish()
 
 
 if __name__ == "__main__":
+    claim_stdout()
     sys.exit(main())
